@@ -1,0 +1,181 @@
+/*
+ * inferi_b200 — C ABI of the B200-native (sm_100a) batch-1 Llama token loop over GGUF-quantized weights.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an int32_t status
+ * (IB_OK == 0) and never throws or aborts.  `ib_last_error_string()` gives the text of the last
+ * failure on the calling thread.  "dev" pointers are CUDA device pointers on the context's device;
+ * `stream` is a `cudaStream_t` passed as `void*` (NULL = the legacy default stream).  Handles are not
+ * thread-safe; distinct handles may be used from distinct threads.
+ *
+ * Each declaration cites the interface of the reference project (dimforge/inferi, paths relative to
+ * its root) that it replaces.
+ */
+#ifndef INFERI_B200_H
+#define INFERI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define IB_API __attribute__((visibility("default")))
+#else
+#define IB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---- */
+enum {
+    IB_OK = 0,
+    IB_ERR_INVALID = 1,      /* bad argument: null handle, shape contract violated, unsupported type */
+    IB_ERR_CUDA = 2,         /* a CUDA runtime call failed */
+    IB_ERR_OOM = 3,          /* device allocation failed */
+    IB_ERR_UNSUPPORTED = 4,  /* valid request this build cannot serve */
+    IB_ERR_TIMEOUT = 5,      /* a bounded device-side wait gave up */
+    IB_ERR_COMM = 6          /* tensor-parallel set-up or exchange failed */
+};
+
+/* GGUF tensor type ids (crates/inferi/src/gguf.rs:74-106). */
+enum { IB_F32 = 0, IB_Q8_0 = 8, IB_Q4_K = 12, IB_Q5_K = 13, IB_Q6_K = 14 };
+
+/* KV-cache element type.  F32 is the reference's layout (crates/inferi/src/models/llama2/transformer.rs:85-104);
+ * F16 halves the cache traffic and is what the throughput figures are quoted on. */
+enum { IB_KV_F32 = 0, IB_KV_F16 = 1 };
+
+/* RoPE variants (crates/inferi/src/ops/rope.rs:12-23). */
+enum { IB_ROPE_ORIGINAL = 0, IB_ROPE_NEOX = 1 };
+
+typedef struct ib_ctx ib_ctx;
+typedef struct ib_qtensor ib_qtensor;
+typedef struct ib_llama ib_llama;
+
+IB_API const char *ib_last_error_string(void);
+
+/* Replaces `LlmOps::new` (crates/inferi/src/context.rs:58-85): binds a device and owns scratch memory. */
+IB_API int32_t ib_ctx_create(int32_t device, ib_ctx **out);
+IB_API int32_t ib_ctx_destroy(ib_ctx *ctx);
+/* Number of kernels this context has launched since creation (or since the last reset). */
+IB_API int32_t ib_ctx_launch_count(ib_ctx *ctx, uint64_t *out);
+IB_API int32_t ib_ctx_reset_launch_count(ib_ctx *ctx);
+
+/* Raw device memory for callers without a CUDA runtime of their own (the reference allocates through
+ * `Tensor::vector` / `TensorBuilder`, crates/inferi/src/ops/gemv_quant.rs:459-490). */
+IB_API int32_t ib_malloc(ib_ctx *ctx, uint64_t nbytes, void **out_dev);
+IB_API int32_t ib_free(ib_ctx *ctx, void *dev);
+IB_API int32_t ib_memcpy_h2d(ib_ctx *ctx, void *stream, void *dst_dev, const void *src_host, uint64_t nbytes);
+IB_API int32_t ib_memcpy_d2h(ib_ctx *ctx, void *stream, void *dst_host, const void *src_dev, uint64_t nbytes);
+IB_API int32_t ib_stream_sync(ib_ctx *ctx, void *stream);
+
+/* Replaces `GgufTensor::to_gpu_quant` (crates/inferi/src/gguf.rs:141-197, 361) and `GpuQuantTensor`
+ * (crates/inferi/src/quantized_matrix.rs:11-54): uploads a [rows, cols] matrix given as consecutive GGUF
+ * blocks, row-major.  Contracts are checked instead of silently truncated: rows % 4 == 0
+ * (crates/inferi/src/ops/gemv_quant.rs:271), cols a multiple of the block length, nbytes exact.
+ * The bytes may be re-tiled on the device (same total size) for 128-bit loads.
+ * `src_is_device` != 0 means `gguf_blocks` is already a device pointer. */
+IB_API int32_t ib_qtensor_upload(ib_ctx *ctx, int32_t qtype, uint64_t rows, uint64_t cols, const void *gguf_blocks,
+                          uint64_t nbytes, int32_t src_is_device, ib_qtensor **out);
+IB_API int32_t ib_qtensor_destroy(ib_qtensor *qt);
+IB_API int32_t ib_qtensor_info(const ib_qtensor *qt, int32_t *qtype, uint64_t *rows, uint64_t *cols, uint64_t *nbytes);
+
+/* Replaces `GemvQuant::launch` (crates/inferi/src/ops/gemv_quant.rs:183-341): out[rows] = W . v[cols]. */
+IB_API int32_t ib_gemv_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *m, const float *v_dev);
+/* The same call for host buffers: copies v in, runs the kernel, copies out back, synchronises. */
+IB_API int32_t ib_gemv_quant_host(ib_ctx *ctx, float *out_host, const ib_qtensor *m, const float *v_host);
+
+/* Replaces `RmsNorm::launch` (crates/inferi/src/ops/rms_norm.rs:16-69; shader
+ * crates/inferi-shaders/src/rms_norm.rs:78-121): out = (x * rsqrt(mean(x^2) + eps)) * w. */
+IB_API int32_t ib_rms_norm(ib_ctx *ctx, void *stream, float *out_dev, const float *x_dev, const float *w_dev, uint32_t n, float eps);
+
+/* Replaces `RoPE::launch` (crates/inferi/src/ops/rope.rs:25-95; shader crates/inferi-shaders/src/rope.rs:51-141):
+ * rotates q[q_len] and the first kv_dim entries of k in place.  Requires q_len even, q_len >= kv_dim. */
+IB_API int32_t ib_rope(ib_ctx *ctx, void *stream, int32_t variant, float *q_dev, uint32_t q_len, float *k_dev, uint32_t kv_dim,
+                uint32_t head_size, uint32_t pos, float base_freq);
+
+/* Replaces `Silu::launch` (crates/inferi/src/ops/silu.rs:14-53; shader crates/inferi-shaders/src/silu.rs:24-53):
+ * h1 <- h2 * (h1 / (1 + exp(-h1))). */
+IB_API int32_t ib_silu_mul(ib_ctx *ctx, void *stream, float *h1_dev, const float *h2_dev, uint32_t n);
+
+/* Replaces `LlmContext::add_assign` (crates/inferi/src/context.rs:516-530): a += b. */
+IB_API int32_t ib_add_assign(ib_ctx *ctx, void *stream, float *a_dev, const float *b_dev, uint32_t n);
+
+/* = `AttentionParams` (crates/inferi-shaders/src/batched_multiquery_attention.rs:18-31), field for field. */
+typedef struct ib_attn_params {
+    uint32_t seq_len;   /* rows allocated in the cache */
+    uint32_t kv_dim;    /* n_kv_heads * head_size */
+    uint32_t kv_mul;    /* query heads per kv head */
+    uint32_t n_heads;   /* query heads */
+    uint32_t head_size; /* 64 or 128 */
+    uint32_t pos;       /* current position; positions 0..=pos are attended */
+} ib_attn_params;
+
+/* Replaces `FusedAttention::launch` (crates/inferi/src/ops/batched_multiquery_attention.rs:27-77; shaders
+ * crates/inferi-shaders/src/fused_attention.rs:63-241, 374-617): out[n_heads*head_size] =
+ * softmax(q K^T / sqrt(head_size)) V over cache rows [pos+1, kv_dim].  One split-K flash-decoding kernel for
+ * every context length (no 2048-token switch). */
+IB_API int32_t ib_attention(ib_ctx *ctx, void *stream, const ib_attn_params *params, const float *q_dev, const void *k_cache_dev,
+                     const void *v_cache_dev, int32_t kv_dtype, float *out_dev);
+
+/* Replaces the greedy branch of `Sampler::sample` (crates/inferi/src/models/sampler.rs:32-36, 54-56), on the
+ * device: index of the largest logit, lowest index on ties. */
+IB_API int32_t ib_argmax(ib_ctx *ctx, void *stream, const float *logits_dev, uint32_t n, uint32_t *out_dev);
+
+/* = `Llama2Config` (crates/inferi/src/models/llama2/cpu.rs:46-66). */
+typedef struct ib_llama_config {
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t num_hidden_layers;
+    uint32_t num_attention_heads;
+    uint32_t num_key_value_heads;
+    uint32_t vocab_size;
+    uint32_t max_position_embeddings;
+    float rope_theta;
+    float rms_norm_eps;
+} ib_llama_config;
+
+/* = `Llama2LayerWeights` (crates/inferi/src/models/llama2/transformer.rs:176-196).  Norm weights are device
+ * pointers to f32[hidden]; the matrices are this rank's shards when tp_size > 1. */
+typedef struct ib_llama_layer_weights {
+    const ib_qtensor *attn_q, *attn_k, *attn_v, *attn_output;
+    const ib_qtensor *ffn_gate, *ffn_up, *ffn_down;
+    const float *attn_norm_dev, *ffn_norm_dev;
+} ib_llama_layer_weights;
+
+/* = `Llama2Weights` (crates/inferi/src/models/llama2/transformer.rs:176-196, 294-394).  `output == NULL`
+ * ties the classifier to `token_embd` (:376-382).  `token_embd` stays quantized; one row is dequantized
+ * per token (the reference dequantizes the whole table to f32, :367-374 — same values). */
+typedef struct ib_llama_weights {
+    const ib_llama_layer_weights *layers; /* [num_hidden_layers] */
+    const ib_qtensor *token_embd;         /* [vocab, hidden], never sharded */
+    const ib_qtensor *output;             /* [vocab / tp_size, hidden] or NULL */
+    const float *output_norm_dev;
+} ib_llama_weights;
+
+/* Replaces `Llama2State::new` + `Llama2::new` (crates/inferi/src/models/llama2/transformer.rs:46-137, 400-407):
+ * allocates activations and the per-layer KV cache [max_pos, kv_dim / tp_size] and records the token graph. */
+IB_API int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_llama_weights *weights, int32_t kv_dtype,
+                        int32_t tp_rank, int32_t tp_size, ib_llama **out);
+IB_API int32_t ib_llama_destroy(ib_llama *model);
+
+/* Replaces `Llama2::launch` + `ChatLlama2::forward_logits` + greedy sampling
+ * (crates/inferi/src/models/llama2/transformer.rs:409-481, crates/inferi-chat/src/chat_llama2.rs:191-255):
+ * runs one token at `pos`, leaves the greedy next token on the device and, when the host pointers are
+ * non-NULL, copies the logits (vocab floats) and/or the next token id back and synchronises. */
+IB_API int32_t ib_llama_forward(ib_llama *model, void *stream, uint32_t token, uint32_t pos, float *logits_host, uint32_t *next_token_host);
+
+/* Replaces the token loop of `ChatLlama2::forward` (crates/inferi-chat/src/chat_llama2.rs:137-171) for greedy
+ * decoding: feeds `tokens[0..n_prompt)` at positions start_pos.. (each through the decode path, as the
+ * reference does), then generates `n_gen` tokens, each fed back on the device.  Only token ids cross PCIe:
+ * out_tokens_host[n_gen] receives the generated ids after one synchronisation at the end. */
+IB_API int32_t ib_llama_generate(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos,
+                          uint32_t n_gen, uint32_t *out_tokens_host);
+
+/* Device pointer of the last forward's logits (f32[vocab / tp_size]) and of the residual stream x (f32[hidden]);
+ * for parity checks (the reference exposes `Llama2State::logits`, transformer.rs:15-43). */
+IB_API int32_t ib_llama_state(ib_llama *model, const float **logits_dev, const float **x_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFERI_B200_H */

@@ -1,0 +1,160 @@
+// Shared declarations of the inferi_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/inferi_b200.h"
+
+namespace ib {
+
+// ---------------------------------------------------------------------------------------------
+// errors: every entry point returns a status and leaves the text in a thread-local string
+// ---------------------------------------------------------------------------------------------
+int32_t set_error(int32_t code, const char *fmt, ...);
+
+#define IB_CHECK_CUDA(expr)                                                                             \
+    do {                                                                                                \
+        cudaError_t _e = (expr);                                                                        \
+        if (_e != cudaSuccess)                                                                          \
+            return ib::set_error(_e == cudaErrorMemoryAllocation ? IB_ERR_OOM : IB_ERR_CUDA, "%s failed: %s (%s:%d)", \
+                                 #expr, cudaGetErrorString(_e), __FILE__, __LINE__);                    \
+    } while (0)
+
+#define IB_REQUIRE(cond, ...)                                      \
+    do {                                                           \
+        if (!(cond)) return ib::set_error(IB_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// quantized tensors
+// ---------------------------------------------------------------------------------------------
+constexpr int QK_K = 256;
+
+// Device layouts.  GGUF: the file's array-of-blocks byte stream, untouched.  SOA: each row re-tiled into
+// sections of equal fields (same row byte length) so that every 128-bit load is aligned:
+//   Q8_0: [nb x 32 B quants][nb x 2 B f16 scale]
+//   Q6_K: [nb x 128 B ql][nb x 64 B qh][nb x 16 B scales][nb x 2 B f16 d]
+enum Layout : uint32_t { LAYOUT_GGUF = 0, LAYOUT_SOA = 1 };
+
+inline uint32_t block_bytes(int qtype) {
+    switch (qtype) {
+    case IB_F32: return 4;
+    case IB_Q8_0: return 34;
+    case IB_Q4_K: return 144;
+    case IB_Q5_K: return 176;
+    case IB_Q6_K: return 210;
+    default: return 0;
+    }
+}
+inline uint32_t block_elems(int qtype) {
+    switch (qtype) {
+    case IB_F32: return 1;
+    case IB_Q8_0: return 32;
+    case IB_Q4_K: case IB_Q5_K: case IB_Q6_K: return QK_K;
+    default: return 0;
+    }
+}
+
+}  // namespace ib
+
+struct ib_ctx {
+    int device = 0;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    // attention split-K scratch (partials + per-kv-head arrival counters), grown on demand
+    float *attn_scratch = nullptr;
+    size_t attn_scratch_bytes = 0;
+    unsigned int *attn_counters = nullptr;
+    // argmax scratch
+    unsigned long long *argmax_scratch = nullptr;
+    unsigned int *argmax_counter = nullptr;
+};
+
+struct ib_qtensor {
+    ib_ctx *ctx = nullptr;
+    int32_t qtype = 0;
+    uint32_t layout = ib::LAYOUT_GGUF;
+    bool fast = false;          // eligible for the 128-bit-load kernels
+    uint64_t rows = 0, cols = 0;
+    uint64_t row_bytes = 0, nbytes = 0;
+    uint32_t nb = 0;            // blocks per row
+    uint8_t *dev = nullptr;
+};
+
+namespace ib {
+
+// ---------------------------------------------------------------------------------------------
+// GEMV launch description (gemv.cu)
+// ---------------------------------------------------------------------------------------------
+struct GemvSeg {
+    const uint8_t *w;
+    float *out;
+    uint64_t row_bytes;
+    uint32_t rows, qtype, layout, nb;
+};
+
+enum GemvEpilogue : uint32_t {
+    EPI_STORE = 0,     // out[r] = dot
+    EPI_RESIDUAL = 1,  // out[r] = resid[r] + dot
+    EPI_SWIGLU = 2,    // seg0 = gate, seg1 = up: seg0.out[r] = up * gate / (1 + exp(-gate))
+    EPI_QKV = 3,       // seg0 = q (rope, store f32), seg1 = k (rope, store to cache), seg2 = v (store to cache)
+    EPI_ARGMAX = 4     // store (if out != null) and track the arg-max over all rows
+};
+
+struct GemvParams {
+    GemvSeg seg[3];
+    uint32_t nseg, cols, epi;
+    const float *x;        // f32 input vector [cols]
+    const float *norm_w;   // non-null: x is RMS-normalised with these weights first
+    float eps;
+    const float *resid;    // EPI_RESIDUAL
+    // EPI_QKV
+    const uint32_t *pos_ptr;    // device scalar: current position
+    const float2 *rope_cs;      // [head_size/2] (cos, sin) of pos * theta_j for the current token
+    uint32_t head_size, kv_dim, kv_dtype;
+    void *k_cache, *v_cache;    // [max_pos, kv_dim] of this layer
+    // EPI_ARGMAX
+    unsigned long long *argmax_slots;  // one packed (value, ~index) per CTA
+    unsigned int *argmax_counter;
+    uint32_t *argmax_out;
+    uint32_t row_offset;               // added to the row index (tensor-parallel vocabulary shard)
+    uint32_t pdl;                      // 1: launched with programmatic dependent launch
+};
+
+int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p);
+int32_t launch_gemv_generic(ib_ctx *ctx, cudaStream_t stream, const ib_qtensor *m, const float *v, float *out);
+int32_t retile_to_soa(ib_ctx *ctx, cudaStream_t stream, int qtype, const uint8_t *src, uint8_t *dst, uint64_t rows, uint32_t nb);
+bool gemv_fast_eligible(int qtype, uint64_t rows, uint64_t cols);
+void fill_seg(GemvSeg &s, const ib_qtensor *m, float *out);
+
+// ops.cu
+int32_t launch_rms_norm(ib_ctx *ctx, cudaStream_t s, float *out, const float *x, const float *w, uint32_t n, float eps);
+int32_t launch_rope(ib_ctx *ctx, cudaStream_t s, int variant, float *q, uint32_t q_len, float *k, uint32_t kv_dim, uint32_t head_size,
+                    uint32_t pos, float base_freq);
+int32_t launch_silu_mul(ib_ctx *ctx, cudaStream_t s, float *h1, const float *h2, uint32_t n);
+int32_t launch_add_assign(ib_ctx *ctx, cudaStream_t s, float *a, const float *b, uint32_t n);
+int32_t launch_argmax(ib_ctx *ctx, cudaStream_t s, const float *x, uint32_t n, uint32_t *out);
+int32_t ensure_argmax_scratch(ib_ctx *ctx);
+
+// attention.cu
+struct AttnLaunch {
+    ib_attn_params p;          // p.pos is ignored when pos_ptr != null
+    const uint32_t *pos_ptr;   // device scalar (graph replay) or null
+    const float *q;
+    const void *k_cache, *v_cache;
+    int kv_dtype;
+    float *out;
+    float *scratch;            // [n_kv_heads][max_splits][kv_mul][head_size + 2]
+    unsigned int *counters;    // [n_kv_heads], zero before the first launch; the kernel re-zeroes them
+    uint32_t max_splits;
+    uint32_t pdl;
+};
+size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits);
+uint32_t attn_max_splits(const ib_ctx *ctx, const ib_attn_params &p);
+int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a);
+
+}  // namespace ib

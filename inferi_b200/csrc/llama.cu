@@ -1,0 +1,461 @@
+// The Llama-architecture token loop: state, per-token kernel sequence, CUDA graph and greedy generation.
+//
+// Replaces `Llama2State::new` / `Llama2::launch` (crates/inferi/src/models/llama2/transformer.rs:46-137, 409-481)
+// and the token loop of `ChatLlama2::forward` / `forward_logits` (crates/inferi-chat/src/chat_llama2.rs:92-255).
+//
+// Per token the reference records 15 dispatches per layer + 2.  Here a token is 5 kernels per layer + 2:
+//   begin      : embedding row dequantisation -> x, RoPE cos/sin table for this position
+//   qkv        : RMSNorm(x) prologue, Wq|Wk|Wv GEMV, RoPE on q and k, k/v appended to the cache
+//   attention  : split-K flash-decoding over the cache -> xb
+//   o_proj     : x += Wo . xb
+//   gate_up    : RMSNorm(x) prologue, Wgate and Wup GEMV, SwiGLU -> hb
+//   down       : x += Wdown . hb
+//   classifier : RMSNorm(x) prologue, Woutput GEMV -> logits, greedy arg-max, token/position bookkeeping
+// All of it is captured once into a CUDA graph whose kernels read the token, the position and the step from a
+// device control block, so that generation replays the same graph with no host round trip; kernels are chained
+// with programmatic dependent launch.
+#include "common.cuh"
+
+#include <math.h>
+#include <new>
+#include <vector>
+
+using namespace ib;
+
+namespace ib {
+
+struct TokenCtl {
+    uint32_t step;      // index into seq of the token being processed
+    uint32_t pos;       // its position in the context
+    uint32_t n_prompt;  // tokens of seq that are given; beyond them the arg-max is fed back
+    uint32_t next;      // greedy token of the last forward
+};
+
+struct QDesc {
+    const uint8_t *w;
+    uint64_t row_bytes;
+    uint32_t qtype, layout, nb;
+};
+
+__device__ __forceinline__ float half_at(const uint8_t *p) {
+    return __half2float(__ushort_as_half((unsigned short)((uint32_t)p[0] | ((uint32_t)p[1] << 8))));
+}
+
+// Value of element `col` of a quantized row under either device layout (block arithmetic of
+// crates/inferi/src/quantization.rs:51-54, 227-256, 287-329, 364-402).
+__device__ float dequant_at(const QDesc &q, const uint8_t *row, uint32_t col) {
+    if (q.qtype == IB_F32) return reinterpret_cast<const float *>(row)[col];
+    if (q.qtype == IB_Q8_0) {
+        const uint32_t b = col >> 5, i = col & 31;
+        if (q.layout == LAYOUT_SOA) return (float)(int8_t)row[(size_t)32 * b + i] * half_at(row + (size_t)32 * q.nb + 2 * b);
+        const uint8_t *blk = row + (size_t)b * 34;
+        return (float)(int8_t)blk[2 + i] * half_at(blk);
+    }
+    const uint32_t b = col >> 8, e = col & 255;
+    if (q.qtype == IB_Q4_K || q.qtype == IB_Q5_K) {
+        const uint8_t *blk = row + (size_t)b * (q.qtype == IB_Q4_K ? 144 : 176);
+        const uint8_t *sc = blk + 4, *qs = blk + (q.qtype == IB_Q4_K ? 16 : 48);
+        const uint32_t c = e >> 6, hi = (e >> 5) & 1, l = e & 31, j = 2 * c + hi;
+        uint32_t s, m;
+        if (j < 4) { s = sc[j] & 63; m = sc[j + 4] & 63; }
+        else { s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4); m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+        uint32_t qv = hi ? (qs[32 * c + l] >> 4) : (qs[32 * c + l] & 0xF);
+        if (q.qtype == IB_Q5_K && (blk[16 + l] & ((hi ? 2u : 1u) << (2 * c)))) qv += 16;
+        return half_at(blk) * (float)s * (float)qv - half_at(blk + 2) * (float)m;
+    }
+    // Q6_K
+    const uint8_t *ql, *qh, *sc, *dp;
+    if (q.layout == LAYOUT_SOA) {
+        ql = row + (size_t)128 * b; qh = row + (size_t)128 * q.nb + 64 * b; sc = row + (size_t)192 * q.nb + 16 * b; dp = row + (size_t)208 * q.nb + 2 * b;
+    } else {
+        const uint8_t *blk = row + (size_t)b * 210;
+        ql = blk; qh = blk + 128; sc = blk + 192; dp = blk + 208;
+    }
+    const uint32_t i = e >> 7, g = (e >> 5) & 3, l = e & 31;
+    const uint32_t lo = ql[64 * i + 32 * (g & 1) + l], h = qh[32 * i + l];
+    const int qv = (int)(((g & 2) ? (lo >> 4) : (lo & 0xF)) | (((h >> (2 * g)) & 3) << 4)) - 32;
+    return half_at(dp) * (float)(int8_t)sc[8 * i + 2 * g + l / 16] * (float)qv;
+}
+
+// begin: x <- dequantized embedding row of the current token (transformer.rs:367-374, chat_llama2.rs:217-220);
+// rope_cs[j] <- (cos, sin)(pos * theta_j) shared by every layer of this token (rope.rs:75-79).
+__global__ void __launch_bounds__(256) begin_token_kernel(const TokenCtl *ctl, const uint32_t *seq, QDesc embd, uint32_t hidden, float *x,
+                                                           const float *theta, uint32_t half_head, float2 *rope_cs, uint32_t vocab, uint32_t pdl) {
+    if (pdl) {
+        asm volatile("griddepcontrol.launch_dependents;");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    const uint32_t step = ctl->step, pos = ctl->pos;
+    uint32_t token = __ldcg(seq + step);
+    if (token >= vocab) token = vocab - 1;  // never index outside the table
+    const uint8_t *row = embd.w + (size_t)token * embd.row_bytes;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) x[i] = dequant_at(embd, row, i);
+    if (blockIdx.x == 0 && threadIdx.x < half_head) {
+        float sn, cs;
+        sincosf((float)pos * theta[threadIdx.x], &sn, &cs);
+        rope_cs[threadIdx.x] = make_float2(cs, sn);
+    }
+}
+
+// end of token: feed the arg-max back when the prompt is exhausted, advance step and position
+// (crates/inferi-chat/src/sampler.rs:102-110, chat_llama2.rs:137-171).
+__global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap, uint32_t pdl) {
+    if (pdl) {
+        asm volatile("griddepcontrol.launch_dependents;");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const uint32_t step = ctl->step;
+        if (step + 1 >= ctl->n_prompt && step + 1 < seq_cap) seq[step + 1] = ctl->next;
+        ctl->step = step + 1;
+        ctl->pos = ctl->pos + 1;
+    }
+}
+
+}  // namespace ib
+
+struct ib_llama {
+    ib_ctx *ctx = nullptr;
+    ib_llama_config cfg{};
+    int32_t kv_dtype = IB_KV_F16, tp_rank = 0, tp_size = 1;
+    uint32_t head_size = 0, n_heads_l = 0, n_kv_l = 0, q_dim_l = 0, kv_dim_l = 0, ffn_l = 0, vocab_l = 0;
+    std::vector<ib_llama_layer_weights> layers;
+    const ib_qtensor *token_embd = nullptr, *output = nullptr;
+    const float *output_norm = nullptr;
+    // device state (transformer.rs:15-43)
+    float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr, *theta = nullptr;
+    float2 *rope_cs = nullptr;
+    std::vector<void *> k_cache, v_cache;
+    TokenCtl *ctl = nullptr;
+    uint32_t *seq = nullptr;
+    uint32_t seq_cap = 0;
+    float *attn_scratch = nullptr;
+    unsigned int *attn_counters = nullptr;
+    uint32_t attn_splits = 0;
+    unsigned long long *argmax_slots = nullptr;
+    unsigned int *argmax_counter = nullptr;
+    uint32_t *h_pinned = nullptr;  // [4 + seq_cap] staging for control block and token ids
+    cudaEvent_t staged = nullptr;  // the last copy out of h_pinned has been issued and finished
+    cudaGraphExec_t graph_exec = nullptr;
+    cudaStream_t own_stream = nullptr;
+    uint64_t launches_per_token = 0;
+};
+
+namespace ib {
+
+static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
+    ib_ctx *ctx = m->ctx;
+    const ib_llama_config &c = m->cfg;
+    int32_t rc;
+    {
+        QDesc e{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((c.hidden_size + 255) / 256);
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 0;  // first node of the token graph: nothing to overlap with
+        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, begin_token_kernel, (const TokenCtl *)m->ctl, (const uint32_t *)m->seq, e, c.hidden_size, m->x,
+                                         (const float *)m->theta, m->head_size / 2, m->rope_cs, c.vocab_size, pdl));
+        ctx->launches++;
+    }
+    ib_attn_params ap{c.max_position_embeddings, m->kv_dim_l, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
+    for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
+        const ib_llama_layer_weights &w = m->layers[l];
+        GemvParams p = {};
+        // qkv (transformer.rs:420-445)
+        fill_seg(p.seg[0], w.attn_q, m->q);
+        fill_seg(p.seg[1], w.attn_k, nullptr);
+        fill_seg(p.seg[2], w.attn_v, nullptr);
+        p.nseg = 3; p.cols = c.hidden_size; p.epi = EPI_QKV; p.x = m->x; p.norm_w = w.attn_norm_dev; p.eps = c.rms_norm_eps;
+        p.pos_ptr = &m->ctl->pos; p.rope_cs = m->rope_cs; p.head_size = m->head_size; p.kv_dim = m->kv_dim_l; p.kv_dtype = (uint32_t)m->kv_dtype;
+        p.k_cache = m->k_cache[l]; p.v_cache = m->v_cache[l]; p.pdl = pdl;
+        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        // attention (transformer.rs:448)
+        AttnLaunch a = {};
+        a.p = ap; a.pos_ptr = &m->ctl->pos; a.q = m->q; a.k_cache = m->k_cache[l]; a.v_cache = m->v_cache[l]; a.kv_dtype = m->kv_dtype;
+        a.out = m->xb; a.scratch = m->attn_scratch; a.counters = m->attn_counters; a.max_splits = m->attn_splits; a.pdl = pdl;
+        if ((rc = launch_attention(ctx, s, a))) return rc;
+        // o_proj + residual (transformer.rs:450-453)
+        p = GemvParams{};
+        fill_seg(p.seg[0], w.attn_output, m->x);
+        p.nseg = 1; p.cols = m->q_dim_l; p.epi = EPI_RESIDUAL; p.x = m->xb; p.resid = m->x; p.pdl = pdl;
+        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        // gate/up + SwiGLU (transformer.rs:454-464)
+        p = GemvParams{};
+        fill_seg(p.seg[0], w.ffn_gate, m->hb);
+        fill_seg(p.seg[1], w.ffn_up, nullptr);
+        p.nseg = 2; p.cols = c.hidden_size; p.epi = EPI_SWIGLU; p.x = m->x; p.norm_w = w.ffn_norm_dev; p.eps = c.rms_norm_eps; p.pdl = pdl;
+        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        // down + residual (transformer.rs:465-468)
+        p = GemvParams{};
+        fill_seg(p.seg[0], w.ffn_down, m->x);
+        p.nseg = 1; p.cols = m->ffn_l; p.epi = EPI_RESIDUAL; p.x = m->hb; p.resid = m->x; p.pdl = pdl;
+        if ((rc = launch_gemv(ctx, s, p))) return rc;
+    }
+    // classifier + greedy arg-max (transformer.rs:471-478, models/sampler.rs:54-56)
+    GemvParams p = {};
+    fill_seg(p.seg[0], m->output, m->logits);
+    p.nseg = 1; p.cols = c.hidden_size; p.epi = EPI_ARGMAX; p.x = m->x; p.norm_w = m->output_norm; p.eps = c.rms_norm_eps;
+    p.argmax_slots = m->argmax_slots; p.argmax_counter = m->argmax_counter; p.argmax_out = &m->ctl->next; p.row_offset = 0; p.pdl = pdl;
+    if ((rc = launch_gemv(ctx, s, p))) return rc;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1);
+        cfg.blockDim = dim3(32);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, end_token_kernel, m->ctl, m->seq, m->seq_cap, pdl));
+        ctx->launches++;
+    }
+    return IB_OK;
+}
+
+static int32_t check_matrix(const ib_qtensor *t, const char *name, uint64_t rows, uint64_t cols, bool need_fast) {
+    IB_REQUIRE(t != nullptr, "ib_llama_create: missing tensor %s", name);
+    IB_REQUIRE(t->rows == rows && t->cols == cols, "ib_llama_create: %s is %llux%llu, expected %llux%llu", name, (unsigned long long)t->rows,
+               (unsigned long long)t->cols, (unsigned long long)rows, (unsigned long long)cols);
+    if (need_fast && !t->fast)
+        return set_error(IB_ERR_UNSUPPORTED,
+                         "ib_llama_create: %s (%llux%llu, type %d) does not meet the alignment rules of the fused kernels "
+                         "(quantized; Q4_K/Q5_K cols %% 256, Q8_0 cols %% 256, Q6_K cols %% 2048)",
+                         name, (unsigned long long)rows, (unsigned long long)cols, t->qtype);
+    return IB_OK;
+}
+
+}  // namespace ib
+
+extern "C" {
+
+int32_t ib_llama_destroy(ib_llama *m) {
+    if (!m) return IB_OK;
+    cudaSetDevice(m->ctx->device);
+    cudaDeviceSynchronize();
+    if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+    if (m->own_stream) cudaStreamDestroy(m->own_stream);
+    if (m->staged) cudaEventDestroy(m->staged);
+    void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
+                    m->argmax_counter};
+    for (void *b : bufs)
+        if (b) cudaFree(b);
+    for (void *b : m->k_cache)
+        if (b) cudaFree(b);
+    for (void *b : m->v_cache)
+        if (b) cudaFree(b);
+    if (m->h_pinned) cudaFreeHost(m->h_pinned);
+    delete m;
+    return IB_OK;
+}
+
+int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_llama_weights *weights, int32_t kv_dtype, int32_t tp_rank,
+                        int32_t tp_size, ib_llama **out) {
+    IB_REQUIRE(ctx && config && weights && out, "ib_llama_create: null argument");
+    *out = nullptr;
+    IB_REQUIRE(cudaSetDevice(ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    const ib_llama_config &c = *config;
+    IB_REQUIRE(kv_dtype == IB_KV_F32 || kv_dtype == IB_KV_F16, "ib_llama_create: unknown kv dtype %d", kv_dtype);
+    IB_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "ib_llama_create: bad tensor-parallel rank %d of %d", tp_rank, tp_size);
+    if (tp_size != 1) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_create: tensor parallelism is not available in this build");
+    IB_REQUIRE(c.num_hidden_layers > 0 && c.hidden_size > 0 && c.num_attention_heads > 0 && c.num_key_value_heads > 0 && c.vocab_size > 0 &&
+                   c.max_position_embeddings > 0 && c.intermediate_size > 0,
+               "ib_llama_create: zero-sized configuration field");
+    // derived sizes: crates/inferi/src/models/llama2/cpu.rs:110-141
+    IB_REQUIRE(c.hidden_size % c.num_attention_heads == 0 && c.num_attention_heads % c.num_key_value_heads == 0,
+               "ib_llama_create: head counts do not divide the hidden size");
+    IB_REQUIRE(weights->layers != nullptr, "ib_llama_create: null layer array");
+    ib_llama *m = new (std::nothrow) ib_llama();
+    if (!m) return set_error(IB_ERR_OOM, "host allocation failed");
+    m->ctx = ctx; m->cfg = c; m->kv_dtype = kv_dtype; m->tp_rank = tp_rank; m->tp_size = tp_size;
+    m->head_size = c.hidden_size / c.num_attention_heads;
+    m->n_heads_l = c.num_attention_heads / tp_size;
+    m->n_kv_l = c.num_key_value_heads / tp_size;
+    m->q_dim_l = m->n_heads_l * m->head_size;
+    m->kv_dim_l = m->n_kv_l * m->head_size;
+    m->ffn_l = c.intermediate_size / tp_size;
+    m->vocab_l = c.vocab_size / tp_size;
+    int32_t rc = IB_OK;
+#define FAIL_IF(expr)                 \
+    do {                              \
+        if ((rc = (expr)) != IB_OK) { \
+            ib_llama_destroy(m);      \
+            return rc;                \
+        }                             \
+    } while (0)
+#define CU(expr)                                                                                                       \
+    do {                                                                                                               \
+        cudaError_t _e = (expr);                                                                                       \
+        if (_e != cudaSuccess) {                                                                                       \
+            ib_llama_destroy(m);                                                                                       \
+            return set_error(_e == cudaErrorMemoryAllocation ? IB_ERR_OOM : IB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+        }                                                                                                              \
+    } while (0)
+    if (m->head_size != 64 && m->head_size != 128) {
+        ib_llama_destroy(m);
+        return set_error(IB_ERR_UNSUPPORTED, "ib_llama_create: head_size=%u (supported: 64, 128)", m->head_size);
+    }
+    m->layers.assign(weights->layers, weights->layers + c.num_hidden_layers);
+    for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
+        const ib_llama_layer_weights &w = m->layers[l];
+        FAIL_IF(check_matrix(w.attn_q, "attn_q", m->q_dim_l, c.hidden_size, true));
+        FAIL_IF(check_matrix(w.attn_k, "attn_k", m->kv_dim_l, c.hidden_size, true));
+        FAIL_IF(check_matrix(w.attn_v, "attn_v", m->kv_dim_l, c.hidden_size, true));
+        FAIL_IF(check_matrix(w.attn_output, "attn_output", c.hidden_size, m->q_dim_l, true));
+        FAIL_IF(check_matrix(w.ffn_gate, "ffn_gate", m->ffn_l, c.hidden_size, true));
+        FAIL_IF(check_matrix(w.ffn_up, "ffn_up", m->ffn_l, c.hidden_size, true));
+        FAIL_IF(check_matrix(w.ffn_down, "ffn_down", c.hidden_size, m->ffn_l, true));
+        if (!w.attn_norm_dev || !w.ffn_norm_dev) {
+            ib_llama_destroy(m);
+            return set_error(IB_ERR_INVALID, "ib_llama_create: layer %u has a null norm weight", l);
+        }
+        if (w.ffn_gate->qtype != w.ffn_up->qtype) {
+            ib_llama_destroy(m);
+            return set_error(IB_ERR_UNSUPPORTED, "ib_llama_create: layer %u gate/up types differ", l);
+        }
+    }
+    FAIL_IF(check_matrix(weights->token_embd, "token_embd", c.vocab_size, c.hidden_size, false));
+    m->token_embd = weights->token_embd;
+    m->output = weights->output ? weights->output : weights->token_embd;  // tied classifier: transformer.rs:376-382
+    FAIL_IF(check_matrix(m->output, "output", m->vocab_l, c.hidden_size, true));
+    if (!weights->output_norm_dev) {
+        ib_llama_destroy(m);
+        return set_error(IB_ERR_INVALID, "ib_llama_create: null output_norm");
+    }
+    m->output_norm = weights->output_norm_dev;
+
+    // state (transformer.rs:46-137)
+    CU(cudaMalloc(&m->x, sizeof(float) * c.hidden_size));
+    CU(cudaMalloc(&m->xb, sizeof(float) * m->q_dim_l));
+    CU(cudaMalloc(&m->q, sizeof(float) * m->q_dim_l));
+    CU(cudaMalloc(&m->hb, sizeof(float) * m->ffn_l));
+    CU(cudaMalloc(&m->logits, sizeof(float) * m->vocab_l));
+    CU(cudaMalloc(&m->theta, sizeof(float) * (m->head_size / 2)));
+    CU(cudaMalloc(&m->rope_cs, sizeof(float2) * (m->head_size / 2)));
+    {
+        // theta_j = base^(-2j/head_size) with the C library's powf (crates/inferi-shaders/src/rope.rs:76-77)
+        std::vector<float> th(m->head_size / 2);
+        for (uint32_t j = 0; j < m->head_size / 2; j++) th[j] = powf(c.rope_theta, -(float)(2 * j) / (float)m->head_size);
+        CU(cudaMemcpy(m->theta, th.data(), th.size() * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    const size_t kv_elem = kv_dtype == IB_KV_F16 ? 2 : 4;
+    const size_t kv_bytes = (size_t)c.max_position_embeddings * m->kv_dim_l * kv_elem;
+    m->k_cache.assign(c.num_hidden_layers, nullptr);
+    m->v_cache.assign(c.num_hidden_layers, nullptr);
+    for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
+        CU(cudaMalloc(&m->k_cache[l], kv_bytes));
+        CU(cudaMalloc(&m->v_cache[l], kv_bytes));
+        CU(cudaMemset(m->k_cache[l], 0, kv_bytes));
+        CU(cudaMemset(m->v_cache[l], 0, kv_bytes));
+    }
+    m->seq_cap = c.max_position_embeddings + 1;
+    CU(cudaMalloc(&m->ctl, sizeof(TokenCtl)));
+    CU(cudaMemset(m->ctl, 0, sizeof(TokenCtl)));
+    CU(cudaMalloc(&m->seq, sizeof(uint32_t) * m->seq_cap));
+    CU(cudaMemset(m->seq, 0, sizeof(uint32_t) * m->seq_cap));
+    CU(cudaMallocHost(&m->h_pinned, sizeof(uint32_t) * (4 + (size_t)m->seq_cap)));
+    CU(cudaEventCreateWithFlags(&m->staged, cudaEventDisableTiming));
+    ib_attn_params ap{c.max_position_embeddings, m->kv_dim_l, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
+    m->attn_splits = attn_max_splits(ctx, ap);
+    CU(cudaMalloc(&m->attn_scratch, attn_scratch_bytes(ap, m->attn_splits)));
+    CU(cudaMalloc(&m->attn_counters, sizeof(unsigned int) * m->n_kv_l));
+    CU(cudaMemset(m->attn_counters, 0, sizeof(unsigned int) * m->n_kv_l));
+    CU(cudaMalloc(&m->argmax_slots, sizeof(unsigned long long) * (size_t)ctx->sm_count * 2));
+    CU(cudaMalloc(&m->argmax_counter, sizeof(unsigned int)));
+    CU(cudaMemset(m->argmax_counter, 0, sizeof(unsigned int)));
+
+    // record the token graph once
+    CU(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
+    CU(cudaDeviceSynchronize());
+    const uint64_t before = ctx->launches;
+    CU(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
+    rc = record_token(m, m->own_stream, 1);
+    cudaGraph_t graph = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(m->own_stream, &graph);
+    m->launches_per_token = ctx->launches - before;
+    ctx->launches = before;  // recording is not launching
+    if (rc != IB_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        ib_llama_destroy(m);
+        return rc;
+    }
+    if (ce != cudaSuccess) {
+        ib_llama_destroy(m);
+        return set_error(IB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+    }
+    ce = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) {
+        m->graph_exec = nullptr;
+        ib_llama_destroy(m);
+        return set_error(IB_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(ce));
+    }
+#undef FAIL_IF
+#undef CU
+    *out = m;
+    return IB_OK;
+}
+
+static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, uint32_t n_prompt, uint32_t start_pos, uint32_t n_steps) {
+    // control block + given tokens in one pinned staging buffer -> two small async copies
+    uint32_t *h = m->h_pinned;
+    IB_CHECK_CUDA(cudaEventSynchronize(m->staged));  // an earlier call's copies out of the staging buffer are done
+    h[0] = 0; h[1] = start_pos; h[2] = n_prompt; h[3] = 0;
+    for (uint32_t i = 0; i < n_prompt; i++) h[4 + i] = tokens[i];
+    IB_CHECK_CUDA(cudaMemcpyAsync(m->ctl, h, sizeof(TokenCtl), cudaMemcpyHostToDevice, s));
+    IB_CHECK_CUDA(cudaMemcpyAsync(m->seq, h + 4, sizeof(uint32_t) * n_prompt, cudaMemcpyHostToDevice, s));
+    IB_CHECK_CUDA(cudaEventRecord(m->staged, s));
+    for (uint32_t i = 0; i < n_steps; i++) {
+        IB_CHECK_CUDA(cudaGraphLaunch(m->graph_exec, s));
+        m->ctx->launches += m->launches_per_token;
+    }
+    return IB_OK;
+}
+
+int32_t ib_llama_forward(ib_llama *m, void *stream, uint32_t token, uint32_t pos, float *logits_host, uint32_t *next_token_host) {
+    IB_REQUIRE(m, "ib_llama_forward: null model");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    IB_REQUIRE(token < m->cfg.vocab_size, "ib_llama_forward: token %u outside the vocabulary of %u", token, m->cfg.vocab_size);
+    IB_REQUIRE(pos < m->cfg.max_position_embeddings, "ib_llama_forward: pos %u outside the context of %u", pos, m->cfg.max_position_embeddings);
+    cudaStream_t s = (cudaStream_t)stream;
+    int32_t rc = run_tokens(m, s, &token, 1, pos, 1);
+    if (rc) return rc;
+    if (logits_host) IB_CHECK_CUDA(cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * m->vocab_l, cudaMemcpyDeviceToHost, s));
+    if (next_token_host) IB_CHECK_CUDA(cudaMemcpyAsync(next_token_host, &m->ctl->next, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    if (logits_host || next_token_host) IB_CHECK_CUDA(cudaStreamSynchronize(s));
+    return IB_OK;
+}
+
+int32_t ib_llama_generate(ib_llama *m, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos, uint32_t n_gen,
+                          uint32_t *out_tokens_host) {
+    IB_REQUIRE(m && tokens_host, "ib_llama_generate: null argument");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    IB_REQUIRE(n_prompt >= 1, "ib_llama_generate: empty prompt");
+    IB_REQUIRE(n_gen == 0 || out_tokens_host, "ib_llama_generate: null output buffer");
+    const uint64_t steps = (uint64_t)n_prompt + (n_gen ? n_gen - 1 : 0);  // the last generated token is not fed back
+    IB_REQUIRE((uint64_t)start_pos + steps <= m->cfg.max_position_embeddings, "ib_llama_generate: %llu positions from %u exceed the context of %u",
+               (unsigned long long)steps, start_pos, m->cfg.max_position_embeddings);
+    for (uint32_t i = 0; i < n_prompt; i++)
+        IB_REQUIRE(tokens_host[i] < m->cfg.vocab_size, "ib_llama_generate: token %u outside the vocabulary", tokens_host[i]);
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t n_steps = n_gen ? (uint32_t)steps : n_prompt;
+    int32_t rc = run_tokens(m, s, tokens_host, n_prompt, start_pos, n_steps);
+    if (rc) return rc;
+    if (n_gen) IB_CHECK_CUDA(cudaMemcpyAsync(out_tokens_host, m->seq + n_prompt, sizeof(uint32_t) * n_gen, cudaMemcpyDeviceToHost, s));
+    IB_CHECK_CUDA(cudaStreamSynchronize(s));
+    return IB_OK;
+}
+
+int32_t ib_llama_state(ib_llama *m, const float **logits_dev, const float **x_dev) {
+    IB_REQUIRE(m, "ib_llama_state: null model");
+    if (logits_dev) *logits_dev = m->logits;
+    if (x_dev) *x_dev = m->x;
+    return IB_OK;
+}
+
+}  // extern "C"
