@@ -1,0 +1,106 @@
+"""GPU parity of the whole token loop against the CPU oracle: logits within 2e-2 max-abs, greedy tokens identical."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import LOGITS_MAX_ABS, TOKENS_EXACT
+from inferi_b200 import quant
+from inferi_b200.llama2 import LLAMA_3_2_1B, Llama2, Llama2Config, Llama2Weights, Q4_K_M, synth_weights, weights_to_host
+from inferi_b200.ops import GpuQuantTensor, InferiError
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_cfg(c: Llama2Config) -> dict:
+    return dict(hidden=c.hidden_size, ffn=c.intermediate_size, n_layers=c.num_hidden_layers, n_heads=c.num_attention_heads,
+                n_kv_heads=c.num_key_value_heads, vocab=c.vocab_size, max_pos=c.max_position_embeddings, rope_theta=c.rope_theta,
+                rms_eps=c.rms_norm_eps)
+
+
+TINY = Llama2Config(256, 2048, 2, 4, 2, 512, 64, 500000.0, 1e-5)
+TINY_RECIPE = dict(attn_q=quant.Q4_K, attn_k=quant.Q5_K, attn_v=quant.Q8_0, attn_output=quant.Q4_K, ffn_gate=quant.Q4_K, ffn_up=quant.Q4_K,
+                   ffn_down=quant.Q6_K, token_embd=quant.Q4_K, output=quant.Q8_0)
+SMALL = Llama2Config(2048, 8192, 2, 32, 8, 1024, 128, 500000.0, 1e-5)       # Llama-3.2-1B layer shapes, 2 layers
+SMALL_TIED = dict(Q4_K_M, token_embd=quant.Q6_K)
+
+
+def check_loop(backend, cfg, weights, kv_f16, prompt, n_gen, tied=False):
+    host = weights_to_host(weights)
+    ref = oracle.Llama(oracle_cfg(cfg), host, kv_f16=kv_f16)
+    model = Llama2(backend, cfg, Llama2Weights(backend, cfg, weights), kv_f16=kv_f16)
+    # 1. token by token with logits read back (the reference's forward_logits loop), prompt tokens forced
+    tok, pos, worst = prompt[0], 0, 0.0
+    fed, ref_tokens = [], []
+    for step in range(len(prompt) + n_gen - 1):
+        fed.append(tok)
+        nxt, logits = model.forward(tok, pos, want_logits=True)
+        want = ref.forward(tok, pos)
+        worst = max(worst, float(np.abs(logits - want).max()))
+        assert worst <= LOGITS_MAX_ABS, f"logits differ by {worst} at position {pos}"
+        top2 = np.partition(want, -2)[-2:]
+        want_next = oracle.argmax(want)
+        assert nxt == oracle.argmax(logits), "device arg-max disagrees with the arg-max of its own logits"
+        assert nxt == want_next, f"greedy token differs at position {pos}: {nxt} vs {want_next} (oracle margin {top2[1] - top2[0]:.3e})"
+        pos += 1
+        if step + 1 < len(prompt):
+            tok = prompt[step + 1]
+        else:
+            ref_tokens.append(want_next)
+            tok = want_next
+    # 2. the on-device loop (one graph replay per token, no host round trip) must give the same ids
+    out = model.generate(prompt, n_gen, start_pos=0)
+    assert out.tolist() == ref_tokens
+    # 3. continuing from a later start_pos with the cache kept (chat turns) reproduces the tail
+    k = len(prompt) + n_gen // 2
+    seq = list(prompt) + ref_tokens
+    tail = model.generate(seq[k:k + 1], n_gen - (k - len(prompt)) - 1, start_pos=k)
+    assert tail.tolist() == ref_tokens[k - len(prompt) + 1:]
+    model.close()
+    ref.close()
+    return worst
+
+
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_tiny_model_all_quant_types(backend, kv_f16):
+    w = synth_weights(TINY, seed=3001, recipe=TINY_RECIPE)
+    check_loop(backend, TINY, w, kv_f16, prompt=[3, 500, 41, 7], n_gen=24)
+
+
+def test_small_model_tied_classifier(backend):
+    w = synth_weights(SMALL, seed=3003, device="cuda", recipe=SMALL_TIED, tied=True)
+    assert w["output"] is None
+    check_loop(backend, SMALL, w, True, prompt=[1, 1000, 512], n_gen=12)
+
+
+def test_llama_3_2_1b_architecture_64_tokens(backend):
+    """16 layers, hidden 2048, 32 q / 8 kv heads of 64, FFN 8192, vocab 128256, Q4_K_M mix, f16 KV cache, context 4096:
+    32 random prompt tokens through the decode path, then greedy decoding; the first 64 tokens must match the oracle."""
+    cfg = LLAMA_3_2_1B
+    w = synth_weights(cfg, seed=3001, device="cuda")
+    prompt = np.random.default_rng(3002).integers(0, cfg.vocab_size, 32).tolist()
+    worst = check_loop(backend, cfg, w, True, prompt=prompt, n_gen=TOKENS_EXACT - 32 + 1)
+    print(f"1B-architecture: worst logits max-abs difference over 64 positions = {worst:.3e}")
+
+
+def test_model_contract_violations(backend):
+    w = synth_weights(TINY, seed=1, recipe=TINY_RECIPE)
+    weights = Llama2Weights(backend, TINY, w)
+    bad = Llama2Config(256, 2048, 2, 4, 3, 512, 64)
+    with pytest.raises(InferiError):
+        Llama2(backend, bad, weights)                                 # head counts do not divide
+    m = Llama2(backend, TINY, weights)
+    with pytest.raises(InferiError):
+        m.forward(512, 0)                                             # token outside the vocabulary
+    with pytest.raises(InferiError):
+        m.forward(0, 64)                                              # position outside the context
+    with pytest.raises(InferiError):
+        m.generate([1, 2, 3], 70)                                     # would run past the context
+    with pytest.raises(InferiError):
+        Llama2(backend, TINY, weights, tp_rank=2, tp_size=2)          # rank outside the group
+    m.close()
+    # a matrix that misses the alignment rules of the fused kernels is refused, not silently mis-read
+    w2 = synth_weights(TINY, seed=1, recipe=dict(TINY_RECIPE, attn_v=quant.Q6_K))
+    with pytest.raises(InferiError) as e:
+        Llama2(backend, TINY, Llama2Weights(backend, TINY, w2))
+    assert "alignment" in str(e.value)
