@@ -65,6 +65,7 @@ def lib():
         L.orc_llama_set_norms.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.orc_llama_set_globals.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.orc_llama_free.argtypes = [C.c_void_p]
+        L.orc_llama_set_gemv_mode.argtypes = [C.c_void_p, C.c_int]
         L.orc_llama_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
         L.orc_llama_hidden.restype = C.POINTER(C.c_float)
         L.orc_llama_hidden.argtypes = [C.c_void_p]
@@ -208,6 +209,10 @@ class Llama:
             return logits
         lib().orc_llama_forward(self.h, token, pos, None)
         return None
+
+    def set_gemv_mode(self, shader_structured: bool) -> None:
+        """True: every GEMV runs the lane-structured f32 shader restatement (CPU baseline); False: dequantize + f64 dot."""
+        lib().orc_llama_set_gemv_mode(self.h, int(shader_structured))
 
     def hidden_state(self) -> np.ndarray:
         return np.ctypeslib.as_array(lib().orc_llama_hidden(self.h), shape=(self.hidden,)).copy()

@@ -466,7 +466,7 @@ typedef struct orc_llama {
     const float **ffn_norm;    /* [n_layers] */
     orc_qmat token_embd, output;
     const float *output_norm;
-    int kv_f16, nthreads;
+    int kv_f16, nthreads, gemv_mode; /* gemv_mode 0: dequantize + f64 dot; 1: shader-structured f32 (CPU baseline) */
     uint32_t kv_dim, head_size, kv_mul;
     float *x, *xb, *xb2, *hb, *hb2, *q, *krow, *vrow;
     void **kc, **vc;           /* per layer [max_pos, kv_dim] f32 or f16 */
@@ -517,8 +517,12 @@ void orc_llama_free(orc_llama *m) {
 }
 
 static void model_gemv(const orc_llama *m, const orc_qmat *w, size_t rows, size_t cols, const float *v, float *out) {
+    if (m->gemv_mode == 1 && orc_gemv_shader(w->qtype, rows, cols, w->data, v, out, m->nthreads) == 0) return;
     orc_gemv_ref(w->qtype, rows, cols, w->data, v, out, m->nthreads);
 }
+
+/* mode 1 runs every GEMV through the lane-structured shader restatement (the timed CPU baseline). */
+void orc_llama_set_gemv_mode(orc_llama *m, int mode) { m->gemv_mode = mode; }
 
 /* One token through the decoder; logits may be NULL.  The current hidden state stays in m->x. */
 void orc_llama_forward(orc_llama *m, uint32_t token, uint32_t pos, float *logits) {
