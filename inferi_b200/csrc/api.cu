@@ -31,6 +31,14 @@ struct DeviceGuard {
     }
 };
 
+int32_t check_device_error(ib_ctx *ctx) {
+    const uint32_t e = *(volatile uint32_t *)ctx->err_host;
+    if (e == 0) return IB_OK;
+    *(volatile uint32_t *)ctx->err_host = 0;
+    return set_error(IB_ERR_TIMEOUT, "a kernel gave up waiting on a shared-memory barrier (%s); results of that launch are invalid",
+                     e == 1 ? "weights never arrived" : e == 2 ? "ring stage never released" : "unknown wait");
+}
+
 }  // namespace ib
 
 using namespace ib;
@@ -62,6 +70,16 @@ int32_t ib_ctx_create(int32_t device, ib_ctx **out) {
     if (!ctx) return set_error(IB_ERR_OOM, "host allocation failed");
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
+    cudaError_t he = cudaHostAlloc((void **)&ctx->err_host, sizeof(uint32_t), cudaHostAllocMapped);
+    if (he == cudaSuccess) {
+        *ctx->err_host = 0;
+        he = cudaHostGetDevicePointer((void **)&ctx->err_dev, ctx->err_host, 0);
+    }
+    if (he != cudaSuccess) {
+        if (ctx->err_host) cudaFreeHost(ctx->err_host);
+        delete ctx;
+        return set_error(IB_ERR_CUDA, "allocating the error word failed: %s", cudaGetErrorString(he));
+    }
     *out = ctx;
     return IB_OK;
 }
@@ -73,6 +91,7 @@ int32_t ib_ctx_destroy(ib_ctx *ctx) {
     if (ctx->attn_counters) cudaFree(ctx->attn_counters);
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
     if (ctx->argmax_counter) cudaFree(ctx->argmax_counter);
+    if (ctx->err_host) cudaFreeHost(ctx->err_host);
     delete ctx;
     return IB_OK;
 }
@@ -114,7 +133,7 @@ int32_t ib_memcpy_d2h(ib_ctx *ctx, void *stream, void *dst_host, const void *src
 int32_t ib_stream_sync(ib_ctx *ctx, void *stream) {
     IB_ENTER(ctx);
     IB_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    return IB_OK;
+    return check_device_error(ctx);
 }
 
 // ---- quantized tensors ----
@@ -221,6 +240,7 @@ int32_t ib_gemv_quant_host(ib_ctx *ctx, float *out_host, const ib_qtensor *m, co
         e = cudaMemcpyAsync(out_host, o, m->rows * sizeof(float), cudaMemcpyDeviceToHost, 0);
         if (e == cudaSuccess) e = cudaStreamSynchronize(0);
         if (e != cudaSuccess) rc = set_error(IB_ERR_CUDA, "d2h copy failed: %s", cudaGetErrorString(e));
+        if (rc == IB_OK) rc = check_device_error(ctx);
     }
     cudaFree(buf);
     return rc;

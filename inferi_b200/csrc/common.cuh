@@ -34,10 +34,11 @@ int32_t set_error(int32_t code, const char *fmt, ...);
 // ---------------------------------------------------------------------------------------------
 constexpr int QK_K = 256;
 
-// Device layouts.  GGUF: the file's array-of-blocks byte stream, untouched.  SOA: each row re-tiled into
-// sections of equal fields (same row byte length) so that every 128-bit load is aligned:
-//   Q8_0: [nb x 32 B quants][nb x 2 B f16 scale]
-//   Q6_K: [nb x 128 B ql][nb x 64 B qh][nb x 16 B scales][nb x 2 B f16 d]
+// Device layouts.  GGUF: the file's array-of-blocks byte stream, untouched.  SOA: every run of 8 blocks of a row
+// re-tiled into sections of equal fields (same bytes, same row length) so that every 128-bit access is aligned and a
+// row stays one contiguous stream that can be cut at any multiple of 8 blocks:
+//   Q8_0: [8 x 32 B quants][8 x 2 B f16 scale]                              = 272 B per 256 columns
+//   Q6_K: [8 x 128 B ql][8 x 64 B qh][8 x 16 B scales][8 x 2 B f16 d]       = 1680 B per 2048 columns
 enum Layout : uint32_t { LAYOUT_GGUF = 0, LAYOUT_SOA = 1 };
 
 inline uint32_t block_bytes(int qtype) {
@@ -72,6 +73,10 @@ struct ib_ctx {
     // argmax scratch
     unsigned long long *argmax_scratch = nullptr;
     unsigned int *argmax_counter = nullptr;
+    // error word raised by kernels whose bounded waits give up: mapped pinned host memory, so the host reads it
+    // after any synchronisation without a copy
+    uint32_t *err_host = nullptr;
+    uint32_t *err_dev = nullptr;
 };
 
 struct ib_qtensor {
@@ -123,9 +128,14 @@ struct GemvParams {
     uint32_t *argmax_out;
     uint32_t row_offset;               // added to the row index (tensor-parallel vocabulary shard)
     uint32_t pdl;                      // 1: launched with programmatic dependent launch
+    uint32_t *err;                     // device view of the context's error word (set by launch_gemv)
 };
 
 int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p);
+bool gemv_stream_eligible(const GemvParams &p);
+int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p);
+// IB_OK, or IB_ERR_TIMEOUT when a kernel raised the context's error word (call after a synchronisation)
+int32_t check_device_error(ib_ctx *ctx);
 int32_t launch_gemv_generic(ib_ctx *ctx, cudaStream_t stream, const ib_qtensor *m, const float *v, float *out);
 int32_t retile_to_soa(ib_ctx *ctx, cudaStream_t stream, int qtype, const uint8_t *src, uint8_t *dst, uint64_t rows, uint32_t nb);
 bool gemv_fast_eligible(int qtype, uint64_t rows, uint64_t cols);

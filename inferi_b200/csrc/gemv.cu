@@ -1,44 +1,19 @@
-// Batch-1 quantized GEMV for sm_100a: GGUF block dequantisation fused with the dot product.
+// Quantized GEMV, second-line kernels and host dispatch.
 //
-// Replaces the reference shaders crates/inferi-shaders/src/gemv_quant_{q8_0x2,q4_k,q5_k,q6_kx2}.rs and their
-// launcher crates/inferi/src/ops/gemv_quant.rs:183-341.
-//
-// Design (HBM-bound integer work, no tensor cores):
-//  * The activation vector is converted once per CTA into a block-fixed-point form held in shared memory:
-//    per 32 elements one f32 scale s/127 and three int8 "limbs" a0,a1,a2 with
-//        x ~= (s/127) * (a0 + a1/254 + a2/254^2)            (resolution 6e-8 * max|x| of the group),
-//    plus f32 sums of x over every 16 elements (for the K-quant minimum / the Q6_K -32 offset terms).
-//    The per-weight work is then dp4a on packed bytes: no int->float conversion and no f32 multiply per weight.
-//  * Weights stream straight from HBM with aligned 128-bit loads; a warp owns two output rows at a time so the
-//    activation limbs it loads from shared memory are used twice.  Q4_K / Q5_K keep the GGUF byte stream
-//    (144 / 176-byte blocks are 16-byte multiples); Q8_0 / Q6_K rows are re-tiled at upload into equal-field
-//    sections of the same total size (see Layout in common.cuh).
-//  * Epilogues fuse what follows the GEMV in the token loop: residual add, SwiGLU, RoPE + KV-cache append,
-//    and the greedy arg-max of the classifier.  RMSNorm is fused into the prologue.
-#include "common.cuh"
+// The token loop runs on the streaming kernel (gemv_stream.cu).  This file holds
+//  * gemv_wide_kernel: direct 128-bit global loads, one warp per row pair, activations in shared memory; used for
+//    matrices too wide for the streaming kernel's register-resident activations (16384 < cols <= 32768);
+//  * gemv_generic_kernel: any shape the contracts allow, straight from the GGUF byte stream with scalar loads; used
+//    where the alignment rules of the 128-bit kernels fail (for instance Q6_K with cols % 2048 != 0);
+//  * the upload-time re-tiling of Q8_0 / Q6_K rows into groups of 8 blocks, and the launch dispatch.
+// All of them replace crates/inferi-shaders/src/gemv_quant_*.rs behind crates/inferi/src/ops/gemv_quant.rs:183-341.
+#include "gemv_common.cuh"
 
 namespace ib {
 
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr uint32_t GEMV_MAX_COLS = 32768;
 
-__host__ __device__ inline size_t act_smem_bytes(uint32_t cols) { return (size_t)cols * 3 + cols / 32 * 4 + cols / 16 * 4; }
-
-struct Act {
-    const uint8_t *base;
-    uint32_t cols;
-    __device__ __forceinline__ const uint4 *limb(int k) const { return reinterpret_cast<const uint4 *>(base + (size_t)k * cols); }
-    __device__ __forceinline__ const float *sc() const { return reinterpret_cast<const float *>(base + (size_t)3 * cols); }
-    __device__ __forceinline__ const float *sx16() const { return sc() + cols / 32; }
-};
-
-__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
 // streaming 128-bit weight load: read-only path, no L1 allocation (every weight byte is used exactly once)
 __device__ __forceinline__ uint4 ldg_stream(const void *p) {
     uint4 v;
@@ -49,62 +24,6 @@ __device__ __forceinline__ uint32_t ldg_u16(const void *p) {
     uint16_t v;
     asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return v;
-}
-__device__ __forceinline__ float limb_combine(int d0, int d1, int d2) {
-    return (float)d0 + (float)d1 * (1.0f / 254.0f) + (float)d2 * (1.0f / 64516.0f);
-}
-__device__ __forceinline__ float h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
-
-// -------------------------------------------------------------------------------------------------
-// prologue: (optional RMSNorm) + conversion of x into the limb form in shared memory
-// -------------------------------------------------------------------------------------------------
-__device__ void pack_activation(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                float *red /* [GEMV_WARPS + 1] */) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float rms = 1.0f;
-    if (norm_w) {
-        // crates/inferi-shaders/src/rms_norm.rs:112-120
-        float ss = 0.f;
-        for (uint32_t i = tid; i < cols; i += GEMV_THREADS) {
-            float v = __ldcg(x + i);
-            ss += v * v;
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        if (tid == 0) {
-            float t = 0.f;
-            for (int w = 0; w < GEMV_WARPS; w++) t += red[w];
-            red[GEMV_WARPS] = 1.0f / sqrtf(t / (float)cols + eps);
-        }
-        __syncthreads();
-        rms = red[GEMV_WARPS];
-    }
-    int8_t *l0 = reinterpret_cast<int8_t *>(smem), *l1 = l0 + cols, *l2 = l1 + cols;
-    float *sc = reinterpret_cast<float *>(smem + (size_t)3 * cols), *sx16 = sc + cols / 32;
-    for (uint32_t g = warp; g < cols / 32; g += GEMV_WARPS) {
-        uint32_t i = g * 32 + lane;
-        float v = __ldcg(x + i);
-        if (norm_w) v = (v * rms) * __ldg(norm_w + i);
-        float amax = fabsf(v), sum = v;
-#pragma unroll
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-#pragma unroll
-        for (int o = 8; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        float inv = amax > 0.f ? 127.0f / amax : 0.f;
-        float t = v * inv;
-        float a0 = rintf(t);
-        float t1 = (t - a0) * 254.0f;
-        float a1 = rintf(t1);
-        float a2 = rintf((t1 - a1) * 254.0f);
-        l0[i] = (int8_t)(int)a0;
-        l1[i] = (int8_t)(int)a1;
-        l2[i] = (int8_t)(int)a2;
-        if (lane == 0) sc[g] = amax * (1.0f / 127.0f);
-        if ((lane & 15) == 0) sx16[i >> 4] = sum;
-    }
-    __syncthreads();
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -217,23 +136,24 @@ __device__ __forceinline__ void dot_q5k(const uint8_t *const (&row)[NR], uint32_
     }
 }
 
-// Q6_K, SOA rows: [nb*128 ql][nb*64 qh][nb*16 scales][nb*2 d].  A unit is (block b, 128-half i, 16-byte half h):
-// 64 weights = 4 groups g of 16 elements at 256b + 128i + 32g + 16h, each with its own int8 scale [8i + 2g + h].
+// Q6_K rows are stored as groups of 8 blocks: [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d] = 1680 bytes per 2048 columns.
+// A unit is (block b, 128-half i, 16-byte half h): 64 weights = 4 groups g of 16 elements at 256b + 128i + 32g + 16h, each
+// with its own int8 scale [8i + 2g + h].
 template <int NR>
 __device__ __forceinline__ void dot_q6k(const uint8_t *const (&row)[NR], uint32_t nb, const Act &A, int lane, float (&acc)[NR]) {
     const float *SC = A.sc(), *SX = A.sx16();
     for (uint32_t u = lane; u < 4 * nb; u += 32) {
-        const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1;
+        const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1, bb = b & 7;
         uint4 qa[NR], qb[NR], qh[NR], scw[NR];
         uint32_t dbits[NR];
 #pragma unroll
         for (int r = 0; r < NR; r++) {
-            const uint8_t *p = row[r];
-            qa[r] = ldg_stream(p + (size_t)128 * b + 64 * i + 16 * h);
-            qb[r] = ldg_stream(p + (size_t)128 * b + 64 * i + 32 + 16 * h);
-            qh[r] = ldg_stream(p + (size_t)128 * nb + 64 * b + 32 * i + 16 * h);
-            scw[r] = ldg_stream(p + (size_t)192 * nb + 16 * b);
-            dbits[r] = ldg_u16(p + (size_t)208 * nb + 2 * b);
+            const uint8_t *p = row[r] + (size_t)(b >> 3) * 1680;
+            qa[r] = ldg_stream(p + 128 * bb + 64 * i + 16 * h);
+            qb[r] = ldg_stream(p + 128 * bb + 64 * i + 32 + 16 * h);
+            qh[r] = ldg_stream(p + 1024 + 64 * bb + 32 * i + 16 * h);
+            scw[r] = ldg_stream(p + 1536 + 16 * bb);
+            dbits[r] = ldg_u16(p + 1664 + 2 * bb);
         }
         const uint32_t e16 = 16 * b + 8 * i + h;  // 16-element group index of g = 0; group g is at e16 + 2g
         const uint32_t j0 = 8 * b + 4 * i;        // 32-element sub-block of g = 0
@@ -283,7 +203,7 @@ __device__ __forceinline__ void dot_q6k(const uint8_t *const (&row)[NR], uint32_
     }
 }
 
-// Q8_0, SOA rows: [nb*32 quants][nb*2 scales]; a unit is one block.
+// Q8_0 rows are stored as groups of 8 blocks: [8 x 32 quants][8 x 2 scale] = 272 bytes per 256 columns; a unit is one block.
 template <int NR>
 __device__ __forceinline__ void dot_q80(const uint8_t *const (&row)[NR], uint32_t nb, const Act &A, int lane, float (&acc)[NR]) {
     const float *SC = A.sc();
@@ -292,9 +212,10 @@ __device__ __forceinline__ void dot_q80(const uint8_t *const (&row)[NR], uint32_
         uint32_t dbits[NR];
 #pragma unroll
         for (int r = 0; r < NR; r++) {
-            q0[r] = ldg_stream(row[r] + (size_t)32 * b);
-            q1[r] = ldg_stream(row[r] + (size_t)32 * b + 16);
-            dbits[r] = ldg_u16(row[r] + (size_t)32 * nb + 2 * b);
+            const uint8_t *p = row[r] + (size_t)(b >> 3) * 272;
+            q0[r] = ldg_stream(p + 32 * (b & 7));
+            q1[r] = ldg_stream(p + 32 * (b & 7) + 16);
+            dbits[r] = ldg_u16(p + 256 + 2 * (b & 7));
         }
         int D[NR][3];
 #pragma unroll
@@ -326,17 +247,11 @@ __device__ __forceinline__ void dot_rows(uint32_t qtype, const uint8_t *const (&
     }
 }
 
-__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t idx) {
-    uint32_t u = __float_as_uint(v);
-    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - idx);  // ties -> lowest index
-}
-
 // -------------------------------------------------------------------------------------------------
-// the kernel: one warp per pair of rows, CTA-strided
+// the wide kernel: one warp per pair of rows, CTA-strided, activations in shared memory
 // -------------------------------------------------------------------------------------------------
 template <uint32_t EPI>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_wide_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ float red[GEMV_WARPS + 1];
     __shared__ unsigned long long best_sm[GEMV_WARPS];
@@ -539,21 +454,21 @@ __global__ void retile_kernel(int qtype, const uint8_t *__restrict__ src, uint8_
     const uint64_t total = rows * nb;
     for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t r = t / nb;
-        const uint32_t b = (uint32_t)(t % nb);
+        const uint32_t b = (uint32_t)(t % nb), bb = b & 7;
         if (qtype == IB_Q8_0) {
             const uint8_t *s = src + (r * nb + b) * 34;
-            uint8_t *d = dst + r * nb * 34;
-            for (int i = 0; i < 32; i++) d[(size_t)32 * b + i] = s[2 + i];
-            d[(size_t)32 * nb + 2 * b] = s[0];
-            d[(size_t)32 * nb + 2 * b + 1] = s[1];
+            uint8_t *d = dst + r * nb * 34 + (size_t)(b >> 3) * 272;
+            for (int i = 0; i < 32; i++) d[32 * bb + i] = s[2 + i];
+            d[256 + 2 * bb] = s[0];
+            d[256 + 2 * bb + 1] = s[1];
         } else {  // Q6_K
             const uint8_t *s = src + (r * nb + b) * 210;
-            uint8_t *d = dst + r * nb * 210;
-            for (int i = 0; i < 128; i++) d[(size_t)128 * b + i] = s[i];
-            for (int i = 0; i < 64; i++) d[(size_t)128 * nb + 64 * b + i] = s[128 + i];
-            for (int i = 0; i < 16; i++) d[(size_t)192 * nb + 16 * b + i] = s[192 + i];
-            d[(size_t)208 * nb + 2 * b] = s[208];
-            d[(size_t)208 * nb + 2 * b + 1] = s[209];
+            uint8_t *d = dst + r * nb * 210 + (size_t)(b >> 3) * 1680;
+            for (int i = 0; i < 128; i++) d[128 * bb + i] = s[i];
+            for (int i = 0; i < 64; i++) d[1024 + 64 * bb + i] = s[128 + i];
+            for (int i = 0; i < 16; i++) d[1536 + 16 * bb + i] = s[192 + i];
+            d[1664 + 2 * bb] = s[208];
+            d[1664 + 2 * bb + 1] = s[209];
         }
     }
 }
@@ -587,7 +502,7 @@ template <uint32_t EPI>
 static int32_t launch_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, size_t smem) {
     static bool attr_set[8] = {false};
     if (!attr_set[ctx->device & 7]) {
-        IB_CHECK_CUDA(cudaFuncSetAttribute(gemv_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(GEMV_MAX_COLS)));
+        IB_CHECK_CUDA(cudaFuncSetAttribute(gemv_wide_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(GEMV_MAX_COLS)));
         attr_set[ctx->device & 7] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -600,13 +515,16 @@ static int32_t launch_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl ? 1 : 0;
-    IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<EPI>, p));
+    IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemv_wide_kernel<EPI>, p));
     ctx->launches++;
     return IB_OK;
 }
 
-int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p) {
+int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p_in) {
+    GemvParams p = p_in;
+    p.err = ctx->err_dev;
     IB_REQUIRE(p.nseg >= 1 && p.nseg <= 3, "gemv: bad segment count %u", p.nseg);
+    if (gemv_stream_eligible(p)) return launch_gemv_stream(ctx, stream, p);
     IB_REQUIRE(p.cols % 32 == 0 && p.cols <= GEMV_MAX_COLS, "gemv: cols=%u unsupported by the fast kernels", p.cols);
     uint32_t pairs = 0;
     for (uint32_t s = 0; s < p.nseg; s++) {

@@ -47,7 +47,10 @@ __device__ float dequant_at(const QDesc &q, const uint8_t *row, uint32_t col) {
     if (q.qtype == IB_F32) return reinterpret_cast<const float *>(row)[col];
     if (q.qtype == IB_Q8_0) {
         const uint32_t b = col >> 5, i = col & 31;
-        if (q.layout == LAYOUT_SOA) return (float)(int8_t)row[(size_t)32 * b + i] * half_at(row + (size_t)32 * q.nb + 2 * b);
+        if (q.layout == LAYOUT_SOA) {
+            const uint8_t *grp = row + (size_t)(b >> 3) * 272;
+            return (float)(int8_t)grp[32 * (b & 7) + i] * half_at(grp + 256 + 2 * (b & 7));
+        }
         const uint8_t *blk = row + (size_t)b * 34;
         return (float)(int8_t)blk[2 + i] * half_at(blk);
     }
@@ -66,7 +69,9 @@ __device__ float dequant_at(const QDesc &q, const uint8_t *row, uint32_t col) {
     // Q6_K
     const uint8_t *ql, *qh, *sc, *dp;
     if (q.layout == LAYOUT_SOA) {
-        ql = row + (size_t)128 * b; qh = row + (size_t)128 * q.nb + 64 * b; sc = row + (size_t)192 * q.nb + 16 * b; dp = row + (size_t)208 * q.nb + 2 * b;
+        const uint8_t *grp = row + (size_t)(b >> 3) * 1680;
+        const uint32_t bb = b & 7;
+        ql = grp + 128 * bb; qh = grp + 1024 + 64 * bb; sc = grp + 1536 + 16 * bb; dp = grp + 1664 + 2 * bb;
     } else {
         const uint8_t *blk = row + (size_t)b * 210;
         ql = blk; qh = blk + 128; sc = blk + 192; dp = blk + 208;
@@ -427,7 +432,10 @@ int32_t ib_llama_forward(ib_llama *m, void *stream, uint32_t token, uint32_t pos
     if (rc) return rc;
     if (logits_host) IB_CHECK_CUDA(cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * m->vocab_l, cudaMemcpyDeviceToHost, s));
     if (next_token_host) IB_CHECK_CUDA(cudaMemcpyAsync(next_token_host, &m->ctl->next, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
-    if (logits_host || next_token_host) IB_CHECK_CUDA(cudaStreamSynchronize(s));
+    if (logits_host || next_token_host) {
+        IB_CHECK_CUDA(cudaStreamSynchronize(s));
+        return check_device_error(m->ctx);
+    }
     return IB_OK;
 }
 
@@ -448,7 +456,7 @@ int32_t ib_llama_generate(ib_llama *m, void *stream, const uint32_t *tokens_host
     if (rc) return rc;
     if (n_gen) IB_CHECK_CUDA(cudaMemcpyAsync(out_tokens_host, m->seq + n_prompt, sizeof(uint32_t) * n_gen, cudaMemcpyDeviceToHost, s));
     IB_CHECK_CUDA(cudaStreamSynchronize(s));
-    return IB_OK;
+    return check_device_error(m->ctx);
 }
 
 int32_t ib_llama_state(ib_llama *m, const float **logits_dev, const float **x_dev) {

@@ -38,7 +38,8 @@ def test_golden_vectors(backend, qt):
 @pytest.mark.parametrize("qt,rows,cols", [
     (quant.Q8_0, 64, 256), (quant.Q4_K, 64, 256), (quant.Q5_K, 64, 256), (quant.Q6_K, 64, 512),
     (quant.Q8_0, 64, 128), (quant.Q6_K, 8, 256), (quant.Q6_K, 64, 2048), (quant.Q6_K, 36, 6144), (quant.Q8_0, 260, 1024),
-    (quant.Q4_K, 4, 256), (quant.Q4_K, 1000, 2560), (quant.Q5_K, 12, 14336), (quant.Q4_K, 8, 32768), (quant.Q4_K, 8, 33024),
+    (quant.Q4_K, 4, 256), (quant.Q4_K, 1000, 2560), (quant.Q4_K, 128, 11008), (quant.Q6_K, 64, 8192), (quant.Q8_0, 64, 14336),
+    (quant.Q5_K, 296, 4096), (quant.Q4_K, 300, 6144), (quant.Q6_K, 1184, 4096), (quant.Q4_K, 2372, 2048), (quant.Q4_K, 16, 16384), (quant.Q4_K, 16, 16640), (quant.Q5_K, 12, 14336), (quant.Q4_K, 8, 32768), (quant.Q4_K, 8, 33024),
 ])
 def test_reference_test_shapes_and_edges(backend, qt, rows, cols):
     blocks = quant.random_blocks(qt, rows, cols, seed=rows * 31 + cols + qt, scale=1.0, subnormal_frac=0.25)
