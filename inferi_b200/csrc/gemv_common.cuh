@@ -66,18 +66,23 @@ __device__ __forceinline__ void pack_float4(float4 v, uint32_t idx, uint32_t col
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     const float inv = amax > 0.f ? 127.0f / amax : 0.f;
     const float e[4] = {v.x, v.y, v.z, v.w};
-    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    // round-to-nearest-even by adding 1.5 * 2^23: the sum's low mantissa byte is the rounded value in two's complement
+    // (|t| <= 127), and subtracting the constant again gives it back as a float - no conversion instructions
+    constexpr float MAGIC = 12582912.0f;
+    uint32_t b0[4], b1[4], b2[4];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         const float t = e[k] * inv;
-        const float a0 = rintf(t);
-        const float t1 = (t - a0) * 254.0f;
-        const float a1 = rintf(t1);
-        const float a2 = rintf((t1 - a1) * 254.0f);
-        w0 |= ((uint32_t)(int)a0 & 0xFFu) << (8 * k);
-        w1 |= ((uint32_t)(int)a1 & 0xFFu) << (8 * k);
-        w2 |= ((uint32_t)(int)a2 & 0xFFu) << (8 * k);
+        const float r0 = t + MAGIC;
+        const float t1 = (t - (r0 - MAGIC)) * 254.0f;
+        const float r1 = t1 + MAGIC;
+        const float r2 = (t1 - (r1 - MAGIC)) * 254.0f + MAGIC;
+        b0[k] = __float_as_uint(r0); b1[k] = __float_as_uint(r1); b2[k] = __float_as_uint(r2);
     }
+    // low bytes of four words -> one word
+    const uint32_t w0 = __byte_perm(__byte_perm(b0[0], b0[1], 0x0040), __byte_perm(b0[2], b0[3], 0x0040), 0x5410);
+    const uint32_t w1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
+    const uint32_t w2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
     if (store) {
         uint32_t *l0 = reinterpret_cast<uint32_t *>(smem), *l1 = l0 + cols / 4, *l2 = l1 + cols / 4;
         float *sc = reinterpret_cast<float *>(smem + (size_t)3 * cols), *sx16 = sc + cols / 32;
@@ -95,12 +100,18 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *w4 = reinterpret_cast<const float4 *>(norm_w);
     const bool in_regs = nv <= (uint32_t)MAXV * PACK_THREADS;
-    float4 xv[MAXV];
+    constexpr int MAXG = 4;   // norm weights fetched together with x (covers 4096 columns; wider rows fetch them later)
+    float4 xv[MAXV], gv[MAXG];
     if (in_regs) {
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
             const uint32_t idx = tid + PACK_THREADS * i;
             xv[i] = idx < nv ? __ldcg(x4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < MAXG; i++) {
+            const uint32_t idx = tid + PACK_THREADS * i;
+            gv[i] = (norm_w && idx < nv) ? __ldg(w4 + idx) : make_float4(1.f, 1.f, 1.f, 1.f);
         }
     }
     float rms = 1.0f;
@@ -133,7 +144,7 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
                 float4 v = xv[i];
                 const bool ok = idx < nv;
                 if (norm_w && ok) {
-                    const float4 g = __ldg(w4 + idx);
+                    const float4 g = i < MAXG ? gv[i < MAXG ? i : 0] : __ldg(w4 + idx);
                     v.x = (v.x * rms) * g.x; v.y = (v.y * rms) * g.y; v.z = (v.z * rms) * g.z; v.w = (v.w * rms) * g.w;
                 }
                 pack_float4(v, idx, cols, smem, ok);

@@ -24,6 +24,21 @@ constexpr int STREAM_THREADS = (CW + 1) * 32;   // + 1 producer warp
 constexpr int PT_MAX = 8;                       // row pairs per tile
 constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;   // a wait on an mbarrier gives up after 4 s
 
+#ifdef IB_STREAM_TRACE
+// Timeline probes for latency studies: globaltimer stamps of a few CTAs, read back with ib_debug_stream_trace().
+__device__ unsigned long long g_trace[64 * 16];
+#define TRACE(slot)                                                                    \
+    do {                                                                               \
+        if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {               \
+            unsigned long long _t;                                                     \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                     \
+            g_trace[(warp == CW ? 32 : 0) + (slot)] = _t;                              \
+        }                                                                              \
+    } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
+
 struct StreamGeom {
     uint32_t stages, stage_bytes, act_off, part_off, bar_off;
 };
@@ -69,63 +84,71 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 }
 
 // ---- this CTA's share of the work: per segment a contiguous range of row pairs, balanced by bytes ----
+// (three scalar sets instead of arrays: indexing them with a run-time segment number would put them in local memory)
 struct Share {
-    uint32_t a[3], b[3];     // pair range per segment
-    uint32_t cost[3];        // bytes per pair
-    uint32_t pt[3];          // pairs per tile
+    uint32_t a0, a1, a2, b0, b1, b2;   // pair range per segment
+    uint32_t c0, c1, c2;               // bytes per pair
+    uint32_t t0, t1, t2;               // pairs per tile
     uint32_t nseg;
+    __device__ __forceinline__ uint32_t a(uint32_t s) const { return s == 0 ? a0 : (s == 1 ? a1 : a2); }
+    __device__ __forceinline__ uint32_t b(uint32_t s) const { return s == 0 ? b0 : (s == 1 ? b1 : b2); }
+    __device__ __forceinline__ uint32_t cost(uint32_t s) const { return s == 0 ? c0 : (s == 1 ? c1 : c2); }
+    __device__ __forceinline__ uint32_t pt(uint32_t s) const { return s == 0 ? t0 : (s == 1 ? t1 : t2); }
 };
 
+// all byte counts in units of 16 bytes so that the arithmetic stays in 32 bits (64-bit divisions cost ~0.2 us each)
+__device__ __forceinline__ void share_range(uint32_t lo, uint32_t hi, uint32_t start, uint32_t cost16, uint32_t pairs, uint32_t &a, uint32_t &b) {
+    const uint32_t x = lo > start ? (lo - start + cost16 - 1) / cost16 : 0;
+    const uint32_t y = hi > start ? (hi - start + cost16 - 1) / cost16 : 0;
+    a = x > pairs ? pairs : x;
+    b = y > pairs ? pairs : y;
+}
+
+__device__ __forceinline__ uint32_t tile_pairs(uint32_t stage_bytes, uint32_t cost, uint32_t RG) {
+    uint32_t pt = stage_bytes / cost;
+    pt = pt < 1 ? 1 : (pt > PT_MAX ? PT_MAX : pt);
+    if (pt > RG) pt = pt / RG * RG;   // whole rounds of the row groups
+    return pt;
+}
+
 template <uint32_t EPI>
-__device__ __forceinline__ void make_share(const GemvParams &p, uint32_t stage_bytes, Share &sh) {
-    uint32_t pairs[3];
-    unsigned long long start[4];
+__device__ __forceinline__ void make_share(const GemvParams &p, uint32_t stage_bytes, uint32_t RG, Share &sh) {
+    uint32_t n0, n1 = 0, n2 = 0;
     sh.nseg = (EPI == EPI_SWIGLU) ? 1u : p.nseg;
-    start[0] = 0;
-#pragma unroll
-    for (int s = 0; s < 3; s++) {
-        if (s < (int)sh.nseg) {
-            if (EPI == EPI_SWIGLU) { pairs[s] = p.seg[0].rows; sh.cost[s] = (uint32_t)(p.seg[0].row_bytes + p.seg[1].row_bytes); }
-            else { pairs[s] = p.seg[s].rows / 2; sh.cost[s] = (uint32_t)(2 * p.seg[s].row_bytes); }
-        } else { pairs[s] = 0; sh.cost[s] = 1; }
-        start[s + 1] = start[s] + (unsigned long long)pairs[s] * sh.cost[s];
-        uint32_t pt = stage_bytes / sh.cost[s];
-        sh.pt[s] = pt < 1 ? 1 : (pt > PT_MAX ? PT_MAX : pt);
+    sh.c1 = sh.c2 = 16;
+    if (EPI == EPI_SWIGLU) { n0 = p.seg[0].rows; sh.c0 = (uint32_t)(p.seg[0].row_bytes + p.seg[1].row_bytes); }
+    else {
+        n0 = p.seg[0].rows / 2; sh.c0 = (uint32_t)(2 * p.seg[0].row_bytes);
+        if (sh.nseg > 1) { n1 = p.seg[1].rows / 2; sh.c1 = (uint32_t)(2 * p.seg[1].row_bytes); }
+        if (sh.nseg > 2) { n2 = p.seg[2].rows / 2; sh.c2 = (uint32_t)(2 * p.seg[2].row_bytes); }
     }
-    const unsigned long long total = start[3];
-    const unsigned long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-#pragma unroll
-    for (int s = 0; s < 3; s++) {
-        const unsigned long long c = sh.cost[s];
-        unsigned long long a = lo > start[s] ? (lo - start[s] + c - 1) / c : 0;
-        unsigned long long b = hi > start[s] ? (hi - start[s] + c - 1) / c : 0;
-        sh.a[s] = (uint32_t)(a > pairs[s] ? pairs[s] : a);
-        sh.b[s] = (uint32_t)(b > pairs[s] ? pairs[s] : b);
-    }
+    const uint32_t k0 = sh.c0 / 16, k1 = sh.c1 / 16, k2 = sh.c2 / 16;
+    const uint32_t s1 = n0 * k0, s2 = s1 + n1 * k1, total = s2 + n2 * k2;
+    const uint32_t G = gridDim.x, q = total / G, r = total % G;
+    const uint32_t lo = q * blockIdx.x + r * blockIdx.x / G, hi = q * (blockIdx.x + 1) + r * (blockIdx.x + 1) / G;
+    share_range(lo, hi, 0, k0, n0, sh.a0, sh.b0);
+    share_range(lo, hi, s1, k1, n1, sh.a1, sh.b1);
+    share_range(lo, hi, s2, k2, n2, sh.a2, sh.b2);
+    sh.t0 = tile_pairs(stage_bytes, sh.c0, RG);
+    sh.t1 = tile_pairs(stage_bytes, sh.c1, RG);
+    sh.t2 = tile_pairs(stage_bytes, sh.c2, RG);
 }
 
 struct TileCursor {
-    uint32_t seg, next;   // segment and first pair of the next tile
-    __device__ __forceinline__ void init(const Share &sh) {
-        seg = 0;
-        next = sh.a[0];
-        skip(sh);
-    }
-    __device__ __forceinline__ void skip(const Share &sh) {
-        while (seg < sh.nseg && next >= sh.b[seg]) {
+    uint32_t seg, next, end, pt;   // segment, first pair of the next tile, end of the segment's range, pairs per tile
+    __device__ __forceinline__ void enter(const Share &sh) {
+        while (seg < sh.nseg) {
+            next = sh.a(seg); end = sh.b(seg); pt = sh.pt(seg);
+            if (next < end) break;
             seg++;
-            if (seg < sh.nseg) next = sh.a[seg];
         }
     }
+    __device__ __forceinline__ void init(const Share &sh) { seg = 0; next = end = pt = 0; enter(sh); }
     __device__ __forceinline__ bool valid(const Share &sh) const { return seg < sh.nseg; }
-    // current tile: pairs [next, next + n) of segment seg
-    __device__ __forceinline__ uint32_t count(const Share &sh) const {
-        const uint32_t left = sh.b[seg] - next;
-        return left < sh.pt[seg] ? left : sh.pt[seg];
-    }
+    __device__ __forceinline__ uint32_t count(const Share &) const { return (end - next) < pt ? (end - next) : pt; }
     __device__ __forceinline__ void advance(const Share &sh) {
         next += count(sh);
-        skip(sh);
+        if (next >= end) { seg++; enter(sh); }
     }
 };
 
@@ -151,12 +174,20 @@ __device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const 
 #pragma unroll
         for (int g = 0; g < 4; g++) e16[g] = 4 * u + g;
     }
+    // asm volatile loads: they must stay where they are.  As ordinary loads they are loop-invariant and the compiler
+    // hoists the copies of every format's consumer loop to one place, where they all stay live at once.
 #pragma unroll
     for (int g = 0; g < 4; g++) {
 #pragma unroll
-        for (int k = 0; k < 3; k++) ua.l[k][g] = A.limb(k)[e16[g]];
-        ua.s[g] = SC[e16[g] >> 1];
-        ua.x[g] = SX[e16[g]];
+        for (int k = 0; k < 3; k++) {
+            const uint32_t addr = smem_u32(A.limb(k) + e16[g]);
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(ua.l[k][g].x), "=r"(ua.l[k][g].y), "=r"(ua.l[k][g].z), "=r"(ua.l[k][g].w)
+                         : "r"(addr)
+                         : "memory");
+        }
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.s[g]) : "r"(smem_u32(SC + (e16[g] >> 1))) : "memory");
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.x[g]) : "r"(smem_u32(SX + e16[g])) : "memory");
     }
     if (qtype == IB_Q4_K) { ua.s[2] *= (1.0f / 16.0f); ua.s[3] *= (1.0f / 16.0f); }  // high nibbles are used in place (16 q)
 }
@@ -169,128 +200,159 @@ __device__ __forceinline__ int dot4_us(const uint4 &q, const uint4 &a, int d) {
 }
 __device__ __forceinline__ uint4 and4(const uint4 &q, uint32_t m) { return make_uint4(q.x & m, q.y & m, q.z & m, q.w & m); }
 
-// One row (in shared memory) x one unit.  Returns the lane's partial dot product.
-__device__ __forceinline__ float unit_dot_q4k(const uint8_t *row, uint32_t u, const UnitAct &ua) {
-    const uint32_t b = u >> 2, c = u & 3;
-    const uint8_t *blk = row + b * 144;
-    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-    const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
-    const uint4 q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
-    const uint4 l0 = and4(q0, 0x0F0F0F0Fu), l1 = and4(q1, 0x0F0F0F0Fu), h0 = and4(q0, 0xF0F0F0F0u), h1 = and4(q1, 0xF0F0F0F0u);
-    int D[4][3];
-#pragma unroll
-    for (int k = 0; k < 3; k++) {
-        D[0][k] = dot4_ss(l0, ua.l[k][0], 0);
-        D[1][k] = dot4_ss(l1, ua.l[k][1], 0);
-        D[2][k] = dot4_us(h0, ua.l[k][2], 0);
-        D[3][k] = dot4_us(h1, ua.l[k][3], 0);
-    }
-    uint32_t sc2, m2;
-    kquant_scales(hdr, c, sc2, m2);
-    const float d = h2f(hdr.x & 0xFFFFu), dmin = h2f(hdr.x >> 16);
-    const float lo = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
-    const float hi = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
-    return (d * (float)(sc2 & 0xFFu)) * lo - (dmin * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (d * (float)(sc2 >> 8)) * hi -
-           (dmin * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
-}
+// One row (in shared memory) x one unit -> the lane's partial dot product.  Everything that depends only on the
+// lane (byte offsets inside a row, shift amounts) is computed once in init().
+struct LaneConst { uint32_t o0, o1, o2, o3, k; };
+template <uint32_t QT> struct Unit;
 
-__device__ __forceinline__ float unit_dot_q5k(const uint8_t *row, uint32_t u, const UnitAct &ua) {
-    const uint32_t b = u >> 2, c = u & 3;
-    const uint8_t *blk = row + b * 176;
-    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-    const uint4 hA = *reinterpret_cast<const uint4 *>(blk + 16), hB = *reinterpret_cast<const uint4 *>(blk + 32);
-    const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 48 + 32 * c), q1 = *reinterpret_cast<const uint4 *>(blk + 64 + 32 * c);
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const uint32_t hw[8] = {hA.x, hA.y, hA.z, hA.w, hB.x, hB.y, hB.z, hB.w};
-    uint32_t lo[8], hi[8];
+template <> struct Unit<IB_Q4_K> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) { lc.k = u & 3; lc.o0 = (u >> 2) * 144; lc.o1 = lc.o0 + 16 + 32 * lc.k; }
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_hdr = lc.o0, off_q = lc.o1, c = lc.k;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + off_hdr);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+        const uint4 l0 = and4(q0, 0x0F0F0F0Fu), l1 = and4(q1, 0x0F0F0F0Fu), h0 = and4(q0, 0xF0F0F0F0u), h1 = and4(q1, 0xF0F0F0F0u);
+        int D[4][3];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const uint32_t t = hw[i] >> (2 * c);  // bit 0 of each byte: flag of the low-nibble element, bit 1: of the high-nibble element
-        lo[i] = (qw[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
-        hi[i] = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(l0, ua.l[k][0], 0);
+            D[1][k] = dot4_ss(l1, ua.l[k][1], 0);
+            D[2][k] = dot4_us(h0, ua.l[k][2], 0);
+            D[3][k] = dot4_us(h1, ua.l[k][3], 0);
+        }
+        uint32_t sc2, m2;
+        kquant_scales(hdr, c, sc2, m2);
+        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        const float lo = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
+        const float hi = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
+        return (dm.x * (float)(sc2 & 0xFFu)) * lo - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi -
+               (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
     }
-    int D[4][3];
+};
+
+template <> struct Unit<IB_Q5_K> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) { lc.k = u & 3; lc.o0 = (u >> 2) * 176; lc.o1 = lc.o0 + 48 + 32 * lc.k; }
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_hdr = lc.o0, off_q = lc.o1, c = lc.k;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + off_hdr);
+        const uint4 hA = *reinterpret_cast<const uint4 *>(row + off_hdr + 16), hB = *reinterpret_cast<const uint4 *>(row + off_hdr + 32);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q), q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hw[8] = {hA.x, hA.y, hA.z, hA.w, hB.x, hB.y, hB.z, hB.w};
+        uint32_t lo[8], hi[8];
 #pragma unroll
-    for (int k = 0; k < 3; k++) {
-        D[0][k] = dot4_ss(make_uint4(lo[0], lo[1], lo[2], lo[3]), ua.l[k][0], 0);
-        D[1][k] = dot4_ss(make_uint4(lo[4], lo[5], lo[6], lo[7]), ua.l[k][1], 0);
-        D[2][k] = dot4_ss(make_uint4(hi[0], hi[1], hi[2], hi[3]), ua.l[k][2], 0);
-        D[3][k] = dot4_ss(make_uint4(hi[4], hi[5], hi[6], hi[7]), ua.l[k][3], 0);
+        for (int i = 0; i < 8; i++) {
+            const uint32_t t = hw[i] >> (2 * c);  // bit 0 of each byte: flag of the low-nibble element, bit 1: of the high-nibble element
+            lo[i] = (qw[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
+            hi[i] = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
+        }
+        int D[4][3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(make_uint4(lo[0], lo[1], lo[2], lo[3]), ua.l[k][0], 0);
+            D[1][k] = dot4_ss(make_uint4(lo[4], lo[5], lo[6], lo[7]), ua.l[k][1], 0);
+            D[2][k] = dot4_ss(make_uint4(hi[0], hi[1], hi[2], hi[3]), ua.l[k][2], 0);
+            D[3][k] = dot4_ss(make_uint4(hi[4], hi[5], hi[6], hi[7]), ua.l[k][3], 0);
+        }
+        uint32_t sc2, m2;
+        kquant_scales(hdr, c, sc2, m2);
+        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        const float lo_f = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
+        const float hi_f = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
+        return (dm.x * (float)(sc2 & 0xFFu)) * lo_f - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi_f -
+               (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
     }
-    uint32_t sc2, m2;
-    kquant_scales(hdr, c, sc2, m2);
-    const float d = h2f(hdr.x & 0xFFFFu), dmin = h2f(hdr.x >> 16);
-    const float lo_f = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
-    const float hi_f = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
-    return (d * (float)(sc2 & 0xFFu)) * lo_f - (dmin * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (d * (float)(sc2 >> 8)) * hi_f -
-           (dmin * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
-}
+};
 
 // Q6_K rows are stored as groups of 8 blocks: [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d] = 1680 bytes per 2048 columns.
-__device__ __forceinline__ float unit_dot_q6k(const uint8_t *row, uint32_t u, const UnitAct &ua) {
-    const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1;
-    const uint8_t *grp = row + (b >> 3) * 1680;
-    const uint32_t bb = b & 7;
-    const uint4 qa = *reinterpret_cast<const uint4 *>(grp + 128 * bb + 64 * i + 16 * h);
-    const uint4 qb = *reinterpret_cast<const uint4 *>(grp + 128 * bb + 64 * i + 32 + 16 * h);
-    const uint4 qh = *reinterpret_cast<const uint4 *>(grp + 1024 + 64 * bb + 32 * i + 16 * h);
-    const uint2 scw = *reinterpret_cast<const uint2 *>(grp + 1536 + 16 * bb + 8 * i);  // scales[8i .. 8i+7]
-    const float d = h2f(*reinterpret_cast<const unsigned short *>(grp + 1664 + 2 * bb));
-    const uint32_t la[4] = {qa.x, qa.y, qa.z, qa.w}, lb[4] = {qb.x, qb.y, qb.z, qb.w}, hh[4] = {qh.x, qh.y, qh.z, qh.w};
-    uint32_t g0[4], g1[4], g2[4], g3[4];
-#pragma unroll
-    for (int w = 0; w < 4; w++) {
-        // crates/inferi/src/quantization.rs:237-246: 4 low bits from ql, 2 high bits from qh
-        g0[w] = (la[w] & 0x0F0F0F0Fu) | ((hh[w] << 4) & 0x30303030u);
-        g1[w] = (lb[w] & 0x0F0F0F0Fu) | ((hh[w] << 2) & 0x30303030u);
-        g2[w] = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
-        g3[w] = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
+template <> struct Unit<IB_Q6_K> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) {
+        const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1, grp = (b >> 3) * 1680, bb = b & 7;
+        lc.o0 = grp + 128 * bb + 64 * i + 16 * h;
+        lc.o1 = grp + 1024 + 64 * bb + 32 * i + 16 * h;
+        lc.o2 = grp + 1536 + 16 * bb + 8 * i;
+        lc.o3 = grp + 1664 + 2 * bb;
+        lc.k = 8 * h;
     }
-    int D[4][3];
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_qa = lc.o0, off_qh = lc.o1, off_sc = lc.o2, off_d = lc.o3, sh = lc.k;
+        const uint4 qa = *reinterpret_cast<const uint4 *>(row + off_qa);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(row + off_qa + 32);
+        const uint4 qh = *reinterpret_cast<const uint4 *>(row + off_qh);
+        const uint2 scw = *reinterpret_cast<const uint2 *>(row + off_sc);   // scales[8i .. 8i+7]
+        const float d = h2f(*reinterpret_cast<const unsigned short *>(row + off_d));
+        const uint32_t la[4] = {qa.x, qa.y, qa.z, qa.w}, lb[4] = {qb.x, qb.y, qb.z, qb.w}, hh[4] = {qh.x, qh.y, qh.z, qh.w};
+        uint32_t g0[4], g1[4], g2[4], g3[4];
 #pragma unroll
-    for (int k = 0; k < 3; k++) {
-        D[0][k] = dot4_ss(make_uint4(g0[0], g0[1], g0[2], g0[3]), ua.l[k][0], 0);
-        D[1][k] = dot4_ss(make_uint4(g1[0], g1[1], g1[2], g1[3]), ua.l[k][1], 0);
-        D[2][k] = dot4_ss(make_uint4(g2[0], g2[1], g2[2], g2[3]), ua.l[k][2], 0);
-        D[3][k] = dot4_ss(make_uint4(g3[0], g3[1], g3[2], g3[3]), ua.l[k][3], 0);
-    }
-    float v = 0.f;
+        for (int w = 0; w < 4; w++) {
+            // crates/inferi/src/quantization.rs:237-246: 4 low bits from ql, 2 high bits from qh
+            g0[w] = (la[w] & 0x0F0F0F0Fu) | ((hh[w] << 4) & 0x30303030u);
+            g1[w] = (lb[w] & 0x0F0F0F0Fu) | ((hh[w] << 2) & 0x30303030u);
+            g2[w] = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
+            g3[w] = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
+        }
+        int D[4][3];
 #pragma unroll
-    for (int g = 0; g < 4; g++) {
-        const uint32_t word = (g < 2) ? scw.x : scw.y;   // scale index 8i + 2g + h
-        const int sc = (int)(int8_t)(word >> (8 * (2 * (g & 1) + h)));
-        v += (d * (float)sc) * (ua.s[g] * limb_combine(D[g][0], D[g][1], D[g][2]) - 32.0f * ua.x[g]);
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(make_uint4(g0[0], g0[1], g0[2], g0[3]), ua.l[k][0], 0);
+            D[1][k] = dot4_ss(make_uint4(g1[0], g1[1], g1[2], g1[3]), ua.l[k][1], 0);
+            D[2][k] = dot4_ss(make_uint4(g2[0], g2[1], g2[2], g2[3]), ua.l[k][2], 0);
+            D[3][k] = dot4_ss(make_uint4(g3[0], g3[1], g3[2], g3[3]), ua.l[k][3], 0);
+        }
+        // scale of group g is byte 2g + h of the 8 loaded: bytes {h, 2+h} of word x, {h, 2+h} of word y
+        const uint32_t sx = scw.x >> sh, sy = scw.y >> sh;
+        const float s0 = (float)(int)(int8_t)(sx & 0xFF), s1 = (float)(int)(int8_t)((sx >> 16) & 0xFF);
+        const float s2 = (float)(int)(int8_t)(sy & 0xFF), s3 = (float)(int)(int8_t)((sy >> 16) & 0xFF);
+        float v = s0 * (ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) - 32.0f * ua.x[0]);
+        v += s1 * (ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]) - 32.0f * ua.x[1]);
+        v += s2 * (ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) - 32.0f * ua.x[2]);
+        v += s3 * (ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]) - 32.0f * ua.x[3]);
+        return d * v;
     }
-    return v;
-}
+};
 
 // Q8_0 rows are stored as groups of 8 blocks: [8 x 32 quants][8 x 2 scale] = 272 bytes per 256 columns.
-__device__ __forceinline__ float unit_dot_q80(const uint8_t *row, uint32_t u, const UnitAct &ua) {
-    const uint32_t b0 = 2 * u;
-    const uint8_t *grp = row + (b0 >> 3) * 272;
-    const uint32_t bb = b0 & 7;
-    const uint4 q0 = *reinterpret_cast<const uint4 *>(grp + 32 * bb), q1 = *reinterpret_cast<const uint4 *>(grp + 32 * bb + 16);
-    const uint4 q2 = *reinterpret_cast<const uint4 *>(grp + 32 * bb + 32), q3 = *reinterpret_cast<const uint4 *>(grp + 32 * bb + 48);
-    const uint32_t dd = *reinterpret_cast<const uint32_t *>(grp + 256 + 2 * bb);   // two f16 scales
-    int D[4][3];
-#pragma unroll
-    for (int k = 0; k < 3; k++) {
-        D[0][k] = dot4_ss(q0, ua.l[k][0], 0);
-        D[1][k] = dot4_ss(q1, ua.l[k][1], 0);
-        D[2][k] = dot4_ss(q2, ua.l[k][2], 0);
-        D[3][k] = dot4_ss(q3, ua.l[k][3], 0);
+template <> struct Unit<IB_Q8_0> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) {
+        const uint32_t b0 = 2 * u, grp = (b0 >> 3) * 272, bb = b0 & 7;
+        lc.o0 = grp + 32 * bb;
+        lc.o1 = grp + 256 + 2 * bb;
     }
-    const float a = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
-    const float c = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
-    return h2f(dd & 0xFFFFu) * a + h2f(dd >> 16) * c;
-}
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_q = lc.o0, off_d = lc.o1;
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q), q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+        const uint4 q2 = *reinterpret_cast<const uint4 *>(row + off_q + 32), q3 = *reinterpret_cast<const uint4 *>(row + off_q + 48);
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(row + off_d));   // scales of the two blocks
+        int D[4][3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(q0, ua.l[k][0], 0);
+            D[1][k] = dot4_ss(q1, ua.l[k][1], 0);
+            D[2][k] = dot4_ss(q2, ua.l[k][2], 0);
+            D[3][k] = dot4_ss(q3, ua.l[k][3], 0);
+        }
+        const float a = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
+        const float c = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
+        return dd.x * a + dd.y * c;
+    }
+};
 
-__device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, uint32_t u, const UnitAct &ua) {
+__device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst &lc) {
+    lc.o0 = lc.o1 = lc.o2 = lc.o3 = lc.k = 0;
     switch (qtype) {
-    case IB_Q4_K: return unit_dot_q4k(row, u, ua);
-    case IB_Q6_K: return unit_dot_q6k(row, u, ua);
-    case IB_Q5_K: return unit_dot_q5k(row, u, ua);
-    default: return unit_dot_q80(row, u, ua);
+    case IB_Q4_K: Unit<IB_Q4_K>::init(u, lc); break;
+    case IB_Q6_K: Unit<IB_Q6_K>::init(u, lc); break;
+    case IB_Q5_K: Unit<IB_Q5_K>::init(u, lc); break;
+    default: Unit<IB_Q8_0>::init(u, lc); break;
+    }
+}
+__device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+    switch (qtype) {
+    case IB_Q4_K: return Unit<IB_Q4_K>::dot(row, lc, ua);
+    case IB_Q6_K: return Unit<IB_Q6_K>::dot(row, lc, ua);
+    case IB_Q5_K: return Unit<IB_Q5_K>::dot(row, lc, ua);
+    default: return Unit<IB_Q8_0>::dot(row, lc, ua);
     }
 }
 
@@ -330,6 +392,91 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
     }
 }
 
+// ---- consumer side ----
+struct Consumer {
+    const uint8_t *ring;
+    float *part;          // [stages][PT_MAX][2][CW] per-warp column partials
+    uint32_t *cnt;        // [stages][CW] arrivals of a row group's warps
+    uint32_t bar0, S, stage_bytes;
+    uint32_t CG, RG, cg, rg, u;
+    bool has_unit;
+    int lane;
+};
+
+// Consumes this warp's share of every tile.  One loop for all formats (the format switch sits at the dot product):
+// separate inlined loops per format made the register allocator spill.
+template <uint32_t EPI>
+__device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &sh, const Consumer &c, const Act &A, unsigned long long &best) {
+    const int lane = c.lane;
+    UnitAct ua;
+    LaneConst lc;
+    uint32_t cur_type = 0xFFFFFFFFu;
+    const uint32_t S = c.S, CG = c.CG, RG = c.RG;
+    TileCursor tc;
+    tc.init(sh);
+#pragma unroll 1
+    for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
+        const uint32_t st = k % S, s = tc.seg, n = tc.count(sh);
+        const uint32_t qtype = p.seg[s].qtype;
+        if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
+            unit_init(qtype, c.u, lc);
+            if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
+            cur_type = qtype;
+        }
+        if (!mbar_wait(c.bar0 + 8 * st, (k / S) & 1, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
+        const uint8_t *tile = c.ring + (size_t)st * c.stage_bytes;
+        const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
+        const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
+        const uint32_t strideA = (EPI == EPI_SWIGLU) ? rbA : 2 * rbA, offB = (EPI == EPI_SWIGLU) ? n * rbA : rbA;
+        float *pt = c.part + (size_t)st * PT_MAX * 2 * CW;
+        for (uint32_t pr = c.rg; pr < n; pr += RG) {
+            const uint8_t *rowA = tile + pr * strideA;
+            const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + offB + pr * rbB : rowA + rbA;
+            float va = 0.f, vb = 0.f;
+            if (c.has_unit) {
+                va = unit_dot(qtype, rowA, lc, ua);
+                vb = unit_dot(qtype, rowB, lc, ua);
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                va += __shfl_xor_sync(0xffffffffu, va, o);
+                vb += __shfl_xor_sync(0xffffffffu, vb, o);
+            }
+            if (CG == 1) {
+                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
+            } else if (lane == 0) {
+                pt[(pr * 2 + 0) * CW + c.cg] = va;
+                pt[(pr * 2 + 1) * CW + c.cg] = vb;
+            }
+        }
+        if (CG > 1) {
+            // the last warp of the row group to finish the tile folds the column partials in a fixed order
+            uint32_t last = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                last = (atomicAdd(c.cnt + st * CW + c.rg, 1u) == CG - 1) ? 1u : 0u;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_block();
+                const uint32_t pr = c.rg + RG * lane;
+                if (pr < n) {
+                    float va = 0.f, vb = 0.f;
+                    for (uint32_t g = 0; g < CG; g++) {
+                        va += pt[(pr * 2 + 0) * CW + g];
+                        vb += pt[(pr * 2 + 1) * CW + g];
+                    }
+                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
+                }
+                __syncwarp();
+                if (lane == 0) c.cnt[st * CW + c.rg] = 0;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.bar0 + 8 * (S + st));   // this warp is done with the stage
+    }
+}
+
 // ---- the kernel ----
 template <uint32_t EPI>
 __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const GemvParams p, const StreamGeom geo) {
@@ -338,6 +485,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
     __shared__ unsigned long long best_sm[CW];
     __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    TRACE(0);
 
     uint8_t *ring = smem;
     uint8_t *act_sm = smem + geo.act_off;
@@ -352,7 +500,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
     const uint32_t active = CG * RG;             // consumer warps with work
 
     Share sh;
-    make_share<EPI>(p, geo.stage_bytes, sh);
+    make_share<EPI>(p, geo.stage_bytes, RG, sh);
+
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; s++) {
@@ -363,6 +512,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    TRACE(1);
     if (p.pdl) asm volatile("griddepcontrol.launch_dependents;");
 
     if (warp == CW) {
@@ -382,10 +532,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
                     bulk_g2s(dst, p.seg[0].w + (size_t)tc.next * p.seg[0].row_bytes, ba, full);
                     bulk_g2s(dst + ba, p.seg[1].w + (size_t)tc.next * p.seg[1].row_bytes, bb, full);
                 } else {
-                    const uint32_t bytes = n * sh.cost[s];
+                    const uint32_t bytes = n * sh.cost(s);
                     mbar_expect_tx(full, bytes);
-                    bulk_g2s(dst, p.seg[s].w + (size_t)tc.next * sh.cost[s], bytes, full);
+                    bulk_g2s(dst, p.seg[s].w + (size_t)tc.next * sh.cost(s), bytes, full);
                 }
+                TRACE(2 + (k < 6 ? k : 6));
             }
         }
         return;
@@ -393,78 +544,19 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
 
     // ================= consumer warps =================
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    TRACE(2);
     pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red);
     const Act A{act_sm, p.cols};
+    TRACE(3);
 
-    const uint32_t cg = warp % CG, rg = warp / CG;
-    const uint32_t u = cg * 32 + lane;
-    const bool has_unit = (uint32_t)warp < active && u < units;
     unsigned long long best = 0ull;
-
     if ((uint32_t)warp < active) {
-        UnitAct ua;
-        uint32_t ua_type = 0xFFFFFFFFu;
-        TileCursor tc;
-        tc.init(sh);
-        for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
-            const uint32_t st = k % S, s = tc.seg, n = tc.count(sh);
-            const uint32_t qtype = p.seg[s].qtype;
-            if (qtype != ua_type) {   // (re)load this lane's activations in the layout of the segment's format
-                if (has_unit) load_unit_act(qtype, u, A, ua);
-                ua_type = qtype;
-            }
-            if (!mbar_wait(bar0 + 8 * st, (k / S) & 1, p.err, 1)) break;   // the error word is raised; give up on this CTA's rows
-            const uint8_t *tile = ring + (size_t)st * geo.stage_bytes;
-            const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
-            const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
-            float *pt = part + (size_t)st * PT_MAX * 2 * CW;
-            for (uint32_t pr = rg; pr < n; pr += RG) {
-                const uint8_t *rowA = (EPI == EPI_SWIGLU) ? tile + (size_t)pr * rbA : tile + (size_t)(2 * pr) * rbA;
-                const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + (size_t)n * rbA + (size_t)pr * rbB : rowA + rbA;
-                float va = 0.f, vb = 0.f;
-                if (has_unit) {
-                    va = unit_dot(qtype, rowA, u, ua);
-                    vb = unit_dot(qtype, rowB, u, ua);
-                }
-#pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    va += __shfl_xor_sync(0xffffffffu, va, o);
-                    vb += __shfl_xor_sync(0xffffffffu, vb, o);
-                }
-                if (CG == 1) {
-                    if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
-                } else if (lane == 0) {
-                    pt[(pr * 2 + 0) * CW + cg] = va;
-                    pt[(pr * 2 + 1) * CW + cg] = vb;
-                }
-            }
-            if (CG > 1) {
-                // the last warp of the row group to finish the tile folds the column partials in a fixed order
-                uint32_t last = 0;
-                if (lane == 0) {
-                    __threadfence_block();
-                    last = (atomicAdd(cnt + st * CW + rg, 1u) == CG - 1) ? 1u : 0u;
-                }
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence_block();
-                    const uint32_t pr = rg + RG * lane;
-                    if (pr < n) {
-                        float va = 0.f, vb = 0.f;
-                        for (uint32_t c = 0; c < CG; c++) {
-                            va += pt[(pr * 2 + 0) * CW + c];
-                            vb += pt[(pr * 2 + 1) * CW + c];
-                        }
-                        epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
-                    }
-                    __syncwarp();
-                    if (lane == 0) cnt[st * CW + rg] = 0;
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar0 + 8 * (S + st));   // this warp is done with the stage
-        }
+        Consumer c;
+        c.ring = ring; c.part = part; c.cnt = cnt; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
+        c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
+        consume_tiles<EPI>(p, sh, c, A, best);
     }
+    TRACE(15);
 
     if (EPI == EPI_ARGMAX) {
 #pragma unroll
@@ -547,38 +639,44 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
             pairs += p.seg[s].rows / 2;
         }
     }
-    // stage: as many pairs as fit in ~20 KB (at least one), the same byte budget for every segment
-    uint32_t stage = 0;
-    if (p.epi == EPI_SWIGLU) {
-        uint32_t pt = 20480 / max_cost;
-        pt = pt < 1 ? 1 : (pt > PT_MAX ? PT_MAX : pt);
-        stage = pt * max_cost;
-    } else {
-        for (uint32_t s = 0; s < p.nseg; s++) {
-            const uint32_t c = (uint32_t)(2 * p.seg[s].row_bytes);
-            uint32_t pt = 20480 / c;
-            pt = pt < 1 ? 1 : (pt > PT_MAX ? PT_MAX : pt);
-            if (pt * c > stage) stage = pt * c;
-        }
-    }
-    stage = (stage + 127) & ~127u;
+    // tile = whole "rounds" of the row groups (RG pairs each): two rounds when they fit in ~37 KB, so that the
+    // per-tile hand-offs are paid once per two pairs of a warp; at least two stages must fit beside the activations
+    const uint32_t units = p.cols / 64, CG = (units + 31) / 32, RG = CW / CG;
     const size_t act = (act_smem_bytes(p.cols) + 127) & ~(size_t)127;
-    StreamGeom geo;
-    uint32_t S = 4;
+    auto layout = [&](uint32_t max_tile_bytes, uint32_t &stage, uint32_t &S, size_t &total) {
+        auto pairs_per_tile = [&](uint32_t cost) {
+            uint32_t pt = RG;
+            while (pt * 2 <= PT_MAX && pt * 2 * cost <= max_tile_bytes) pt *= 2;
+            while (pt > 1 && pt * cost > max_tile_bytes) pt--;
+            return pt;
+        };
+        stage = 0;
+        if (p.epi == EPI_SWIGLU) stage = pairs_per_tile(max_cost) * max_cost;
+        else
+            for (uint32_t s = 0; s < p.nseg; s++) {
+                const uint32_t c = (uint32_t)(2 * p.seg[s].row_bytes);
+                const uint32_t b = pairs_per_tile(c) * c;
+                if (b > stage) stage = b;
+            }
+        stage = (stage + 127) & ~127u;
+        for (S = 4;; S--) {
+            const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4;
+            total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8;
+            if (total <= STREAM_SMEM_BUDGET || S == 2) break;
+        }
+        return total <= STREAM_SMEM_BUDGET;
+    };
+    uint32_t stage = 0, S = 0;
     size_t total = 0;
-    for (;; S--) {
-        const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4;
-        total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8;
-        if (total <= STREAM_SMEM_BUDGET || S == 2) break;
-    }
-    if (total > STREAM_SMEM_BUDGET)
+    if (!layout(37888, stage, S, total) && !layout(28672, stage, S, total) && !layout(16384, stage, S, total) && !layout(max_cost, stage, S, total))
         return set_error(IB_ERR_UNSUPPORTED, "gemv: a row pair of %u bytes with %u columns does not fit the streaming kernel's ring", max_cost, p.cols);
+    StreamGeom geo;
     geo.stages = S;
     geo.stage_bytes = stage;
     geo.act_off = S * stage;
     geo.part_off = (uint32_t)(geo.act_off + act);
     geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4 + 127) & ~(size_t)127));
-    int grid = ctx->sm_count;
+    int grid = ctx->sm_count * 2;   // two CTAs per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
     if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
     switch (p.epi) {
@@ -590,5 +688,11 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     default: return set_error(IB_ERR_INVALID, "gemv: unknown epilogue %u", p.epi);
     }
 }
+
+#ifdef IB_STREAM_TRACE
+extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(unsigned long long *out64) {
+    return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 }  // namespace ib
