@@ -262,7 +262,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_wide_kernel(const GemvPa
         asm volatile("griddepcontrol.launch_dependents;");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
-    pack_activation(smem, p.cols, p.x, p.norm_w, p.eps, red);
+    float4 norm_g[4];
+    pack_prefetch_norm(p.norm_w, p.cols, norm_g);
+    pack_activation<GEMV_THREADS>(smem, p.cols, p.x, p.norm_w, p.eps, red, norm_g);
     const Act A{smem, p.cols};
 
     uint32_t pairs[3], total = 0;

@@ -6,7 +6,7 @@
 
 namespace ib {
 
-constexpr int PACK_THREADS = 256;        // threads that take part in the activation prologue
+constexpr int PACK_THREADS = 512;        // threads that take part in the activation prologue of the streaming kernel
 constexpr uint32_t GEMV_MAX_COLS = 32768;
 
 // Activation form in shared memory, for `cols` columns (a multiple of 32):
@@ -53,116 +53,140 @@ __device__ __forceinline__ void kquant_scales(const uint4 &hdr, uint32_t c, uint
 // -------------------------------------------------------------------------------------------------
 // prologue: (optional RMSNorm) + conversion of x into the limb form in shared memory.
 // Called by the first PACK_THREADS threads of the CTA; synchronises them on named barrier 1.
-// Each thread owns float4 number tid + 256 i, so a 32-column group is 8 consecutive lanes.
+// A thread owns runs of 16 consecutive columns (run number tid + 256 i): the 16-column sum needs no shuffle, the
+// 32-column maximum one shuffle with the neighbour lane, and the 16 conversions are independent of each other.
 // -------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void pack_float4(float4 v, uint32_t idx, uint32_t cols, uint8_t *smem, bool store) {
-    const int lane = threadIdx.x & 31;
-    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-    float sum = (v.x + v.y) + (v.z + v.w);
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    const float inv = amax > 0.f ? 127.0f / amax : 0.f;
-    const float e[4] = {v.x, v.y, v.z, v.w};
-    // round-to-nearest-even by adding 1.5 * 2^23: the sum's low mantissa byte is the rounded value in two's complement
-    // (|t| <= 127), and subtracting the constant again gives it back as a float - no conversion instructions
-    constexpr float MAGIC = 12582912.0f;
-    uint32_t b0[4], b1[4], b2[4];
+constexpr int PACK_RUNS = 2;   // runs of 16 columns kept in registers per thread (covers 16384 columns with 512 threads)
+
+struct PackRegs {
+    float4 x[PACK_RUNS][4];
+};
+
+// Issues the loads of this thread's norm weights.  They are weights, so a kernel may call this before it waits for
+// its predecessor.
+__device__ __forceinline__ void pack_prefetch_norm(const float *__restrict__ norm_w, uint32_t cols, float4 (&g)[4]) {
+    const uint32_t run = threadIdx.x;   // only the first run's weights are kept (cols <= 4096); wider rows re-fetch
+    if (norm_w && run < cols / 16) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(norm_w) + 4 * run;
 #pragma unroll
-    for (int k = 0; k < 4; k++) {
-        const float t = e[k] * inv;
-        const float r0 = t + MAGIC;
-        const float t1 = (t - (r0 - MAGIC)) * 254.0f;
-        const float r1 = t1 + MAGIC;
-        const float r2 = (t1 - (r1 - MAGIC)) * 254.0f + MAGIC;
-        b0[k] = __float_as_uint(r0); b1[k] = __float_as_uint(r1); b2[k] = __float_as_uint(r2);
-    }
-    // low bytes of four words -> one word
-    const uint32_t w0 = __byte_perm(__byte_perm(b0[0], b0[1], 0x0040), __byte_perm(b0[2], b0[3], 0x0040), 0x5410);
-    const uint32_t w1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
-    const uint32_t w2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
-    if (store) {
-        uint32_t *l0 = reinterpret_cast<uint32_t *>(smem), *l1 = l0 + cols / 4, *l2 = l1 + cols / 4;
-        float *sc = reinterpret_cast<float *>(smem + (size_t)3 * cols), *sx16 = sc + cols / 32;
-        l0[idx] = w0; l1[idx] = w1; l2[idx] = w2;
-        if ((lane & 7) == 0) sc[idx >> 3] = amax * (1.0f / 127.0f);
-        if ((lane & 3) == 0) sx16[idx >> 2] = sum;
+        for (int j = 0; j < 4; j++) g[j] = __ldg(w4 + j);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) g[j] = make_float4(1.f, 1.f, 1.f, 1.f);
     }
 }
 
+__device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uint32_t cols, uint8_t *smem, bool store) {
+    const int lane = threadIdx.x & 31;
+    float amax = 0.f, sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+        sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));   // the other half of the 32-column group
+    const float inv = amax > 0.f ? __fdividef(127.0f, amax) : 0.f;   // 2 ulp: the limbs absorb it (|t| stays within 127 + 1e-5)
+    // round-to-nearest-even by adding 1.5 * 2^23: the sum's low mantissa byte is the rounded value in two's complement
+    // (|t| <= 127), and subtracting the constant again gives it back as a float - no conversion instructions
+    constexpr float MAGIC = 12582912.0f;
+    uint32_t w0[4], w1[4], w2[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        uint32_t b0[4], b1[4], b2[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float t = e[k] * inv;
+            const float r0 = t + MAGIC;
+            const float t1 = (t - (r0 - MAGIC)) * 254.0f;
+            const float r1 = t1 + MAGIC;
+            const float r2 = (t1 - (r1 - MAGIC)) * 254.0f + MAGIC;
+            b0[k] = __float_as_uint(r0); b1[k] = __float_as_uint(r1); b2[k] = __float_as_uint(r2);
+        }
+        // low bytes of four words -> one word
+        w0[j] = __byte_perm(__byte_perm(b0[0], b0[1], 0x0040), __byte_perm(b0[2], b0[3], 0x0040), 0x5410);
+        w1[j] = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
+        w2[j] = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
+    }
+    if (store) {
+        uint4 *l0 = reinterpret_cast<uint4 *>(smem), *l1 = reinterpret_cast<uint4 *>(smem + cols), *l2 = reinterpret_cast<uint4 *>(smem + 2 * (size_t)cols);
+        float *sc = reinterpret_cast<float *>(smem + (size_t)3 * cols), *sx16 = sc + cols / 32;
+        l0[run] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+        l1[run] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+        l2[run] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+        if ((lane & 1) == 0) sc[run >> 1] = amax * (1.0f / 127.0f);
+        sx16[run] = sum;
+    }
+}
+
+// `g` holds the norm weights of the thread's first run (from pack_prefetch_norm).
+template <int NT = PACK_THREADS>
 __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                float *red /* [PACK_THREADS/32 + 1] */) {
-    constexpr int MAXV = 14;  // float4 registers per thread: covers 14336 columns without re-reading x
+                                                float *red /* [NT/32 + 1] */, const float4 (&g)[4]) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t nv = cols / 4;
+    const uint32_t nruns = cols / 16;    // cols is a multiple of 32, so runs pair up inside a warp
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *w4 = reinterpret_cast<const float4 *>(norm_w);
-    const bool in_regs = nv <= (uint32_t)MAXV * PACK_THREADS;
-    constexpr int MAXG = 4;   // norm weights fetched together with x (covers 4096 columns; wider rows fetch them later)
-    float4 xv[MAXV], gv[MAXG];
-    if (in_regs) {
+    PackRegs r;
 #pragma unroll
-        for (int i = 0; i < MAXV; i++) {
-            const uint32_t idx = tid + PACK_THREADS * i;
-            xv[i] = idx < nv ? __ldcg(x4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int i = 0; i < PACK_RUNS; i++) {
+        const uint32_t run = tid + NT * i;
 #pragma unroll
-        for (int i = 0; i < MAXG; i++) {
-            const uint32_t idx = tid + PACK_THREADS * i;
-            gv[i] = (norm_w && idx < nv) ? __ldg(w4 + idx) : make_float4(1.f, 1.f, 1.f, 1.f);
-        }
+        for (int j = 0; j < 4; j++) r.x[i][j] = run < nruns ? __ldcg(x4 + 4 * run + j) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float rms = 1.0f;
     if (norm_w) {
         // crates/inferi-shaders/src/rms_norm.rs:112-120
         float ss = 0.f;
-        if (in_regs) {
 #pragma unroll
-            for (int i = 0; i < MAXV; i++) ss += (xv[i].x * xv[i].x + xv[i].y * xv[i].y) + (xv[i].z * xv[i].z + xv[i].w * xv[i].w);
-        } else {
-            for (uint32_t idx = tid; idx < nv; idx += PACK_THREADS) {
-                const float4 v = __ldcg(x4 + idx);
+        for (int i = 0; i < PACK_RUNS; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) ss += (r.x[i][j].x * r.x[i][j].x + r.x[i][j].y * r.x[i][j].y) + (r.x[i][j].z * r.x[i][j].z + r.x[i][j].w * r.x[i][j].w);
+        for (uint32_t run = tid + NT * PACK_RUNS; run < nruns; run += NT)   // rows wider than the registers hold
+            for (int j = 0; j < 4; j++) {
+                const float4 v = __ldcg(x4 + 4 * run + j);
                 ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
             }
-        }
 #pragma unroll
         for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) red[warp] = ss;
-        named_barrier(1, PACK_THREADS);
+        named_barrier(1, NT);
         float t = 0.f;
 #pragma unroll
-        for (int w = 0; w < PACK_THREADS / 32; w++) t += red[w];
+        for (int w = 0; w < NT / 32; w++) t += red[w];
         rms = 1.0f / sqrtf(t / (float)cols + eps);
     }
-    if (in_regs) {
 #pragma unroll
-        for (int i = 0; i < MAXV; i++) {
-            const uint32_t idx = tid + PACK_THREADS * i;
-            if ((uint32_t)(warp * 32 + PACK_THREADS * i) < nv) {  // warp-uniform: the whole warp shuffles together
-                float4 v = xv[i];
-                const bool ok = idx < nv;
-                if (norm_w && ok) {
-                    const float4 g = i < MAXG ? gv[i < MAXG ? i : 0] : __ldg(w4 + idx);
-                    v.x = (v.x * rms) * g.x; v.y = (v.y * rms) * g.y; v.z = (v.z * rms) * g.z; v.w = (v.w * rms) * g.w;
-                }
-                pack_float4(v, idx, cols, smem, ok);
-            }
-        }
-    } else {
-        for (uint32_t base = warp * 32; base < nv; base += PACK_THREADS) {
-            const uint32_t idx = base + lane;
-            const bool ok = idx < nv;
-            float4 v = ok ? __ldcg(x4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < PACK_RUNS; i++) {
+        const uint32_t run = tid + NT * i;
+        if ((uint32_t)(warp * 32 + NT * i) < nruns) {   // warp-uniform: both lanes of a 32-column group are present
+            const bool ok = run < nruns;
             if (norm_w && ok) {
-                const float4 g = __ldg(w4 + idx);
-                v.x = (v.x * rms) * g.x; v.y = (v.y * rms) * g.y; v.z = (v.z * rms) * g.z; v.w = (v.w * rms) * g.w;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 w = (i == 0) ? g[j] : __ldg(w4 + 4 * run + j);
+                    float4 &v = r.x[i][j];
+                    v.x = (v.x * rms) * w.x; v.y = (v.y * rms) * w.y; v.z = (v.z * rms) * w.z; v.w = (v.w * rms) * w.w;
+                }
             }
-            pack_float4(v, idx, cols, smem, ok);
+            pack_run(r.x[i], run, cols, smem, ok);
         }
     }
-    named_barrier(1, PACK_THREADS);
+    for (uint32_t base = warp * 32 + NT * PACK_RUNS; base < nruns; base += NT) {   // rows wider than the registers hold
+        const uint32_t run = base + lane;
+        const bool ok = run < nruns;
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            v[j] = ok ? __ldcg(x4 + 4 * run + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (norm_w && ok) {
+                const float4 w = __ldg(w4 + 4 * run + j);
+                v[j].x = (v[j].x * rms) * w.x; v[j].y = (v[j].y * rms) * w.y; v[j].z = (v[j].z * rms) * w.z; v[j].w = (v[j].w * rms) * w.w;
+            }
+        }
+        pack_run(v, run, cols, smem, ok);
+    }
+    named_barrier(1, NT);
 }
 
 }  // namespace ib

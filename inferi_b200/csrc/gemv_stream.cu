@@ -8,7 +8,7 @@
 //    (cp.async.bulk, one copy per tile of up to 8 contiguous row pairs, completion on an mbarrier).  It starts
 //    before the kernel waits for its predecessor (programmatic dependent launch): weights never depend on the
 //    previous kernel, so the ring fills while that kernel is still finishing.
-//  * Eight consumer warps split a row's columns: every lane owns one 64-weight unit of the row and keeps that
+//  * Sixteen consumer warps split a row's columns: every lane owns one 64-weight unit of the row and keeps that
 //    unit's activations — three int8 limbs per column, see gemv_common.cuh — in registers for the whole kernel, so
 //    the inner loop touches shared memory only for weights.  Per weight the work is a byte mask and dp4a.
 //  * Per row the lane partials are shuffled down, per-warp partials meet in shared memory, and the last warp of a
@@ -19,21 +19,27 @@
 
 namespace ib {
 
-constexpr int CW = 8;                           // consumer warps
+constexpr int CW = 16;                          // consumer warps
 constexpr int STREAM_THREADS = (CW + 1) * 32;   // + 1 producer warp
-constexpr int PT_MAX = 8;                       // row pairs per tile
+constexpr int PT_MAX = 16;                      // row pairs per tile
 constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;   // a wait on an mbarrier gives up after 4 s
 
 #ifdef IB_STREAM_TRACE
-// Timeline probes for latency studies: globaltimer stamps of a few CTAs, read back with ib_debug_stream_trace().
-__device__ unsigned long long g_trace[64 * 16];
-#define TRACE(slot)                                                                    \
-    do {                                                                               \
-        if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {               \
-            unsigned long long _t;                                                     \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                     \
-            g_trace[(warp == CW ? 32 : 0) + (slot)] = _t;                              \
-        }                                                                              \
+// Timeline probes for latency studies: globaltimer stamps of CTA 0 (and of the last CTA's end), one row of 16 slots
+// per epilogue kind, read back with ib_debug_stream_trace().  Never compiled into the shipped library.
+__device__ unsigned long long g_trace[16 * 16];
+#define TRACE(slot)                                                                                   \
+    do {                                                                                              \
+        if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {                              \
+            unsigned long long _t;                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
+            g_trace[(warp == CW ? 128 : 0) + EPI * 16 + (slot)] = _t;                                 \
+        }                                                                                             \
+        if (lane == 0 && blockIdx.x == gridDim.x - 1 && warp == 0 && (slot) == 15) {                  \
+            unsigned long long _t;                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
+            g_trace[EPI * 16 + 14] = _t;                                                              \
+        }                                                                                             \
     } while (0)
 #else
 #define TRACE(slot) do { } while (0)
@@ -52,9 +58,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarri
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(2000u)   // suspend-time hint in ns: a waiting warp sleeps instead of spinning through issue slots
         : "memory");
     return ok != 0;
 }
@@ -224,8 +230,9 @@ template <> struct Unit<IB_Q4_K> {
         uint32_t sc2, m2;
         kquant_scales(hdr, c, sc2, m2);
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-        const float lo = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
-        const float hi = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
+        // groups 0,1 (and 2,3) share the activation scale and the sub-block scale: add them as integers
+        const float lo = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
+        const float hi = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
         return (dm.x * (float)(sc2 & 0xFFu)) * lo - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi -
                (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
     }
@@ -258,8 +265,8 @@ template <> struct Unit<IB_Q5_K> {
         uint32_t sc2, m2;
         kquant_scales(hdr, c, sc2, m2);
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-        const float lo_f = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
-        const float hi_f = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
+        const float lo_f = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
+        const float hi_f = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
         return (dm.x * (float)(sc2 & 0xFFu)) * lo_f - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi_f -
                (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
     }
@@ -332,14 +339,18 @@ template <> struct Unit<IB_Q8_0> {
             D[2][k] = dot4_ss(q2, ua.l[k][2], 0);
             D[3][k] = dot4_ss(q3, ua.l[k][3], 0);
         }
-        const float a = ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) + ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]);
-        const float c = ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) + ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]);
+        const float a = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
+        const float c = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
         return dd.x * a + dd.y * c;
     }
 };
 
+constexpr uint32_t QT_MIXED = 0xFFu;   // kernel instance for launches whose segments differ in format
+
+template <uint32_t QT>
 __device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst &lc) {
     lc.o0 = lc.o1 = lc.o2 = lc.o3 = lc.k = 0;
+    if (QT != QT_MIXED) { Unit<QT == QT_MIXED ? IB_Q4_K : QT>::init(u, lc); return; }
     switch (qtype) {
     case IB_Q4_K: Unit<IB_Q4_K>::init(u, lc); break;
     case IB_Q6_K: Unit<IB_Q6_K>::init(u, lc); break;
@@ -347,7 +358,9 @@ __device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst 
     default: Unit<IB_Q8_0>::init(u, lc); break;
     }
 }
+template <uint32_t QT>
 __device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+    if (QT != QT_MIXED) return Unit<QT == QT_MIXED ? IB_Q4_K : QT>::dot(row, lc, ua);
     switch (qtype) {
     case IB_Q4_K: return Unit<IB_Q4_K>::dot(row, lc, ua);
     case IB_Q6_K: return Unit<IB_Q6_K>::dot(row, lc, ua);
@@ -405,7 +418,7 @@ struct Consumer {
 
 // Consumes this warp's share of every tile.  One loop for all formats (the format switch sits at the dot product):
 // separate inlined loops per format made the register allocator spill.
-template <uint32_t EPI>
+template <uint32_t EPI, uint32_t QT>
 __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &sh, const Consumer &c, const Act &A, unsigned long long &best) {
     const int lane = c.lane;
     UnitAct ua;
@@ -417,9 +430,9 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
 #pragma unroll 1
     for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
         const uint32_t st = k % S, s = tc.seg, n = tc.count(sh);
-        const uint32_t qtype = p.seg[s].qtype;
+        const uint32_t qtype = (QT != QT_MIXED) ? QT : p.seg[s].qtype;
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
-            unit_init(qtype, c.u, lc);
+            unit_init<QT>(qtype, c.u, lc);
             if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
             cur_type = qtype;
         }
@@ -434,8 +447,8 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
             const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + offB + pr * rbB : rowA + rbA;
             float va = 0.f, vb = 0.f;
             if (c.has_unit) {
-                va = unit_dot(qtype, rowA, lc, ua);
-                vb = unit_dot(qtype, rowB, lc, ua);
+                va = unit_dot<QT>(qtype, rowA, lc, ua);
+                vb = unit_dot<QT>(qtype, rowB, lc, ua);
             }
 #pragma unroll
             for (int o = 16; o; o >>= 1) {
@@ -478,8 +491,8 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
 }
 
 // ---- the kernel ----
-template <uint32_t EPI>
-__global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const GemvParams p, const StreamGeom geo) {
+template <uint32_t EPI, uint32_t QT>
+__global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const GemvParams p, const StreamGeom geo) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[PACK_THREADS / 32 + 1];
     __shared__ unsigned long long best_sm[CW];
@@ -543,9 +556,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
     }
 
     // ================= consumer warps =================
+    float4 norm_g[4];
+    pack_prefetch_norm(p.norm_w, p.cols, norm_g);   // weights: fetched while the previous kernel is still running
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(2);
-    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red);
+    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g);
     const Act A{act_sm, p.cols};
     TRACE(3);
 
@@ -554,7 +569,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
         Consumer c;
         c.ring = ring; c.part = part; c.cnt = cnt; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
         c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
-        consume_tiles<EPI>(p, sh, c, A, best);
+        consume_tiles<EPI, QT>(p, sh, c, A, best);
     }
     TRACE(15);
 
@@ -593,7 +608,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) gemv_stream_kernel(const Ge
 // -------------------------------------------------------------------------------------------------
 // host side
 // -------------------------------------------------------------------------------------------------
-constexpr size_t STREAM_SMEM_BUDGET = 108 * 1024;   // two CTAs (this kernel and the next one, prefetching) share an SM
+constexpr size_t STREAM_SMEM_BUDGET = 200 * 1024;   // one CTA per SM
 
 bool gemv_stream_eligible(const GemvParams &p) {
     if (p.cols % 64 || p.cols > 16384) return false;
@@ -605,11 +620,11 @@ bool gemv_stream_eligible(const GemvParams &p) {
     return true;
 }
 
-template <uint32_t EPI>
-static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
+template <uint32_t EPI, uint32_t QT>
+static int32_t launch_stream_inst(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
-        IB_CHECK_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM_BUDGET));
+        IB_CHECK_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<EPI, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM_BUDGET));
         attr_set[ctx->device & 15] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -622,9 +637,23 @@ static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvPar
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl ? 1 : 0;
-    IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<EPI>, p, geo));
+    IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<EPI, QT>, p, geo));
     ctx->launches++;
     return IB_OK;
+}
+
+template <uint32_t EPI>
+static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
+    uint32_t qt = p.seg[0].qtype;
+    for (uint32_t s = 1; s < p.nseg; s++)
+        if (p.seg[s].qtype != qt) qt = QT_MIXED;
+    switch (qt) {
+    case IB_Q4_K: return launch_stream_inst<EPI, IB_Q4_K>(ctx, stream, p, grid, geo, smem);
+    case IB_Q6_K: return launch_stream_inst<EPI, IB_Q6_K>(ctx, stream, p, grid, geo, smem);
+    case IB_Q5_K: return launch_stream_inst<EPI, IB_Q5_K>(ctx, stream, p, grid, geo, smem);
+    case IB_Q8_0: return launch_stream_inst<EPI, IB_Q8_0>(ctx, stream, p, grid, geo, smem);
+    default: return launch_stream_inst<EPI, QT_MIXED>(ctx, stream, p, grid, geo, smem);
+    }
 }
 
 int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p) {
@@ -668,7 +697,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     };
     uint32_t stage = 0, S = 0;
     size_t total = 0;
-    if (!layout(37888, stage, S, total) && !layout(28672, stage, S, total) && !layout(16384, stage, S, total) && !layout(max_cost, stage, S, total))
+    if (!layout(75776, stage, S, total) && !layout(49152, stage, S, total) && !layout(32768, stage, S, total) && !layout(max_cost, stage, S, total))
         return set_error(IB_ERR_UNSUPPORTED, "gemv: a row pair of %u bytes with %u columns does not fit the streaming kernel's ring", max_cost, p.cols);
     StreamGeom geo;
     geo.stages = S;
@@ -676,7 +705,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     geo.act_off = S * stage;
     geo.part_off = (uint32_t)(geo.act_off + act);
     geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4 + 127) & ~(size_t)127));
-    int grid = ctx->sm_count * 2;   // two CTAs per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
+    int grid = ctx->sm_count;       // one persistent CTA per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
     if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
     switch (p.epi) {
@@ -691,7 +720,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
 
 #ifdef IB_STREAM_TRACE
 extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(unsigned long long *out64) {
-    return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : 2;
+    return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 2;
 }
 #endif
 

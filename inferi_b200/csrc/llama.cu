@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 #include <new>
 #include <vector>
 
@@ -379,7 +380,9 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     CU(cudaDeviceSynchronize());
     const uint64_t before = ctx->launches;
     CU(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
-    rc = record_token(m, m->own_stream, 1);
+    // INFERI_B200_NO_PDL=1 records the graph with plain kernel-to-kernel dependencies (for comparisons)
+    const char *no_pdl = getenv("INFERI_B200_NO_PDL");
+    rc = record_token(m, m->own_stream, (no_pdl && no_pdl[0] == '1') ? 0 : 1);
     cudaGraph_t graph = nullptr;
     cudaError_t ce = cudaStreamEndCapture(m->own_stream, &graph);
     m->launches_per_token = ctx->launches - before;
