@@ -303,7 +303,7 @@ def main():
         torch.cuda.synchronize()
         us = start.elapsed_time(end) * 1e3 / (reps * len(mats))
         b = mats[0].nbytes + 4 * (mats[0].rows + mats[0].cols)
-        kernels.append({"kernel": f"gemv_kernel {name}", "us_per_launch": round(us, 2), "algorithmic_bytes": b, "gbs": round(b / us / 1e3, 1),
+        kernels.append({"kernel": f"gemv_stream_kernel {name}", "us_per_launch": round(us, 2), "algorithmic_bytes": b, "gbs": round(b / us / 1e3, 1),
                         "frac": round(b / us / 1e3 / peak, 3)})
 
     line = {

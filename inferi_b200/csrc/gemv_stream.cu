@@ -28,12 +28,18 @@ constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;   // a wait on an mb
 // Timeline probes for latency studies: globaltimer stamps of CTA 0 (and of the last CTA's end), one row of 16 slots
 // per epilogue kind, read back with ib_debug_stream_trace().  Never compiled into the shipped library.
 __device__ unsigned long long g_trace[16 * 16];
+__device__ unsigned long long g_cta_end[5 * 160], g_cta_start[5 * 160];
 #define TRACE(slot)                                                                                   \
     do {                                                                                              \
         if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {                              \
             unsigned long long _t;                                                                    \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
             g_trace[(warp == CW ? 128 : 0) + EPI * 16 + (slot)] = _t;                                 \
+        }                                                                                             \
+        if (lane == 0 && warp == 0 && ((slot) == 15 || (slot) == 3) && blockIdx.x < 160) {            \
+            unsigned long long _t;                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
+            if ((slot) == 15) g_cta_end[EPI * 160 + blockIdx.x] = _t; else g_cta_start[EPI * 160 + blockIdx.x] = _t; \
         }                                                                                             \
         if (lane == 0 && blockIdx.x == gridDim.x - 1 && warp == 0 && (slot) == 15) {                  \
             unsigned long long _t;                                                                    \
@@ -719,6 +725,10 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
 }
 
 #ifdef IB_STREAM_TRACE
+extern "C" __attribute__((visibility("default"))) int32_t ib_debug_cta_times(unsigned long long *ends, unsigned long long *starts) {
+    if (cudaMemcpyFromSymbol(ends, g_cta_end, sizeof(unsigned long long) * 800) != cudaSuccess) return 2;
+    return cudaMemcpyFromSymbol(starts, g_cta_start, sizeof(unsigned long long) * 800) == cudaSuccess ? 0 : 2;
+}
 extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(unsigned long long *out64) {
     return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 2;
 }
