@@ -75,7 +75,6 @@ int32_t ib_ctx_create(int32_t device, ib_ctx **out) {
         *ctx->err_host = 0;
         he = cudaHostGetDevicePointer((void **)&ctx->err_dev, ctx->err_host, 0);
     }
-    if (he == cudaSuccess) he = cudaMalloc((void **)&ctx->tile_ctr, sizeof(uint32_t));
     if (he != cudaSuccess) {
         if (ctx->err_host) cudaFreeHost(ctx->err_host);
         delete ctx;
@@ -93,7 +92,6 @@ int32_t ib_ctx_destroy(ib_ctx *ctx) {
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
     if (ctx->argmax_counter) cudaFree(ctx->argmax_counter);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
-    if (ctx->tile_ctr) cudaFree(ctx->tile_ctr);
     delete ctx;
     return IB_OK;
 }

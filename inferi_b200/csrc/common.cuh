@@ -77,7 +77,6 @@ struct ib_ctx {
     // after any synchronisation without a copy
     uint32_t *err_host = nullptr;
     uint32_t *err_dev = nullptr;
-    uint32_t *tile_ctr = nullptr;   // tile hand-out counter of stand-alone streaming GEMV launches
 };
 
 struct ib_qtensor {
@@ -130,10 +129,6 @@ struct GemvParams {
     uint32_t row_offset;               // added to the row index (tensor-parallel vocabulary shard)
     uint32_t pdl;                      // 1: launched with programmatic dependent launch
     uint32_t *err;                     // device view of the context's error word (set by launch_gemv)
-    // tile hand-out of the streaming kernel: a counter that only ever grows, and (inside a token graph) the number of
-    // graph launches so far; null counter = stand-alone launch, the context's counter is zeroed in stream order
-    uint32_t *tile_ctr;
-    const uint32_t *epoch_ptr;
 };
 
 int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p);

@@ -28,18 +28,12 @@ constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;   // a wait on an mb
 // Timeline probes for latency studies: globaltimer stamps of CTA 0 (and of the last CTA's end), one row of 16 slots
 // per epilogue kind, read back with ib_debug_stream_trace().  Never compiled into the shipped library.
 __device__ unsigned long long g_trace[16 * 16];
-__device__ unsigned long long g_cta_end[5 * 160], g_cta_start[5 * 160];
 #define TRACE(slot)                                                                                   \
     do {                                                                                              \
         if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {                              \
             unsigned long long _t;                                                                    \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
             g_trace[(warp == CW ? 128 : 0) + EPI * 16 + (slot)] = _t;                                 \
-        }                                                                                             \
-        if (lane == 0 && warp == 0 && ((slot) == 15 || (slot) == 3) && blockIdx.x < 160) {            \
-            unsigned long long _t;                                                                    \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
-            if ((slot) == 15) g_cta_end[EPI * 160 + blockIdx.x] = _t; else g_cta_start[EPI * 160 + blockIdx.x] = _t; \
         }                                                                                             \
         if (lane == 0 && blockIdx.x == gridDim.x - 1 && warp == 0 && (slot) == 15) {                  \
             unsigned long long _t;                                                                    \
@@ -53,10 +47,6 @@ __device__ unsigned long long g_cta_end[5 * 160], g_cta_start[5 * 160];
 
 struct StreamGeom {
     uint32_t stages, stage_bytes, act_off, part_off, bar_off;
-    uint32_t pt0, pt1, pt2;              // pairs per tile, per segment
-    uint32_t pairs0, pairs1, pairs2;     // row pairs per segment
-    uint32_t tiles_end0, tiles_end1;     // cumulative tile counts
-    uint32_t tiles;                      // T
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,25 +89,74 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  : "memory");
 }
 
-// ---- work distribution: tiles of whole row pairs, handed out through a global counter ----
-// The rows of a launch are cut into T tiles (per segment: pt pairs each, the last one shorter).  Every CTA's producer
-// takes the next tile number with one atomicAdd, so a CTA that starts late or runs on a slower SM simply takes fewer.
-// The counter is never reset: launch number e of a graph node uses the numbers [e (T + G), e (T + G) + T), because each
-// of the G CTAs overshoots exactly once.
-struct Tile {
-    uint32_t seg, first, n;   // segment, first pair, number of pairs
+// ---- this CTA's share of the work: per segment a contiguous range of row pairs, balanced by bytes ----
+// (three scalar sets instead of arrays: indexing them with a run-time segment number would put them in local memory)
+struct Share {
+    uint32_t a0, a1, a2, b0, b1, b2;   // pair range per segment
+    uint32_t c0, c1, c2;               // bytes per pair
+    uint32_t t0, t1, t2;               // pairs per tile
+    uint32_t nseg;
+    __device__ __forceinline__ uint32_t a(uint32_t s) const { return s == 0 ? a0 : (s == 1 ? a1 : a2); }
+    __device__ __forceinline__ uint32_t b(uint32_t s) const { return s == 0 ? b0 : (s == 1 ? b1 : b2); }
+    __device__ __forceinline__ uint32_t cost(uint32_t s) const { return s == 0 ? c0 : (s == 1 ? c1 : c2); }
+    __device__ __forceinline__ uint32_t pt(uint32_t s) const { return s == 0 ? t0 : (s == 1 ? t1 : t2); }
 };
-__device__ __forceinline__ Tile decode_tile(const StreamGeom &g, uint32_t id) {
-    Tile t;
-    t.seg = id < g.tiles_end0 ? 0u : (id < g.tiles_end1 ? 1u : 2u);
-    const uint32_t local = id - (t.seg == 0 ? 0u : (t.seg == 1 ? g.tiles_end0 : g.tiles_end1));
-    const uint32_t pt = t.seg == 0 ? g.pt0 : (t.seg == 1 ? g.pt1 : g.pt2);
-    const uint32_t pairs = t.seg == 0 ? g.pairs0 : (t.seg == 1 ? g.pairs1 : g.pairs2);
-    t.first = local * pt;
-    t.n = pairs - t.first < pt ? pairs - t.first : pt;
-    return t;
+
+// all byte counts in units of 16 bytes so that the arithmetic stays in 32 bits (64-bit divisions cost ~0.2 us each)
+__device__ __forceinline__ void share_range(uint32_t lo, uint32_t hi, uint32_t start, uint32_t cost16, uint32_t pairs, uint32_t &a, uint32_t &b) {
+    const uint32_t x = lo > start ? (lo - start + cost16 - 1) / cost16 : 0;
+    const uint32_t y = hi > start ? (hi - start + cost16 - 1) / cost16 : 0;
+    a = x > pairs ? pairs : x;
+    b = y > pairs ? pairs : y;
 }
-constexpr uint32_t NO_TILE = 0xFFFFFFFFu;
+
+__device__ __forceinline__ uint32_t tile_pairs(uint32_t stage_bytes, uint32_t cost, uint32_t RG) {
+    uint32_t pt = stage_bytes / cost;
+    pt = pt < 1 ? 1 : (pt > PT_MAX ? PT_MAX : pt);
+    if (pt > RG) pt = pt / RG * RG;   // whole rounds of the row groups
+    return pt;
+}
+
+template <uint32_t EPI>
+__device__ __forceinline__ void make_share(const GemvParams &p, uint32_t stage_bytes, uint32_t RG, Share &sh) {
+    uint32_t n0, n1 = 0, n2 = 0;
+    sh.nseg = (EPI == EPI_SWIGLU) ? 1u : p.nseg;
+    sh.c1 = sh.c2 = 16;
+    if (EPI == EPI_SWIGLU) { n0 = p.seg[0].rows; sh.c0 = (uint32_t)(p.seg[0].row_bytes + p.seg[1].row_bytes); }
+    else {
+        n0 = p.seg[0].rows / 2; sh.c0 = (uint32_t)(2 * p.seg[0].row_bytes);
+        if (sh.nseg > 1) { n1 = p.seg[1].rows / 2; sh.c1 = (uint32_t)(2 * p.seg[1].row_bytes); }
+        if (sh.nseg > 2) { n2 = p.seg[2].rows / 2; sh.c2 = (uint32_t)(2 * p.seg[2].row_bytes); }
+    }
+    const uint32_t k0 = sh.c0 / 16, k1 = sh.c1 / 16, k2 = sh.c2 / 16;
+    const uint32_t s1 = n0 * k0, s2 = s1 + n1 * k1, total = s2 + n2 * k2;
+    const uint32_t G = gridDim.x, q = total / G, r = total % G;
+    const uint32_t lo = q * blockIdx.x + r * blockIdx.x / G, hi = q * (blockIdx.x + 1) + r * (blockIdx.x + 1) / G;
+    share_range(lo, hi, 0, k0, n0, sh.a0, sh.b0);
+    share_range(lo, hi, s1, k1, n1, sh.a1, sh.b1);
+    share_range(lo, hi, s2, k2, n2, sh.a2, sh.b2);
+    sh.t0 = tile_pairs(stage_bytes, sh.c0, RG);
+    sh.t1 = tile_pairs(stage_bytes, sh.c1, RG);
+    sh.t2 = tile_pairs(stage_bytes, sh.c2, RG);
+}
+
+struct TileCursor {
+    uint32_t seg, next, end, pt;   // segment, first pair of the next tile, end of the segment's range, pairs per tile
+    __device__ __forceinline__ void enter(const Share &sh) {
+        while (seg < sh.nseg) {
+            next = sh.a(seg); end = sh.b(seg); pt = sh.pt(seg);
+            if (next < end) break;
+            seg++;
+        }
+    }
+    __device__ __forceinline__ void init(const Share &sh) { seg = 0; next = end = pt = 0; enter(sh); }
+    __device__ __forceinline__ bool valid(const Share &sh) const { return seg < sh.nseg; }
+    __device__ __forceinline__ uint32_t count(const Share &) const { return (end - next) < pt ? (end - next) : pt; }
+    __device__ __forceinline__ void advance(const Share &sh) {
+        next += count(sh);
+        if (next >= end) { seg++; enter(sh); }
+    }
+};
 
 // ---- per-lane activation registers of one 64-weight unit ----
 struct UnitAct {
@@ -371,7 +410,6 @@ struct Consumer {
     const uint8_t *ring;
     float *part;          // [stages][PT_MAX][2][CW] per-warp column partials
     uint32_t *cnt;        // [stages][CW] arrivals of a row group's warps
-    const uint32_t *meta; // [stages] tile number held by each stage
     uint32_t bar0, S, stage_bytes;
     uint32_t CG, RG, cg, rg, u;
     bool has_unit;
@@ -381,26 +419,24 @@ struct Consumer {
 // Consumes this warp's share of every tile.  One loop for all formats (the format switch sits at the dot product):
 // separate inlined loops per format made the register allocator spill.
 template <uint32_t EPI, uint32_t QT>
-__device__ __forceinline__ void consume_tiles(const GemvParams &p, const StreamGeom &geo, const Consumer &c, const Act &A, unsigned long long &best) {
+__device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &sh, const Consumer &c, const Act &A, unsigned long long &best) {
     const int lane = c.lane;
     UnitAct ua;
     LaneConst lc;
     uint32_t cur_type = 0xFFFFFFFFu;
     const uint32_t S = c.S, CG = c.CG, RG = c.RG;
+    TileCursor tc;
+    tc.init(sh);
 #pragma unroll 1
-    for (uint32_t k = 0;; k++) {
-        const uint32_t st = k % S;
-        if (!mbar_wait(c.bar0 + 8 * st, (k / S) & 1, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
-        const uint32_t id = *reinterpret_cast<const volatile uint32_t *>(c.meta + st);   // tile number the producer put in this stage
-        if (id == NO_TILE) return;
-        const Tile tl = decode_tile(geo, id);
-        const uint32_t s = tl.seg, n = tl.n;
+    for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
+        const uint32_t st = k % S, s = tc.seg, n = tc.count(sh);
         const uint32_t qtype = (QT != QT_MIXED) ? QT : p.seg[s].qtype;
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
             unit_init<QT>(qtype, c.u, lc);
             if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
             cur_type = qtype;
         }
+        if (!mbar_wait(c.bar0 + 8 * st, (k / S) & 1, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
         const uint8_t *tile = c.ring + (size_t)st * c.stage_bytes;
         const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
         const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
@@ -420,7 +456,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const StreamG
                 vb += __shfl_xor_sync(0xffffffffu, vb, o);
             }
             if (CG == 1) {
-                if (lane == 0) epilogue<EPI>(p, s, tl.first + pr, va, vb, best);
+                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
             } else if (lane == 0) {
                 pt[(pr * 2 + 0) * CW + c.cg] = va;
                 pt[(pr * 2 + 1) * CW + c.cg] = vb;
@@ -443,7 +479,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const StreamG
                         va += pt[(pr * 2 + 0) * CW + g];
                         vb += pt[(pr * 2 + 1) * CW + g];
                     }
-                    epilogue<EPI>(p, s, tl.first + pr, va, vb, best);
+                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
                 }
                 __syncwarp();
                 if (lane == 0) c.cnt[st * CW + c.rg] = 0;
@@ -476,7 +512,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     const uint32_t RG = CW / CG;                 // row groups working side by side
     const uint32_t active = CG * RG;             // consumer warps with work
 
-    uint32_t *meta = cnt + S * CW;               // [stages]
+    Share sh;
+    make_share<EPI>(p, geo.stage_bytes, RG, sh);
+
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; s++) {
@@ -493,32 +531,23 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     if (warp == CW) {
         // ================= producer warp: one lane streams this CTA's tiles =================
         if (lane == 0) {
-            const uint32_t T = geo.tiles;
-            const uint32_t base = p.epoch_ptr ? (*p.epoch_ptr) * (T + gridDim.x) : 0u;   // see "work distribution" above
-            for (uint32_t k = 0;; k++) {
+            TileCursor tc;
+            tc.init(sh);
+            for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
                 const uint32_t st = k % S;
                 if (k >= S && !mbar_wait(bar0 + 8 * (S + st), ((k / S) - 1) & 1, p.err, 2)) break;
-                const uint32_t full = bar0 + 8 * st;
-                const uint32_t id = atomicAdd(p.tile_ctr, 1u) - base;
-                if (id >= T) {                       // nothing left: hand the consumers the end marker and stop
-                    meta[st] = NO_TILE;
-                    mbar_arrive(full);
-                    break;
-                }
-                meta[st] = id;
-                const Tile tl = decode_tile(geo, id);
-                const uint32_t n = tl.n, s = tl.seg;
-                const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes);
+                const uint32_t n = tc.count(sh), s = tc.seg;
+                const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes), full = bar0 + 8 * st;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (EPI == EPI_SWIGLU) {
                     const uint32_t ba = n * (uint32_t)p.seg[0].row_bytes, bb = n * (uint32_t)p.seg[1].row_bytes;
                     mbar_expect_tx(full, ba + bb);
-                    bulk_g2s(dst, p.seg[0].w + (size_t)tl.first * p.seg[0].row_bytes, ba, full);
-                    bulk_g2s(dst + ba, p.seg[1].w + (size_t)tl.first * p.seg[1].row_bytes, bb, full);
+                    bulk_g2s(dst, p.seg[0].w + (size_t)tc.next * p.seg[0].row_bytes, ba, full);
+                    bulk_g2s(dst + ba, p.seg[1].w + (size_t)tc.next * p.seg[1].row_bytes, bb, full);
                 } else {
-                    const uint32_t cost = 2 * (uint32_t)p.seg[s].row_bytes, bytes = n * cost;
+                    const uint32_t bytes = n * sh.cost(s);
                     mbar_expect_tx(full, bytes);
-                    bulk_g2s(dst, p.seg[s].w + (size_t)tl.first * cost, bytes, full);
+                    bulk_g2s(dst, p.seg[s].w + (size_t)tc.next * sh.cost(s), bytes, full);
                 }
                 TRACE(2 + (k < 6 ? k : 6));
             }
@@ -538,9 +567,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     unsigned long long best = 0ull;
     if ((uint32_t)warp < active) {
         Consumer c;
-        c.ring = ring; c.part = part; c.cnt = cnt; c.meta = meta; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
+        c.ring = ring; c.part = part; c.cnt = cnt; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
         c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
-        consume_tiles<EPI, QT>(p, geo, c, A, best);
+        consume_tiles<EPI, QT>(p, sh, c, A, best);
     }
     TRACE(15);
 
@@ -627,75 +656,58 @@ static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvPar
     }
 }
 
-int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p_in) {
-    GemvParams p = p_in;
-    const bool swiglu = p.epi == EPI_SWIGLU;
-    const uint32_t nseg = swiglu ? 1u : p.nseg;
-    uint32_t cost[3] = {16, 16, 16}, npairs[3] = {0, 0, 0};
-    for (uint32_t s = 0; s < nseg; s++) {
-        cost[s] = swiglu ? (uint32_t)(p.seg[0].row_bytes + p.seg[1].row_bytes) : (uint32_t)(2 * p.seg[s].row_bytes);
-        npairs[s] = swiglu ? p.seg[0].rows : p.seg[s].rows / 2;
+int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p) {
+    uint32_t max_cost = 0, pairs = 0;
+    if (p.epi == EPI_SWIGLU) {
+        max_cost = (uint32_t)(p.seg[0].row_bytes + p.seg[1].row_bytes);
+        pairs = p.seg[0].rows;
+    } else {
+        for (uint32_t s = 0; s < p.nseg; s++) {
+            const uint32_t c = (uint32_t)(2 * p.seg[s].row_bytes);
+            if (c > max_cost) max_cost = c;
+            pairs += p.seg[s].rows / 2;
+        }
     }
-    // A tile is a whole number of "rounds" of the row groups (RG pairs each) and at most `limit` bytes.  Larger tiles
-    // amortise the per-tile hand-offs, smaller ones balance better: take the largest limit that still gives every CTA
-    // about four tiles; the ring needs at least two stages beside the activations.
+    // tile = whole "rounds" of the row groups (RG pairs each): two rounds when they fit in ~37 KB, so that the
+    // per-tile hand-offs are paid once per two pairs of a warp; at least two stages must fit beside the activations
     const uint32_t units = p.cols / 64, CG = (units + 31) / 32, RG = CW / CG;
     const size_t act = (act_smem_bytes(p.cols) + 127) & ~(size_t)127;
-    struct Plan { uint32_t pt[3], stage, S, tiles; size_t total; bool fits; };
-    auto plan = [&](uint32_t limit) {
-        Plan pl = {};
-        for (uint32_t s = 0; s < nseg; s++) {
+    auto layout = [&](uint32_t max_tile_bytes, uint32_t &stage, uint32_t &S, size_t &total) {
+        auto pairs_per_tile = [&](uint32_t cost) {
             uint32_t pt = RG;
-            while (pt * 2 <= (uint32_t)PT_MAX && pt * 2 * cost[s] <= limit) pt *= 2;
-            while (pt > 1 && pt * cost[s] > limit) pt--;
-            pl.pt[s] = pt;
-            if (pt * cost[s] > pl.stage) pl.stage = pt * cost[s];
-            pl.tiles += (npairs[s] + pt - 1) / pt;
+            while (pt * 2 <= PT_MAX && pt * 2 * cost <= max_tile_bytes) pt *= 2;
+            while (pt > 1 && pt * cost > max_tile_bytes) pt--;
+            return pt;
+        };
+        stage = 0;
+        if (p.epi == EPI_SWIGLU) stage = pairs_per_tile(max_cost) * max_cost;
+        else
+            for (uint32_t s = 0; s < p.nseg; s++) {
+                const uint32_t c = (uint32_t)(2 * p.seg[s].row_bytes);
+                const uint32_t b = pairs_per_tile(c) * c;
+                if (b > stage) stage = b;
+            }
+        stage = (stage + 127) & ~127u;
+        for (S = 4;; S--) {
+            const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4;
+            total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8;
+            if (total <= STREAM_SMEM_BUDGET || S == 2) break;
         }
-        pl.stage = (pl.stage + 127) & ~127u;
-        for (pl.S = 4;; pl.S--) {
-            const size_t part = (size_t)pl.S * PT_MAX * 2 * CW * 4 + (size_t)pl.S * CW * 4 + (size_t)pl.S * 4;
-            pl.total = (size_t)pl.S * pl.stage + act + ((part + 127) & ~(size_t)127) + 2 * pl.S * 8;
-            if (pl.total <= STREAM_SMEM_BUDGET || pl.S == 2) break;
-        }
-        pl.fits = pl.total <= STREAM_SMEM_BUDGET;
-        return pl;
+        return total <= STREAM_SMEM_BUDGET;
     };
-    const uint32_t limits[] = {75776, 49152, 37888, 28672, 19456, 12288, 0};
-    Plan best = {};
-    bool have = false;
-    for (uint32_t limit : limits) {
-        uint32_t max_cost = 0;
-        for (uint32_t s = 0; s < nseg; s++) max_cost = cost[s] > max_cost ? cost[s] : max_cost;
-        const Plan pl = plan(limit ? limit : max_cost);
-        if (!pl.fits) continue;
-        if (!have || pl.tiles > best.tiles) { best = pl; have = true; }
-        if (pl.tiles >= 4u * (uint32_t)ctx->sm_count) break;
-    }
-    if (!have) return set_error(IB_ERR_UNSUPPORTED, "gemv: a row pair of %u columns does not fit the streaming kernel's ring", p.cols);
-    StreamGeom geo = {};
-    geo.stages = best.S;
-    geo.stage_bytes = best.stage;
-    geo.act_off = best.S * best.stage;
+    uint32_t stage = 0, S = 0;
+    size_t total = 0;
+    if (!layout(75776, stage, S, total) && !layout(49152, stage, S, total) && !layout(32768, stage, S, total) && !layout(max_cost, stage, S, total))
+        return set_error(IB_ERR_UNSUPPORTED, "gemv: a row pair of %u bytes with %u columns does not fit the streaming kernel's ring", max_cost, p.cols);
+    StreamGeom geo;
+    geo.stages = S;
+    geo.stage_bytes = stage;
+    geo.act_off = S * stage;
     geo.part_off = (uint32_t)(geo.act_off + act);
-    const size_t part = (size_t)best.S * PT_MAX * 2 * CW * 4 + (size_t)best.S * CW * 4 + (size_t)best.S * 4;
-    geo.bar_off = (uint32_t)(geo.part_off + ((part + 127) & ~(size_t)127));
-    geo.pt0 = best.pt[0]; geo.pt1 = best.pt[1] ? best.pt[1] : 1; geo.pt2 = best.pt[2] ? best.pt[2] : 1;
-    geo.pairs0 = npairs[0]; geo.pairs1 = npairs[1]; geo.pairs2 = npairs[2];
-    geo.tiles_end0 = (npairs[0] + geo.pt0 - 1) / geo.pt0;
-    geo.tiles_end1 = geo.tiles_end0 + (npairs[1] + geo.pt1 - 1) / geo.pt1;
-    geo.tiles = best.tiles;
+    geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4 + 127) & ~(size_t)127));
     int grid = ctx->sm_count;       // one persistent CTA per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
-    if ((uint32_t)grid > geo.tiles) grid = (int)geo.tiles;
+    if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
-    if (!p.tile_ctr) {
-        // stand-alone launch: the context's counter, zeroed in stream order (inside a graph the model supplies one
-        // counter per node and an epoch instead)
-        IB_CHECK_CUDA(cudaMemsetAsync(ctx->tile_ctr, 0, sizeof(uint32_t), stream));
-        p.tile_ctr = ctx->tile_ctr;
-        p.epoch_ptr = nullptr;
-    }
-    const size_t total = best.total;
     switch (p.epi) {
     case EPI_STORE: return launch_stream_epi<EPI_STORE>(ctx, stream, p, grid, geo, total);
     case EPI_RESIDUAL: return launch_stream_epi<EPI_RESIDUAL>(ctx, stream, p, grid, geo, total);
@@ -707,10 +719,6 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
 }
 
 #ifdef IB_STREAM_TRACE
-extern "C" __attribute__((visibility("default"))) int32_t ib_debug_cta_times(unsigned long long *ends, unsigned long long *starts) {
-    if (cudaMemcpyFromSymbol(ends, g_cta_end, sizeof(unsigned long long) * 800) != cudaSuccess) return 2;
-    return cudaMemcpyFromSymbol(starts, g_cta_start, sizeof(unsigned long long) * 800) == cudaSuccess ? 0 : 2;
-}
 extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(unsigned long long *out64) {
     return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 2;
 }

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(256) begin_token_kernel(const TokenCtl *ctl, c
 
 // end of token: feed the arg-max back when the prompt is exhausted, advance step and position
 // (crates/inferi-chat/src/sampler.rs:102-110, chat_llama2.rs:137-171).
-__global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap, uint32_t *epoch, uint32_t pdl) {
+__global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap, uint32_t pdl) {
     if (pdl) {
         asm volatile("griddepcontrol.launch_dependents;");
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -115,7 +115,6 @@ __global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap,
         if (step + 1 >= ctl->n_prompt && step + 1 < seq_cap) seq[step + 1] = ctl->next;
         ctl->step = step + 1;
         ctl->pos = ctl->pos + 1;
-        *epoch = *epoch + 1;   // graph launches so far: the streaming GEMVs derive their tile-number range from it
     }
 }
 
@@ -141,8 +140,6 @@ struct ib_llama {
     uint32_t attn_splits = 0;
     unsigned long long *argmax_slots = nullptr;
     unsigned int *argmax_counter = nullptr;
-    uint32_t *tile_ctrs = nullptr; // one tile hand-out counter per GEMV node of the token graph, never reset
-    uint32_t *epoch = nullptr;     // number of completed graph launches
     uint32_t *h_pinned = nullptr;  // [4 + seq_cap] staging for control block and token ids
     cudaEvent_t staged = nullptr;  // the last copy out of h_pinned has been issued and finished
     cudaGraphExec_t graph_exec = nullptr;
@@ -172,7 +169,6 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         ctx->launches++;
     }
     ib_attn_params ap{c.max_position_embeddings, m->kv_dim_l, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
-    uint32_t node = 0;
     for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
         const ib_llama_layer_weights &w = m->layers[l];
         GemvParams p = {};
@@ -183,7 +179,6 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         p.nseg = 3; p.cols = c.hidden_size; p.epi = EPI_QKV; p.x = m->x; p.norm_w = w.attn_norm_dev; p.eps = c.rms_norm_eps;
         p.pos_ptr = &m->ctl->pos; p.rope_cs = m->rope_cs; p.head_size = m->head_size; p.kv_dim = m->kv_dim_l; p.kv_dtype = (uint32_t)m->kv_dtype;
         p.k_cache = m->k_cache[l]; p.v_cache = m->v_cache[l]; p.pdl = pdl;
-        p.tile_ctr = m->tile_ctrs + node++; p.epoch_ptr = m->epoch;
         if ((rc = launch_gemv(ctx, s, p))) return rc;
         // attention (transformer.rs:448)
         AttnLaunch a = {};
@@ -194,20 +189,17 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         p = GemvParams{};
         fill_seg(p.seg[0], w.attn_output, m->x);
         p.nseg = 1; p.cols = m->q_dim_l; p.epi = EPI_RESIDUAL; p.x = m->xb; p.resid = m->x; p.pdl = pdl;
-        p.tile_ctr = m->tile_ctrs + node++; p.epoch_ptr = m->epoch;
         if ((rc = launch_gemv(ctx, s, p))) return rc;
         // gate/up + SwiGLU (transformer.rs:454-464)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_gate, m->hb);
         fill_seg(p.seg[1], w.ffn_up, nullptr);
         p.nseg = 2; p.cols = c.hidden_size; p.epi = EPI_SWIGLU; p.x = m->x; p.norm_w = w.ffn_norm_dev; p.eps = c.rms_norm_eps; p.pdl = pdl;
-        p.tile_ctr = m->tile_ctrs + node++; p.epoch_ptr = m->epoch;
         if ((rc = launch_gemv(ctx, s, p))) return rc;
         // down + residual (transformer.rs:465-468)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_down, m->x);
         p.nseg = 1; p.cols = m->ffn_l; p.epi = EPI_RESIDUAL; p.x = m->hb; p.resid = m->x; p.pdl = pdl;
-        p.tile_ctr = m->tile_ctrs + node++; p.epoch_ptr = m->epoch;
         if ((rc = launch_gemv(ctx, s, p))) return rc;
     }
     // classifier + greedy arg-max (transformer.rs:471-478, models/sampler.rs:54-56)
@@ -215,7 +207,6 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     fill_seg(p.seg[0], m->output, m->logits);
     p.nseg = 1; p.cols = c.hidden_size; p.epi = EPI_ARGMAX; p.x = m->x; p.norm_w = m->output_norm; p.eps = c.rms_norm_eps;
     p.argmax_slots = m->argmax_slots; p.argmax_counter = m->argmax_counter; p.argmax_out = &m->ctl->next; p.row_offset = 0; p.pdl = pdl;
-    p.tile_ctr = m->tile_ctrs + node++; p.epoch_ptr = m->epoch;
     if ((rc = launch_gemv(ctx, s, p))) return rc;
     {
         cudaLaunchConfig_t cfg = {};
@@ -227,7 +218,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl ? 1 : 0;
-        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, end_token_kernel, m->ctl, m->seq, m->seq_cap, m->epoch, pdl));
+        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, end_token_kernel, m->ctl, m->seq, m->seq_cap, pdl));
         ctx->launches++;
     }
     return IB_OK;
@@ -257,7 +248,7 @@ int32_t ib_llama_destroy(ib_llama *m) {
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
     if (m->staged) cudaEventDestroy(m->staged);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter, m->tile_ctrs, m->epoch};
+                    m->argmax_counter};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -383,11 +374,6 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     CU(cudaMalloc(&m->argmax_slots, sizeof(unsigned long long) * (size_t)ctx->sm_count * 2));
     CU(cudaMalloc(&m->argmax_counter, sizeof(unsigned int)));
     CU(cudaMemset(m->argmax_counter, 0, sizeof(unsigned int)));
-    const size_t n_ctr = 4 * (size_t)c.num_hidden_layers + 1;
-    CU(cudaMalloc(&m->tile_ctrs, sizeof(uint32_t) * n_ctr));
-    CU(cudaMemset(m->tile_ctrs, 0, sizeof(uint32_t) * n_ctr));
-    CU(cudaMalloc(&m->epoch, sizeof(uint32_t)));
-    CU(cudaMemset(m->epoch, 0, sizeof(uint32_t)));
 
     // record the token graph once
     CU(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
