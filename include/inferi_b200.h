@@ -117,6 +117,18 @@ typedef struct ib_attn_params {
 IB_API int32_t ib_attention(ib_ctx *ctx, void *stream, const ib_attn_params *params, const float *q_dev, const void *k_cache_dev,
                      const void *v_cache_dev, int32_t kv_dtype, float *out_dev);
 
+/* No counterpart in the reference.  The same attention as ib_attention for callers that must not allocate device
+ * memory when they call it (a latency-critical thread that may not take the allocator's locks, a plugin whose host owns
+ * the memory budget): it takes no context and calls no cudaMalloc/cudaFree.  The split-K scratch is a fixed array inside
+ * the library, so every GPU that loads the library holds about 1 MiB for it until the process exits.
+ * Limits: n_heads * (head_size + 2) <= 262144 and at most 256 kv heads, else IB_ERR_UNSUPPORTED with a message.
+ * The device that is current when it is called is used.  The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress); make that first call during set-up, before any stream capture.
+ * All calls share the one array: two calls whose kernels may overlap on the GPU (different streams) race; calls on one
+ * stream are safe, each call leaves the array's counters at zero for the next. */
+IB_API int32_t ib_attention_static(void *stream, const ib_attn_params *params, const float *q_dev, const void *k_cache_dev,
+                                   const void *v_cache_dev, int32_t kv_dtype, float *out_dev);
+
 /* Replaces the greedy branch of `Sampler::sample` (crates/inferi/src/models/sampler.rs:32-36, 54-56), on the
  * device: index of the largest logit, lowest index on ties. */
 IB_API int32_t ib_argmax(ib_ctx *ctx, void *stream, const float *logits_dev, uint32_t n, uint32_t *out_dev);

@@ -67,6 +67,7 @@ SIGNATURES = {
     "ib_silu_mul": (_i32, [_vp, _vp, _vp, _vp, _u32]),
     "ib_add_assign": (_i32, [_vp, _vp, _vp, _vp, _u32]),
     "ib_attention": (_i32, [_vp, _vp, C.POINTER(AttnParams), _vp, _vp, _vp, _i32, _vp]),
+    "ib_attention_static": (_i32, [_vp, C.POINTER(AttnParams), _vp, _vp, _vp, _i32, _vp]),
     "ib_argmax": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "ib_llama_create": (_i32, [_vp, C.POINTER(LlamaConfig), C.POINTER(LlamaWeights), _i32, _i32, _i32, C.POINTER(_vp)]),
     "ib_llama_destroy": (_i32, [_vp]),

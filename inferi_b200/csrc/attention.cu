@@ -282,3 +282,69 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
 }
 
 }  // namespace ib
+
+// -------------------------------------------------------------------------------------------------------------------
+// ib_attention_static: decode attention for callers that must not allocate.
+//
+// Some hosts of this library run where device allocation is off limits once set-up is over: a real-time audio/serving
+// thread that may not take the allocator's locks, a plugin whose host application owns the memory budget, code running
+// inside a region where cudaMalloc would synchronise the device.  ib_attention() grows a scratch buffer with cudaMalloc
+// on demand and needs a context (whose creation allocates); this variant needs neither.  Its split-K scratch is the
+// fixed array below, part of the library image: every GPU that loads the library carries these ~1 MiB until the process
+// exits, whether or not the entry point is ever called.
+// -------------------------------------------------------------------------------------------------------------------
+namespace ib {
+constexpr uint32_t STATIC_ATTN_FLOATS = 262144;    // 1 MiB of partials: bounds n_heads * (head_size + 2) * splits
+constexpr uint32_t STATIC_ATTN_KV_HEADS = 256;     // arrival counters, one per kv head
+constexpr uint32_t STATIC_ATTN_MAX_SPLITS = 32;
+constexpr int STATIC_ATTN_MAX_DEVICES = 64;
+}  // namespace ib
+
+static __device__ __align__(256) float g_static_attn_scratch[ib::STATIC_ATTN_FLOATS];
+static __device__ __align__(256) unsigned int g_static_attn_counters[ib::STATIC_ATTN_KV_HEADS];
+
+// Device addresses of the two arrays, looked up once per device.  In host code the array names above are only
+// host-side stand-ins for the symbols; the addresses a kernel can use come from cudaGetSymbolAddress, called with the
+// device in question current.
+static float *g_static_scratch_addr[ib::STATIC_ATTN_MAX_DEVICES];
+static unsigned int *g_static_counters_addr[ib::STATIC_ATTN_MAX_DEVICES];
+
+extern "C" int32_t ib_attention_static(void *stream, const ib_attn_params *params, const float *q_dev, const void *k_cache_dev,
+                                       const void *v_cache_dev, int32_t kv_dtype, float *out_dev) {
+    using namespace ib;
+    IB_REQUIRE(params && q_dev && k_cache_dev && v_cache_dev && out_dev, "ib_attention_static: null argument");
+    IB_REQUIRE(kv_dtype == IB_KV_F32 || kv_dtype == IB_KV_F16, "ib_attention_static: unknown kv dtype %d", kv_dtype);
+    const ib_attn_params &p = *params;
+    IB_REQUIRE(p.kv_mul >= 1 && p.n_heads >= p.kv_mul && p.n_heads % p.kv_mul == 0 && p.head_size > 0, "ib_attention_static: bad head counts");
+    const uint32_t n_kv = p.n_heads / p.kv_mul;
+    const uint64_t per_split = (uint64_t)p.n_heads * (p.head_size + 2);   // floats one split of all heads leaves behind
+    if (n_kv > STATIC_ATTN_KV_HEADS || per_split > STATIC_ATTN_FLOATS)
+        return set_error(IB_ERR_UNSUPPORTED,
+                         "ib_attention_static: %u heads of %u exceed the built-in scratch (n_heads * (head_size + 2) <= %u, kv heads <= %u); "
+                         "use ib_attention, which allocates",
+                         p.n_heads, p.head_size, STATIC_ATTN_FLOATS, STATIC_ATTN_KV_HEADS);
+    uint32_t splits = (uint32_t)(STATIC_ATTN_FLOATS / per_split);
+    if (splits > STATIC_ATTN_MAX_SPLITS) splits = STATIC_ATTN_MAX_SPLITS;
+
+    int dev = -1;
+    IB_CHECK_CUDA(cudaGetDevice(&dev));
+    IB_REQUIRE(dev >= 0 && dev < STATIC_ATTN_MAX_DEVICES, "ib_attention_static: device ordinal %d not supported", dev);
+    if (!g_static_scratch_addr[dev]) {
+        // first call on this device: resolve the symbols (no allocation takes place; the arrays already exist)
+        float *s = nullptr;
+        unsigned int *c = nullptr;
+        IB_CHECK_CUDA(cudaGetSymbolAddress((void **)&s, g_static_attn_scratch));
+        IB_CHECK_CUDA(cudaGetSymbolAddress((void **)&c, g_static_attn_counters));
+        g_static_counters_addr[dev] = c;
+        g_static_scratch_addr[dev] = s;
+    }
+    ib_ctx local;                 // plain bookkeeping struct on the stack: launch_attention only counts launches in it
+    local.device = dev;
+    AttnLaunch a = {};
+    a.p = p;
+    a.q = q_dev; a.k_cache = k_cache_dev; a.v_cache = v_cache_dev; a.kv_dtype = kv_dtype; a.out = out_dev;
+    a.scratch = g_static_scratch_addr[dev];
+    a.counters = g_static_counters_addr[dev];   // zero when the library is loaded; the kernel puts every counter back to zero
+    a.max_splits = splits;
+    return launch_attention(&local, (cudaStream_t)stream, a);
+}
