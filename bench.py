@@ -238,31 +238,51 @@ def main():
 
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run); got {world}")
-    if world > 1:
-        raise SystemExit("tensor-parallel decode is not available in this build")
     W, K = max(args.warmup, 3), args.steps
     torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        from inferi_b200 import tp
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     backend = Backend(local_rank)
 
-    weights = synth_weights(cfg, seed=WEIGHT_SEED, device="cuda")
-    dev_w = Llama2Weights(backend, cfg, weights)
+    weights = synth_weights(cfg, seed=WEIGHT_SEED, device="cuda")     # same seed, same values on every rank
+    shapes = None
+    if world > 1:
+        # tensor parallel: each rank keeps its shard (rows of q/k/v/gate/up/classifier, columns of attn_output/ffn_down)
+        shapes = tp.shard_shapes(cfg, world, weights["layers"][0]["ffn_down"][0])
+        weights = tp.shard_weights(cfg, weights, rank, world)
+    dev_w = Llama2Weights(backend, cfg, weights, shapes=shapes)
     del weights
     torch.cuda.empty_cache()
-    model = Llama2(backend, cfg, dev_w, kv_f16=True)
+    model = Llama2(backend, cfg, dev_w, kv_f16=True, tp_rank=rank, tp_size=world)
     prompt = np.random.default_rng(PROMPT_SEED).integers(0, cfg.vocab_size, W).astype(np.uint32)
+
+    def rank_sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     # ---- value: device-resident loop -------------------------------------------------------------------------
     first = model.generate(prompt, 1, start_pos=0)          # W warm-up steps through the decode path
-    torch.cuda.synchronize()
+    rank_sync()
     backend.reset_launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
-        torch.cuda.synchronize()
+        rank_sync()
         start.record()
         out = model.generate(first, K, start_pos=W)         # exactly K timed steps
         end.record()
-        torch.cuda.synchronize()
-    ms = start.elapsed_time(end)
+        rank_sync()
+    ms = max_over_ranks(start.elapsed_time(end))            # device time, maximum over the ranks
     launches = backend.launch_count()
     tok_s = K / (ms * 1e-3)
 
@@ -270,24 +290,25 @@ def main():
     tok = int(first[0])
     for i in range(3):
         model.forward(tok, W + i)
-    torch.cuda.synchronize()
+    rank_sync()
     t0 = time.perf_counter()
     pos = W
     for _ in range(K):
         tok, _ = model.forward(tok, pos)
         pos += 1
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    rank_sync()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_tok_s = K / e2e_s
 
     # ---- roofline --------------------------------------------------------------------------------------------
     peak, peak_src = measured_peaks()
+    peak *= world                                            # aggregate HBM bandwidth of the ranks
     avg_pos = W + (K - 1) / 2.0
     bytes_per_token = cfg.weight_bytes() + cfg.kv_bytes_per_position(True) * (avg_pos + 1) + cfg.kv_bytes_per_position(True)
     achieved = bytes_per_token / (ms * 1e-3 / K) / 1e9
     kernels = []
     gemv = GemvQuant(backend)
-    for name, mats in (("ffn_gate Q4_K 14336x4096", [l["ffn_gate"] for l in dev_w.layers]), ("ffn_down Q6_K 4096x14336", [l["ffn_down"] for l in dev_w.layers]),
+    for name, mats in () if world > 1 else (("ffn_gate Q4_K 14336x4096", [l["ffn_gate"] for l in dev_w.layers]), ("ffn_down Q6_K 4096x14336", [l["ffn_down"] for l in dev_w.layers]),
                        ("attn_q Q4_K 4096x4096", [l["attn_q"] for l in dev_w.layers]), ("output Q6_K 128256x4096", [dev_w.output])):
         v = torch.randn(mats[0].cols, device="cuda")
         o = torch.empty(mats[0].rows, device="cuda")
@@ -310,20 +331,24 @@ def main():
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a weights x 3-limb int8 activations, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": workload_name(cfg), "prompt_tokens": W, "decode_tokens": K, "l2": "weights per token (4.9 GB) exceed L2 (126 MB)",
+        "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}" if world > 1 else "single GPU", "prompt_tokens": W, "decode_tokens": K, "l2": "weights per token (4.9 GB) exceed L2 (126 MB)",
                    "prefill": "prompt fed through the decode path (as the reference does), untimed"},
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": 20, "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                      "peak_source": peak_src, "per": "token (one graph launch)", "algorithmic_bytes": bytes_per_token,
-                     "frac_of_8TBs": achieved / 8000.0, "kernels": kernels},
+                     "frac_of_8TBs": achieved / (8000.0 * world), "kernels": kernels},
         "clocks": clocks.summary(),
         "checksum": int(np.bitwise_xor.reduce(out.astype(np.uint64))),
     }
     if not args.no_cpu_baseline and rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(cfg)
-    print(json.dumps(line))
+    if rank == 0:
+        print(json.dumps(line))
     model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

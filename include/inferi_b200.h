@@ -183,6 +183,18 @@ IB_API int32_t ib_llama_forward(ib_llama *model, void *stream, uint32_t token, u
 IB_API int32_t ib_llama_generate(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos,
                           uint32_t n_gen, uint32_t *out_tokens_host);
 
+/* Tensor parallelism inside one NVLink/NVSwitch box (no counterpart in the reference, which is single-GPU): one process
+ * per GPU, each creating its model with (tp_rank, tp_size > 1) and ITS SHARD of every matrix — q/k/v, gate/up and the
+ * classifier split by rows (heads, FFN units, vocabulary), attn_output and ffn_down split by columns at block
+ * granularity (Q6_K: multiples of 2048 columns), token_embd and the norm vectors replicated.  Partial sums of the two
+ * row-split GEMVs are exchanged by a one-shot push all-reduce fused into the kernels (peer stores into each rank's
+ * exchange area + arrival counters, every wait bounded).  Set-up: every rank calls ib_llama_tp_export, the hosts exchange
+ * the IB_TP_HANDLE_BYTES-byte handles (any transport), every rank calls ib_llama_tp_connect with all handles ordered by
+ * rank; only then can the model run.  All ranks must then issue the same forward/generate calls. */
+#define IB_TP_HANDLE_BYTES 64
+IB_API int32_t ib_llama_tp_export(ib_llama *model, void *handle_out);
+IB_API int32_t ib_llama_tp_connect(ib_llama *model, const void *handles_by_rank);
+
 /* Device pointer of the last forward's logits (f32[vocab / tp_size]) and of the residual stream x (f32[hidden]);
  * for parity checks (the reference exposes `Llama2State::logits`, transformer.rs:15-43). */
 IB_API int32_t ib_llama_state(ib_llama *model, const float **logits_dev, const float **x_dev);

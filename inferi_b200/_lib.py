@@ -14,6 +14,7 @@ IB_OK = 0
 STATUS_NAMES = {0: "IB_OK", 1: "IB_ERR_INVALID", 2: "IB_ERR_CUDA", 3: "IB_ERR_OOM", 4: "IB_ERR_UNSUPPORTED", 5: "IB_ERR_TIMEOUT", 6: "IB_ERR_COMM"}
 KV_F32, KV_F16 = 0, 1
 ROPE_ORIGINAL, ROPE_NEOX = 0, 1
+TP_HANDLE_BYTES = 64
 
 
 class InferiError(RuntimeError):
@@ -74,6 +75,8 @@ SIGNATURES = {
     "ib_llama_forward": (_i32, [_vp, _vp, _u32, _u32, _vp, _vp]),
     "ib_llama_generate": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "ib_llama_state": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "ib_llama_tp_export": (_i32, [_vp, _vp]),
+    "ib_llama_tp_connect": (_i32, [_vp, _vp]),
 }
 
 _lib = None

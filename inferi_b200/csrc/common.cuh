@@ -107,8 +107,11 @@ enum GemvEpilogue : uint32_t {
     EPI_RESIDUAL = 1,  // out[r] = resid[r] + dot
     EPI_SWIGLU = 2,    // seg0 = gate, seg1 = up: seg0.out[r] = up * gate / (1 + exp(-gate))
     EPI_QKV = 3,       // seg0 = q (rope, store f32), seg1 = k (rope, store to cache), seg2 = v (store to cache)
-    EPI_ARGMAX = 4     // store (if out != null) and track the arg-max over all rows
+    EPI_ARGMAX = 4,    // store (if out != null) and track the arg-max over all rows
+    EPI_PUSH = 5       // tensor parallel: store the pair into every rank's partial-sum slot of this rank (peer stores)
 };
+
+constexpr int IB_MAX_TP = 8;
 
 struct GemvParams {
     GemvSeg seg[3];
@@ -129,6 +132,21 @@ struct GemvParams {
     uint32_t row_offset;               // added to the row index (tensor-parallel vocabulary shard)
     uint32_t pdl;                      // 1: launched with programmatic dependent launch
     uint32_t *err;                     // device view of the context's error word (set by launch_gemv)
+    // ---- tensor parallel (tp > 1): one-shot push all-reduce fused into epilogue and prologue ----
+    uint32_t tp;                                // number of ranks; 0 or 1 = single GPU
+    const uint32_t *epoch_ptr;                  // device scalar: completed token-graph launches (arrival counters only ever grow)
+    // EPI_PUSH: rank p keeps this rank's partial at push_dst[p]; after the last CTA every rank's counter gets +1
+    float *push_dst[IB_MAX_TP];
+    uint32_t *push_flag[IB_MAX_TP];
+    unsigned int *push_done;                    // local CTA arrival counter (self-resetting)
+    // prologue: x + sum over ranks of reduce_src[r][cols] once reduce_flag has reached ((*epoch) * per_epoch + use) * tp
+    const float *reduce_src;
+    const uint32_t *reduce_flag;
+    uint32_t reduce_use, reduce_per_epoch;
+    float *x_out;                               // CTA 0 stores the reduced residual stream here
+    // EPI_ARGMAX with a sharded vocabulary: this rank's candidate goes to amax_dst[p] of every rank
+    unsigned long long *amax_dst[IB_MAX_TP];
+    uint32_t *amax_flag[IB_MAX_TP];
 };
 
 int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p);

@@ -527,6 +527,8 @@ int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p_in) {
     p.err = ctx->err_dev;
     IB_REQUIRE(p.nseg >= 1 && p.nseg <= 3, "gemv: bad segment count %u", p.nseg);
     if (gemv_stream_eligible(p)) return launch_gemv_stream(ctx, stream, p);
+    if (p.tp > 1 || p.epi == EPI_PUSH)   // the cross-GPU exchange exists only in the streaming kernel
+        return set_error(IB_ERR_UNSUPPORTED, "gemv: a tensor-parallel shard (cols=%u) does not meet the streaming kernel's shape rules", p.cols);
     IB_REQUIRE(p.cols % 32 == 0 && p.cols <= GEMV_MAX_COLS, "gemv: cols=%u unsupported by the fast kernels", p.cols);
     uint32_t pairs = 0;
     for (uint32_t s = 0; s < p.nseg; s++) {

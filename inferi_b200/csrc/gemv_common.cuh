@@ -119,10 +119,18 @@ __device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uin
     }
 }
 
+// Tensor-parallel input: x + the partial sums every rank left in this rank's slots (fixed rank order, so every rank gets
+// the same bits); CTA 0 also stores the result as the new residual stream.  Only for rows that fit the registers.
+struct PackReduce {
+    const float *src;   // [tp][cols], null = plain x
+    uint32_t tp;
+    float *x_out;       // may be null
+};
+
 // `g` holds the norm weights of the thread's first run (from pack_prefetch_norm).
 template <int NT = PACK_THREADS>
 __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                float *red /* [NT/32 + 1] */, const float4 (&g)[4]) {
+                                                float *red /* [NT/32 + 1] */, const float4 (&g)[4], const PackReduce rd = PackReduce{nullptr, 0, nullptr}) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nruns = cols / 16;    // cols is a multiple of 32, so runs pair up inside a warp
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
@@ -133,6 +141,26 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
         const uint32_t run = tid + NT * i;
 #pragma unroll
         for (int j = 0; j < 4; j++) r.x[i][j] = run < nruns ? __ldcg(x4 + 4 * run + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (rd.src) {
+#pragma unroll
+        for (int i = 0; i < PACK_RUNS; i++) {
+            const uint32_t run = tid + NT * i;
+            if (run < nruns) {
+                for (uint32_t rk = 0; rk < rd.tp; rk++) {
+                    const float4 *s4 = reinterpret_cast<const float4 *>(rd.src + (size_t)rk * cols) + 4 * run;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float4 a = __ldcg(s4 + j);
+                        r.x[i][j].x += a.x; r.x[i][j].y += a.y; r.x[i][j].z += a.z; r.x[i][j].w += a.w;
+                    }
+                }
+                if (rd.x_out && blockIdx.x == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) reinterpret_cast<float4 *>(rd.x_out)[4 * run + j] = r.x[i][j];
+                }
+            }
+        }
     }
     float rms = 1.0f;
     if (norm_w) {

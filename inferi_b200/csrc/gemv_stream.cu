@@ -22,7 +22,7 @@ namespace ib {
 constexpr int CW = 16;                          // consumer warps
 constexpr int STREAM_THREADS = (CW + 1) * 32;   // + 1 producer warp
 constexpr int PT_MAX = 16;                      // row pairs per tile
-constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;   // a wait on an mbarrier gives up after 4 s
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait on an mbarrier or on a peer gives up after 2 s
 
 #ifdef IB_STREAM_TRACE
 // Timeline probes for latency studies: globaltimer stamps of CTA 0 (and of the last CTA's end), one row of 16 slots
@@ -84,6 +84,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     }
     return false;
 }
+// ---- cross-GPU arrival counters (tensor parallel).  Counters only grow; a rank waits until its own counter has
+// reached the value that the current use implies.  The wait is bounded like every other wait here. ----
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_counter(const uint32_t *flag, uint32_t target, uint32_t *err, uint32_t code) {
+    if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
+    if (err) {
+        *(volatile uint32_t *)err = code;
+        __threadfence_system();
+    }
+    return false;
+}
+
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
@@ -399,6 +421,9 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
             if (p.kv_dtype == IB_KV_F16) reinterpret_cast<__half2 *>(cache)[off >> 1] = __floats2half2_rn(a, b);
             else reinterpret_cast<float2 *>(cache)[off >> 1] = make_float2(a, b);
         }
+    } else if (EPI == EPI_PUSH) {
+        // row-split matrix of a tensor-parallel model: this rank's partial goes straight into every rank's memory
+        for (uint32_t rk = 0; rk < p.tp; rk++) *reinterpret_cast<float2 *>(p.push_dst[rk] + r0) = make_float2(a, b);
     } else if (EPI == EPI_ARGMAX) {
         if (p.seg[0].out) *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
         best = max(best, max(argmax_key(a, p.row_offset + r0), argmax_key(b, p.row_offset + r0 + 1)));
@@ -560,7 +585,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     pack_prefetch_norm(p.norm_w, p.cols, norm_g);   // weights: fetched while the previous kernel is still running
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(2);
-    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g);
+    PackReduce rd{nullptr, 0, nullptr};
+    if (p.reduce_src) {
+        // every rank's partial sums of the previous row-split GEMV must have landed in this rank's slots
+        if (threadIdx.x == 0) wait_counter(p.reduce_flag, ((*p.epoch_ptr) * p.reduce_per_epoch + p.reduce_use) * p.tp, p.err, 3);
+        named_barrier(1, PACK_THREADS);
+        rd = PackReduce{p.reduce_src, p.tp, p.x_out};
+    }
+    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g, rd);
     const Act A{act_sm, p.cols};
     TRACE(3);
 
@@ -573,6 +605,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     }
     TRACE(15);
 
+    if (EPI == EPI_PUSH) {
+        // all of this CTA's peer stores are out; the last CTA of the grid tells every rank that this rank has delivered
+        __threadfence_system();
+        named_barrier(1, PACK_THREADS);
+        if (threadIdx.x == 0) {
+            if (atomicAdd(p.push_done, 1u) == gridDim.x - 1) {
+                *p.push_done = 0u;
+                __threadfence_system();
+                for (uint32_t rk = 0; rk < p.tp; rk++) atomicAdd_system(p.push_flag[rk], 1u);
+            }
+        }
+    }
     if (EPI == EPI_ARGMAX) {
 #pragma unroll
         for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -600,6 +644,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
                 for (int w = 0; w < CW; w++) b = max(b, best_sm[w]);
                 *p.argmax_out = 0xFFFFFFFFu - (uint32_t)(b & 0xFFFFFFFFull);
                 *p.argmax_counter = 0u;
+                if (p.tp > 1) {
+                    // sharded vocabulary: every rank gets this rank's candidate; the end-of-token kernel folds them
+                    for (uint32_t rk = 0; rk < p.tp; rk++) *p.amax_dst[rk] = b;
+                    __threadfence_system();
+                    for (uint32_t rk = 0; rk < p.tp; rk++) atomicAdd_system(p.amax_flag[rk], 1u);
+                }
             }
         }
     }
@@ -714,6 +764,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     case EPI_SWIGLU: return launch_stream_epi<EPI_SWIGLU>(ctx, stream, p, grid, geo, total);
     case EPI_QKV: return launch_stream_epi<EPI_QKV>(ctx, stream, p, grid, geo, total);
     case EPI_ARGMAX: return launch_stream_epi<EPI_ARGMAX>(ctx, stream, p, grid, geo, total);
+    case EPI_PUSH: return launch_stream_epi<EPI_PUSH>(ctx, stream, p, grid, geo, total);
     default: return set_error(IB_ERR_INVALID, "gemv: unknown epilogue %u", p.epi);
     }
 }

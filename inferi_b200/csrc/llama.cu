@@ -18,6 +18,7 @@
 
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 #include <new>
 #include <vector>
 
@@ -104,17 +105,44 @@ __global__ void __launch_bounds__(256) begin_token_kernel(const TokenCtl *ctl, c
 }
 
 // end of token: feed the arg-max back when the prompt is exhausted, advance step and position
-// (crates/inferi-chat/src/sampler.rs:102-110, chat_llama2.rs:137-171).
-__global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap, uint32_t pdl) {
+// (crates/inferi-chat/src/sampler.rs:102-110, chat_llama2.rs:137-171).  With a sharded vocabulary the ranks' candidates
+// (packed value / ~index keys, pushed by the classifier kernels) are folded here, on every rank alike.
+__global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap, uint32_t *epoch, uint32_t tp, const unsigned long long *amax_slots,
+                                 const uint32_t *amax_flag, uint32_t *err, uint32_t pdl) {
     if (pdl) {
         asm volatile("griddepcontrol.launch_dependents;");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
     if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const uint32_t e = *epoch;
+        if (tp > 1) {
+            const uint32_t target = (e + 1) * tp;
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {   // bounded wait for the other ranks' candidates
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(amax_flag) : "memory");
+                if ((int32_t)(v - target) >= 0) break;
+                unsigned long long t1;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > 2000000000ull) {
+                    *(volatile uint32_t *)err = 4;
+                    __threadfence_system();
+                    break;
+                }
+            }
+            unsigned long long best = 0ull;
+            for (uint32_t r = 0; r < tp; r++) {
+                const unsigned long long k = __ldcg(amax_slots + r);
+                best = k > best ? k : best;
+            }
+            ctl->next = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
+        }
         const uint32_t step = ctl->step;
         if (step + 1 >= ctl->n_prompt && step + 1 < seq_cap) seq[step + 1] = ctl->next;
         ctl->step = step + 1;
         ctl->pos = ctl->pos + 1;
+        *epoch = e + 1;   // completed token-graph launches: the cross-GPU arrival counters are compared against it
     }
 }
 
@@ -140,6 +168,15 @@ struct ib_llama {
     uint32_t attn_splits = 0;
     unsigned long long *argmax_slots = nullptr;
     unsigned int *argmax_counter = nullptr;
+    // tensor parallel: a second residual buffer (the reduced stream ping-pongs), this rank's exchange area and the
+    // peers' views of theirs (cudaIpc), local CTA counters of the two pushing kernels, completed-launch count
+    float *x2 = nullptr;
+    uint8_t *comm = nullptr;
+    uint8_t *comm_peer[IB_MAX_TP] = {nullptr};
+    bool connected = false;
+    float *x_final = nullptr;            // buffer that holds the residual stream after the last layer
+    unsigned int *push_done = nullptr;   // [2]
+    uint32_t *epoch = nullptr;
     uint32_t *h_pinned = nullptr;  // [4 + seq_cap] staging for control block and token ids
     cudaEvent_t staged = nullptr;  // the last copy out of h_pinned has been issued and finished
     cudaGraphExec_t graph_exec = nullptr;
@@ -149,36 +186,84 @@ struct ib_llama {
 
 namespace ib {
 
+// Exchange area of one rank (tensor parallel).  Rank p stores into rank q's area over NVLink (plain peer stores):
+//   part[set][rank][hidden]  partial sums of the row-split GEMVs: set 0 = o_proj, set 1 = down
+//   amax[rank]               arg-max candidates of the sharded classifier
+//   flag[0], flag[1], flag[2] arrival counters of set 0, set 1 and the arg-max exchange (they only ever grow)
+struct CommLayout {
+    size_t part_bytes, amax_off, flag_off, total;
+    CommLayout(uint32_t hidden, int tp) {
+        part_bytes = (size_t)tp * hidden * sizeof(float);
+        amax_off = 2 * part_bytes;
+        flag_off = amax_off + (size_t)IB_MAX_TP * sizeof(unsigned long long);
+        total = flag_off + 256;
+    }
+    float *part(uint8_t *base, int set, int rank, uint32_t hidden) const { return reinterpret_cast<float *>(base + set * part_bytes) + (size_t)rank * hidden; }
+    unsigned long long *amax(uint8_t *base, int rank) const { return reinterpret_cast<unsigned long long *>(base + amax_off) + rank; }
+    uint32_t *flag(uint8_t *base, int i) const { return reinterpret_cast<uint32_t *>(base + flag_off) + i; }
+};
+
+static void set_pdl(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, uint32_t pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+}
+
 static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     ib_ctx *ctx = m->ctx;
     const ib_llama_config &c = m->cfg;
+    const int tp = m->tp_size, rank = m->tp_rank;
+    const uint32_t H = c.hidden_size, L = c.num_hidden_layers;
+    const CommLayout cl(H, tp);
     int32_t rc;
     {
         QDesc e{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((c.hidden_size + 255) / 256);
+        cfg.gridDim = dim3((H + 255) / 256);
         cfg.blockDim = dim3(256);
         cfg.stream = s;
         cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 0;  // first node of the token graph: nothing to overlap with
-        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, begin_token_kernel, (const TokenCtl *)m->ctl, (const uint32_t *)m->seq, e, c.hidden_size, m->x,
+        set_pdl(cfg, attr, 0);  // first node of the token graph: nothing to overlap with
+        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, begin_token_kernel, (const TokenCtl *)m->ctl, (const uint32_t *)m->seq, e, H, m->x,
                                          (const float *)m->theta, m->head_size / 2, m->rope_cs, c.vocab_size, pdl));
         ctx->launches++;
     }
+    // Single GPU: the residual stream x is updated in place by the o_proj / down epilogues.
+    // Tensor parallel: o_proj / down push partial sums to every rank; the next kernel's prologue adds them to x (fixed rank
+    // order) and CTA 0 stores the sum into the other residual buffer, so the stream alternates between x and x2:
+    //   qkv(l) reads cur (+ set 1 of layer l-1) ; gate/up(l) reads cur (+ set 0) ; classifier reads cur (+ set 1)
+    float *cur = m->x, *other = m->x2;
+    auto add_reduce = [&](GemvParams &p, int set, uint32_t use) {
+        if (tp <= 1) return;
+        p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch;
+        p.reduce_src = cl.part(m->comm, set, 0, H);
+        p.reduce_flag = cl.flag(m->comm, set);
+        p.reduce_use = use; p.reduce_per_epoch = L;
+        p.x_out = other;
+        float *t = cur; cur = other; other = t;
+    };
+    auto add_push = [&](GemvParams &p, int set) {
+        p.epi = EPI_PUSH; p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch; p.resid = nullptr;
+        for (int r = 0; r < tp; r++) {
+            p.push_dst[r] = cl.part(m->comm_peer[r], set, rank, H);
+            p.push_flag[r] = cl.flag(m->comm_peer[r], set);
+        }
+        p.push_done = m->push_done + set;
+        p.seg[0].out = nullptr;
+    };
     ib_attn_params ap{c.max_position_embeddings, m->kv_dim_l, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
-    for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
+    for (uint32_t l = 0; l < L; l++) {
         const ib_llama_layer_weights &w = m->layers[l];
         GemvParams p = {};
         // qkv (transformer.rs:420-445)
         fill_seg(p.seg[0], w.attn_q, m->q);
         fill_seg(p.seg[1], w.attn_k, nullptr);
         fill_seg(p.seg[2], w.attn_v, nullptr);
-        p.nseg = 3; p.cols = c.hidden_size; p.epi = EPI_QKV; p.x = m->x; p.norm_w = w.attn_norm_dev; p.eps = c.rms_norm_eps;
+        p.nseg = 3; p.cols = H; p.epi = EPI_QKV; p.x = cur; p.norm_w = w.attn_norm_dev; p.eps = c.rms_norm_eps;
         p.pos_ptr = &m->ctl->pos; p.rope_cs = m->rope_cs; p.head_size = m->head_size; p.kv_dim = m->kv_dim_l; p.kv_dtype = (uint32_t)m->kv_dtype;
         p.k_cache = m->k_cache[l]; p.v_cache = m->v_cache[l]; p.pdl = pdl;
+        if (l > 0) add_reduce(p, 1, l);   // the down partials of layer l-1: use number l of this token
         if ((rc = launch_gemv(ctx, s, p))) return rc;
         // attention (transformer.rs:448)
         AttnLaunch a = {};
@@ -187,38 +272,48 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         if ((rc = launch_attention(ctx, s, a))) return rc;
         // o_proj + residual (transformer.rs:450-453)
         p = GemvParams{};
-        fill_seg(p.seg[0], w.attn_output, m->x);
-        p.nseg = 1; p.cols = m->q_dim_l; p.epi = EPI_RESIDUAL; p.x = m->xb; p.resid = m->x; p.pdl = pdl;
+        fill_seg(p.seg[0], w.attn_output, cur);
+        p.nseg = 1; p.cols = m->q_dim_l; p.epi = EPI_RESIDUAL; p.x = m->xb; p.resid = cur; p.pdl = pdl;
+        if (tp > 1) add_push(p, 0);
         if ((rc = launch_gemv(ctx, s, p))) return rc;
         // gate/up + SwiGLU (transformer.rs:454-464)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_gate, m->hb);
         fill_seg(p.seg[1], w.ffn_up, nullptr);
-        p.nseg = 2; p.cols = c.hidden_size; p.epi = EPI_SWIGLU; p.x = m->x; p.norm_w = w.ffn_norm_dev; p.eps = c.rms_norm_eps; p.pdl = pdl;
+        p.nseg = 2; p.cols = H; p.epi = EPI_SWIGLU; p.x = cur; p.norm_w = w.ffn_norm_dev; p.eps = c.rms_norm_eps; p.pdl = pdl;
+        add_reduce(p, 0, l + 1);          // the o_proj partials of this layer
         if ((rc = launch_gemv(ctx, s, p))) return rc;
         // down + residual (transformer.rs:465-468)
         p = GemvParams{};
-        fill_seg(p.seg[0], w.ffn_down, m->x);
-        p.nseg = 1; p.cols = m->ffn_l; p.epi = EPI_RESIDUAL; p.x = m->hb; p.resid = m->x; p.pdl = pdl;
+        fill_seg(p.seg[0], w.ffn_down, cur);
+        p.nseg = 1; p.cols = m->ffn_l; p.epi = EPI_RESIDUAL; p.x = m->hb; p.resid = cur; p.pdl = pdl;
+        if (tp > 1) add_push(p, 1);
         if ((rc = launch_gemv(ctx, s, p))) return rc;
     }
     // classifier + greedy arg-max (transformer.rs:471-478, models/sampler.rs:54-56)
     GemvParams p = {};
     fill_seg(p.seg[0], m->output, m->logits);
-    p.nseg = 1; p.cols = c.hidden_size; p.epi = EPI_ARGMAX; p.x = m->x; p.norm_w = m->output_norm; p.eps = c.rms_norm_eps;
-    p.argmax_slots = m->argmax_slots; p.argmax_counter = m->argmax_counter; p.argmax_out = &m->ctl->next; p.row_offset = 0; p.pdl = pdl;
+    p.nseg = 1; p.cols = H; p.epi = EPI_ARGMAX; p.x = cur; p.norm_w = m->output_norm; p.eps = c.rms_norm_eps;
+    p.argmax_slots = m->argmax_slots; p.argmax_counter = m->argmax_counter; p.argmax_out = &m->ctl->next; p.pdl = pdl;
+    p.row_offset = (uint32_t)rank * m->vocab_l;
+    add_reduce(p, 1, L);                  // the down partials of the last layer
+    if (tp > 1)
+        for (int r = 0; r < tp; r++) {
+            p.amax_dst[r] = cl.amax(m->comm_peer[r], rank);
+            p.amax_flag[r] = cl.flag(m->comm_peer[r], 2);
+        }
     if ((rc = launch_gemv(ctx, s, p))) return rc;
+    m->x_final = cur;
     {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(32);
         cfg.stream = s;
         cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = pdl ? 1 : 0;
-        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, end_token_kernel, m->ctl, m->seq, m->seq_cap, pdl));
+        set_pdl(cfg, attr, pdl);
+        IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, end_token_kernel, m->ctl, m->seq, m->seq_cap, m->epoch, (uint32_t)tp,
+                                         (const unsigned long long *)(tp > 1 ? cl.amax(m->comm, 0) : nullptr),
+                                         (const uint32_t *)(tp > 1 ? cl.flag(m->comm, 2) : nullptr), ctx->err_dev, pdl));
         ctx->launches++;
     }
     return IB_OK;
@@ -240,6 +335,8 @@ static int32_t check_matrix(const ib_qtensor *t, const char *name, uint64_t rows
 
 extern "C" {
 
+static int32_t finish_graph(ib_llama *m);
+
 int32_t ib_llama_destroy(ib_llama *m) {
     if (!m) return IB_OK;
     cudaSetDevice(m->ctx->device);
@@ -247,8 +344,10 @@ int32_t ib_llama_destroy(ib_llama *m) {
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
     if (m->staged) cudaEventDestroy(m->staged);
+    for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
+        if (m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter};
+                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -268,7 +367,7 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     const ib_llama_config &c = *config;
     IB_REQUIRE(kv_dtype == IB_KV_F32 || kv_dtype == IB_KV_F16, "ib_llama_create: unknown kv dtype %d", kv_dtype);
     IB_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "ib_llama_create: bad tensor-parallel rank %d of %d", tp_rank, tp_size);
-    if (tp_size != 1) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_create: tensor parallelism is not available in this build");
+    IB_REQUIRE(tp_size <= IB_MAX_TP, "ib_llama_create: at most %d tensor-parallel ranks", IB_MAX_TP);
     IB_REQUIRE(c.num_hidden_layers > 0 && c.hidden_size > 0 && c.num_attention_heads > 0 && c.num_key_value_heads > 0 && c.vocab_size > 0 &&
                    c.max_position_embeddings > 0 && c.intermediate_size > 0,
                "ib_llama_create: zero-sized configuration field");
@@ -280,12 +379,18 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     if (!m) return set_error(IB_ERR_OOM, "host allocation failed");
     m->ctx = ctx; m->cfg = c; m->kv_dtype = kv_dtype; m->tp_rank = tp_rank; m->tp_size = tp_size;
     m->head_size = c.hidden_size / c.num_attention_heads;
+    // This rank's share.  Heads and vocabulary split evenly; the FFN width of a rank is read off its gate matrix, because
+    // Q6_K rows can only be cut at multiples of 2048 columns and 14336 = 7 x 2048 does not split evenly.
     m->n_heads_l = c.num_attention_heads / tp_size;
     m->n_kv_l = c.num_key_value_heads / tp_size;
     m->q_dim_l = m->n_heads_l * m->head_size;
     m->kv_dim_l = m->n_kv_l * m->head_size;
-    m->ffn_l = c.intermediate_size / tp_size;
+    m->ffn_l = (tp_size > 1 && weights->layers[0].ffn_gate) ? (uint32_t)weights->layers[0].ffn_gate->rows : c.intermediate_size;
     m->vocab_l = c.vocab_size / tp_size;
+    if (c.num_key_value_heads % tp_size || c.vocab_size % tp_size || m->vocab_l % 4 || m->ffn_l == 0 || m->ffn_l > c.intermediate_size) {
+        delete m;
+        return set_error(IB_ERR_INVALID, "ib_llama_create: %d ranks do not divide %u kv heads / vocabulary %u", tp_size, c.num_key_value_heads, c.vocab_size);
+    }
     int32_t rc = IB_OK;
 #define FAIL_IF(expr)                 \
     do {                              \
@@ -374,9 +479,41 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     CU(cudaMalloc(&m->argmax_slots, sizeof(unsigned long long) * (size_t)ctx->sm_count * 2));
     CU(cudaMalloc(&m->argmax_counter, sizeof(unsigned int)));
     CU(cudaMemset(m->argmax_counter, 0, sizeof(unsigned int)));
-
-    // record the token graph once
+    CU(cudaMalloc(&m->epoch, sizeof(uint32_t)));
+    CU(cudaMemset(m->epoch, 0, sizeof(uint32_t)));
     CU(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
+    if (tp_size > 1) {
+        // exchange area + second residual buffer; the graph is recorded once the peers' areas are mapped (ib_llama_tp_connect)
+        const CommLayout cl(c.hidden_size, tp_size);
+        CU(cudaMalloc(&m->comm, cl.total));
+        CU(cudaMemset(m->comm, 0, cl.total));
+        CU(cudaMalloc(&m->x2, sizeof(float) * c.hidden_size));
+        CU(cudaMalloc(&m->push_done, 2 * sizeof(unsigned int)));
+        CU(cudaMemset(m->push_done, 0, 2 * sizeof(unsigned int)));
+        CU(cudaDeviceSynchronize());
+        *out = m;
+        return IB_OK;
+    }
+    rc = finish_graph(m);
+    if (rc != IB_OK) {
+        ib_llama_destroy(m);
+        return rc;
+    }
+#undef FAIL_IF
+#undef CU
+    *out = m;
+    return IB_OK;
+}
+
+// Records the token graph (once every pointer it needs is known) and instantiates it.
+static int32_t finish_graph(ib_llama *m) {
+    ib_ctx *ctx = m->ctx;
+    int32_t rc;
+#define CU(expr)                                                                                                        \
+    do {                                                                                                                \
+        cudaError_t _e = (expr);                                                                                        \
+        if (_e != cudaSuccess) return set_error(IB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));           \
+    } while (0)
     CU(cudaDeviceSynchronize());
     const uint64_t before = ctx->launches;
     CU(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
@@ -389,27 +526,52 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     ctx->launches = before;  // recording is not launching
     if (rc != IB_OK) {
         if (graph) cudaGraphDestroy(graph);
-        ib_llama_destroy(m);
         return rc;
     }
-    if (ce != cudaSuccess) {
-        ib_llama_destroy(m);
-        return set_error(IB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
-    }
+    if (ce != cudaSuccess) return set_error(IB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
     ce = cudaGraphInstantiate(&m->graph_exec, graph, 0);
     cudaGraphDestroy(graph);
     if (ce != cudaSuccess) {
         m->graph_exec = nullptr;
-        ib_llama_destroy(m);
         return set_error(IB_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(ce));
     }
-#undef FAIL_IF
 #undef CU
-    *out = m;
     return IB_OK;
 }
 
+// ---- tensor parallel set-up: every rank publishes a handle of its exchange area and maps the others' ----
+int32_t ib_llama_tp_export(ib_llama *m, void *handle_out) {
+    IB_REQUIRE(m && handle_out, "ib_llama_tp_export: null argument");
+    IB_REQUIRE(m->tp_size > 1 && m->comm, "ib_llama_tp_export: the model is not tensor parallel");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    static_assert(sizeof(cudaIpcMemHandle_t) == IB_TP_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, m->comm);
+    if (e != cudaSuccess) return set_error(IB_ERR_COMM, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+    memcpy(handle_out, &h, sizeof h);
+    return IB_OK;
+}
+
+int32_t ib_llama_tp_connect(ib_llama *m, const void *handles) {
+    IB_REQUIRE(m && handles, "ib_llama_tp_connect: null argument");
+    IB_REQUIRE(m->tp_size > 1 && m->comm, "ib_llama_tp_connect: the model is not tensor parallel");
+    IB_REQUIRE(!m->connected, "ib_llama_tp_connect: already connected");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    for (int r = 0; r < m->tp_size; r++) {
+        if (r == m->tp_rank) { m->comm_peer[r] = m->comm; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + (size_t)r * IB_TP_HANDLE_BYTES, sizeof h);
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return set_error(IB_ERR_COMM, "cudaIpcOpenMemHandle for rank %d failed: %s (are the GPUs NVLink/P2P peers?)", r, cudaGetErrorString(e));
+        m->comm_peer[r] = (uint8_t *)ptr;
+    }
+    m->connected = true;
+    return finish_graph(m);
+}
+
 static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, uint32_t n_prompt, uint32_t start_pos, uint32_t n_steps) {
+    if (!m->graph_exec) return set_error(IB_ERR_COMM, "the tensor-parallel model is not connected yet: call ib_llama_tp_connect on every rank first");
     // control block + given tokens in one pinned staging buffer -> two small async copies
     uint32_t *h = m->h_pinned;
     IB_CHECK_CUDA(cudaEventSynchronize(m->staged));  // an earlier call's copies out of the staging buffer are done
@@ -465,7 +627,7 @@ int32_t ib_llama_generate(ib_llama *m, void *stream, const uint32_t *tokens_host
 int32_t ib_llama_state(ib_llama *m, const float **logits_dev, const float **x_dev) {
     IB_REQUIRE(m, "ib_llama_state: null model");
     if (logits_dev) *logits_dev = m->logits;
-    if (x_dev) *x_dev = m->x;
+    if (x_dev) *x_dev = m->x_final ? m->x_final : m->x;
     return IB_OK;
 }
 

@@ -117,9 +117,10 @@ def weights_to_host(weights: dict) -> dict:
 class Llama2Weights:
     """≙ `Llama2Weights` (crates/inferi/src/models/llama2/transformer.rs:176-196, 294-394): device tensors of one checkpoint."""
 
-    def __init__(self, backend: Backend, cfg: Llama2Config, weights: dict):
+    def __init__(self, backend: Backend, cfg: Llama2Config, weights: dict, shapes: dict | None = None):
+        """`shapes` overrides the [rows, cols] of the matrices (a tensor-parallel rank's shard, see tp.shard_shapes)."""
         self.backend, self.cfg = backend, cfg
-        sh = cfg.shapes()
+        sh = shapes or cfg.shapes()
         dev = torch.device("cuda", backend.device)
         self.layers = []
         self._keep = []
@@ -151,7 +152,10 @@ class Llama2:
     """≙ `Llama2` + `Llama2State` (crates/inferi/src/models/llama2/transformer.rs:15-137, 396-481) and the greedy token loop of
     `ChatLlama2` (crates/inferi-chat/src/chat_llama2.rs:92-255)."""
 
-    def __init__(self, backend: Backend, cfg: Llama2Config, weights: Llama2Weights, kv_f16: bool = True, tp_rank: int = 0, tp_size: int = 1):
+    def __init__(self, backend: Backend, cfg: Llama2Config, weights: Llama2Weights, kv_f16: bool = True, tp_rank: int = 0, tp_size: int = 1,
+                 group=None):
+        """With tp_size > 1, `weights` holds this rank's shard (tp.shard_weights) and torch.distributed must be initialised:
+        the ranks exchange the handles of their exchange areas here.  `forward` then returns this rank's slice of the logits."""
         self.backend, self.cfg, self.weights = backend, cfg, weights
         self.lib = backend.lib
         c_cfg = cfg.to_c()
@@ -159,7 +163,11 @@ class Llama2:
         h = C.c_void_p()
         check(self.lib.ib_llama_create(backend.handle, C.byref(c_cfg), C.byref(c_w), KV_F16 if kv_f16 else KV_F32, tp_rank, tp_size, C.byref(h)))
         self.handle = h
+        self.tp_rank, self.tp_size = tp_rank, tp_size
         self.vocab_local = cfg.vocab_size // tp_size
+        if tp_size > 1:
+            from . import tp
+            tp.connect(self, group)      # every rank of the group must get here
 
     def forward(self, token: int, pos: int, want_logits: bool = False):
         """One token at `pos`; returns (next_token, logits | None).  Host round trip per call, as in the reference."""
