@@ -10,215 +10,25 @@
 // un-normalised partial (max, sum, accumulator); the last CTA of a kv head to arrive merges the partials — no CTA
 // ever waits for another.  The split count is derived from the position on the device, so the same launch (and
 // the same CUDA graph node) serves every context length.
-#include "common.cuh"
-
-#include <math.h>
+#include "attention.cuh"
 
 namespace ib {
 
-constexpr int ATTN_WARPS = 4;
-constexpr int ATTN_THREADS = ATTN_WARPS * 32;
 constexpr int ATTN_STEPS = 8;              // row steps per tile kept in registers
-constexpr uint32_t ATTN_MIN_PER_SPLIT = 64;  // positions below which a further split does not pay
-
-struct AttnArgs {
-    ib_attn_params p;
-    const uint32_t *pos_ptr;
-    const float *q;
-    const void *kc, *vc;
-    float *out, *scratch;
-    unsigned int *counters;
-    uint32_t max_splits;
-    uint32_t pdl;
-};
-
-template <typename T> struct KvVec;
-template <> struct KvVec<__half> {
-    static constexpr int EPL = 8;
-    __device__ static __forceinline__ void unpack(const uint4 &r, float (&f)[8]) {
-        const __half2 *h = reinterpret_cast<const __half2 *>(&r);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float2 t = __half22float2(h[i]);
-            f[2 * i] = t.x;
-            f[2 * i + 1] = t.y;
-        }
-    }
-};
-template <> struct KvVec<float> {
-    static constexpr int EPL = 4;
-    __device__ static __forceinline__ void unpack(const uint4 &r, float (&f)[4]) {
-        f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
-    }
-};
-
-__device__ __forceinline__ float merge_weight(float m, float mx) { return (m == -INFINITY) ? 0.f : expf(m - mx); }
 
 template <int HS, int KVM, typename T>
 __global__ void __launch_bounds__(ATTN_THREADS) attn_kernel(const AttnArgs a) {
-    constexpr int EPL = KvVec<T>::EPL;   // elements per 16-byte lane load
-    constexpr int LPR = HS / EPL;        // lanes covering one cache row of this kv head
-    constexpr int RPW = 32 / LPR;        // rows per warp step
-    constexpr int TILE = ATTN_STEPS * RPW;
-    static_assert(LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "head size / element type combination unsupported");
-
-    __shared__ float sm_acc[ATTN_WARPS][KVM][HS];
-    __shared__ float sm_m[ATTN_WARPS][KVM], sm_l[ATTN_WARPS][KVM];
-    __shared__ bool is_last;
-
+    __shared__ float sm[attn_block_smem_floats(HS, KVM)];
     if (a.pdl) {
         asm volatile("griddepcontrol.launch_dependents;");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t pos = a.pos_ptr ? *a.pos_ptr : a.p.pos;
-    const uint32_t total = pos + 1;
-    uint32_t nsplit = (total + ATTN_MIN_PER_SPLIT - 1) / ATTN_MIN_PER_SPLIT;
-    if (nsplit > a.max_splits) nsplit = a.max_splits;
-    const uint32_t per = (total + nsplit - 1) / nsplit;
-    nsplit = (total + per - 1) / per;  // every remaining split is non-empty
+    uint32_t nsplit, per;
+    attn_split_plan(pos + 1, a.max_splits, nsplit, per);
     if (split >= nsplit) return;
-    const uint32_t t0 = split * per, t1 = min(total, t0 + per);
-
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane / LPR, li = lane % LPR;
-    const uint32_t kv_dim = a.p.kv_dim;
-    const T *kc = reinterpret_cast<const T *>(a.kc) + (size_t)kvh * HS + li * EPL;
-    const T *vc = reinterpret_cast<const T *>(a.vc) + (size_t)kvh * HS + li * EPL;
-    const float scale = 1.0f / sqrtf((float)HS);
-
-    float qr[KVM][EPL];
-#pragma unroll
-    for (int m = 0; m < KVM; m++)
-#pragma unroll
-        for (int e = 0; e < EPL; e++) qr[m][e] = __ldcg(a.q + (size_t)(kvh * KVM + m) * HS + li * EPL + e);
-
-    float M[KVM], l[KVM], acc[KVM][EPL];
-#pragma unroll
-    for (int m = 0; m < KVM; m++) {
-        M[m] = -INFINITY;
-        l[m] = 0.f;
-#pragma unroll
-        for (int e = 0; e < EPL; e++) acc[m][e] = 0.f;
-    }
-
-    for (uint32_t base = t0 + warp * TILE; base < t1; base += ATTN_WARPS * TILE) {
-        uint4 kraw[ATTN_STEPS], vraw[ATTN_STEPS];
-#pragma unroll
-        for (int s = 0; s < ATTN_STEPS; s++) {
-            const uint32_t t = base + s * RPW + g;
-            const uint32_t tc = t < t1 ? t : t1 - 1;
-            kraw[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
-            vraw[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
-        }
-        float sc[ATTN_STEPS][KVM];
-#pragma unroll
-        for (int s = 0; s < ATTN_STEPS; s++) {
-            float kf[EPL];
-            KvVec<T>::unpack(kraw[s], kf);
-            const bool valid = (base + s * RPW + g) < t1;
-#pragma unroll
-            for (int m = 0; m < KVM; m++) {
-                float d = 0.f;
-#pragma unroll
-                for (int e = 0; e < EPL; e++) d = fmaf(qr[m][e], kf[e], d);
-#pragma unroll
-                for (int o = LPR / 2; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                sc[s][m] = valid ? d * scale : -INFINITY;
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < KVM; m++) {
-            float mx = sc[0][m];
-#pragma unroll
-            for (int s = 1; s < ATTN_STEPS; s++) mx = fmaxf(mx, sc[s][m]);
-#pragma unroll
-            for (int o = LPR; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float mn = fmaxf(M[m], mx);  // finite: the tile holds at least one valid position
-            const float alpha = expf(M[m] - mn);
-            M[m] = mn;
-            l[m] *= alpha;
-#pragma unroll
-            for (int e = 0; e < EPL; e++) acc[m][e] *= alpha;
-#pragma unroll
-            for (int s = 0; s < ATTN_STEPS; s++) {
-                const float pe = expf(sc[s][m] - mn);
-                sc[s][m] = pe;
-                l[m] += pe;
-            }
-        }
-#pragma unroll
-        for (int s = 0; s < ATTN_STEPS; s++) {
-            float vf[EPL];
-            KvVec<T>::unpack(vraw[s], vf);
-#pragma unroll
-            for (int m = 0; m < KVM; m++)
-#pragma unroll
-                for (int e = 0; e < EPL; e++) acc[m][e] = fmaf(sc[s][m], vf[e], acc[m][e]);
-        }
-    }
-
-    // fold the row groups of the warp, then the warps of the CTA
-#pragma unroll
-    for (int m = 0; m < KVM; m++) {
-#pragma unroll
-        for (int o = LPR; o < 32; o <<= 1) {
-            l[m] += __shfl_xor_sync(0xffffffffu, l[m], o);
-#pragma unroll
-            for (int e = 0; e < EPL; e++) acc[m][e] += __shfl_xor_sync(0xffffffffu, acc[m][e], o);
-        }
-        if (g == 0) {
-#pragma unroll
-            for (int e = 0; e < EPL; e++) sm_acc[warp][m][li * EPL + e] = acc[m][e];
-            if (li == 0) { sm_m[warp][m] = M[m]; sm_l[warp][m] = l[m]; }
-        }
-    }
-    __syncthreads();
-
-    const uint32_t slot = HS + 2;
-    float *part = a.scratch + ((size_t)kvh * a.max_splits + split) * KVM * slot;
-    for (int idx = threadIdx.x; idx < KVM * HS; idx += ATTN_THREADS) {
-        const int m = idx / HS, d = idx % HS;
-        float mx = sm_m[0][m];
-#pragma unroll
-        for (int w = 1; w < ATTN_WARPS; w++) mx = fmaxf(mx, sm_m[w][m]);
-        float o = 0.f, ls = 0.f;
-#pragma unroll
-        for (int w = 0; w < ATTN_WARPS; w++) {
-            const float wt = merge_weight(sm_m[w][m], mx);
-            o += wt * sm_acc[w][m][d];
-            ls += wt * sm_l[w][m];
-        }
-        if (nsplit == 1) {
-            a.out[(size_t)(kvh * KVM + m) * HS + d] = o / ls;
-        } else {
-            part[m * slot + d] = o;
-            if (d == 0) { part[m * slot + HS] = mx; part[m * slot + HS + 1] = ls; }
-        }
-    }
-    if (nsplit == 1) return;
-
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = (atomicAdd(a.counters + kvh, 1u) == nsplit - 1);
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    const float *parts = a.scratch + (size_t)kvh * a.max_splits * KVM * slot;
-    for (int idx = threadIdx.x; idx < KVM * HS; idx += ATTN_THREADS) {
-        const int m = idx / HS, d = idx % HS;
-        float mx = -INFINITY;
-        for (uint32_t s = 0; s < nsplit; s++) mx = fmaxf(mx, __ldcg(parts + ((size_t)s * KVM + m) * slot + HS));
-        float o = 0.f, ls = 0.f;
-        for (uint32_t s = 0; s < nsplit; s++) {
-            const float *ps = parts + ((size_t)s * KVM + m) * slot;
-            const float wt = merge_weight(__ldcg(ps + HS), mx);
-            o += wt * __ldcg(ps + d);
-            ls += wt * __ldcg(ps + HS + 1);
-        }
-        a.out[(size_t)(kvh * KVM + m) * HS + d] = o / ls;
-    }
-    if (threadIdx.x == 0) a.counters[kvh] = 0u;
+    attn_block<HS, KVM, T, ATTN_STEPS>(a, kvh, split, nsplit, per, pos + 1, (int)threadIdx.x, 1, sm);
 }
 
 size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits) {

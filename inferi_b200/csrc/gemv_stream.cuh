@@ -1,0 +1,406 @@
+// Device-side building blocks of the streaming quantized GEMV (shared by the stand-alone GEMV kernel and the
+// whole-token kernel): mbarrier / bulk-copy wrappers with bounded waits, the byte-balanced row split, the per-format
+// 64-weight unit dot products and the row-pair epilogues.
+#pragma once
+
+#include "gemv_common.cuh"
+
+namespace ib {
+
+
+constexpr int CW = 16;                          // consumer warps
+constexpr int STREAM_THREADS = (CW + 1) * 32;   // + 1 producer warp
+constexpr int PT_MAX = 16;                      // row pairs per tile
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait on an mbarrier or on a peer gives up after 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(2000u)   // suspend-time hint in ns: a waiting warp sleeps instead of spinning through issue slots
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and raises *err) if the phase never completes.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
+    if (err) {
+        *(volatile uint32_t *)err = code;   // mapped host memory: a plain store, made visible system-wide
+        __threadfence_system();
+    }
+    return false;
+}
+// ---- cross-GPU arrival counters (tensor parallel).  Counters only grow; a rank waits until its own counter has
+// reached the value that the current use implies.  The wait is bounded like every other wait here. ----
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_counter(const uint32_t *flag, uint32_t target, uint32_t *err, uint32_t code) {
+    if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
+    if (err) {
+        *(volatile uint32_t *)err = code;
+        __threadfence_system();
+    }
+    return false;
+}
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// ---- this CTA's share of the work: per segment a contiguous range of row pairs, balanced by bytes ----
+// (three scalar sets instead of arrays: indexing them with a run-time segment number would put them in local memory)
+struct Share {
+    uint32_t a0, a1, a2, b0, b1, b2;   // pair range per segment
+    uint32_t c0, c1, c2;               // bytes per pair
+    uint32_t t0, t1, t2;               // pairs per tile
+    uint32_t nseg;
+    __device__ __forceinline__ uint32_t a(uint32_t s) const { return s == 0 ? a0 : (s == 1 ? a1 : a2); }
+    __device__ __forceinline__ uint32_t b(uint32_t s) const { return s == 0 ? b0 : (s == 1 ? b1 : b2); }
+    __device__ __forceinline__ uint32_t cost(uint32_t s) const { return s == 0 ? c0 : (s == 1 ? c1 : c2); }
+    __device__ __forceinline__ uint32_t pt(uint32_t s) const { return s == 0 ? t0 : (s == 1 ? t1 : t2); }
+};
+
+// all byte counts in units of 16 bytes so that the arithmetic stays in 32 bits (64-bit divisions cost ~0.2 us each)
+__device__ __forceinline__ void share_range(uint32_t lo, uint32_t hi, uint32_t start, uint32_t cost16, uint32_t pairs, uint32_t &a, uint32_t &b) {
+    const uint32_t x = lo > start ? (lo - start + cost16 - 1) / cost16 : 0;
+    const uint32_t y = hi > start ? (hi - start + cost16 - 1) / cost16 : 0;
+    a = x > pairs ? pairs : x;
+    b = y > pairs ? pairs : y;
+}
+
+__device__ __forceinline__ uint32_t tile_pairs(uint32_t stage_bytes, uint32_t cost, uint32_t RG) {
+    uint32_t pt = stage_bytes / cost;
+    pt = pt < 1 ? 1 : (pt > PT_MAX ? PT_MAX : pt);
+    if (pt > RG) pt = pt / RG * RG;   // whole rounds of the row groups
+    return pt;
+}
+
+// `swiglu`: gate and up rows travel together (one "pair" = gate row r + up row r).  `sources`/`me`: the CTAs sharing the
+// work and this CTA's index among them.
+__device__ __forceinline__ void make_share_rt(bool swiglu, uint32_t nseg, uint32_t rows0, uint32_t rows1, uint32_t rows2, uint32_t rb0, uint32_t rb1,
+                                              uint32_t rb2, uint32_t stage_bytes, uint32_t RG, uint32_t G, uint32_t me, Share &sh) {
+    uint32_t n0, n1 = 0, n2 = 0;
+    sh.nseg = swiglu ? 1u : nseg;
+    sh.c1 = sh.c2 = 16;
+    if (swiglu) { n0 = rows0; sh.c0 = rb0 + rb1; }
+    else {
+        n0 = rows0 / 2; sh.c0 = 2 * rb0;
+        if (sh.nseg > 1) { n1 = rows1 / 2; sh.c1 = 2 * rb1; }
+        if (sh.nseg > 2) { n2 = rows2 / 2; sh.c2 = 2 * rb2; }
+    }
+    const uint32_t k0 = sh.c0 / 16, k1 = sh.c1 / 16, k2 = sh.c2 / 16;
+    const uint32_t s1 = n0 * k0, s2 = s1 + n1 * k1, total = s2 + n2 * k2;
+    const uint32_t q = total / G, r = total % G;
+    const uint32_t lo = q * me + r * me / G, hi = q * (me + 1) + r * (me + 1) / G;
+    share_range(lo, hi, 0, k0, n0, sh.a0, sh.b0);
+    share_range(lo, hi, s1, k1, n1, sh.a1, sh.b1);
+    share_range(lo, hi, s2, k2, n2, sh.a2, sh.b2);
+    sh.t0 = tile_pairs(stage_bytes, sh.c0, RG);
+    sh.t1 = tile_pairs(stage_bytes, sh.c1, RG);
+    sh.t2 = tile_pairs(stage_bytes, sh.c2, RG);
+}
+
+template <uint32_t EPI>
+__device__ __forceinline__ void make_share(const GemvParams &p, uint32_t stage_bytes, uint32_t RG, Share &sh) {
+    make_share_rt(EPI == EPI_SWIGLU, p.nseg, p.seg[0].rows, p.seg[1].rows, p.seg[2].rows, (uint32_t)p.seg[0].row_bytes, (uint32_t)p.seg[1].row_bytes,
+                  (uint32_t)p.seg[2].row_bytes, stage_bytes, RG, gridDim.x, blockIdx.x, sh);
+}
+
+struct TileCursor {
+    uint32_t seg, next, end, pt;   // segment, first pair of the next tile, end of the segment's range, pairs per tile
+    __device__ __forceinline__ void enter(const Share &sh) {
+        while (seg < sh.nseg) {
+            next = sh.a(seg); end = sh.b(seg); pt = sh.pt(seg);
+            if (next < end) break;
+            seg++;
+        }
+    }
+    __device__ __forceinline__ void init(const Share &sh) { seg = 0; next = end = pt = 0; enter(sh); }
+    __device__ __forceinline__ bool valid(const Share &sh) const { return seg < sh.nseg; }
+    __device__ __forceinline__ uint32_t count(const Share &) const { return (end - next) < pt ? (end - next) : pt; }
+    __device__ __forceinline__ void advance(const Share &sh) {
+        next += count(sh);
+        if (next >= end) { seg++; enter(sh); }
+    }
+};
+
+// ---- per-lane activation registers of one 64-weight unit ----
+struct UnitAct {
+    uint4 l[3][4];   // 3 limbs x 4 groups of 16 columns
+    float s[4];      // per-group scale (already divided where the format needs it)
+    float x[4];      // per-group sum of x
+};
+
+// Unit u of a row, by format:
+//   Q4_K / Q5_K: block u>>2, 64-column chunk c = u&3: columns 256b + 64c .. +63; groups 0,1 = low nibbles, 2,3 = high nibbles
+//   Q6_K       : block u>>2, half i = (u>>1)&1, 16-byte half h = u&1: groups g = 0..3 at 256b + 128i + 32g + 16h
+//   Q8_0       : blocks 2u, 2u+1: columns 64u .. +63
+__device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const Act &A, UnitAct &ua) {
+    const float *SC = A.sc(), *SX = A.sx16();
+    uint32_t e16[4];
+    if (qtype == IB_Q6_K) {
+        const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1, base = 16 * b + 8 * i + h;
+#pragma unroll
+        for (int g = 0; g < 4; g++) e16[g] = base + 2 * g;
+    } else {
+#pragma unroll
+        for (int g = 0; g < 4; g++) e16[g] = 4 * u + g;
+    }
+    // asm volatile loads: they must stay where they are.  As ordinary loads they are loop-invariant and the compiler
+    // hoists the copies of every format's consumer loop to one place, where they all stay live at once.
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const uint32_t addr = smem_u32(A.limb(k) + e16[g]);
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(ua.l[k][g].x), "=r"(ua.l[k][g].y), "=r"(ua.l[k][g].z), "=r"(ua.l[k][g].w)
+                         : "r"(addr)
+                         : "memory");
+        }
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.s[g]) : "r"(smem_u32(SC + (e16[g] >> 1))) : "memory");
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.x[g]) : "r"(smem_u32(SX + e16[g])) : "memory");
+    }
+    if (qtype == IB_Q4_K) { ua.s[2] *= (1.0f / 16.0f); ua.s[3] *= (1.0f / 16.0f); }  // high nibbles are used in place (16 q)
+}
+
+__device__ __forceinline__ int dot4_ss(const uint4 &q, const uint4 &a, int d) {
+    d = dp4a_ss(q.x, a.x, d); d = dp4a_ss(q.y, a.y, d); d = dp4a_ss(q.z, a.z, d); return dp4a_ss(q.w, a.w, d);
+}
+__device__ __forceinline__ int dot4_us(const uint4 &q, const uint4 &a, int d) {
+    d = dp4a_us(q.x, a.x, d); d = dp4a_us(q.y, a.y, d); d = dp4a_us(q.z, a.z, d); return dp4a_us(q.w, a.w, d);
+}
+__device__ __forceinline__ uint4 and4(const uint4 &q, uint32_t m) { return make_uint4(q.x & m, q.y & m, q.z & m, q.w & m); }
+
+// One row (in shared memory) x one unit -> the lane's partial dot product.  Everything that depends only on the
+// lane (byte offsets inside a row, shift amounts) is computed once in init().
+struct LaneConst { uint32_t o0, o1, o2, o3, k; };
+template <uint32_t QT> struct Unit;
+
+template <> struct Unit<IB_Q4_K> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) { lc.k = u & 3; lc.o0 = (u >> 2) * 144; lc.o1 = lc.o0 + 16 + 32 * lc.k; }
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_hdr = lc.o0, off_q = lc.o1, c = lc.k;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + off_hdr);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+        const uint4 l0 = and4(q0, 0x0F0F0F0Fu), l1 = and4(q1, 0x0F0F0F0Fu), h0 = and4(q0, 0xF0F0F0F0u), h1 = and4(q1, 0xF0F0F0F0u);
+        int D[4][3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(l0, ua.l[k][0], 0);
+            D[1][k] = dot4_ss(l1, ua.l[k][1], 0);
+            D[2][k] = dot4_us(h0, ua.l[k][2], 0);
+            D[3][k] = dot4_us(h1, ua.l[k][3], 0);
+        }
+        uint32_t sc2, m2;
+        kquant_scales(hdr, c, sc2, m2);
+        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        // groups 0,1 (and 2,3) share the activation scale and the sub-block scale: add them as integers
+        const float lo = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
+        const float hi = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
+        return (dm.x * (float)(sc2 & 0xFFu)) * lo - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi -
+               (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
+    }
+};
+
+template <> struct Unit<IB_Q5_K> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) { lc.k = u & 3; lc.o0 = (u >> 2) * 176; lc.o1 = lc.o0 + 48 + 32 * lc.k; }
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_hdr = lc.o0, off_q = lc.o1, c = lc.k;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + off_hdr);
+        const uint4 hA = *reinterpret_cast<const uint4 *>(row + off_hdr + 16), hB = *reinterpret_cast<const uint4 *>(row + off_hdr + 32);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q), q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hw[8] = {hA.x, hA.y, hA.z, hA.w, hB.x, hB.y, hB.z, hB.w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t t = hw[i] >> (2 * c);  // bit 0 of each byte: flag of the low-nibble element, bit 1: of the high-nibble element
+            lo[i] = (qw[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
+            hi[i] = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
+        }
+        int D[4][3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(make_uint4(lo[0], lo[1], lo[2], lo[3]), ua.l[k][0], 0);
+            D[1][k] = dot4_ss(make_uint4(lo[4], lo[5], lo[6], lo[7]), ua.l[k][1], 0);
+            D[2][k] = dot4_ss(make_uint4(hi[0], hi[1], hi[2], hi[3]), ua.l[k][2], 0);
+            D[3][k] = dot4_ss(make_uint4(hi[4], hi[5], hi[6], hi[7]), ua.l[k][3], 0);
+        }
+        uint32_t sc2, m2;
+        kquant_scales(hdr, c, sc2, m2);
+        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        const float lo_f = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
+        const float hi_f = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
+        return (dm.x * (float)(sc2 & 0xFFu)) * lo_f - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi_f -
+               (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
+    }
+};
+
+// Q6_K rows are stored as groups of 8 blocks: [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d] = 1680 bytes per 2048 columns.
+template <> struct Unit<IB_Q6_K> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) {
+        const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1, grp = (b >> 3) * 1680, bb = b & 7;
+        lc.o0 = grp + 128 * bb + 64 * i + 16 * h;
+        lc.o1 = grp + 1024 + 64 * bb + 32 * i + 16 * h;
+        lc.o2 = grp + 1536 + 16 * bb + 8 * i;
+        lc.o3 = grp + 1664 + 2 * bb;
+        lc.k = 8 * h;
+    }
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_qa = lc.o0, off_qh = lc.o1, off_sc = lc.o2, off_d = lc.o3, sh = lc.k;
+        const uint4 qa = *reinterpret_cast<const uint4 *>(row + off_qa);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(row + off_qa + 32);
+        const uint4 qh = *reinterpret_cast<const uint4 *>(row + off_qh);
+        const uint2 scw = *reinterpret_cast<const uint2 *>(row + off_sc);   // scales[8i .. 8i+7]
+        const float d = h2f(*reinterpret_cast<const unsigned short *>(row + off_d));
+        const uint32_t la[4] = {qa.x, qa.y, qa.z, qa.w}, lb[4] = {qb.x, qb.y, qb.z, qb.w}, hh[4] = {qh.x, qh.y, qh.z, qh.w};
+        uint32_t g0[4], g1[4], g2[4], g3[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            // crates/inferi/src/quantization.rs:237-246: 4 low bits from ql, 2 high bits from qh
+            g0[w] = (la[w] & 0x0F0F0F0Fu) | ((hh[w] << 4) & 0x30303030u);
+            g1[w] = (lb[w] & 0x0F0F0F0Fu) | ((hh[w] << 2) & 0x30303030u);
+            g2[w] = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
+            g3[w] = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
+        }
+        int D[4][3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(make_uint4(g0[0], g0[1], g0[2], g0[3]), ua.l[k][0], 0);
+            D[1][k] = dot4_ss(make_uint4(g1[0], g1[1], g1[2], g1[3]), ua.l[k][1], 0);
+            D[2][k] = dot4_ss(make_uint4(g2[0], g2[1], g2[2], g2[3]), ua.l[k][2], 0);
+            D[3][k] = dot4_ss(make_uint4(g3[0], g3[1], g3[2], g3[3]), ua.l[k][3], 0);
+        }
+        // scale of group g is byte 2g + h of the 8 loaded: bytes {h, 2+h} of word x, {h, 2+h} of word y
+        const uint32_t sx = scw.x >> sh, sy = scw.y >> sh;
+        const float s0 = (float)(int)(int8_t)(sx & 0xFF), s1 = (float)(int)(int8_t)((sx >> 16) & 0xFF);
+        const float s2 = (float)(int)(int8_t)(sy & 0xFF), s3 = (float)(int)(int8_t)((sy >> 16) & 0xFF);
+        float v = s0 * (ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) - 32.0f * ua.x[0]);
+        v += s1 * (ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]) - 32.0f * ua.x[1]);
+        v += s2 * (ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) - 32.0f * ua.x[2]);
+        v += s3 * (ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]) - 32.0f * ua.x[3]);
+        return d * v;
+    }
+};
+
+// Q8_0 rows are stored as groups of 8 blocks: [8 x 32 quants][8 x 2 scale] = 272 bytes per 256 columns.
+template <> struct Unit<IB_Q8_0> {
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) {
+        const uint32_t b0 = 2 * u, grp = (b0 >> 3) * 272, bb = b0 & 7;
+        lc.o0 = grp + 32 * bb;
+        lc.o1 = grp + 256 + 2 * bb;
+    }
+    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+        const uint32_t off_q = lc.o0, off_d = lc.o1;
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q), q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+        const uint4 q2 = *reinterpret_cast<const uint4 *>(row + off_q + 32), q3 = *reinterpret_cast<const uint4 *>(row + off_q + 48);
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(row + off_d));   // scales of the two blocks
+        int D[4][3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            D[0][k] = dot4_ss(q0, ua.l[k][0], 0);
+            D[1][k] = dot4_ss(q1, ua.l[k][1], 0);
+            D[2][k] = dot4_ss(q2, ua.l[k][2], 0);
+            D[3][k] = dot4_ss(q3, ua.l[k][3], 0);
+        }
+        const float a = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
+        const float c = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
+        return dd.x * a + dd.y * c;
+    }
+};
+
+constexpr uint32_t QT_MIXED = 0xFFu;   // kernel instance for launches whose segments differ in format
+
+template <uint32_t QT>
+__device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst &lc) {
+    lc.o0 = lc.o1 = lc.o2 = lc.o3 = lc.k = 0;
+    if (QT != QT_MIXED) { Unit<QT == QT_MIXED ? IB_Q4_K : QT>::init(u, lc); return; }
+    switch (qtype) {
+    case IB_Q4_K: Unit<IB_Q4_K>::init(u, lc); break;
+    case IB_Q6_K: Unit<IB_Q6_K>::init(u, lc); break;
+    case IB_Q5_K: Unit<IB_Q5_K>::init(u, lc); break;
+    default: Unit<IB_Q8_0>::init(u, lc); break;
+    }
+}
+template <uint32_t QT>
+__device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+    if (QT != QT_MIXED) return Unit<QT == QT_MIXED ? IB_Q4_K : QT>::dot(row, lc, ua);
+    switch (qtype) {
+    case IB_Q4_K: return Unit<IB_Q4_K>::dot(row, lc, ua);
+    case IB_Q6_K: return Unit<IB_Q6_K>::dot(row, lc, ua);
+    case IB_Q5_K: return Unit<IB_Q5_K>::dot(row, lc, ua);
+    default: return Unit<IB_Q8_0>::dot(row, lc, ua);
+    }
+}
+
+// ---- epilogue of one row pair ----
+template <uint32_t EPI>
+__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best) {
+    if (EPI == EPI_SWIGLU) {
+        // crates/inferi-shaders/src/silu.rs:16-19,46-52: a = gate row, b = up row
+        p.seg[0].out[pair] = b * (a / (1.0f + expf(-a)));
+        return;
+    }
+    const uint32_t r0 = 2 * pair;
+    if (EPI == EPI_STORE) {
+        *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(a, b);
+    } else if (EPI == EPI_RESIDUAL) {
+        const float2 r = __ldcg(reinterpret_cast<const float2 *>(p.resid + r0));
+        *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(r.x + a, r.y + b);
+    } else if (EPI == EPI_QKV) {
+        if (s < 2) {
+            // crates/inferi-shaders/src/rope.rs:75-91 (adjacent pairs)
+            const float2 cs = __ldcg(p.rope_cs + ((r0 % p.head_size) >> 1));
+            const float x = a, y = b;
+            a = cs.x * x - cs.y * y;
+            b = cs.y * x + cs.x * y;
+        }
+        if (s == 0) {
+            *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
+        } else {
+            void *cache = (s == 1) ? p.k_cache : p.v_cache;
+            const size_t off = (size_t)(*p.pos_ptr) * p.kv_dim + r0;
+            if (p.kv_dtype == IB_KV_F16) reinterpret_cast<__half2 *>(cache)[off >> 1] = __floats2half2_rn(a, b);
+            else reinterpret_cast<float2 *>(cache)[off >> 1] = make_float2(a, b);
+        }
+    } else if (EPI == EPI_PUSH) {
+        // row-split matrix of a tensor-parallel model: this rank's partial goes straight into every rank's memory
+        for (uint32_t rk = 0; rk < p.tp; rk++) *reinterpret_cast<float2 *>(p.push_dst[rk] + r0) = make_float2(a, b);
+    } else if (EPI == EPI_ARGMAX) {
+        if (p.seg[0].out) *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
+        best = max(best, max(argmax_key(a, p.row_offset + r0), argmax_key(b, p.row_offset + r0 + 1)));
+    }
+}
+
+
+}  // namespace ib

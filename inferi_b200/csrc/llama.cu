@@ -14,7 +14,7 @@
 // All of it is captured once into a CUDA graph whose kernels read the token, the position and the step from a
 // device control block, so that generation replays the same graph with no host round trip; kernels are chained
 // with programmatic dependent launch.
-#include "common.cuh"
+#include "token.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -25,64 +25,6 @@
 using namespace ib;
 
 namespace ib {
-
-struct TokenCtl {
-    uint32_t step;      // index into seq of the token being processed
-    uint32_t pos;       // its position in the context
-    uint32_t n_prompt;  // tokens of seq that are given; beyond them the arg-max is fed back
-    uint32_t next;      // greedy token of the last forward
-};
-
-struct QDesc {
-    const uint8_t *w;
-    uint64_t row_bytes;
-    uint32_t qtype, layout, nb;
-};
-
-__device__ __forceinline__ float half_at(const uint8_t *p) {
-    return __half2float(__ushort_as_half((unsigned short)((uint32_t)p[0] | ((uint32_t)p[1] << 8))));
-}
-
-// Value of element `col` of a quantized row under either device layout (block arithmetic of
-// crates/inferi/src/quantization.rs:51-54, 227-256, 287-329, 364-402).
-__device__ float dequant_at(const QDesc &q, const uint8_t *row, uint32_t col) {
-    if (q.qtype == IB_F32) return reinterpret_cast<const float *>(row)[col];
-    if (q.qtype == IB_Q8_0) {
-        const uint32_t b = col >> 5, i = col & 31;
-        if (q.layout == LAYOUT_SOA) {
-            const uint8_t *grp = row + (size_t)(b >> 3) * 272;
-            return (float)(int8_t)grp[32 * (b & 7) + i] * half_at(grp + 256 + 2 * (b & 7));
-        }
-        const uint8_t *blk = row + (size_t)b * 34;
-        return (float)(int8_t)blk[2 + i] * half_at(blk);
-    }
-    const uint32_t b = col >> 8, e = col & 255;
-    if (q.qtype == IB_Q4_K || q.qtype == IB_Q5_K) {
-        const uint8_t *blk = row + (size_t)b * (q.qtype == IB_Q4_K ? 144 : 176);
-        const uint8_t *sc = blk + 4, *qs = blk + (q.qtype == IB_Q4_K ? 16 : 48);
-        const uint32_t c = e >> 6, hi = (e >> 5) & 1, l = e & 31, j = 2 * c + hi;
-        uint32_t s, m;
-        if (j < 4) { s = sc[j] & 63; m = sc[j + 4] & 63; }
-        else { s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4); m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
-        uint32_t qv = hi ? (qs[32 * c + l] >> 4) : (qs[32 * c + l] & 0xF);
-        if (q.qtype == IB_Q5_K && (blk[16 + l] & ((hi ? 2u : 1u) << (2 * c)))) qv += 16;
-        return half_at(blk) * (float)s * (float)qv - half_at(blk + 2) * (float)m;
-    }
-    // Q6_K
-    const uint8_t *ql, *qh, *sc, *dp;
-    if (q.layout == LAYOUT_SOA) {
-        const uint8_t *grp = row + (size_t)(b >> 3) * 1680;
-        const uint32_t bb = b & 7;
-        ql = grp + 128 * bb; qh = grp + 1024 + 64 * bb; sc = grp + 1536 + 16 * bb; dp = grp + 1664 + 2 * bb;
-    } else {
-        const uint8_t *blk = row + (size_t)b * 210;
-        ql = blk; qh = blk + 128; sc = blk + 192; dp = blk + 208;
-    }
-    const uint32_t i = e >> 7, g = (e >> 5) & 3, l = e & 31;
-    const uint32_t lo = ql[64 * i + 32 * (g & 1) + l], h = qh[32 * i + l];
-    const int qv = (int)(((g & 2) ? (lo >> 4) : (lo & 0xF)) | (((h >> (2 * g)) & 3) << 4)) - 32;
-    return half_at(dp) * (float)(int8_t)sc[8 * i + 2 * g + l / 16] * (float)qv;
-}
 
 // begin: x <- dequantized embedding row of the current token (transformer.rs:367-374, chat_llama2.rs:217-220);
 // rope_cs[j] <- (cos, sin)(pos * theta_j) shared by every layer of this token (rope.rs:75-79).
@@ -182,6 +124,12 @@ struct ib_llama {
     cudaGraphExec_t graph_exec = nullptr;
     cudaStream_t own_stream = nullptr;
     uint64_t launches_per_token = 0;
+    // whole-token kernel (single GPU): the phase list on the device, the grid-barrier counter, the launch plan
+    ib::TokenPhase *phases_dev = nullptr;
+    uint32_t *grid_bar = nullptr;
+    ib::TokenProgram prog{};
+    ib::TokenKernelPlan plan{};
+    bool use_token_kernel = false;
 };
 
 namespace ib {
@@ -210,14 +158,41 @@ static void set_pdl(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, uint32_t
     cfg.numAttrs = pdl ? 1 : 0;
 }
 
-static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
+// Issues the kernels of one token into `s`, or - with `collect` - appends them as phases of the whole-token kernel
+// (which does the begin / end book-keeping itself).
+static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vector<TokenPhase> *collect = nullptr) {
     ib_ctx *ctx = m->ctx;
     const ib_llama_config &c = m->cfg;
     const int tp = m->tp_size, rank = m->tp_rank;
     const uint32_t H = c.hidden_size, L = c.num_hidden_layers;
     const CommLayout cl(H, tp);
     int32_t rc;
-    {
+    auto emit_gemv = [&](const GemvParams &p) -> int32_t {
+        if (!collect) return launch_gemv(ctx, s, p);
+        TokenPhase ph;
+        memset(&ph, 0, sizeof ph);
+        ph.ps.kind = PH_GEMV; ph.ps.nseg = p.nseg; ph.ps.epi = p.epi; ph.ps.cols = p.cols; ph.ps.norm_w = p.norm_w;
+        ph.qt = p.seg[0].qtype;
+        for (uint32_t i = 0; i < p.nseg; i++) {
+            ph.ps.w[i] = p.seg[i].w; ph.ps.row_bytes[i] = (uint32_t)p.seg[i].row_bytes; ph.ps.rows[i] = p.seg[i].rows;
+            if (p.seg[i].qtype != ph.qt) ph.qt = 0xFFu;
+        }
+        ph.g = p;
+        ph.g.err = ctx->err_dev;
+        ph.g.pdl = 0;
+        collect->push_back(ph);
+        return IB_OK;
+    };
+    auto emit_attn = [&](const AttnLaunch &a) -> int32_t {
+        if (!collect) return launch_attention(ctx, s, a);
+        TokenPhase ph;
+        memset(&ph, 0, sizeof ph);
+        ph.ps.kind = PH_ATTN;
+        ph.a = AttnArgs{a.p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, 0};
+        collect->push_back(ph);
+        return IB_OK;
+    };
+    if (!collect) {
         QDesc e{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((H + 255) / 256);
@@ -264,31 +239,31 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         p.pos_ptr = &m->ctl->pos; p.rope_cs = m->rope_cs; p.head_size = m->head_size; p.kv_dim = m->kv_dim_l; p.kv_dtype = (uint32_t)m->kv_dtype;
         p.k_cache = m->k_cache[l]; p.v_cache = m->v_cache[l]; p.pdl = pdl;
         if (l > 0) add_reduce(p, 1, l);   // the down partials of layer l-1: use number l of this token
-        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        if ((rc = emit_gemv(p))) return rc;
         // attention (transformer.rs:448)
         AttnLaunch a = {};
         a.p = ap; a.pos_ptr = &m->ctl->pos; a.q = m->q; a.k_cache = m->k_cache[l]; a.v_cache = m->v_cache[l]; a.kv_dtype = m->kv_dtype;
         a.out = m->xb; a.scratch = m->attn_scratch; a.counters = m->attn_counters; a.max_splits = m->attn_splits; a.pdl = pdl;
-        if ((rc = launch_attention(ctx, s, a))) return rc;
+        if ((rc = emit_attn(a))) return rc;
         // o_proj + residual (transformer.rs:450-453)
         p = GemvParams{};
         fill_seg(p.seg[0], w.attn_output, cur);
         p.nseg = 1; p.cols = m->q_dim_l; p.epi = EPI_RESIDUAL; p.x = m->xb; p.resid = cur; p.pdl = pdl;
         if (tp > 1) add_push(p, 0);
-        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        if ((rc = emit_gemv(p))) return rc;
         // gate/up + SwiGLU (transformer.rs:454-464)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_gate, m->hb);
         fill_seg(p.seg[1], w.ffn_up, nullptr);
         p.nseg = 2; p.cols = H; p.epi = EPI_SWIGLU; p.x = cur; p.norm_w = w.ffn_norm_dev; p.eps = c.rms_norm_eps; p.pdl = pdl;
         add_reduce(p, 0, l + 1);          // the o_proj partials of this layer
-        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        if ((rc = emit_gemv(p))) return rc;
         // down + residual (transformer.rs:465-468)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_down, cur);
         p.nseg = 1; p.cols = m->ffn_l; p.epi = EPI_RESIDUAL; p.x = m->hb; p.resid = cur; p.pdl = pdl;
         if (tp > 1) add_push(p, 1);
-        if ((rc = launch_gemv(ctx, s, p))) return rc;
+        if ((rc = emit_gemv(p))) return rc;
     }
     // classifier + greedy arg-max (transformer.rs:471-478, models/sampler.rs:54-56)
     GemvParams p = {};
@@ -302,9 +277,9 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
             p.amax_dst[r] = cl.amax(m->comm_peer[r], rank);
             p.amax_flag[r] = cl.flag(m->comm_peer[r], 2);
         }
-    if ((rc = launch_gemv(ctx, s, p))) return rc;
+    if ((rc = emit_gemv(p))) return rc;
     m->x_final = cur;
-    {
+    if (!collect) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(32);
@@ -347,7 +322,7 @@ int32_t ib_llama_destroy(ib_llama *m) {
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
         if (m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch};
+                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch, m->phases_dev, m->grid_bar};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -515,6 +490,34 @@ static int32_t finish_graph(ib_llama *m) {
         if (_e != cudaSuccess) return set_error(IB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));           \
     } while (0)
     CU(cudaDeviceSynchronize());
+    // Single GPU: the whole token as one cooperative kernel, unless INFERI_B200_TOKEN_KERNEL=0 asks for the graph of
+    // separate kernels or the model's shapes do not fit the kernel's shared-memory plan.
+    const char *tk = getenv("INFERI_B200_TOKEN_KERNEL");
+    if (m->tp_size == 1 && !(tk && tk[0] == '0')) {
+        std::vector<TokenPhase> phases;
+        rc = record_token(m, nullptr, 0, &phases);
+        if (rc == IB_OK) rc = plan_token_kernel(ctx, phases.data(), (uint32_t)phases.size(), m->head_size, m->cfg.num_attention_heads / m->cfg.num_key_value_heads, m->plan);
+        if (rc == IB_OK) {
+            CU(cudaMalloc(&m->phases_dev, sizeof(TokenPhase) * phases.size()));
+            CU(cudaMemcpy(m->phases_dev, phases.data(), sizeof(TokenPhase) * phases.size(), cudaMemcpyHostToDevice));
+            CU(cudaMalloc(&m->grid_bar, sizeof(uint32_t)));
+            CU(cudaMemset(m->grid_bar, 0, sizeof(uint32_t)));
+            TokenProgram &P = m->prog;
+            P.phases = m->phases_dev; P.n_phases = (uint32_t)phases.size();
+            P.ctl = m->ctl; P.seq = m->seq; P.seq_cap = m->seq_cap;
+            P.embd = QDesc{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
+            P.hidden = m->cfg.hidden_size; P.vocab = m->cfg.vocab_size; P.half_head = m->head_size / 2;
+            P.x = m->x; P.theta = m->theta; P.rope_cs = m->rope_cs;
+            P.grid_bar = m->grid_bar; P.epoch = m->epoch; P.barriers_per_token = (uint32_t)phases.size() + 1;
+            P.argmax_slots = m->argmax_slots; P.err = ctx->err_dev;
+            P.head_size = m->head_size; P.kv_mul = m->cfg.num_attention_heads / m->cfg.num_key_value_heads; P.kv_dtype = (uint32_t)m->kv_dtype;
+            P.geo = m->plan.geo;
+            m->use_token_kernel = true;
+            m->launches_per_token = 1;
+            return IB_OK;
+        }
+        if (rc != IB_ERR_UNSUPPORTED) return rc;   // shapes outside the kernel's plan: the graph of separate kernels serves them
+    }
     const uint64_t before = ctx->launches;
     CU(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
     // INFERI_B200_NO_PDL=1 records the graph with plain kernel-to-kernel dependencies (for comparisons)
@@ -571,7 +574,7 @@ int32_t ib_llama_tp_connect(ib_llama *m, const void *handles) {
 }
 
 static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, uint32_t n_prompt, uint32_t start_pos, uint32_t n_steps) {
-    if (!m->graph_exec) return set_error(IB_ERR_COMM, "the tensor-parallel model is not connected yet: call ib_llama_tp_connect on every rank first");
+    if (!m->graph_exec && !m->use_token_kernel) return set_error(IB_ERR_COMM, "the tensor-parallel model is not connected yet: call ib_llama_tp_connect on every rank first");
     // control block + given tokens in one pinned staging buffer -> two small async copies
     uint32_t *h = m->h_pinned;
     IB_CHECK_CUDA(cudaEventSynchronize(m->staged));  // an earlier call's copies out of the staging buffer are done
@@ -580,6 +583,13 @@ static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, u
     IB_CHECK_CUDA(cudaMemcpyAsync(m->ctl, h, sizeof(TokenCtl), cudaMemcpyHostToDevice, s));
     IB_CHECK_CUDA(cudaMemcpyAsync(m->seq, h + 4, sizeof(uint32_t) * n_prompt, cudaMemcpyHostToDevice, s));
     IB_CHECK_CUDA(cudaEventRecord(m->staged, s));
+    if (m->use_token_kernel) {
+        for (uint32_t i = 0; i < n_steps; i++) {
+            int32_t rc = launch_token_kernel(m->ctx, s, m->prog, m->plan);
+            if (rc) return rc;
+        }
+        return IB_OK;
+    }
     for (uint32_t i = 0; i < n_steps; i++) {
         IB_CHECK_CUDA(cudaGraphLaunch(m->graph_exec, s));
         m->ctx->launches += m->launches_per_token;

@@ -67,6 +67,32 @@ def test_tiny_model_all_quant_types(backend, kv_f16):
     check_loop(backend, TINY, w, kv_f16, prompt=[3, 500, 41, 7], n_gen=24)
 
 
+def test_token_kernel_and_kernel_graph_give_the_same_tokens(backend, monkeypatch):
+    """The default path is one cooperative kernel per token; INFERI_B200_TOKEN_KERNEL=0 selects the graph of separate kernels
+    (5 per layer + 2).  Both must reproduce the oracle's greedy tokens, and the launch counter tells them apart."""
+    w = synth_weights(SMALL, seed=3005, device="cuda")
+    prompt, n_gen = [5, 77, 1001], 10
+    steps = len(prompt) + n_gen - 1
+    outs = {}
+    for mode, per_token in (("1", 1), ("0", 5 * SMALL.num_hidden_layers + 2)):
+        monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", mode)
+        model = Llama2(backend, SMALL, Llama2Weights(backend, SMALL, w), kv_f16=True)
+        backend.reset_launch_count()
+        outs[mode] = model.generate(prompt, n_gen).tolist()
+        assert backend.launch_count() == steps * per_token
+        model.close()
+    assert outs["0"] == outs["1"]
+    ref = oracle.Llama(oracle_cfg(SMALL), weights_to_host(w), kv_f16=True)
+    want, tok = [], None
+    for pos in range(steps):
+        tok = prompt[pos] if pos < len(prompt) else want[-1]
+        lg = ref.forward(tok, pos)
+        if pos >= len(prompt) - 1:
+            want.append(oracle.argmax(lg))
+    ref.close()
+    assert outs["1"] == want
+
+
 def test_small_model_tied_classifier(backend):
     w = synth_weights(SMALL, seed=3003, device="cuda", recipe=SMALL_TIED, tied=True)
     assert w["output"] is None
