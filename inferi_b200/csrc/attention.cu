@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_kernel(const AttnArgs a) {
     uint32_t nsplit, per;
     attn_split_plan(pos + 1, a.max_splits, nsplit, per);
     if (split >= nsplit) return;
-    attn_block<HS, KVM, T, ATTN_STEPS>(a, kvh, split, nsplit, per, pos + 1, (int)threadIdx.x, 1, sm);
+    attn_block<HS, KVM, T, ATTN_STEPS>(a, a.kc, a.vc, kvh, split, nsplit, per, pos + 1, (int)threadIdx.x, 1, sm);
 }
 
 size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits) {

@@ -56,20 +56,23 @@ __device__ __forceinline__ void attn_bar(int id) { asm volatile("bar.sync %0, %1
 __host__ __device__ constexpr uint32_t attn_block_smem_floats(uint32_t hs, uint32_t kvm) { return ATTN_WARPS * kvm * hs + 2 * ATTN_WARPS * kvm + 4; }
 
 // The split of `total` positions: number of non-empty slices and positions per slice.
-__device__ __forceinline__ void attn_split_plan(uint32_t total, uint32_t max_splits, uint32_t &nsplit, uint32_t &per) {
-    nsplit = (total + ATTN_MIN_PER_SPLIT - 1) / ATTN_MIN_PER_SPLIT;
+__device__ __forceinline__ void attn_split_plan(uint32_t total, uint32_t max_splits, uint32_t &nsplit, uint32_t &per,
+                                                uint32_t min_per_split = ATTN_MIN_PER_SPLIT) {
+    nsplit = (total + min_per_split - 1) / min_per_split;
     if (nsplit > max_splits) nsplit = max_splits;
     per = (total + nsplit - 1) / nsplit;
     nsplit = (total + per - 1) / per;  // every remaining split is non-empty
 }
 
+// QS = the group's query vectors are staged in shared memory (KVM * HS more floats after the block's other arrays) and
+// read per use instead of being held in registers: for callers that are short of registers.
 // One block (ATTN_THREADS threads, `tid` = 0..127, synchronised on named barrier `bar`) computes slice `split` of kv head
 // `kvh` for all KVM query heads of the group; K and V rows are read once for the group.  With more than one slice every
 // block leaves an un-normalised partial (max, sum, accumulator) and the last block of the kv head to arrive merges them:
 // no block ever waits for another.  STEPS = cache-row steps per tile kept in registers.
-template <int HS, int KVM, typename T, int STEPS>
-__device__ __forceinline__ void attn_block(const AttnArgs &a, uint32_t kvh, uint32_t split, uint32_t nsplit, uint32_t per, uint32_t total, int tid,
-                                           int bar, float *sm) {
+template <int HS, int KVM, typename T, int STEPS, bool QS = false>
+__device__ __forceinline__ void attn_block(const AttnArgs &a, const void *k_cache, const void *v_cache, uint32_t kvh, uint32_t split, uint32_t nsplit,
+                                           uint32_t per, uint32_t total, int tid, int bar, float *sm) {
     constexpr int EPL = KvVec<T>::EPL;   // elements per 16-byte lane load
     constexpr int LPR = HS / EPL;        // lanes covering one cache row of this kv head
     constexpr int RPW = 32 / LPR;        // rows per warp step
@@ -85,15 +88,21 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, uint32_t kvh, uint
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane / LPR, li = lane % LPR;
     const uint32_t kv_dim = a.p.kv_dim;
-    const T *kc = reinterpret_cast<const T *>(a.kc) + (size_t)kvh * HS + li * EPL;
-    const T *vc = reinterpret_cast<const T *>(a.vc) + (size_t)kvh * HS + li * EPL;
+    const T *kc = reinterpret_cast<const T *>(k_cache) + (size_t)kvh * HS + li * EPL;
+    const T *vc = reinterpret_cast<const T *>(v_cache) + (size_t)kvh * HS + li * EPL;
     const float scale = 1.0f / sqrtf((float)HS);
 
-    float qr[KVM][EPL];
+    float qr[QS ? 1 : KVM][QS ? 1 : EPL];
+    float *sm_q = reinterpret_cast<float *>(sm_last + 4);   // [KVM][HS], only with QS
+    if (QS) {
+        for (int i = tid; i < KVM * HS; i += ATTN_THREADS) sm_q[i] = __ldcg(a.q + (size_t)kvh * KVM * HS + i);
+        attn_bar(bar);
+    } else {
 #pragma unroll
-    for (int m = 0; m < KVM; m++)
+        for (int m = 0; m < KVM; m++)
 #pragma unroll
-        for (int e = 0; e < EPL; e++) qr[m][e] = __ldcg(a.q + (size_t)(kvh * KVM + m) * HS + li * EPL + e);
+            for (int e = 0; e < EPL; e++) qr[QS ? 0 : m][QS ? 0 : e] = __ldcg(a.q + (size_t)(kvh * KVM + m) * HS + li * EPL + e);
+    }
 
     float M[KVM], l[KVM], acc[KVM][EPL];
 #pragma unroll
@@ -123,7 +132,7 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, uint32_t kvh, uint
             for (int m = 0; m < KVM; m++) {
                 float d = 0.f;
 #pragma unroll
-                for (int e = 0; e < EPL; e++) d = fmaf(qr[m][e], kf[e], d);
+                for (int e = 0; e < EPL; e++) d = fmaf(QS ? sm_q[m * HS + li * EPL + e] : qr[QS ? 0 : m][QS ? 0 : e], kf[e], d);
 #pragma unroll
                 for (int o = LPR / 2; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
                 sc[s][m] = valid ? d * scale : -INFINITY;
@@ -206,17 +215,26 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, uint32_t kvh, uint
     attn_bar(bar);
     if (*sm_last == 0u) return;
     __threadfence();
+    // merge of the kv head's partials.  Maxima and sums of all slices first go to shared memory (the block's accumulator
+    // area is free by now), so that the weighted sum over slices is a loop of independent loads.
     const float *parts = a.scratch + (size_t)kvh * a.max_splits * KVM * slot;
+    float *pm = sm_acc, *pl = sm_acc + nsplit * KVM;   // [nsplit][KVM] each; fits: nsplit <= 256 <= 2 * HS
+    for (uint32_t i = tid; i < nsplit * KVM; i += ATTN_THREADS) {
+        const float *ps = parts + (size_t)i * slot;    // slice i / KVM, head i % KVM
+        pm[i] = __ldcg(ps + HS);
+        pl[i] = __ldcg(ps + HS + 1);
+    }
+    attn_bar(bar);
     for (int idx = tid; idx < KVM * HS; idx += ATTN_THREADS) {
         const int m = idx / HS, d = idx % HS;
         float mx = -INFINITY;
-        for (uint32_t s = 0; s < nsplit; s++) mx = fmaxf(mx, __ldcg(parts + ((size_t)s * KVM + m) * slot + HS));
+        for (uint32_t s = 0; s < nsplit; s++) mx = fmaxf(mx, pm[s * KVM + m]);
         float o = 0.f, ls = 0.f;
+#pragma unroll 8
         for (uint32_t s = 0; s < nsplit; s++) {
-            const float *ps = parts + ((size_t)s * KVM + m) * slot;
-            const float wt = merge_weight(__ldcg(ps + HS), mx);
-            o += wt * __ldcg(ps + d);
-            ls += wt * __ldcg(ps + HS + 1);
+            const float wt = merge_weight(pm[s * KVM + m], mx);
+            o += wt * __ldcg(parts + ((size_t)s * KVM + m) * slot + d);
+            ls += wt * pl[s * KVM + m];
         }
         a.out[(size_t)(kvh * KVM + m) * HS + d] = o / ls;
     }

@@ -95,7 +95,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                 vb += __shfl_xor_sync(0xffffffffu, vb, o);
             }
             if (CG == 1) {
-                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
+                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p});
             } else if (lane == 0) {
                 pt[(pr * 2 + 0) * CW + c.cg] = va;
                 pt[(pr * 2 + 1) * CW + c.cg] = vb;
@@ -118,7 +118,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                         va += pt[(pr * 2 + 0) * CW + g];
                         vb += pt[(pr * 2 + 1) * CW + g];
                     }
-                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best);
+                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p});
                 }
                 __syncwarp();
                 if (lane == 0) c.cnt[st * CW + c.rg] = 0;

@@ -363,9 +363,17 @@ __device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, co
     }
 }
 
+// Where EPI_QKV appends the k / v rows: taken from the launch parameters ...
+struct ParamCaches {
+    const GemvParams &p;
+    __device__ __forceinline__ void *k() const { return p.k_cache; }
+    __device__ __forceinline__ void *v() const { return p.v_cache; }
+};
+
 // ---- epilogue of one row pair ----
-template <uint32_t EPI>
-__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best) {
+// `caches`: where the k / v rows of EPI_QKV go; any type with k() and v() (the launch parameters, or a layer-table entry).
+template <uint32_t EPI, typename Caches>
+__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best, const Caches &caches) {
     if (EPI == EPI_SWIGLU) {
         // crates/inferi-shaders/src/silu.rs:16-19,46-52: a = gate row, b = up row
         p.seg[0].out[pair] = b * (a / (1.0f + expf(-a)));
@@ -388,7 +396,7 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
         if (s == 0) {
             *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
         } else {
-            void *cache = (s == 1) ? p.k_cache : p.v_cache;
+            void *cache = (s == 1) ? caches.k() : caches.v();
             const size_t off = (size_t)(*p.pos_ptr) * p.kv_dim + r0;
             if (p.kv_dtype == IB_KV_F16) reinterpret_cast<__half2 *>(cache)[off >> 1] = __floats2half2_rn(a, b);
             else reinterpret_cast<float2 *>(cache)[off >> 1] = make_float2(a, b);

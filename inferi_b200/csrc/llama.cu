@@ -125,7 +125,7 @@ struct ib_llama {
     cudaStream_t own_stream = nullptr;
     uint64_t launches_per_token = 0;
     // whole-token kernel (single GPU): the phase list on the device, the grid-barrier counter, the launch plan
-    ib::TokenPhase *phases_dev = nullptr;
+    ib::PhaseDesc *phases_dev = nullptr;
     uint32_t *grid_bar = nullptr;
     ib::TokenProgram prog{};
     ib::TokenKernelPlan plan{};
@@ -160,7 +160,13 @@ static void set_pdl(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, uint32_t
 
 // Issues the kernels of one token into `s`, or - with `collect` - appends them as phases of the whole-token kernel
 // (which does the begin / end book-keeping itself).
-static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vector<TokenPhase> *collect = nullptr) {
+struct HostPhase {
+    bool attn;
+    GemvParams g;
+    AttnLaunch a;
+};
+
+static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vector<HostPhase> *collect = nullptr) {
     ib_ctx *ctx = m->ctx;
     const ib_llama_config &c = m->cfg;
     const int tp = m->tp_size, rank = m->tp_rank;
@@ -169,14 +175,8 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
     int32_t rc;
     auto emit_gemv = [&](const GemvParams &p) -> int32_t {
         if (!collect) return launch_gemv(ctx, s, p);
-        TokenPhase ph;
+        HostPhase ph;
         memset(&ph, 0, sizeof ph);
-        ph.ps.kind = PH_GEMV; ph.ps.nseg = p.nseg; ph.ps.epi = p.epi; ph.ps.cols = p.cols; ph.ps.norm_w = p.norm_w;
-        ph.qt = p.seg[0].qtype;
-        for (uint32_t i = 0; i < p.nseg; i++) {
-            ph.ps.w[i] = p.seg[i].w; ph.ps.row_bytes[i] = (uint32_t)p.seg[i].row_bytes; ph.ps.rows[i] = p.seg[i].rows;
-            if (p.seg[i].qtype != ph.qt) ph.qt = 0xFFu;
-        }
         ph.g = p;
         ph.g.err = ctx->err_dev;
         ph.g.pdl = 0;
@@ -185,10 +185,10 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
     };
     auto emit_attn = [&](const AttnLaunch &a) -> int32_t {
         if (!collect) return launch_attention(ctx, s, a);
-        TokenPhase ph;
+        HostPhase ph;
         memset(&ph, 0, sizeof ph);
-        ph.ps.kind = PH_ATTN;
-        ph.a = AttnArgs{a.p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, 0};
+        ph.attn = true;
+        ph.a = a;
         collect->push_back(ph);
         return IB_OK;
     };
@@ -490,27 +490,58 @@ static int32_t finish_graph(ib_llama *m) {
         if (_e != cudaSuccess) return set_error(IB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));           \
     } while (0)
     CU(cudaDeviceSynchronize());
-    // Single GPU: the whole token as one cooperative kernel, unless INFERI_B200_TOKEN_KERNEL=0 asks for the graph of
-    // separate kernels or the model's shapes do not fit the kernel's shared-memory plan.
+    // Single GPU with INFERI_B200_TOKEN_KERNEL=1: the whole token as one cooperative kernel (token_kernel.cu), if the
+    // model's shapes fit its shared-memory plan.  The default is the graph of separate kernels, which is the faster of the
+    // two at present.
     const char *tk = getenv("INFERI_B200_TOKEN_KERNEL");
-    if (m->tp_size == 1 && !(tk && tk[0] == '0')) {
-        std::vector<TokenPhase> phases;
+    if (m->tp_size == 1 && tk && tk[0] == '1') {
+        std::vector<HostPhase> phases;
         rc = record_token(m, nullptr, 0, &phases);
-        if (rc == IB_OK) rc = plan_token_kernel(ctx, phases.data(), (uint32_t)phases.size(), m->head_size, m->cfg.num_attention_heads / m->cfg.num_key_value_heads, m->plan);
+        const uint32_t L = m->cfg.num_hidden_layers;
+        if (rc == IB_OK && phases.size() != 5 * (size_t)L + 1) rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: unexpected phase list");
+        std::vector<PhaseDesc> table(phases.size());
+        TokenProgram &P = m->prog;
         if (rc == IB_OK) {
-            CU(cudaMalloc(&m->phases_dev, sizeof(TokenPhase) * phases.size()));
-            CU(cudaMemcpy(m->phases_dev, phases.data(), sizeof(TokenPhase) * phases.size(), cudaMemcpyHostToDevice));
-            CU(cudaMalloc(&m->grid_bar, sizeof(uint32_t)));
-            CU(cudaMemset(m->grid_bar, 0, sizeof(uint32_t)));
-            TokenProgram &P = m->prog;
-            P.phases = m->phases_dev; P.n_phases = (uint32_t)phases.size();
+            memset(table.data(), 0, sizeof(PhaseDesc) * table.size());
+            void *kc = nullptr, *vc = nullptr;
+            for (size_t i = 0; i < phases.size(); i++) {
+                const HostPhase &h = phases[i];
+                PhaseDesc &d = table[i];
+                if (h.attn) {
+                    d.kind = PH_ATTN;
+                    d.k_cache = (void *)h.a.k_cache; d.v_cache = (void *)h.a.v_cache;
+                    continue;
+                }
+                d.kind = PH_GEMV;
+                for (uint32_t sg = 0; sg < h.g.nseg; sg++) {
+                    d.m[sg] = LayerMat{h.g.seg[sg].w, (uint32_t)h.g.seg[sg].row_bytes, h.g.seg[sg].qtype};
+                    d.rows[sg] = h.g.seg[sg].rows;
+                }
+                d.x = h.g.x; d.norm_w = h.g.norm_w; d.eps = h.g.eps;
+                d.nseg = h.g.nseg; d.epi = h.g.epi; d.cols = h.g.cols;
+                if (h.g.epi == EPI_QKV) { kc = h.g.k_cache; vc = h.g.v_cache; }
+                d.k_cache = kc; d.v_cache = vc;
+            }
+            P.phases = nullptr; P.n_phases = (uint32_t)phases.size();
+            P.qkv = phases[0].g; P.res = phases[2].g; P.gu = phases[3].g; P.cls = phases[5 * (size_t)L].g;
+            const AttnLaunch &a0 = phases[1].a;
+            P.attn = AttnArgs{a0.p, a0.pos_ptr, a0.q, a0.k_cache, a0.v_cache, a0.out, a0.scratch, a0.counters, a0.max_splits, 0};
             P.ctl = m->ctl; P.seq = m->seq; P.seq_cap = m->seq_cap;
             P.embd = QDesc{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
             P.hidden = m->cfg.hidden_size; P.vocab = m->cfg.vocab_size; P.half_head = m->head_size / 2;
             P.x = m->x; P.theta = m->theta; P.rope_cs = m->rope_cs;
-            P.grid_bar = m->grid_bar; P.epoch = m->epoch; P.barriers_per_token = (uint32_t)phases.size() + 1;
-            P.argmax_slots = m->argmax_slots; P.err = ctx->err_dev;
+            P.epoch = m->epoch; P.barriers_per_token = (uint32_t)phases.size() + 1;
+            P.err = ctx->err_dev;
             P.head_size = m->head_size; P.kv_mul = m->cfg.num_attention_heads / m->cfg.num_key_value_heads; P.kv_dtype = (uint32_t)m->kv_dtype;
+            rc = plan_token_kernel(ctx, P, table.data(), m->plan);
+        }
+        if (rc == IB_OK) {
+            CU(cudaMalloc(&m->phases_dev, sizeof(PhaseDesc) * table.size()));
+            CU(cudaMemcpy(m->phases_dev, table.data(), sizeof(PhaseDesc) * table.size(), cudaMemcpyHostToDevice));
+            CU(cudaMalloc(&m->grid_bar, sizeof(uint32_t)));
+            CU(cudaMemset(m->grid_bar, 0, sizeof(uint32_t)));
+            P.phases = m->phases_dev;
+            P.grid_bar = m->grid_bar;
             P.geo = m->plan.geo;
             m->use_token_kernel = true;
             m->launches_per_token = 1;

@@ -61,20 +61,22 @@ def check_loop(backend, cfg, weights, kv_f16, prompt, n_gen, tied=False):
     return worst
 
 
+@pytest.mark.parametrize("token_kernel", ["0", "1"])
 @pytest.mark.parametrize("kv_f16", [False, True])
-def test_tiny_model_all_quant_types(backend, kv_f16):
+def test_tiny_model_all_quant_types(backend, kv_f16, token_kernel, monkeypatch):
+    monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", token_kernel)   # 1: the whole token as one cooperative kernel
     w = synth_weights(TINY, seed=3001, recipe=TINY_RECIPE)
     check_loop(backend, TINY, w, kv_f16, prompt=[3, 500, 41, 7], n_gen=24)
 
 
 def test_token_kernel_and_kernel_graph_give_the_same_tokens(backend, monkeypatch):
-    """The default path is one cooperative kernel per token; INFERI_B200_TOKEN_KERNEL=0 selects the graph of separate kernels
-    (5 per layer + 2).  Both must reproduce the oracle's greedy tokens, and the launch counter tells them apart."""
+    """INFERI_B200_TOKEN_KERNEL=1 selects one cooperative kernel per token; the default is the graph of separate kernels
+    (5 per layer + 3: begin, classifier, end).  Both must reproduce the oracle's greedy tokens, and the launch counter tells them apart."""
     w = synth_weights(SMALL, seed=3005, device="cuda")
     prompt, n_gen = [5, 77, 1001], 10
     steps = len(prompt) + n_gen - 1
     outs = {}
-    for mode, per_token in (("1", 1), ("0", 5 * SMALL.num_hidden_layers + 2)):
+    for mode, per_token in (("1", 1), ("0", 5 * SMALL.num_hidden_layers + 3)):
         monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", mode)
         model = Llama2(backend, SMALL, Llama2Weights(backend, SMALL, w), kv_f16=True)
         backend.reset_launch_count()
