@@ -225,18 +225,31 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, const void *k_cach
         pl[i] = __ldcg(ps + HS + 1);
     }
     attn_bar(bar);
-    for (int idx = tid; idx < KVM * HS; idx += ATTN_THREADS) {
-        const int m = idx / HS, d = idx % HS;
-        float mx = -INFINITY;
-        for (uint32_t s = 0; s < nsplit; s++) mx = fmaxf(mx, pm[s * KVM + m]);
-        float o = 0.f, ls = 0.f;
+    // every thread owns KVM * HS / ATTN_THREADS outputs of one head (HS is a multiple of ATTN_THREADS or divides it); the
+    // loads of eight slices are issued together
+    constexpr int PER = (KVM * HS + ATTN_THREADS - 1) / ATTN_THREADS;
+    float o[PER], ls[PER], mx[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int m = min((tid + j * ATTN_THREADS) / HS, KVM - 1);
+        float v = -INFINITY;
+        for (uint32_t s = 0; s < nsplit; s++) v = fmaxf(v, pm[s * KVM + m]);
+        mx[j] = v; o[j] = 0.f; ls[j] = 0.f;
+    }
 #pragma unroll 8
-        for (uint32_t s = 0; s < nsplit; s++) {
-            const float wt = merge_weight(pm[s * KVM + m], mx);
-            o += wt * __ldcg(parts + ((size_t)s * KVM + m) * slot + d);
-            ls += wt * pl[s * KVM + m];
+    for (uint32_t s = 0; s < nsplit; s++) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int idx = min(tid + j * ATTN_THREADS, KVM * HS - 1), m = idx / HS, d = idx % HS;
+            const float wt = merge_weight(pm[s * KVM + m], mx[j]);
+            o[j] += wt * __ldcg(parts + ((size_t)s * KVM + m) * slot + d);
+            ls[j] += wt * pl[s * KVM + m];
         }
-        a.out[(size_t)(kvh * KVM + m) * HS + d] = o / ls;
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int idx = tid + j * ATTN_THREADS, m = idx / HS, d = idx % HS;
+        if (idx < KVM * HS) a.out[(size_t)(kvh * KVM + m) * HS + d] = o[j] / ls[j];
     }
     if (tid == 0) a.counters[kvh] = 0u;
 }

@@ -126,7 +126,7 @@ struct ib_llama {
     uint64_t launches_per_token = 0;
     // whole-token kernel (single GPU): the phase list on the device, the grid-barrier counter, the launch plan
     ib::PhaseDesc *phases_dev = nullptr;
-    uint32_t *grid_bar = nullptr;
+    uint32_t *grid_bar = nullptr, *tile_ctr = nullptr;
     ib::TokenProgram prog{};
     ib::TokenKernelPlan plan{};
     bool use_token_kernel = false;
@@ -322,7 +322,7 @@ int32_t ib_llama_destroy(ib_llama *m) {
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
         if (m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch, m->phases_dev, m->grid_bar};
+                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch, m->phases_dev, m->grid_bar, m->tile_ctr};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -540,8 +540,11 @@ static int32_t finish_graph(ib_llama *m) {
             CU(cudaMemcpy(m->phases_dev, table.data(), sizeof(PhaseDesc) * table.size(), cudaMemcpyHostToDevice));
             CU(cudaMalloc(&m->grid_bar, sizeof(uint32_t)));
             CU(cudaMemset(m->grid_bar, 0, sizeof(uint32_t)));
+            CU(cudaMalloc(&m->tile_ctr, sizeof(uint32_t) * table.size()));
+            CU(cudaMemset(m->tile_ctr, 0, sizeof(uint32_t) * table.size()));
             P.phases = m->phases_dev;
             P.grid_bar = m->grid_bar;
+            P.tile_ctr = m->tile_ctr;
             P.geo = m->plan.geo;
             m->use_token_kernel = true;
             m->launches_per_token = 1;

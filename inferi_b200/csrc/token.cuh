@@ -112,6 +112,7 @@ struct TokenProgram {
     float2 *rope_cs;
     uint32_t *grid_bar;                 // arrival counter of the grid barriers (only ever grows)
     uint32_t *epoch;                    // completed tokens
+    uint32_t *tile_ctr;                 // [n_phases] tile hand-out counters, zero between tokens
     uint32_t barriers_per_token;
     uint32_t *err;
     uint32_t head_size, kv_mul, kv_dtype;

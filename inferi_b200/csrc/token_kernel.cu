@@ -59,9 +59,8 @@ __device__ unsigned long long g_tk_done[64][160];   // when warp 0 of every CTA 
 // The current phase as the consumer threads see it: fetched from the descriptor and worked out (this CTA's share of the
 // rows) by one thread while the CTA waits at the grid barrier, so that none of it costs the others registers or time.
 struct PhaseShared {
-    Share sh;
     uint32_t kind, epi, cols, nseg;
-    uint32_t rb0, rb1, qt0, qt1, qt2;
+    uint32_t rb0, rb1, rb2, qt0, qt1, qt2;
     float eps;
     const float *x, *norm_w;
     void *kc, *vc;
@@ -75,6 +74,7 @@ struct __align__(16) TkShared {
     volatile uint32_t go;               // decision after a grid barrier, identical for every consumer thread
     volatile uint32_t issued;           // tiles the producer has issued (valid once it has stopped)
     uint32_t tile_bytes[NS];            // ring bytes held by the tile in each slot (producer's book-keeping)
+    uint4 meta[NS];                     // what the slot holds: ring offset, first row pair, pairs | segment << 8 | end-of-phase << 16
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
@@ -151,13 +151,8 @@ __device__ __forceinline__ bool phase_sync(const TokenProgram &P, const PhaseDes
     } else if (scribe) {
         PhaseShared &c = ts->cur;
         c.kind = sc.kind; c.epi = sc.epi; c.cols = sc.cols; c.nseg = sc.nseg; c.eps = sc.eps;
-        c.rb0 = m0.row_bytes; c.rb1 = m1.row_bytes; c.qt0 = m0.qtype; c.qt1 = m1.qtype; c.qt2 = m2.qtype;
+        c.rb0 = m0.row_bytes; c.rb1 = m1.row_bytes; c.rb2 = m2.row_bytes; c.qt0 = m0.qtype; c.qt1 = m1.qtype; c.qt2 = m2.qtype;
         c.x = x; c.norm_w = norm_w; c.kc = kc; c.vc = vc;
-        if (sc.kind == PH_GEMV) {
-            const uint32_t units = sc.cols / 64, CG = (units + 31) / 32, RG = TCW / CG;
-            make_share_rt(sc.epi == EPI_SWIGLU, sc.nseg, sc.rows0, sc.rows1, sc.rows2, m0.row_bytes, m1.row_bytes, m2.row_bytes, P.geo.tile_max, RG, gridDim.x,
-                          blockIdx.x, c.sh);
-        }
     }
     named_barrier(1, TK_CONSUMERS);
     return ts->go != 0;
@@ -180,7 +175,15 @@ __device__ __forceinline__ StreamSrc load_src(const PhaseDesc *d) {
     return s;
 }
 
-__device__ __forceinline__ void produce_token(const TokenProgram &P, TkShared *ts) {
+// Pairs per tile: one round of the row groups, doubled while the tile stays under 16 KB (short rows) and within limits.
+__device__ __forceinline__ uint32_t dyn_tile_pairs(uint32_t tile_max, uint32_t cost, uint32_t RG) {
+    uint32_t pt = RG;
+    while (pt * 2 <= (uint32_t)PT_MAX && pt * cost < 16384u && pt * 2 * cost <= tile_max) pt *= 2;
+    while (pt > 1 && pt * cost > tile_max) pt--;
+    return pt;
+}
+
+__device__ __forceinline__ void produce_token(const TokenProgram &P, TkShared *ts, uint32_t epoch) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *ring = smem;
     const uint32_t bar0 = smem_u32(smem + P.geo.bar_off);
@@ -195,15 +198,30 @@ __device__ __forceinline__ void produce_token(const TokenProgram &P, TkShared *t
         if (cur.sc.kind == PH_GEMV) {
             if (cur.norm && blockIdx.x == ph % gridDim.x)   // the phase's norm weights: into L2 ahead of the consumers
                 asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(cur.norm), "r"(cur.sc.cols * 4u) : "memory");
+            // The phase's tiles are handed out through a global counter: a CTA that falls behind simply claims fewer.  Tile
+            // t covers pt row pairs of one segment.  The counters are zeroed at the end of every token.
             const uint32_t units = cur.sc.cols / 64, CG = (units + 31) / 32, RG = TCW / CG;
             const bool swiglu = cur.sc.epi == EPI_SWIGLU;
-            Share sh;
-            make_share_rt(swiglu, cur.sc.nseg, cur.sc.rows0, cur.sc.rows1, cur.sc.rows2, cur.rb0, cur.rb1, cur.rb2, P.geo.tile_max, RG, gridDim.x, blockIdx.x, sh);
-            TileCursor tc;
-            tc.init(sh);
-            for (; tc.valid(sh); tc.advance(sh)) {
-                const uint32_t n = tc.count(sh), s = tc.seg;
-                const uint32_t bytes = n * sh.cost(s), bytes_al = (bytes + 127u) & ~127u;
+            const uint32_t n0 = swiglu ? cur.sc.rows0 : cur.sc.rows0 / 2, c0 = swiglu ? cur.rb0 + cur.rb1 : 2 * cur.rb0;
+            const uint32_t n1 = (!swiglu && cur.sc.nseg > 1) ? cur.sc.rows1 / 2 : 0, c1 = 2 * cur.rb1;
+            const uint32_t n2 = (!swiglu && cur.sc.nseg > 2) ? cur.sc.rows2 / 2 : 0, c2 = 2 * cur.rb2;
+            const uint32_t pt0 = dyn_tile_pairs(P.geo.tile_max, c0, RG), pt1 = dyn_tile_pairs(P.geo.tile_max, c1, RG), pt2 = dyn_tile_pairs(P.geo.tile_max, c2, RG);
+            const uint32_t nt0 = (n0 + pt0 - 1) / pt0, nt1 = (n1 + pt1 - 1) / pt1, nt2 = (n2 + pt2 - 1) / pt2, NT = nt0 + nt1 + nt2;
+            // A CTA may run at most one tile ahead of its fair share (else the CTAs whose producers are furthest ahead would
+            // hoard the tiles of a short phase), and near the end of the phase it claims the next tile only once its
+            // consumers have caught up (else the tiles already sitting in its ring decide when the phase ends).
+            const uint32_t cap = (NT + gridDim.x - 1) / gridDim.x + 1;
+            uint32_t claimed = 1;
+            uint32_t t = atomicAdd(P.tile_ctr + ph, 1u);
+            while (t < NT) {
+                const bool tail_zone = t + 2 * gridDim.x >= NT;
+                uint32_t t_next = NT;   // = no further tile
+                if (!tail_zone && claimed < cap) { t_next = atomicAdd(P.tile_ctr + ph, 1u); claimed++; }   // in flight while this tile waits for ring space
+                uint32_t sgm, first, n, cost;
+                if (t < nt0) { sgm = 0; first = t * pt0; n = min(pt0, n0 - first); cost = c0; }
+                else if (t < nt0 + nt1) { sgm = 1; first = (t - nt0) * pt1; n = min(pt1, n1 - first); cost = c1; }
+                else { sgm = 2; first = (t - nt0 - nt1) * pt2; n = min(pt2, n2 - first); cost = c2; }
+                const uint32_t bytes = n * cost, bytes_al = (bytes + 127u) & ~127u;
                 uint32_t gap = 0;
                 if (off + bytes_al > RING) { gap = RING - off; off = 0; }
                 const uint32_t need = bytes_al + gap;
@@ -213,22 +231,47 @@ __device__ __forceinline__ void produce_token(const TokenProgram &P, TkShared *t
                     tail++;
                 }
                 if (stop || ts->abort_flag) { stop = true; break; }
-                ts->tile_bytes[kt & (NS - 1)] = need;
+                const uint32_t slot = kt & (NS - 1);
+                ts->tile_bytes[slot] = need;
+                ts->meta[slot] = make_uint4(off, first, n | (sgm << 8), 0u);
                 used += need;
-                const uint32_t dst = smem_u32(ring + off), full = bar0 + 8 * (kt & (NS - 1));
+                const uint32_t dst = smem_u32(ring + off), full = bar0 + 8 * slot;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_expect_tx(full, bytes);
                 if (swiglu) {
                     const uint32_t ba = n * cur.rb0, bb = n * cur.rb1;
-                    bulk_g2s(dst, cur.w0 + (size_t)tc.next * cur.rb0, ba, full);
-                    bulk_g2s(dst + ba, cur.w1 + (size_t)tc.next * cur.rb1, bb, full);
+                    bulk_g2s(dst, cur.w0 + (size_t)first * cur.rb0, ba, full);
+                    bulk_g2s(dst + ba, cur.w1 + (size_t)first * cur.rb1, bb, full);
                 } else {
-                    const uint8_t *w = s == 0 ? cur.w0 : (s == 1 ? cur.w1 : cur.w2);
-                    bulk_g2s(dst, w + (size_t)tc.next * sh.cost(s), bytes, full);
+                    const uint8_t *w = sgm == 0 ? cur.w0 : (sgm == 1 ? cur.w1 : cur.w2);
+                    bulk_g2s(dst, w + (size_t)first * cost, bytes, full);
                 }
                 off += bytes_al;
                 kt++;
+                if (tail_zone && claimed < cap) {
+                    while (kt - tail > 1) {   // all but the tile just issued have been consumed
+                        if (ts->abort_flag || !mbar_wait(bar0 + 8 * (NS + (tail & (NS - 1))), (tail / NS) & 1, P.err, 2)) { stop = true; break; }
+                        used -= ts->tile_bytes[tail & (NS - 1)];
+                        tail++;
+                    }
+                    if (stop) break;
+                    t_next = atomicAdd(P.tile_ctr + ph, 1u);
+                    claimed++;
+                }
+                t = t_next;
             }
+            if (stop) break;
+            // end-of-phase marker: a slot without data
+            while (kt - tail >= NS) {
+                if (ts->abort_flag || !mbar_wait(bar0 + 8 * (NS + (tail & (NS - 1))), (tail / NS) & 1, P.err, 2)) { stop = true; break; }
+                used -= ts->tile_bytes[tail & (NS - 1)];
+                tail++;
+            }
+            if (stop) break;
+            ts->tile_bytes[kt & (NS - 1)] = 0;
+            ts->meta[kt & (NS - 1)] = make_uint4(0u, 0u, 1u << 16, 0u);
+            mbar_arrive(bar0 + 8 * (kt & (NS - 1)));
+            kt++;
         }
         TK_TRACE_PROD(ph, 1);
         cur = nxt;
@@ -279,32 +322,39 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
     const bool working = (uint32_t)warp < CG * RG;
     const uint32_t cg = warp % CG, rg = warp / CG, u = cg * 32 + lane;
     const bool has_unit = working && u < units;
-    const Share sh = d->sh;
     TK_TRACE(ph, 5);
 
     UnitAct ua;
     LaneConst lc;
-    uint32_t cur_type = 0xFFFFFFFFu;
-    TileCursor tc;
-    tc.init(sh);
+    uint32_t cur_type = d->qt0;   // the first segment's format: this lane's activations go to registers before any tile is waited for
+    unit_init<QT_MIXED>(cur_type, u, lc);
+    if (has_unit) load_unit_act(cur_type, u, A, ua);
+    TK_TRACE(ph, 6);
+    bool first_tile = true;
 #pragma unroll 1
-    for (; tc.valid(sh); tc.advance(sh)) {
-        const uint32_t st = kt & (NS - 1), s = tc.seg, n = tc.count(sh);
+    for (;;) {
+        const uint32_t st = kt & (NS - 1);
+        if (ts->abort_flag || !mbar_wait(bar0 + 8 * st, (kt / NS) & 1, P.err, 1)) {
+            ts->abort_flag = 1;   // give up on the rest of this phase; the next grid barrier ends the kernel for the whole CTA
+            break;
+        }
+        const uint4 meta = ts->meta[st];
+        if (meta.z >> 16) {   // end of the phase for this CTA
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar0 + 8 * (NS + st));
+            kt++;
+            break;
+        }
+        if (first_tile) { TK_TRACE(ph, 3); first_tile = false; }
+        const uint32_t n = meta.z & 0xFFu, s = (meta.z >> 8) & 0xFFu, first = meta.y;
         const uint32_t qtype = s == 0 ? d->qt0 : (s == 1 ? d->qt1 : d->qt2);
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
             unit_init<QT_MIXED>(qtype, u, lc);
             if (has_unit) load_unit_act(qtype, u, A, ua);
             cur_type = qtype;
         }
-        if (tc.next == sh.a(0) && s == 0) TK_TRACE(ph, 6);   // activations of this lane are in registers
-        const uint32_t cost = sh.cost(s), bytes_al = (n * cost + 127u) & ~127u;
-        if (off + bytes_al > P.geo.ring_bytes) off = 0;
-        if (ts->abort_flag || !mbar_wait(bar0 + 8 * st, (kt / NS) & 1, P.err, 1)) {
-            ts->abort_flag = 1;   // give up on the rest of this phase; the next grid barrier ends the kernel for the whole CTA
-            break;
-        }
-        if (tc.next == sh.a(0) && s == 0) TK_TRACE(ph, 3);   // first tile has landed
-        const uint8_t *tile = ring + off;
+        const uint32_t cost = swiglu ? rb0 + rb1 : 2 * (s == 0 ? rb0 : (s == 1 ? rb1 : d->rb2));
+        const uint8_t *tile = ring + meta.x;
         // pair = rows 2r, 2r+1 of one segment (adjacent in the tile), or gate row r + up row r (two blocks of the tile)
         const uint32_t rbA = swiglu ? rb0 : cost / 2, rbB = swiglu ? rb1 : rbA;
         const uint32_t strideA = swiglu ? rbA : cost, offB = swiglu ? n * rbA : rbA, strideB = swiglu ? rbB : cost;
@@ -324,7 +374,7 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
                     vb += __shfl_xor_sync(0xffffffffu, vb, o);
                 }
                 if (CG == 1) {
-                    if (lane == 0) phase_epilogue(P, d, epi, s, tc.next + pr, va, vb, best);
+                    if (lane == 0) phase_epilogue(P, d, epi, s, first + pr, va, vb, best);
                 } else if (lane == 0) {
                     pt[(pr * 2 + 0) * CW + cg] = va;
                     pt[(pr * 2 + 1) * CW + cg] = vb;
@@ -347,7 +397,7 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
                             va += pt[(pr * 2 + 0) * CW + g];
                             vb += pt[(pr * 2 + 1) * CW + g];
                         }
-                        phase_epilogue(P, d, epi, s, tc.next + pr, va, vb, best);
+                        phase_epilogue(P, d, epi, s, first + pr, va, vb, best);
                     }
                     __syncwarp();
                     if (lane == 0) cnt[st * CW + rg] = 0;
@@ -356,7 +406,6 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar0 + 8 * (NS + st));   // this warp is done with the tile
-        off += bytes_al;
         kt++;
     }
 }
@@ -443,6 +492,7 @@ __device__ __forceinline__ uint32_t consume_token(const TokenProgram &P, TkShare
             P.ctl->pos = pos + 1;
             *P.epoch = epoch + 1;
         }
+        for (uint32_t i = lane; i < P.n_phases; i += 32) P.tile_ctr[i] = 0u;   // every CTA is past every phase
     }
     return kt;
 }
@@ -472,7 +522,7 @@ __global__ void __maxnreg__(TK_REGS) token_kernel(const TokenProgram P) {
 
     uint32_t seen = 0;
     if (warp == TCW) {
-        if (lane == 0) produce_token(P, &ts);
+        if (lane == 0) produce_token(P, &ts, epoch);
     } else {
         seen = consume_token<HS, KVM, T>(P, &ts, epoch);
     }
