@@ -12,13 +12,17 @@ constexpr uint32_t GEMV_MAX_COLS = 32768;
 // Activation form in shared memory, for `cols` columns (a multiple of 32):
 //   3 int8 limbs a0,a1,a2 [cols] each;  f32 scale s/127 per 32 columns;  f32 sum of x per 16 columns
 //   x ~= (s/127) * (a0 + a1/254 + a2/254^2)      (resolution 6e-8 * max|x| of the 32-group)
-__host__ __device__ inline size_t act_smem_bytes(uint32_t cols) { return (size_t)cols * 3 + cols / 32 * 4 + cols / 16 * 4; }
+//   (+ 192 bytes: in the group-major chunk order each limb array carries one 16-byte skew per group, see act_chunk_pos)
+__host__ __device__ inline size_t act_smem_bytes(uint32_t cols) { return (size_t)cols * 3 + cols / 32 * 4 + cols / 16 * 4 + 192; }
 
 struct Act {
     const uint8_t *base;
     uint32_t cols;
-    __device__ __forceinline__ const uint4 *limb(int k) const { return reinterpret_cast<const uint4 *>(base + (size_t)k * cols); }
-    __device__ __forceinline__ const float *sc() const { return reinterpret_cast<const float *>(base + (size_t)3 * cols); }
+    uint32_t nq = 0;   // 0: 16-column chunks in column order; else cols / 64: group-major order, see act_chunk_pos
+    __device__ __forceinline__ uint32_t pos(uint32_t e16) const { return nq ? (e16 & 3u) * (nq + 1) + (e16 >> 2) : e16; }
+    __device__ __forceinline__ uint32_t lstride() const { return cols + (nq ? 64u : 0u); }
+    __device__ __forceinline__ const uint4 *limb(int k) const { return reinterpret_cast<const uint4 *>(base + (size_t)k * lstride()); }
+    __device__ __forceinline__ const float *sc() const { return reinterpret_cast<const float *>(base + (size_t)3 * lstride()); }
     __device__ __forceinline__ const float *sx16() const { return sc() + cols / 32; }
 };
 
@@ -76,7 +80,13 @@ __device__ __forceinline__ void pack_prefetch_norm(const float *__restrict__ nor
     }
 }
 
-__device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uint32_t cols, uint8_t *smem, bool store) {
+// Position of the 16-column chunk `run` inside a limb array.  With nq = cols / 64 the chunks are stored "group-major":
+// chunk 4u + g sits at g * (nq + 1) + u.  The lanes of a warp, each reading chunk 4u + g of its unit u, then touch
+// consecutive 16-byte words (in column order they would be 64 bytes apart: a 4-way bank conflict on every 128-bit load),
+// and the one-chunk skew between groups keeps the four chunks that neighbouring threads store apart as well.
+__device__ __forceinline__ uint32_t act_chunk_pos(uint32_t run, uint32_t nq) { return nq ? (run & 3u) * (nq + 1) + (run >> 2) : run; }
+
+__device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uint32_t cols, uint8_t *smem, bool store, uint32_t nq = 0) {
     const int lane = threadIdx.x & 31;
     float amax = 0.f, sum = 0.f;
 #pragma unroll
@@ -109,11 +119,13 @@ __device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uin
         w2[j] = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
     }
     if (store) {
-        uint4 *l0 = reinterpret_cast<uint4 *>(smem), *l1 = reinterpret_cast<uint4 *>(smem + cols), *l2 = reinterpret_cast<uint4 *>(smem + 2 * (size_t)cols);
-        float *sc = reinterpret_cast<float *>(smem + (size_t)3 * cols), *sx16 = sc + cols / 32;
-        l0[run] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
-        l1[run] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
-        l2[run] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+        const size_t ls = cols + (nq ? 64u : 0u);   // = Act::lstride()
+        uint4 *l0 = reinterpret_cast<uint4 *>(smem), *l1 = reinterpret_cast<uint4 *>(smem + ls), *l2 = reinterpret_cast<uint4 *>(smem + 2 * ls);
+        float *sc = reinterpret_cast<float *>(smem + 3 * ls), *sx16 = sc + cols / 32;
+        const uint32_t at = act_chunk_pos(run, nq);
+        l0[at] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+        l1[at] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+        l2[at] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
         if ((lane & 1) == 0) sc[run >> 1] = amax * (1.0f / 127.0f);
         sx16[run] = sum;
     }
@@ -130,7 +142,8 @@ struct PackReduce {
 // `g` holds the norm weights of the thread's first run (from pack_prefetch_norm).
 template <int NT = PACK_THREADS>
 __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                float *red /* [NT/32 + 1] */, const float4 (&g)[4], const PackReduce rd = PackReduce{nullptr, 0, nullptr}) {
+                                                float *red /* [NT/32 + 1] */, const float4 (&g)[4], const PackReduce rd = PackReduce{nullptr, 0, nullptr},
+                                                uint32_t nq = 0) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nruns = cols / 16;    // cols is a multiple of 32, so runs pair up inside a warp
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
@@ -197,7 +210,7 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
                     v.x = (v.x * rms) * w.x; v.y = (v.y * rms) * w.y; v.z = (v.z * rms) * w.z; v.w = (v.w * rms) * w.w;
                 }
             }
-            pack_run(r.x[i], run, cols, smem, ok);
+            pack_run(r.x[i], run, cols, smem, ok, nq);
         }
     }
     for (uint32_t base = warp * 32 + NT * PACK_RUNS; base < nruns; base += NT) {   // rows wider than the registers hold
@@ -212,7 +225,7 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
                 v[j].x = (v[j].x * rms) * w.x; v[j].y = (v[j].y * rms) * w.y; v[j].z = (v[j].z * rms) * w.z; v[j].w = (v[j].w * rms) * w.w;
             }
         }
-        pack_run(v, run, cols, smem, ok);
+        pack_run(v, run, cols, smem, ok, nq);
     }
     named_barrier(1, NT);
 }
@@ -222,7 +235,7 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
 // first are read twice (sum of squares, then conversion).  Result bit-identical to pack_activation.
 template <int NT = PACK_THREADS>
 __device__ __forceinline__ void pack_activation_lean(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                     float *red /* [NT/32 + 1] */) {
+                                                     float *red /* [NT/32 + 1] */, uint32_t nq = 0) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nruns = cols / 16;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
@@ -273,7 +286,7 @@ __device__ __forceinline__ void pack_activation_lean(uint8_t *smem, uint32_t col
                 v[j].x = (v[j].x * rms) * g[j].x; v[j].y = (v[j].y * rms) * g[j].y; v[j].z = (v[j].z * rms) * g[j].z; v[j].w = (v[j].w * rms) * g[j].w;
             }
         }
-        pack_run(v, run, cols, smem, ok);
+        pack_run(v, run, cols, smem, ok, nq);
     }
     named_barrier(1, NT);
 }

@@ -206,8 +206,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         named_barrier(1, PACK_THREADS);
         rd = PackReduce{p.reduce_src, p.tp, p.x_out};
     }
-    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g, rd);
-    const Act A{act_sm, p.cols};
+    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g, rd, p.cols / 64);
+    const Act A{act_sm, p.cols, p.cols / 64};
     TRACE(3);
 
     unsigned long long best = 0ull;

@@ -180,7 +180,7 @@ __device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const 
     for (int g = 0; g < 4; g++) {
 #pragma unroll
         for (int k = 0; k < 3; k++) {
-            const uint32_t addr = smem_u32(A.limb(k) + e16[g]);
+            const uint32_t addr = smem_u32(A.limb(k) + A.pos(e16[g]));
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(ua.l[k][g].x), "=r"(ua.l[k][g].y), "=r"(ua.l[k][g].z), "=r"(ua.l[k][g].w)
                          : "r"(addr)

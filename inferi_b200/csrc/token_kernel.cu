@@ -311,8 +311,8 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
     float *part = reinterpret_cast<float *>(smem + P.geo.part_off);             // [NS][PT_MAX][2][CW]
     uint32_t *cnt = reinterpret_cast<uint32_t *>(part + NS * PT_MAX * 2 * CW);  // [NS][CW]
     const uint32_t bar0 = smem_u32(smem + P.geo.bar_off);
-    pack_activation_lean<TK_CONSUMERS>(act_sm, cols, d->x, d->norm_w, d->eps, ts->red);
-    const Act A{act_sm, cols};
+    pack_activation_lean<TK_CONSUMERS>(act_sm, cols, d->x, d->norm_w, d->eps, ts->red, cols / 64);
+    const Act A{act_sm, cols, cols / 64};
     TK_TRACE(ph, 2);
 
     const uint32_t epi = d->epi;
