@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     PackReduce rd{nullptr, 0, nullptr};
     if (p.reduce_src) {
         // every rank's partial sums of the previous row-split GEMV must have landed in this rank's slots
-        if (threadIdx.x == 0) wait_counter(p.reduce_flag, ((*p.epoch_ptr) * p.reduce_per_epoch + p.reduce_use) * p.tp, p.err, 3);
+        if (threadIdx.x == 0) wait_counter(p.reduce_flag, ((*p.epoch_ptr) * p.reduce_per_epoch + p.reduce_use) * p.reduce_arrivals, p.err, 3);
         named_barrier(1, PACK_THREADS);
         rd = PackReduce{p.reduce_src, p.tp, p.x_out};
     }
@@ -220,16 +220,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     TRACE(15);
 
     if (EPI == EPI_PUSH) {
-        // all of this CTA's peer stores are out; the last CTA of the grid tells every rank that this rank has delivered
-        __threadfence_system();
+        // All of this CTA's peer stores are issued.  One thread orders them (the CTA barrier makes the release cumulative
+        // over the other threads' stores) and tells every rank that one more CTA of this rank has delivered; a reader
+        // waits for ranks x CTAs arrivals.
         named_barrier(1, PACK_THREADS);
-        if (threadIdx.x == 0) {
-            if (atomicAdd(p.push_done, 1u) == gridDim.x - 1) {
-                *p.push_done = 0u;
-                __threadfence_system();
-                for (uint32_t rk = 0; rk < p.tp; rk++) atomicAdd_system(p.push_flag[rk], 1u);
-            }
-        }
+        if (threadIdx.x == 0)
+            for (uint32_t rk = 0; rk < p.tp; rk++) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[rk]), "r"(1u) : "memory");
     }
     if (EPI == EPI_ARGMAX) {
 #pragma unroll
