@@ -23,6 +23,7 @@ namespace ib {
 // Timeline probes for latency studies: globaltimer stamps of CTA 0 (and of the last CTA's end), one row of 16 slots
 // per epilogue kind, read back with ib_debug_stream_trace().  Never compiled into the shipped library.
 __device__ unsigned long long g_trace[16 * 16];
+__device__ unsigned long long g_cta_end[8][160], g_cta_packed[8][160];   // per CTA: end of the kernel / activations packed
 #define TRACE(slot)                                                                                   \
     do {                                                                                              \
         if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {                              \
@@ -36,8 +37,13 @@ __device__ unsigned long long g_trace[16 * 16];
             g_trace[EPI * 16 + 14] = _t;                                                              \
         }                                                                                             \
     } while (0)
+#define TRACE_CTA(arr)                                                                                \
+    do {                                                                                              \
+        if (lane == 0 && warp == 0 && blockIdx.x < 160) arr[EPI][blockIdx.x] = global_ns();           \
+    } while (0)
 #else
 #define TRACE(slot) do { } while (0)
+#define TRACE_CTA(arr) do { } while (0)
 #endif
 
 struct StreamGeom {
@@ -81,9 +87,14 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
         const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
         const uint32_t strideA = (EPI == EPI_SWIGLU) ? rbA : 2 * rbA, offB = (EPI == EPI_SWIGLU) ? n * rbA : rbA;
         float *pt = c.part + (size_t)st * PT_MAX * 2 * CW;
+        // residual values of the pair this lane may have to finish (CG > 1: as the last warp of the row group; CG == 1: lane 0
+        // of each pair's warp, fetched per pair below): requested now, needed after the dot products
+        float2 rpre = make_float2(0.f, 0.f);
+        if (EPI == EPI_RESIDUAL && CG > 1 && c.rg + RG * lane < n) rpre = residual_prefetch(p.resid, tc.next + c.rg + RG * lane);
         for (uint32_t pr = c.rg; pr < n; pr += RG) {
             const uint8_t *rowA = tile + pr * strideA;
             const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + offB + pr * rbB : rowA + rbA;
+            if (EPI == EPI_RESIDUAL && CG == 1 && lane == 0) rpre = residual_prefetch(p.resid, tc.next + pr);
             float va = 0.f, vb = 0.f;
             if (c.has_unit) {
                 va = unit_dot<QT>(qtype, rowA, lc, ua);
@@ -95,7 +106,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                 vb += __shfl_xor_sync(0xffffffffu, vb, o);
             }
             if (CG == 1) {
-                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p});
+                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p}, rpre);
             } else if (lane == 0) {
                 pt[(pr * 2 + 0) * CW + c.cg] = va;
                 pt[(pr * 2 + 1) * CW + c.cg] = vb;
@@ -118,7 +129,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                         va += pt[(pr * 2 + 0) * CW + g];
                         vb += pt[(pr * 2 + 1) * CW + g];
                     }
-                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p});
+                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p}, rpre);
                 }
                 __syncwarp();
                 if (lane == 0) c.cnt[st * CW + c.rg] = 0;
@@ -155,13 +166,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     make_share<EPI>(p, geo.stage_bytes, RG, sh);
 
 
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S; s++) {
-            mbar_init(bar0 + 8 * s, 1);                 // full: the producer's expect_tx arrival
-            mbar_init(bar0 + 8 * (S + s), active);      // empty: one arrival per working consumer warp
-        }
-        for (uint32_t i = 0; i < S * CW; i++) cnt[i] = 0;
+    // set-up spread over threads: it sits on the critical path of a CTA that starts late (its SM was the last to be freed)
+    if (threadIdx.x < 2 * S) {
+        // full[s]: the producer's expect_tx arrival; empty[s]: one arrival per working consumer warp
+        mbar_init(bar0 + 8 * threadIdx.x, threadIdx.x < S ? 1u : active);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    } else if (threadIdx.x >= 32 && threadIdx.x < 32 + S * CW) {
+        cnt[threadIdx.x - 32] = 0;
     }
     __syncthreads();
     TRACE(1);
@@ -209,6 +220,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g, rd, p.cols / 64);
     const Act A{act_sm, p.cols, p.cols / 64};
     TRACE(3);
+    TRACE_CTA(g_cta_packed);
 
     unsigned long long best = 0ull;
     if ((uint32_t)warp < active) {
@@ -218,6 +230,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         consume_tiles<EPI, QT>(p, sh, c, A, best);
     }
     TRACE(15);
+    TRACE_CTA(g_cta_end);
 
     if (EPI == EPI_PUSH) {
         // All of this CTA's peer stores are issued.  One thread orders them (the CTA barrier makes the release cumulative
@@ -268,7 +281,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
 // -------------------------------------------------------------------------------------------------
 // host side
 // -------------------------------------------------------------------------------------------------
-constexpr size_t STREAM_SMEM_BUDGET = 200 * 1024;   // one CTA per SM
+constexpr size_t STREAM_SMEM_BUDGET = 194 * 1024;   // one CTA per SM; stays under the 196 KB shared-memory configuration, which leaves 60 KB of L1 (register spills live there)
 
 bool gemv_stream_eligible(const GemvParams &p) {
     if (p.cols % 64 || p.cols > 16384) return false;
@@ -382,6 +395,10 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
 #ifdef IB_STREAM_TRACE
 extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(unsigned long long *out64) {
     return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 2;
+}
+extern "C" __attribute__((visibility("default"))) int32_t ib_debug_cta_times(unsigned long long *ends, unsigned long long *packed) {
+    if (cudaMemcpyFromSymbol(ends, g_cta_end, sizeof(unsigned long long) * 8 * 160) != cudaSuccess) return 2;
+    return cudaMemcpyFromSymbol(packed, g_cta_packed, sizeof(unsigned long long) * 8 * 160) == cudaSuccess ? 0 : 2;
 }
 #endif
 

@@ -370,10 +370,15 @@ struct ParamCaches {
     __device__ __forceinline__ void *v() const { return p.v_cache; }
 };
 
+__device__ __forceinline__ float2 residual_prefetch(const float *resid, uint32_t pair) { return __ldcg(reinterpret_cast<const float2 *>(resid + 2 * pair)); }
+
 // ---- epilogue of one row pair ----
 // `caches`: where the k / v rows of EPI_QKV go; any type with k() and v() (the launch parameters, or a layer-table entry).
+// `resid_pre`: the pair's residual values (EPI_RESIDUAL), fetched by the caller ahead of the dot product so that the L2
+// round trip is off the tile's critical path (see residual_prefetch).
 template <uint32_t EPI, typename Caches>
-__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best, const Caches &caches) {
+__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best, const Caches &caches,
+                                         float2 resid_pre) {
     if (EPI == EPI_SWIGLU) {
         // crates/inferi-shaders/src/silu.rs:16-19,46-52: a = gate row, b = up row
         p.seg[0].out[pair] = b * (a / (1.0f + expf(-a)));
@@ -383,12 +388,11 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
     if (EPI == EPI_STORE) {
         *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(a, b);
     } else if (EPI == EPI_RESIDUAL) {
-        const float2 r = __ldcg(reinterpret_cast<const float2 *>(p.resid + r0));
-        *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(r.x + a, r.y + b);
+        *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(resid_pre.x + a, resid_pre.y + b);
     } else if (EPI == EPI_QKV) {
         if (s < 2) {
             // crates/inferi-shaders/src/rope.rs:75-91 (adjacent pairs)
-            const float2 cs = __ldcg(p.rope_cs + ((r0 % p.head_size) >> 1));
+            const float2 cs = __ldg(p.rope_cs + ((r0 % p.head_size) >> 1));   // written by an earlier kernel: read-only here, L1 may keep it
             const float x = a, y = b;
             a = cs.x * x - cs.y * y;
             b = cs.y * x + cs.x * y;

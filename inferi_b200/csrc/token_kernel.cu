@@ -289,12 +289,12 @@ struct DescCaches {
 
 // Epilogue of one row pair, by the phase's kind.  The parameters of each kind are the same for every layer.
 __device__ __forceinline__ void phase_epilogue(const TokenProgram &P, const PhaseShared *d, uint32_t epi, uint32_t s, uint32_t pair, float a, float b,
-                                               unsigned long long &best) {
+                                               unsigned long long &best, float2 rpre) {
     switch (epi) {
-    case EPI_QKV: epilogue<EPI_QKV>(P.qkv, s, pair, a, b, best, DescCaches{d}); break;
-    case EPI_RESIDUAL: epilogue<EPI_RESIDUAL>(P.res, s, pair, a, b, best, DescCaches{d}); break;
-    case EPI_SWIGLU: epilogue<EPI_SWIGLU>(P.gu, s, pair, a, b, best, DescCaches{d}); break;
-    default: epilogue<EPI_ARGMAX>(P.cls, s, pair, a, b, best, DescCaches{d}); break;
+    case EPI_QKV: epilogue<EPI_QKV>(P.qkv, s, pair, a, b, best, DescCaches{d}, rpre); break;
+    case EPI_RESIDUAL: epilogue<EPI_RESIDUAL>(P.res, s, pair, a, b, best, DescCaches{d}, rpre); break;
+    case EPI_SWIGLU: epilogue<EPI_SWIGLU>(P.gu, s, pair, a, b, best, DescCaches{d}, rpre); break;
+    default: epilogue<EPI_ARGMAX>(P.cls, s, pair, a, b, best, DescCaches{d}, rpre); break;
     }
 }
 
@@ -360,9 +360,13 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
         const uint32_t strideA = swiglu ? rbA : cost, offB = swiglu ? n * rbA : rbA, strideB = swiglu ? rbB : cost;
         float *pt = part + (size_t)st * PT_MAX * 2 * CW;
         if (working) {
+            // residual values of the pair this lane may have to finish: requested now, needed after the dot products
+            float2 rpre = make_float2(0.f, 0.f);
+            if (epi == EPI_RESIDUAL && CG > 1 && rg + RG * lane < n) rpre = residual_prefetch(P.res.resid, first + rg + RG * lane);
             for (uint32_t pr = rg; pr < n; pr += RG) {
                 const uint8_t *rowA = tile + pr * strideA;
                 const uint8_t *rowB = tile + offB + pr * strideB;
+                if (epi == EPI_RESIDUAL && CG == 1 && lane == 0) rpre = residual_prefetch(P.res.resid, first + pr);
                 float va = 0.f, vb = 0.f;
                 if (has_unit) {
                     va = unit_dot<QT_MIXED>(qtype, rowA, lc, ua);
@@ -374,7 +378,7 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
                     vb += __shfl_xor_sync(0xffffffffu, vb, o);
                 }
                 if (CG == 1) {
-                    if (lane == 0) phase_epilogue(P, d, epi, s, first + pr, va, vb, best);
+                    if (lane == 0) phase_epilogue(P, d, epi, s, first + pr, va, vb, best, rpre);
                 } else if (lane == 0) {
                     pt[(pr * 2 + 0) * CW + cg] = va;
                     pt[(pr * 2 + 1) * CW + cg] = vb;
@@ -397,7 +401,7 @@ __device__ __forceinline__ void gemv_phase(const TokenProgram &P, TkShared *ts, 
                             va += pt[(pr * 2 + 0) * CW + g];
                             vb += pt[(pr * 2 + 1) * CW + g];
                         }
-                        phase_epilogue(P, d, epi, s, first + pr, va, vb, best);
+                        phase_epilogue(P, d, epi, s, first + pr, va, vb, best, rpre);
                     }
                     __syncwarp();
                     if (lane == 0) cnt[st * CW + rg] = 0;
