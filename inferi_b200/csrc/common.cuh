@@ -135,11 +135,12 @@ struct GemvParams {
     // ---- tensor parallel (tp > 1): one-shot push all-reduce fused into epilogue and prologue ----
     uint32_t tp;                                // number of ranks; 0 or 1 = single GPU
     const uint32_t *epoch_ptr;                  // device scalar: completed token-graph launches (arrival counters only ever grow)
-    // EPI_PUSH: rank p keeps this rank's partial at push_dst[p]; every CTA adds 1 to every rank's counter when it is done
+    // EPI_PUSH: rank p keeps this rank's partial at push_dst[p]; the last CTA adds 1 to every rank's counter
     float *push_dst[IB_MAX_TP];
     uint32_t *push_flag[IB_MAX_TP];
+    unsigned int *push_done;                    // local CTA arrival counter (self-resetting)
     // prologue: x + sum over ranks of reduce_src[r][cols] once reduce_flag has reached ((*epoch) * per_epoch + use) * arrivals,
-    // arrivals = ranks x CTAs of the pushing kernel
+    // arrivals = one per rank
     const float *reduce_src;
     const uint32_t *reduce_flag;
     uint32_t reduce_use, reduce_per_epoch, reduce_arrivals;

@@ -215,8 +215,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
         p.reduce_src = cl.part(m->comm, set, 0, H);
         p.reduce_flag = cl.flag(m->comm, set);
         p.reduce_use = use; p.reduce_per_epoch = L;
-        const uint32_t pairs = H / 2;   // rows of the pushing kernel (o_proj / down): its grid is min(SMs, row pairs)
-        p.reduce_arrivals = (uint32_t)tp * (pairs < (uint32_t)ctx->sm_count ? pairs : (uint32_t)ctx->sm_count);
+        p.reduce_arrivals = (uint32_t)tp;
         p.x_out = other;
         float *t = cur; cur = other; other = t;
     };
@@ -226,6 +225,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
             p.push_dst[r] = cl.part(m->comm_peer[r], set, rank, H);
             p.push_flag[r] = cl.flag(m->comm_peer[r], set);
         }
+        p.push_done = m->push_done + set;
         p.seg[0].out = nullptr;
     };
     ib_attn_params ap{c.max_position_embeddings, m->kv_dim_l, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
