@@ -33,6 +33,7 @@ import numpy as np  # noqa: E402
 METRIC = "batch-1 decode tok/s, Llama-3-8B-arch Q4_K_M"
 UNIT = "tok/s"
 PROMPT_SEED, WEIGHT_SEED = 4002, 4001
+DRAM_TRAFFIC_RATIO = 1.0003   # dram__bytes_read+write / algorithmic bytes of the streaming GEMV (33.11 MB moved for a 33.10 MB matrix)
 
 
 def measured_peaks():
@@ -335,7 +336,10 @@ def main():
                    "prefill": "prompt fed through the decode path (as the reference does), untimed"},
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": 20, "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     # DRAM bytes per token: algorithmic bytes x the read+write / algorithmic ratio of the ncu captures of the
+                     # GEMV kernels (a whole token is too large to capture at once)
+                     "traffic": bytes_per_token * DRAM_TRAFFIC_RATIO, "traffic_source": "ncu per-kernel captures (profiles/), scaled to a token",
                      "peak_source": peak_src, "per": "token (one graph launch)", "algorithmic_bytes": bytes_per_token,
                      "frac_of_8TBs": achieved / (8000.0 * world), "kernels": kernels},
         "clocks": clocks.summary(),
