@@ -199,6 +199,46 @@ IB_API int32_t ib_llama_tp_connect(ib_llama *model, const void *handles_by_rank)
  * for parity checks (the reference exposes `Llama2State::logits`, transformer.rs:15-43). */
 IB_API int32_t ib_llama_state(ib_llama *model, const float **logits_dev, const float **x_dev);
 
+/* ---- GGUF container and GGUF -> device loader ----
+ * Replaces `Gguf::from_bytes` (crates/inferi/src/gguf.rs:516-692: header, metadata, tensor table, data alignment),
+ * `Llama2Config::from_gguf` (crates/inferi/src/models/llama2/cpu.rs:74-107) and `Llama2Weights::from_gguf`
+ * (crates/inferi/src/models/llama2/transformer.rs:294-394).  The file is memory-mapped; tensors go to the device straight
+ * from the mapping (no typed copies), `token_embd` stays quantized, a tensor-parallel rank uploads only its slice.
+ * Malformed files give IB_ERR_INVALID (the reference panics on rank > 4, gguf.rs:583-586). */
+typedef struct ib_gguf ib_gguf;
+
+typedef struct ib_gguf_tensor_info {
+    int32_t type;        /* ggml tensor type id (gguf.rs:74-106) */
+    uint32_t n_dims;
+    uint64_t dims[4];    /* slowest first: a matrix is [rows, cols] (the file stores them fastest first, gguf.rs:587-593) */
+    uint64_t offset;     /* from the start of the file */
+    uint64_t nbytes;     /* 0 for a type this reader does not size */
+    const void *data;    /* inside the mapping; valid until ib_gguf_close */
+} ib_gguf_tensor_info;
+
+IB_API int32_t ib_gguf_open(const char *path, ib_gguf **out);
+IB_API int32_t ib_gguf_open_memory(const void *bytes, uint64_t nbytes, ib_gguf **out);   /* the caller keeps the bytes alive */
+IB_API int32_t ib_gguf_close(ib_gguf *g);
+IB_API int32_t ib_gguf_counts(const ib_gguf *g, uint32_t *version, uint64_t *n_tensors, uint64_t *n_metadata, uint32_t *alignment);
+IB_API int32_t ib_gguf_tensor_by_name(const ib_gguf *g, const char *name, ib_gguf_tensor_info *info);
+IB_API int32_t ib_gguf_tensor_by_index(const ib_gguf *g, uint64_t index, char *name_out, uint64_t name_cap, ib_gguf_tensor_info *info);
+/* Metadata (gguf.rs:397-513).  Value type ids: 0 U8, 1 I8, 2 U16, 3 I16, 4 U32, 5 I32, 6 F32, 7 Bool, 8 String, 9 Array,
+ * 10 U64, 11 I64, 12 F64.  Numbers of any type read as u64 (two's complement for signed) or f64. */
+IB_API int32_t ib_gguf_meta_key(const ib_gguf *g, uint64_t index, char *key_out, uint64_t key_cap, int32_t *type);
+IB_API int32_t ib_gguf_meta_u64(const ib_gguf *g, const char *key, uint64_t *value);
+IB_API int32_t ib_gguf_meta_f64(const ib_gguf *g, const char *key, double *value);
+IB_API int32_t ib_gguf_meta_str(const ib_gguf *g, const char *key, char *out, uint64_t cap, uint64_t *len);
+IB_API int32_t ib_gguf_meta_array(const ib_gguf *g, const char *key, int32_t *elem_type, uint64_t *count, const void **data);
+IB_API int32_t ib_gguf_meta_array_str(ib_gguf *g, const char *key, uint64_t index, char *out, uint64_t cap, uint64_t *len);
+/* `arch`: metadata prefix, null = "llama".  vocab_size = length of tokenizer.ggml.tokens (rows of token_embd.weight when
+ * the file carries no tokenizer); rope_theta and rms_norm_eps default to 10000 and 1e-6 as in the reference. */
+IB_API int32_t ib_gguf_llama_config(const ib_gguf *g, const char *arch, ib_llama_config *out);
+/* Uploads this rank's share of every tensor and creates the model, which owns the uploaded weights (ib_llama_destroy frees
+ * them; the file may be closed afterwards).  `max_context` > 0 caps the KV cache below the file's context length.
+ * With tp_size > 1 continue with ib_llama_tp_export / ib_llama_tp_connect. */
+IB_API int32_t ib_gguf_load_llama(ib_ctx *ctx, const ib_gguf *g, const char *arch, int32_t kv_dtype, uint32_t max_context, int32_t tp_rank,
+                                  int32_t tp_size, ib_llama **out);
+
 #ifdef __cplusplus
 }
 #endif

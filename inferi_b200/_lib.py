@@ -45,6 +45,12 @@ class LlamaWeights(C.Structure):
     _fields_ = [("layers", C.POINTER(LlamaLayerWeights)), ("token_embd", C.c_void_p), ("output", C.c_void_p), ("output_norm_dev", C.c_void_p)]
 
 
+class GgufTensorInfo(C.Structure):
+    """= ib_gguf_tensor_info: dims slowest first ([rows, cols] for a matrix), as the reference keeps them (gguf.rs:587-593)."""
+    _fields_ = [("type", C.c_int32), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("offset", C.c_uint64), ("nbytes", C.c_uint64),
+                ("data", C.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/inferi_b200.h declares
 _vp, _u32, _u64, _i32, _f = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float
 SIGNATURES = {
@@ -77,6 +83,20 @@ SIGNATURES = {
     "ib_llama_state": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "ib_llama_tp_export": (_i32, [_vp, _vp]),
     "ib_llama_tp_connect": (_i32, [_vp, _vp]),
+    "ib_gguf_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
+    "ib_gguf_open_memory": (_i32, [_vp, _u64, C.POINTER(_vp)]),
+    "ib_gguf_close": (_i32, [_vp]),
+    "ib_gguf_counts": (_i32, [_vp, C.POINTER(_u32), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32)]),
+    "ib_gguf_tensor_by_name": (_i32, [_vp, C.c_char_p, C.POINTER(GgufTensorInfo)]),
+    "ib_gguf_tensor_by_index": (_i32, [_vp, _u64, C.c_char_p, _u64, C.POINTER(GgufTensorInfo)]),
+    "ib_gguf_meta_key": (_i32, [_vp, _u64, C.c_char_p, _u64, C.POINTER(_i32)]),
+    "ib_gguf_meta_u64": (_i32, [_vp, C.c_char_p, C.POINTER(_u64)]),
+    "ib_gguf_meta_f64": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "ib_gguf_meta_str": (_i32, [_vp, C.c_char_p, C.c_char_p, _u64, C.POINTER(_u64)]),
+    "ib_gguf_meta_array": (_i32, [_vp, C.c_char_p, C.POINTER(_i32), C.POINTER(_u64), C.POINTER(_vp)]),
+    "ib_gguf_meta_array_str": (_i32, [_vp, C.c_char_p, _u64, C.c_char_p, _u64, C.POINTER(_u64)]),
+    "ib_gguf_llama_config": (_i32, [_vp, C.c_char_p, C.POINTER(LlamaConfig)]),
+    "ib_gguf_load_llama": (_i32, [_vp, _vp, C.c_char_p, _i32, _u32, _i32, _i32, C.POINTER(_vp)]),
 }
 
 _lib = None

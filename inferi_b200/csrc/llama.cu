@@ -130,6 +130,9 @@ struct ib_llama {
     ib::TokenProgram prog{};
     ib::TokenKernelPlan plan{};
     bool use_token_kernel = false;
+    // tensors and device vectors the model owns (a model loaded from a GGUF file frees its weights with itself)
+    std::vector<ib_qtensor *> owned_tensors;
+    std::vector<void *> owned_device;
 };
 
 namespace ib {
@@ -309,6 +312,13 @@ static int32_t check_matrix(const ib_qtensor *t, const char *name, uint64_t rows
 
 }  // namespace ib
 
+namespace ib {
+void llama_adopt(ib_llama *m, std::vector<ib_qtensor *> &&tensors, std::vector<void *> &&device) {
+    m->owned_tensors = std::move(tensors);
+    m->owned_device = std::move(device);
+}
+}  // namespace ib
+
 extern "C" {
 
 static int32_t finish_graph(ib_llama *m);
@@ -331,6 +341,8 @@ int32_t ib_llama_destroy(ib_llama *m) {
     for (void *b : m->v_cache)
         if (b) cudaFree(b);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
+    for (ib_qtensor *t : m->owned_tensors) ib_qtensor_destroy(t);
+    for (void *b : m->owned_device) cudaFree(b);
     delete m;
     return IB_OK;
 }

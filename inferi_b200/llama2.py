@@ -169,6 +169,19 @@ class Llama2:
             from . import tp
             tp.connect(self, group)      # every rank of the group must get here
 
+    @classmethod
+    def from_handle(cls, backend: Backend, cfg: Llama2Config, handle, tp_rank: int = 0, tp_size: int = 1, group=None) -> "Llama2":
+        """Wraps a model the library created itself (the GGUF loader); the model owns its weights."""
+        self = cls.__new__(cls)
+        self.backend, self.cfg, self.weights, self.lib, self._arr = backend, cfg, None, backend.lib, None
+        self.handle = handle
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        self.vocab_local = cfg.vocab_size // tp_size
+        if tp_size > 1:
+            from . import tp
+            tp.connect(self, group)
+        return self
+
     def forward(self, token: int, pos: int, want_logits: bool = False):
         """One token at `pos`; returns (next_token, logits | None).  Host round trip per call, as in the reference."""
         nxt = C.c_uint32()

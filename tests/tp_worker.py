@@ -31,7 +31,15 @@ def main():
     mine = tp.shard_weights(cfg, full, rank, world)
     be = Backend(local)
     shapes = tp.shard_shapes(cfg, world, Q4_K_M["ffn_down"])
-    model = Llama2(be, cfg, Llama2Weights(be, cfg, mine, shapes=shapes), kv_f16=True, tp_rank=rank, tp_size=world)
+    path = os.environ.get("TP_FROM_GGUF")
+    if path:
+        # every rank maps the same file and uploads its slice itself (the library cuts the GGUF bytes)
+        from inferi_b200.gguf import Gguf
+        f = Gguf(path)
+        model = f.load_llama(be, kv_f16=True, tp_rank=rank, tp_size=world)
+        f.close()
+    else:
+        model = Llama2(be, cfg, Llama2Weights(be, cfg, mine, shapes=shapes), kv_f16=True, tp_rank=rank, tp_size=world)
     prompt = [7, 900, 33, 512]
     n_gen = 20
     ids = model.generate(prompt, n_gen).tolist()
