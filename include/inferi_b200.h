@@ -38,7 +38,9 @@ enum {
 };
 
 /* GGUF tensor type ids (crates/inferi/src/gguf.rs:74-106). */
-enum { IB_F32 = 0, IB_Q8_0 = 8, IB_Q4_K = 12, IB_Q5_K = 13, IB_Q6_K = 14 };
+/* Q8_0, Q4_K, Q5_K, Q6_K run on the streaming kernels (the token loop needs them); Q4_0, Q4_1, Q5_0, Q5_1, Q8_K complete the
+ * reference's `GpuQuantTensor` variants at the op level (ib_gemv_quant) on the generic kernel. */
+enum { IB_F32 = 0, IB_Q4_0 = 2, IB_Q4_1 = 3, IB_Q5_0 = 6, IB_Q5_1 = 7, IB_Q8_0 = 8, IB_Q4_K = 12, IB_Q5_K = 13, IB_Q6_K = 14, IB_Q8_K = 15 };
 
 /* KV-cache element type.  F32 is the reference's layout (crates/inferi/src/models/llama2/transformer.rs:85-104);
  * F16 halves the cache traffic and is what the throughput figures are quoted on. */

@@ -144,7 +144,7 @@ int32_t ib_qtensor_upload(ib_ctx *ctx, int32_t qtype, uint64_t rows, uint64_t co
     *out = nullptr;
     IB_REQUIRE(gguf_blocks != nullptr, "ib_qtensor_upload: null data pointer");
     const uint32_t be = block_elems(qtype), bb = block_bytes(qtype);
-    IB_REQUIRE(be != 0, "ib_qtensor_upload: unsupported tensor type id %d (supported: F32=0, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14)", qtype);
+    IB_REQUIRE(be != 0, "ib_qtensor_upload: unsupported tensor type id %d (supported: F32=0, Q4_0=2, Q4_1=3, Q5_0=6, Q5_1=7, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14, Q8_K=15)", qtype);
     IB_REQUIRE(rows > 0 && cols > 0, "ib_qtensor_upload: empty matrix %llux%llu", (unsigned long long)rows, (unsigned long long)cols);
     // the reference truncates rows/4 silently (crates/inferi/src/ops/gemv_quant.rs:271); here it is an error
     IB_REQUIRE(rows % 4 == 0, "ib_qtensor_upload: rows=%llu must be a multiple of 4", (unsigned long long)rows);

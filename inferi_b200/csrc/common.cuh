@@ -41,21 +41,26 @@ constexpr int QK_K = 256;
 //   Q6_K: [8 x 128 B ql][8 x 64 B qh][8 x 16 B scales][8 x 2 B f16 d]       = 1680 B per 2048 columns
 enum Layout : uint32_t { LAYOUT_GGUF = 0, LAYOUT_SOA = 1 };
 
-inline uint32_t block_bytes(int qtype) {
+__host__ __device__ inline uint32_t block_bytes(int qtype) {
     switch (qtype) {
     case IB_F32: return 4;
     case IB_Q8_0: return 34;
     case IB_Q4_K: return 144;
     case IB_Q5_K: return 176;
     case IB_Q6_K: return 210;
+    case IB_Q4_0: return 18;
+    case IB_Q4_1: return 20;
+    case IB_Q5_0: return 22;
+    case IB_Q5_1: return 24;
+    case IB_Q8_K: return 292;
     default: return 0;
     }
 }
-inline uint32_t block_elems(int qtype) {
+__host__ __device__ inline uint32_t block_elems(int qtype) {
     switch (qtype) {
     case IB_F32: return 1;
-    case IB_Q8_0: return 32;
-    case IB_Q4_K: case IB_Q5_K: case IB_Q6_K: return QK_K;
+    case IB_Q8_0: case IB_Q4_0: case IB_Q4_1: case IB_Q5_0: case IB_Q5_1: return 32;
+    case IB_Q4_K: case IB_Q5_K: case IB_Q6_K: case IB_Q8_K: return QK_K;
     default: return 0;
     }
 }

@@ -409,6 +409,24 @@ __device__ float generic_block_dot(int qtype, const uint8_t *b, const float *__r
                 acc += (d2 * (float)hi - m2) * v[64 * c + 32 + l];
             }
         }
+    } else if (qtype == IB_Q4_0 || qtype == IB_Q4_1 || qtype == IB_Q5_0 || qtype == IB_Q5_1) {
+        // crates/inferi/src/quantization.rs:68-82, 96-111, 125-142, 157-175: 32 elements, low nibbles first, optional
+        // minimum (the _1 types) and fifth bit (the Q5 types)
+        const bool has_m = qtype == IB_Q4_1 || qtype == IB_Q5_1, five = qtype == IB_Q5_0 || qtype == IB_Q5_1;
+        const float d = ld_h(b), m = has_m ? ld_h(b + 2) : 0.f;
+        const uint8_t *qhp = b + (has_m ? 4 : 2), *qs = qhp + (five ? 4 : 0);
+        const uint32_t qh = five ? ((uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24)) : 0u;
+        const int off = has_m ? 0 : (five ? 16 : 8);
+        for (int j = 0; j < 16; j++) {
+            const uint32_t x0 = (qs[j] & 0x0Fu) | (((qh >> j) << 4) & 0x10u), x1 = (uint32_t)(qs[j] >> 4) | ((qh >> (j + 12)) & 0x10u);
+            acc += ((float)((int)x0 - off) * d + m) * v[j];
+            acc += ((float)((int)x1 - off) * d + m) * v[j + 16];
+        }
+    } else if (qtype == IB_Q8_K) {
+        // crates/inferi/src/quantization.rs:205-211: f32 scale, 256 int8 quants (the block sums are not used by the GEMV)
+        float d;
+        memcpy(&d, b, 4);
+        for (int j = 0; j < 256; j++) acc += (d * (float)(int8_t)b[4 + j]) * v[j];
     } else if (qtype == IB_Q6_K) {
         const uint8_t *ql = b, *qh = b + 128;
         const int8_t *sc = reinterpret_cast<const int8_t *>(b + 192);
@@ -441,7 +459,7 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const uint8_t *__rest
         const float *fr = reinterpret_cast<const float *>(row);
         for (uint32_t c = lane; c < cols; c += 32) acc += fr[c] * v[c];
     } else {
-        const uint32_t be = (qtype == IB_Q8_0) ? 32 : 256, bb = (qtype == IB_Q8_0) ? 34 : (qtype == IB_Q4_K ? 144 : (qtype == IB_Q5_K ? 176 : 210));
+        const uint32_t be = block_elems(qtype), bb = block_bytes(qtype);
         for (uint32_t b = lane; b < cols / be; b += 32) acc += generic_block_dot(qtype, row + (size_t)b * bb, v + (size_t)b * be);
     }
 #pragma unroll

@@ -419,6 +419,13 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
         }
     }
     FAIL_IF(check_matrix(weights->token_embd, "token_embd", c.vocab_size, c.hidden_size, false));
+    {
+        const int tq = weights->token_embd->qtype;
+        if (tq != IB_F32 && tq != IB_Q8_0 && tq != IB_Q4_K && tq != IB_Q5_K && tq != IB_Q6_K) {
+            ib_llama_destroy(m);
+            return set_error(IB_ERR_UNSUPPORTED, "ib_llama_create: token_embd of type %d (the embedding look-up takes F32, Q8_0, Q4_K, Q5_K, Q6_K)", tq);
+        }
+    }
     m->token_embd = weights->token_embd;
     m->output = weights->output ? weights->output : weights->token_embd;  // tied classifier: transformer.rs:376-382
     FAIL_IF(check_matrix(m->output, "output", m->vocab_l, c.hidden_size, true));

@@ -12,11 +12,12 @@ import torch
 
 # GGUF tensor type ids (crates/inferi/src/gguf.rs:74-106)
 F32, Q8_0, Q4_K, Q5_K, Q6_K = 0, 8, 12, 13, 14
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_K = 2, 3, 6, 7, 15   # op-level only (generic kernel); the token loop takes the five above
 QK_K = 256
 
-BLOCK_BYTES = {F32: 4, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210}
-BLOCK_ELEMS = {F32: 1, Q8_0: 32, Q4_K: QK_K, Q5_K: QK_K, Q6_K: QK_K}
-NAMES = {F32: "F32", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
+BLOCK_BYTES = {F32: 4, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_K: 292}
+BLOCK_ELEMS = {F32: 1, Q8_0: 32, Q4_K: QK_K, Q5_K: QK_K, Q6_K: QK_K, Q4_0: 32, Q4_1: 32, Q5_0: 32, Q5_1: 32, Q8_K: QK_K}
+NAMES = {F32: "F32", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", Q4_0: "Q4_0", Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q8_K: "Q8_K"}
 
 
 def row_bytes(qtype: int, cols: int) -> int:
@@ -67,6 +68,14 @@ def random_blocks(qtype: int, rows: int, cols: int, seed: int, scale: float = 0.
         put_u16(2, f16_scales(nb))
     elif qtype == Q6_K:
         put_u16(208, f16_scales(nb))
+    elif qtype in (Q4_0, Q5_0):
+        put_u16(0, f16_scales(nb))
+    elif qtype in (Q4_1, Q5_1):
+        put_u16(0, f16_scales(nb))
+        put_u16(2, f16_scales(nb))
+    elif qtype == Q8_K:
+        d = (np.abs(rng.standard_normal(nb)).astype(np.float32) * scale).view(np.uint8).reshape(nb, 4)   # f32 scale (random bytes could be NaN)
+        blocks[:, 0:4] = d
     else:
         raise ValueError(f"unsupported qtype {qtype}")
     return blocks.reshape(rows, -1)

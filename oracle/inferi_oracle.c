@@ -29,7 +29,7 @@
 
 #define QK_K 256
 
-enum { ORC_F32 = 0, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q5_K = 13, ORC_Q6_K = 14 };
+enum { ORC_F32 = 0, ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q5_K = 13, ORC_Q6_K = 14, ORC_Q8_K = 15 };
 
 /* ---- block formats: crates/inferi/src/quantization.rs:42-45, 217-222, 262-268, 335-340 ---- */
 #pragma pack(push, 1)
@@ -37,6 +37,11 @@ typedef struct { uint16_t scale; int8_t data[32]; } blk_q8_0;                   
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[128]; } blk_q4_k;             /* 144 B */
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; } blk_q5_k; /* 176 B */
 typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; } blk_q6_k;    /* 210 B */
+typedef struct { uint16_t d; uint8_t qs[16]; } blk_q4_0;                                        /* 18 B  */
+typedef struct { uint16_t d, m; uint8_t qs[16]; } blk_q4_1;                                     /* 20 B  */
+typedef struct { uint16_t d; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_0;                         /* 22 B  */
+typedef struct { uint16_t d, m; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_1;                      /* 24 B  */
+typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8_k;                        /* 292 B */
 #pragma pack(pop)
 
 size_t orc_block_bytes(int qtype) {
@@ -46,6 +51,11 @@ size_t orc_block_bytes(int qtype) {
     case ORC_Q4_K: return sizeof(blk_q4_k);
     case ORC_Q5_K: return sizeof(blk_q5_k);
     case ORC_Q6_K: return sizeof(blk_q6_k);
+    case ORC_Q4_0: return sizeof(blk_q4_0);
+    case ORC_Q4_1: return sizeof(blk_q4_1);
+    case ORC_Q5_0: return sizeof(blk_q5_0);
+    case ORC_Q5_1: return sizeof(blk_q5_1);
+    case ORC_Q8_K: return sizeof(blk_q8_k);
     default: return 0;
     }
 }
@@ -53,8 +63,8 @@ size_t orc_block_bytes(int qtype) {
 size_t orc_block_elems(int qtype) {
     switch (qtype) {
     case ORC_F32: return 1;
-    case ORC_Q8_0: return 32;
-    case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: return QK_K;
+    case ORC_Q8_0: case ORC_Q4_0: case ORC_Q4_1: case ORC_Q5_0: case ORC_Q5_1: return 32;
+    case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: case ORC_Q8_K: return QK_K;
     default: return 0;
     }
 }
@@ -161,8 +171,58 @@ static void deq_q6_k(const blk_q6_k *b, float *out) {
     }
 }
 
+/* crates/inferi/src/quantization.rs:68-82 (BlockQ4_0::dequantize). */
+static void deq_q4_0(const blk_q4_0 *b, float *out) {
+    float d = orc_decode_f16(b->d);
+    for (int j = 0; j < 16; j++) {
+        out[j] = (float)((int)(b->qs[j] & 0x0F) - 8) * d;
+        out[j + 16] = (float)((int)(b->qs[j] >> 4) - 8) * d;
+    }
+}
+
+/* crates/inferi/src/quantization.rs:96-111 (BlockQ4_1::dequantize). */
+static void deq_q4_1(const blk_q4_1 *b, float *out) {
+    float d = orc_decode_f16(b->d), m = orc_decode_f16(b->m);
+    for (int j = 0; j < 16; j++) {
+        out[j] = (float)(b->qs[j] & 0x0F) * d + m;
+        out[j + 16] = (float)(b->qs[j] >> 4) * d + m;
+    }
+}
+
+/* crates/inferi/src/quantization.rs:125-142 (BlockQ5_0::dequantize). */
+static void deq_q5_0(const blk_q5_0 *b, float *out) {
+    float d = orc_decode_f16(b->d);
+    uint32_t qh; memcpy(&qh, b->qh, 4);
+    for (int j = 0; j < 16; j++) {
+        uint32_t xh0 = ((qh >> j) << 4) & 0x10, xh1 = (qh >> (j + 12)) & 0x10;
+        out[j] = (float)((int)((b->qs[j] & 0x0Fu) | xh0) - 16) * d;
+        out[j + 16] = (float)((int)((uint32_t)(b->qs[j] >> 4) | xh1) - 16) * d;
+    }
+}
+
+/* crates/inferi/src/quantization.rs:157-175 (BlockQ5_1::dequantize). */
+static void deq_q5_1(const blk_q5_1 *b, float *out) {
+    float d = orc_decode_f16(b->d), m = orc_decode_f16(b->m);
+    uint32_t qh; memcpy(&qh, b->qh, 4);
+    for (int j = 0; j < 16; j++) {
+        uint32_t xh0 = ((qh >> j) << 4) & 0x10, xh1 = (qh >> (j + 12)) & 0x10;
+        out[j] = (float)((b->qs[j] & 0x0Fu) | xh0) * d + m;
+        out[j + 16] = (float)((uint32_t)(b->qs[j] >> 4) | xh1) * d + m;
+    }
+}
+
+/* crates/inferi/src/quantization.rs:205-211 (BlockQ8K::dequantize). */
+static void deq_q8_k(const blk_q8_k *b, float *out) {
+    for (int j = 0; j < QK_K; j++) out[j] = b->d * (float)b->qs[j];
+}
+
 static void deq_block(int qtype, const uint8_t *blk, float *out) {
     switch (qtype) {
+    case ORC_Q4_0: deq_q4_0((const blk_q4_0 *)blk, out); break;
+    case ORC_Q4_1: deq_q4_1((const blk_q4_1 *)blk, out); break;
+    case ORC_Q5_0: deq_q5_0((const blk_q5_0 *)blk, out); break;
+    case ORC_Q5_1: deq_q5_1((const blk_q5_1 *)blk, out); break;
+    case ORC_Q8_K: deq_q8_k((const blk_q8_k *)blk, out); break;
     case ORC_Q8_0: deq_q8_0((const blk_q8_0 *)blk, out); break;
     case ORC_Q4_K: deq_q4_k((const blk_q4_k *)blk, out); break;
     case ORC_Q5_K: deq_q5_k((const blk_q5_k *)blk, out); break;

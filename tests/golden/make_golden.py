@@ -20,13 +20,16 @@ from gguf.quants import dequantize  # noqa: E402
 from inferi_b200 import quant  # noqa: E402
 
 GG = {quant.Q8_0: gguf.GGMLQuantizationType.Q8_0, quant.Q4_K: gguf.GGMLQuantizationType.Q4_K,
-      quant.Q5_K: gguf.GGMLQuantizationType.Q5_K, quant.Q6_K: gguf.GGMLQuantizationType.Q6_K}
+      quant.Q5_K: gguf.GGMLQuantizationType.Q5_K, quant.Q6_K: gguf.GGMLQuantizationType.Q6_K,
+      quant.Q4_0: gguf.GGMLQuantizationType.Q4_0, quant.Q4_1: gguf.GGMLQuantizationType.Q4_1,
+      quant.Q5_0: gguf.GGMLQuantizationType.Q5_0, quant.Q5_1: gguf.GGMLQuantizationType.Q5_1}
 ROWS, COLS = 4, 512
 
 
 def main():
     out = {}
-    for qt in (quant.Q8_0, quant.Q4_K, quant.Q5_K, quant.Q6_K):
+    # (Q8_K is not in the gguf package's dequantizers: its pin is the closed form d * q in tests/test_oracle.py)
+    for qt in (quant.Q8_0, quant.Q4_K, quant.Q5_K, quant.Q6_K, quant.Q4_0, quant.Q4_1, quant.Q5_0, quant.Q5_1):
         name = quant.NAMES[qt]
         # a quarter of the f16 scales in the subnormal range, as the reference's test helper does
         blocks = quant.random_blocks(qt, ROWS, COLS, seed=7000 + qt, subnormal_frac=0.25)

@@ -13,6 +13,7 @@ from inferi_b200.ops import GemvQuant, GpuQuantTensor, InferiError
 pytestmark = pytest.mark.gpu
 GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "blocks.npz"))
 QTYPES = [quant.Q8_0, quant.Q4_K, quant.Q5_K, quant.Q6_K]
+LEGACY = [quant.Q4_0, quant.Q4_1, quant.Q5_0, quant.Q5_1]   # the reference's other GpuQuantTensor variants (op level, generic kernel)
 
 
 def run_gemv(backend, qt, rows, cols, blocks, v):
@@ -25,7 +26,7 @@ def run_gemv(backend, qt, rows, cols, blocks, v):
     return res
 
 
-@pytest.mark.parametrize("qt", QTYPES)
+@pytest.mark.parametrize("qt", QTYPES + LEGACY)
 def test_golden_vectors(backend, qt):
     n = quant.NAMES[qt]
     rows, cols = GOLDEN[f"{n}_deq"].shape
@@ -42,6 +43,17 @@ def test_golden_vectors(backend, qt):
     (quant.Q5_K, 296, 4096), (quant.Q4_K, 300, 6144), (quant.Q6_K, 1184, 4096), (quant.Q4_K, 2372, 2048), (quant.Q4_K, 16, 16384), (quant.Q4_K, 16, 16640), (quant.Q5_K, 12, 14336), (quant.Q4_K, 8, 32768), (quant.Q4_K, 8, 33024),
 ])
 def test_reference_test_shapes_and_edges(backend, qt, rows, cols):
+    _shape_case(backend, qt, rows, cols)
+
+
+# the legacy formats at the shape of the reference's tests (gemv_quant.rs:502-816: 64 x 256; Q8_K blocks span 256 columns)
+# and at a layer-sized one
+@pytest.mark.parametrize("qt,rows,cols", [(q, 64, 256) for q in LEGACY + [quant.Q8_K]] + [(q, 512, 4096) for q in LEGACY + [quant.Q8_K]])
+def test_legacy_formats(backend, qt, rows, cols):
+    _shape_case(backend, qt, rows, cols)
+
+
+def _shape_case(backend, qt, rows, cols):
     blocks = quant.random_blocks(qt, rows, cols, seed=rows * 31 + cols + qt, scale=1.0, subnormal_frac=0.25)
     v = np.random.default_rng(cols).standard_normal(cols).astype(np.float32)
     got = run_gemv(backend, qt, rows, cols, blocks, v)

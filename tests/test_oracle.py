@@ -10,9 +10,10 @@ from inferi_b200 import quant
 
 GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "blocks.npz"))
 QTYPES = [quant.Q8_0, quant.Q4_K, quant.Q5_K, quant.Q6_K]
+LEGACY = [quant.Q4_0, quant.Q4_1, quant.Q5_0, quant.Q5_1]          # op-level formats with golden vectors from the gguf package
 
 
-@pytest.mark.parametrize("qt", QTYPES)
+@pytest.mark.parametrize("qt", QTYPES + LEGACY)
 def test_dequantize_matches_golden_bit_for_bit(qt):
     n = quant.NAMES[qt]
     blocks, deq = GOLDEN[f"{n}_blocks"], GOLDEN[f"{n}_deq"]
@@ -32,12 +33,35 @@ def test_gemv_ref_and_shader_match_golden(qt):
     assert np.abs(sh - want).max() <= 2e-6 * scale                 # f32 lane partials + tree
 
 
-@pytest.mark.parametrize("qt", QTYPES)
+@pytest.mark.parametrize("qt", LEGACY)
+def test_legacy_gemv_ref_matches_golden(qt):
+    n = quant.NAMES[qt]
+    blocks, v, want = GOLDEN[f"{n}_blocks"], GOLDEN[f"{n}_v"], GOLDEN[f"{n}_gemv"]
+    rows, cols = GOLDEN[f"{n}_deq"].shape
+    assert np.array_equal(oracle.gemv_ref(qt, rows, cols, blocks, v), want.astype(np.float32))
+
+
+def test_q8_k_dequantize_closed_form():
+    """Q8_K (crates/inferi/src/quantization.rs:205-211): f32 scale times int8 quants; the 16 block sums are not used."""
+    blocks = quant.random_blocks(quant.Q8_K, 8, 512, seed=123)
+    b = blocks.reshape(-1, 292)
+    d = b[:, :4].copy().view(np.float32)
+    want = (d * b[:, 4:260].view(np.int8).astype(np.float32)).reshape(-1)
+    mine = oracle.dequantize(quant.Q8_K, blocks, want.size)
+    assert np.array_equal(mine.view(np.uint32), want.view(np.uint32))
+    v = np.random.default_rng(1).standard_normal(512).astype(np.float32)
+    ref = oracle.gemv_ref(quant.Q8_K, 8, 512, blocks, v)
+    assert np.array_equal(ref, (want.reshape(8, 512).astype(np.float64) @ v.astype(np.float64)).astype(np.float32))
+
+
+@pytest.mark.parametrize("qt", QTYPES + LEGACY)
 def test_dequantize_matches_gguf_package_on_fresh_blocks(qt):
     gguf = pytest.importorskip("gguf")
     from gguf.quants import dequantize
     gt = {quant.Q8_0: gguf.GGMLQuantizationType.Q8_0, quant.Q4_K: gguf.GGMLQuantizationType.Q4_K,
-          quant.Q5_K: gguf.GGMLQuantizationType.Q5_K, quant.Q6_K: gguf.GGMLQuantizationType.Q6_K}[qt]
+          quant.Q5_K: gguf.GGMLQuantizationType.Q5_K, quant.Q6_K: gguf.GGMLQuantizationType.Q6_K,
+          quant.Q4_0: gguf.GGMLQuantizationType.Q4_0, quant.Q4_1: gguf.GGMLQuantizationType.Q4_1,
+          quant.Q5_0: gguf.GGMLQuantizationType.Q5_0, quant.Q5_1: gguf.GGMLQuantizationType.Q5_1}[qt]
     blocks = quant.random_blocks(qt, 64, 512, seed=99 + qt, subnormal_frac=0.25)
     want = dequantize(blocks, gt).reshape(-1).astype(np.float32)
     mine = oracle.dequantize(qt, blocks, want.size)
