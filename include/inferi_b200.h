@@ -135,6 +135,13 @@ IB_API int32_t ib_attention_static(void *stream, const ib_attn_params *params, c
  * device: index of the largest logit, lowest index on ties. */
 IB_API int32_t ib_argmax(ib_ctx *ctx, void *stream, const float *logits_dev, uint32_t n, uint32_t *out_dev);
 
+/* Replaces the non-greedy branches of `Sampler::sample` (crates/inferi/src/models/sampler.rs:32-52): logits / temperature,
+ * softmax (crates/inferi/src/ops/softmax.rs:130-143), then `sample_mult` (:62-77) when topp <= 0 or >= 1, else
+ * `sample_topp` (:84-129), all on the device; `coin` in [0, 1) is the caller's random number (the reference draws it
+ * with rand::random()).  temperature == 0 is the arg-max.  The logits are not modified. */
+IB_API int32_t ib_sample(ib_ctx *ctx, void *stream, const float *logits_dev, uint32_t n, float temperature, float topp, float coin,
+                         uint32_t *out_dev);
+
 /* = `Llama2Config` (crates/inferi/src/models/llama2/cpu.rs:46-66). */
 typedef struct ib_llama_config {
     uint32_t hidden_size;
@@ -199,6 +206,10 @@ IB_API int32_t ib_llama_tp_connect(ib_llama *model, const void *handles_by_rank)
 
 /* Device pointer of the last forward's logits (f32[vocab / tp_size]) and of the residual stream x (f32[hidden]);
  * for parity checks (the reference exposes `Llama2State::logits`, transformer.rs:15-43). */
+/* ≙ `Sampler::new(vocab, temperature, topp)` (models/sampler.rs:22-30) for the model's own token loop: after this,
+ * ib_llama_forward / ib_llama_generate feed back sampled tokens instead of the arg-max (temperature 0 = greedy again).
+ * The coin of a position is splitmix64(seed, position) -> [0, 1), so a run can be reproduced.  Single GPU only. */
+IB_API int32_t ib_llama_set_sampler(ib_llama *model, float temperature, float topp, uint64_t seed);
 IB_API int32_t ib_llama_state(ib_llama *model, const float **logits_dev, const float **x_dev);
 
 /* ---- GGUF container and GGUF -> device loader ----

@@ -76,6 +76,8 @@ SIGNATURES = {
     "ib_attention": (_i32, [_vp, _vp, C.POINTER(AttnParams), _vp, _vp, _vp, _i32, _vp]),
     "ib_attention_static": (_i32, [_vp, C.POINTER(AttnParams), _vp, _vp, _vp, _i32, _vp]),
     "ib_argmax": (_i32, [_vp, _vp, _vp, _u32, _vp]),
+    "ib_sample": (_i32, [_vp, _vp, _vp, _u32, _f, _f, _f, _vp]),
+    "ib_llama_set_sampler": (_i32, [_vp, _f, _f, _u64]),
     "ib_llama_create": (_i32, [_vp, C.POINTER(LlamaConfig), C.POINTER(LlamaWeights), _i32, _i32, _i32, C.POINTER(_vp)]),
     "ib_llama_destroy": (_i32, [_vp]),
     "ib_llama_forward": (_i32, [_vp, _vp, _u32, _u32, _vp, _vp]),

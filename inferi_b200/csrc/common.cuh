@@ -173,6 +173,10 @@ int32_t launch_silu_mul(ib_ctx *ctx, cudaStream_t s, float *h1, const float *h2,
 int32_t launch_add_assign(ib_ctx *ctx, cudaStream_t s, float *a, const float *b, uint32_t n);
 int32_t launch_argmax(ib_ctx *ctx, cudaStream_t s, const float *x, uint32_t n, uint32_t *out);
 int32_t ensure_argmax_scratch(ib_ctx *ctx);
+// sampler.cu
+int32_t launch_sample(ib_ctx *ctx, cudaStream_t s, const float *logits, uint32_t n, float temperature, float topp, uint64_t seed, const uint32_t *pos_ptr,
+                      float coin, float *probs, unsigned long long *keys, uint32_t *out, uint32_t *out2, uint32_t pdl);
+size_t sample_keys_capacity(uint32_t n);
 
 // attention.cu
 struct AttnLaunch {

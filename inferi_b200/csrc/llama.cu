@@ -130,6 +130,13 @@ struct ib_llama {
     ib::TokenProgram prog{};
     ib::TokenKernelPlan plan{};
     bool use_token_kernel = false;
+    // sampling beyond greedy (ib_llama_set_sampler): parameters, scratch, and the graph that carries the sampler node
+    float temperature = 0.f, topp = 0.f;
+    uint64_t sample_seed = 0;
+    float *sample_probs = nullptr;
+    unsigned long long *sample_keys = nullptr;
+    cudaGraphExec_t graph_exec_sample = nullptr;
+    uint64_t launches_per_token_sample = 0;
     // tensors and device vectors the model owns (a model loaded from a GGUF file frees its weights with itself)
     std::vector<ib_qtensor *> owned_tensors;
     std::vector<void *> owned_device;
@@ -283,6 +290,13 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
         }
     if ((rc = emit_gemv(p))) return rc;
     m->x_final = cur;
+    if (!collect && m->temperature > 0.f) {
+        // temperature / top-p sampling replaces the greedy token (models/sampler.rs:32-52); the coin is a function of
+        // (seed, position)
+        if ((rc = launch_sample(ctx, s, m->logits, c.vocab_size, m->temperature, m->topp, m->sample_seed, &m->ctl->pos, 0.f, m->sample_probs, m->sample_keys,
+                                &m->ctl->next, nullptr, pdl)))
+            return rc;
+    }
     if (!collect) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1);
@@ -322,12 +336,16 @@ void llama_adopt(ib_llama *m, std::vector<ib_qtensor *> &&tensors, std::vector<v
 extern "C" {
 
 static int32_t finish_graph(ib_llama *m);
+static int32_t capture_graph(ib_llama *m, cudaGraphExec_t *exec, uint64_t *launches_per_token);
 
 int32_t ib_llama_destroy(ib_llama *m) {
     if (!m) return IB_OK;
     cudaSetDevice(m->ctx->device);
     cudaDeviceSynchronize();
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+    if (m->graph_exec_sample) cudaGraphExecDestroy(m->graph_exec_sample);
+    if (m->sample_probs) cudaFree(m->sample_probs);
+    if (m->sample_keys) cudaFree(m->sample_keys);
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
     if (m->staged) cudaEventDestroy(m->staged);
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
@@ -572,27 +590,54 @@ static int32_t finish_graph(ib_llama *m) {
         }
         if (rc != IB_ERR_UNSUPPORTED) return rc;   // shapes outside the kernel's plan: the graph of separate kernels serves them
     }
+#undef CU
+    return capture_graph(m, &m->graph_exec, &m->launches_per_token);
+}
+
+// Records the token's kernels (with the sampler node when a temperature is set) into a graph and instantiates it.
+static int32_t capture_graph(ib_llama *m, cudaGraphExec_t *exec, uint64_t *launches_per_token) {
+    ib_ctx *ctx = m->ctx;
     const uint64_t before = ctx->launches;
-    CU(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
+    IB_CHECK_CUDA(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
     // INFERI_B200_NO_PDL=1 records the graph with plain kernel-to-kernel dependencies (for comparisons)
     const char *no_pdl = getenv("INFERI_B200_NO_PDL");
-    rc = record_token(m, m->own_stream, (no_pdl && no_pdl[0] == '1') ? 0 : 1);
+    const int32_t rc = record_token(m, m->own_stream, (no_pdl && no_pdl[0] == '1') ? 0 : 1);
     cudaGraph_t graph = nullptr;
     cudaError_t ce = cudaStreamEndCapture(m->own_stream, &graph);
-    m->launches_per_token = ctx->launches - before;
+    *launches_per_token = ctx->launches - before;
     ctx->launches = before;  // recording is not launching
     if (rc != IB_OK) {
         if (graph) cudaGraphDestroy(graph);
         return rc;
     }
     if (ce != cudaSuccess) return set_error(IB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
-    ce = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+    ce = cudaGraphInstantiate(exec, graph, 0);
     cudaGraphDestroy(graph);
     if (ce != cudaSuccess) {
-        m->graph_exec = nullptr;
+        *exec = nullptr;
         return set_error(IB_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(ce));
     }
-#undef CU
+    return IB_OK;
+}
+
+int32_t ib_llama_set_sampler(ib_llama *m, float temperature, float topp, uint64_t seed) {
+    IB_REQUIRE(m, "ib_llama_set_sampler: null model");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    IB_REQUIRE(temperature >= 0.f, "ib_llama_set_sampler: negative temperature");
+    if (temperature > 0.f) {
+        if (m->tp_size > 1) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_set_sampler: sampling needs the whole vocabulary on one GPU (tensor-parallel models are greedy)");
+        if (m->use_token_kernel) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_set_sampler: the whole-token kernel is greedy; unset INFERI_B200_TOKEN_KERNEL");
+    }
+    IB_CHECK_CUDA(cudaDeviceSynchronize());
+    if (m->graph_exec_sample) { cudaGraphExecDestroy(m->graph_exec_sample); m->graph_exec_sample = nullptr; }
+    m->temperature = temperature; m->topp = topp; m->sample_seed = seed;
+    if (temperature == 0.f) return IB_OK;   // greedy: the graph recorded at creation
+    if (!m->sample_probs) {
+        IB_CHECK_CUDA(cudaMalloc(&m->sample_probs, sizeof(float) * m->cfg.vocab_size));
+        IB_CHECK_CUDA(cudaMalloc(&m->sample_keys, sizeof(unsigned long long) * sample_keys_capacity(m->cfg.vocab_size)));
+    }
+    const int32_t rc = capture_graph(m, &m->graph_exec_sample, &m->launches_per_token_sample);
+    if (rc != IB_OK) { m->temperature = 0.f; return rc; }
     return IB_OK;
 }
 
@@ -644,9 +689,10 @@ static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, u
         }
         return IB_OK;
     }
+    const bool sampled = m->temperature > 0.f && m->graph_exec_sample;
     for (uint32_t i = 0; i < n_steps; i++) {
-        IB_CHECK_CUDA(cudaGraphLaunch(m->graph_exec, s));
-        m->ctx->launches += m->launches_per_token;
+        IB_CHECK_CUDA(cudaGraphLaunch(sampled ? m->graph_exec_sample : m->graph_exec, s));
+        m->ctx->launches += sampled ? m->launches_per_token_sample : m->launches_per_token;
     }
     return IB_OK;
 }

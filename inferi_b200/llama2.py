@@ -182,6 +182,11 @@ class Llama2:
             tp.connect(self, group)
         return self
 
+    def set_sampler(self, temperature: float, topp: float = 0.0, seed: int = 0) -> None:
+        """≙ `Sampler::new(vocab, temperature, topp)` for the model's own token loop: forward / generate then feed back sampled
+        tokens (temperature 0 = greedy).  The coin of a position is a function of (seed, position)."""
+        check(self.lib.ib_llama_set_sampler(self.handle, float(temperature), float(topp), int(seed)))
+
     def forward(self, token: int, pos: int, want_logits: bool = False):
         """One token at `pos`; returns (next_token, logits | None).  Host round trip per call, as in the reference."""
         nxt = C.c_uint32()

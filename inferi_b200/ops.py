@@ -212,3 +212,20 @@ def argmax(backend: Backend, logits: torch.Tensor, out: torch.Tensor) -> None:
     if not (out.is_cuda and out.element_size() == 4):
         raise InferiError(1, "argmax: out must be a 4-byte CUDA tensor")
     check(backend.lib.ib_argmax(backend.handle, _stream_ptr(), _f32_dev(logits, "logits"), logits.numel(), out.data_ptr()))
+
+
+class Sampler:
+    """≙ `Sampler` (crates/inferi/src/models/sampler.rs:14-52) with the logits left on the device.  `coin` in [0, 1) is the
+    caller's random number; temperature 0 is the greedy arg-max."""
+
+    def __init__(self, backend: Backend, vocab_size: int, temperature: float, topp: float):
+        self.backend, self.vocab_size, self.temperature, self.topp = backend, vocab_size, float(temperature), float(topp)
+
+    def sample(self, logits: torch.Tensor, coin: float, out: torch.Tensor | None = None) -> torch.Tensor:
+        if logits.numel() != self.vocab_size:
+            raise ValueError(f"expected {self.vocab_size} logits, got {logits.numel()}")
+        out = out if out is not None else torch.empty(1, dtype=torch.int32, device=logits.device)
+        check(self.backend.lib.ib_sample(self.backend.handle, _stream_ptr(), _f32_dev(logits, "logits"), self.vocab_size, self.temperature, self.topp,
+                                         float(coin), out.data_ptr()))
+        return out
+

@@ -155,6 +155,22 @@ def argmax(x) -> int:
     return int(lib().orc_argmax(_p(x), x.size))
 
 
+def sample_coin(seed: int, pos: int) -> float:
+    f = lib().orc_sample_coin
+    f.restype, f.argtypes = C.c_float, [C.c_uint64, C.c_uint32]
+    return float(f(seed, pos))
+
+
+def sample(logits, temperature: float, topp: float, coin: float):
+    """(token, margin): the reference's Sampler::sample with the given coin; margin = distance of the decision to its threshold."""
+    x = _f32(logits)
+    f = lib().orc_sample
+    f.restype, f.argtypes = C.c_uint32, [C.c_void_p, C.c_size_t, C.c_float, C.c_float, C.c_float, C.POINTER(C.c_float)]
+    m = C.c_float()
+    tok = f(_p(x), x.size, temperature, topp, coin, C.byref(m))
+    return int(tok), float(m.value)
+
+
 def attention(q, k_cache, v_cache, *, n_heads, kv_mul, head_size, pos, seq_len=None):
     """k_cache / v_cache: [>=pos+1, kv_dim] float32 or float16 arrays."""
     q = _f32(q)

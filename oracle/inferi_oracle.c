@@ -458,6 +458,74 @@ uint32_t orc_argmax(const float *x, size_t n) {
     return (uint32_t)best;
 }
 
+/* Coin of a position: splitmix64 of (seed, position), top 24 bits -> [0, 1).  The reference draws its coin with an
+ * unseeded rand::random() (sampler.rs:41); a reproducible stand-in shared with the device sampler. */
+float orc_sample_coin(uint64_t seed, uint32_t pos) {
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull * ((uint64_t)pos + 1ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (float)(uint32_t)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+typedef struct { float prob; uint32_t index; } orc_prob_index;
+static int cmp_prob_desc(const void *a, const void *b) {
+    const orc_prob_index *x = (const orc_prob_index *)a, *y = (const orc_prob_index *)b;
+    if (x->prob != y->prob) return x->prob > y->prob ? -1 : 1;   /* decreasing probability */
+    return x->index < y->index ? -1 : (x->index > y->index);      /* stable: the reference's sort_by_key keeps index order */
+}
+
+/* crates/inferi/src/models/sampler.rs:32-130 (Sampler::sample with sample_mult / sample_topp) and the CPU softmax it calls
+ * (crates/inferi/src/ops/softmax.rs:130-143), sequential f32 sums as there.  `logits` is not modified.  *margin receives the
+ * smallest distance between a threshold (the coin, topp, coin * cumulative) and the running sums next to the decision: a
+ * parallel sum may decide differently only when it is tiny. */
+uint32_t orc_sample(const float *logits, size_t n, float temperature, float topp, float coin, float *margin) {
+    float mg = 1.0f;
+    if (margin) *margin = mg;
+    if (temperature == 0.0f) return orc_argmax(logits, n);
+    float *p = (float *)malloc(n * sizeof(float));
+    float mx = -INFINITY, sum = 0.0f;
+    for (size_t i = 0; i < n; i++) { p[i] = logits[i] / temperature; if (p[i] > mx) mx = p[i]; }
+    for (size_t i = 0; i < n; i++) { p[i] = expf(p[i] - mx); sum += p[i]; }
+    for (size_t i = 0; i < n; i++) p[i] /= sum;
+    uint32_t tok;
+    if (topp <= 0.0f || topp >= 1.0f) {
+        float cdf = 0.0f;
+        tok = (uint32_t)(n - 1);
+        for (size_t i = 0; i < n; i++) {
+            const float prev = cdf;
+            cdf += p[i];
+            if (coin < cdf) { tok = (uint32_t)i; mg = fminf(cdf - coin, i ? coin - prev : 1.0f); break; }
+        }
+    } else {
+        orc_prob_index *pi = (orc_prob_index *)malloc(n * sizeof(orc_prob_index));
+        size_t n0 = 0;
+        const float cutoff = (1.0f - topp) / ((float)n - 1.0f);
+        for (size_t i = 0; i < n; i++)
+            if (p[i] >= cutoff) { pi[n0].index = (uint32_t)i; pi[n0].prob = p[i]; n0++; }
+        qsort(pi, n0, sizeof(orc_prob_index), cmp_prob_desc);
+        float cumulative = 0.0f;
+        size_t last = n0 - 1;
+        for (size_t i = 0; i < n0; i++) {
+            const float prev = cumulative;
+            cumulative += pi[i].prob;
+            if (cumulative > topp) { last = i; mg = fminf(mg, fminf(cumulative - topp, i ? topp - prev : 1.0f)); break; }
+        }
+        const float r = coin * cumulative;
+        float cdf = 0.0f;
+        tok = pi[last].index;
+        for (size_t i = 0; i <= last; i++) {
+            const float prev = cdf;
+            cdf += pi[i].prob;
+            if (r < cdf) { tok = pi[i].index; mg = fminf(mg, fminf(cdf - r, i ? r - prev : 1.0f)); break; }
+        }
+        free(pi);
+    }
+    free(p);
+    if (margin) *margin = mg;
+    return tok;
+}
+
 /* crates/inferi/src/ops/batched_multiquery_attention.rs:191-245 (run_cpu) with the softmax of
  * crates/inferi/src/models/llama2/cpu.rs:359-372.  KV rows are [pos, kv_dim] row-major
  * (crates/inferi-shaders/src/fused_attention.rs:107-108); kv_f16 selects a cache of binary16 values.

@@ -217,3 +217,43 @@ def test_llama_forward_matches_numpy_restatement():
         got = m.forward(tok, pos)
         assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max()), pos
     m.close()
+
+
+def _np_sample(logits, temperature, topp, coin):
+    """numpy restatement of crates/inferi/src/models/sampler.rs:32-130 (sequential float32 sums via cumsum)."""
+    if temperature == 0.0:
+        return int(np.argmax(logits))
+    x = (logits / np.float32(temperature)).astype(np.float32)
+    e = np.exp(x - x.max()).astype(np.float32)
+    p = (e / np.cumsum(e, dtype=np.float32)[-1]).astype(np.float32)
+    if topp <= 0.0 or topp >= 1.0:
+        cdf = np.cumsum(p, dtype=np.float32)
+        hit = np.nonzero(np.float32(coin) < cdf)[0]
+        return int(hit[0]) if hit.size else p.size - 1
+    cutoff = np.float32((np.float32(1.0) - np.float32(topp)) / (np.float32(p.size) - np.float32(1.0)))
+    idx = np.nonzero(p >= cutoff)[0]
+    order = idx[np.argsort(-p[idx], kind="stable")]
+    cum = np.cumsum(p[order], dtype=np.float32)
+    over = np.nonzero(cum > np.float32(topp))[0]
+    last = int(over[0]) if over.size else order.size - 1
+    r = np.float32(coin) * cum[last]
+    hit = np.nonzero(r < cum[:last + 1])[0]
+    return int(order[hit[0]]) if hit.size else int(order[last])
+
+
+@pytest.mark.parametrize("temperature,topp", [(0.0, 0.9), (1.0, 0.0), (0.7, 1.0), (1.0, 0.9), (0.5, 0.3), (1.3, 0.99)])
+def test_sampler_restatement(temperature, topp):
+    rng = np.random.default_rng(int(temperature * 10) + int(topp * 100))
+    for n in (2, 17, 1000, 20000):
+        logits = (rng.standard_normal(n) * 2.5).astype(np.float32)
+        for coin in np.concatenate([rng.random(8).astype(np.float32), np.float32([0.0, 0.9999999])]):
+            tok, margin = oracle.sample(logits, temperature, topp, float(coin))
+            want = _np_sample(logits, temperature, topp, float(coin))
+            assert tok == want or margin < 1e-6      # libm expf vs numpy exp may differ in the last bit
+
+
+def test_sample_coin_is_a_function_of_seed_and_position():
+    c = [oracle.sample_coin(42, p) for p in range(2000)]
+    assert all(0.0 <= v < 1.0 for v in c) and len(set(c)) > 1990
+    assert c == [oracle.sample_coin(42, p) for p in range(2000)] and c[:5] != [oracle.sample_coin(43, p) for p in range(5)]
+    assert abs(np.mean(c) - 0.5) < 0.03
