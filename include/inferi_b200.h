@@ -206,6 +206,12 @@ IB_API int32_t ib_llama_tp_connect(ib_llama *model, const void *handles_by_rank)
 
 /* Device pointer of the last forward's logits (f32[vocab / tp_size]) and of the residual stream x (f32[hidden]);
  * for parity checks (the reference exposes `Llama2State::logits`, transformer.rs:15-43). */
+/* ib_llama_generate that stops at `eos_token` (the stop test of the reference's chat loop, crates/inferi-chat/src/
+ * chat_llama2.rs:157-166): generates at most max_gen tokens, *n_out receives how many are valid (the stop token included).
+ * The device loop runs in chunks of 16 tokens between which the host looks for the stop token; the next turn continues at
+ * start_pos + n_prompt + *n_out - 1 with the last token as its prompt (KV reuse). */
+IB_API int32_t ib_llama_generate_until(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos,
+                                       uint32_t max_gen, uint32_t eos_token, uint32_t *out_tokens_host, uint32_t *n_out);
 /* ≙ `Sampler::new(vocab, temperature, topp)` (models/sampler.rs:22-30) for the model's own token loop: after this,
  * ib_llama_forward / ib_llama_generate feed back sampled tokens instead of the arg-max (temperature 0 = greedy again).
  * The coin of a position is splitmix64(seed, position) -> [0, 1), so a run can be reproduced.  Single GPU only. */

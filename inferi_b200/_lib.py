@@ -78,6 +78,7 @@ SIGNATURES = {
     "ib_argmax": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "ib_sample": (_i32, [_vp, _vp, _vp, _u32, _f, _f, _f, _vp]),
     "ib_llama_set_sampler": (_i32, [_vp, _f, _f, _u64]),
+    "ib_llama_generate_until": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, C.POINTER(_u32)]),
     "ib_llama_create": (_i32, [_vp, C.POINTER(LlamaConfig), C.POINTER(LlamaWeights), _i32, _i32, _i32, C.POINTER(_vp)]),
     "ib_llama_destroy": (_i32, [_vp]),
     "ib_llama_forward": (_i32, [_vp, _vp, _u32, _u32, _vp, _vp]),

@@ -734,6 +734,34 @@ int32_t ib_llama_generate(ib_llama *m, void *stream, const uint32_t *tokens_host
     return check_device_error(m->ctx);
 }
 
+int32_t ib_llama_generate_until(ib_llama *m, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos, uint32_t max_gen,
+                                uint32_t eos_token, uint32_t *out_tokens_host, uint32_t *n_out) {
+    IB_REQUIRE(m && tokens_host && out_tokens_host && n_out, "ib_llama_generate_until: null argument");
+    IB_REQUIRE(n_prompt >= 1 && max_gen >= 1, "ib_llama_generate_until: empty prompt or nothing to generate");
+    *n_out = 0;
+    // The device loop runs in chunks; between chunks the host looks for the stop token.  At most CHUNK - 1 tokens are computed
+    // past it (their cache rows are simply overwritten by the next turn, which starts at the position after the stop token).
+    constexpr uint32_t CHUNK = 16;
+    const uint32_t *cur = tokens_host;
+    uint32_t cur_n = n_prompt, pos = start_pos, done = 0;
+    while (done < max_gen) {
+        const uint32_t g = max_gen - done < CHUNK ? max_gen - done : CHUNK;
+        const int32_t rc = ib_llama_generate(m, stream, cur, cur_n, pos, g, out_tokens_host + done);
+        if (rc) return rc;
+        for (uint32_t i = 0; i < g; i++)
+            if (out_tokens_host[done + i] == eos_token) {
+                *n_out = done + i + 1;   // the stop token is reported (chat_llama2.rs:157-166 breaks after seeing it)
+                return IB_OK;
+            }
+        pos += cur_n + g - 1;            // positions consumed: the chunk's last token has not been fed back yet
+        done += g;
+        cur = out_tokens_host + done - 1;
+        cur_n = 1;
+    }
+    *n_out = done;
+    return IB_OK;
+}
+
 int32_t ib_llama_state(ib_llama *m, const float **logits_dev, const float **x_dev) {
     IB_REQUIRE(m, "ib_llama_state: null model");
     if (logits_dev) *logits_dev = m->logits;

@@ -203,6 +203,15 @@ class Llama2:
                                          start_pos, n_gen, out.ctypes.data_as(C.c_void_p)))
         return out[:n_gen]
 
+    def generate_until(self, tokens, max_gen: int, eos_token: int, start_pos: int = 0) -> np.ndarray:
+        """`generate` that stops after `eos_token` (chat_llama2.rs:157-166); returns the valid tokens, stop token included."""
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.empty(max_gen, dtype=np.uint32)
+        n = C.c_uint32()
+        check(self.lib.ib_llama_generate_until(self.handle, torch.cuda.current_stream().cuda_stream, toks.ctypes.data_as(C.c_void_p), toks.size,
+                                               start_pos, max_gen, eos_token, out.ctypes.data_as(C.c_void_p), C.byref(n)))
+        return out[:n.value]
+
     def hidden_state(self) -> np.ndarray:
         x = C.c_void_p()
         check(self.lib.ib_llama_state(self.handle, None, C.byref(x)))

@@ -111,6 +111,27 @@ def test_llama_3_2_1b_architecture_64_tokens(backend):
     print(f"1B-architecture: worst logits max-abs difference over 64 positions = {worst:.3e}")
 
 
+def test_generate_until_stops_at_the_stop_token(backend):
+    w = synth_weights(TINY, seed=3001, recipe=TINY_RECIPE)
+    model = Llama2(backend, TINY, Llama2Weights(backend, TINY, w), kv_f16=True)
+    prompt = [3, 500, 41, 7]
+    full = model.generate(prompt, 40).tolist()
+    for k in (0, 5, 15, 16, 17, 33):                       # around the 16-token chunks of the device loop
+        stop = full[k]
+        first = full.index(stop)
+        got = model.generate_until(prompt, 40, stop).tolist()
+        assert got == full[:first + 1]
+    absent = next(t for t in range(TINY.vocab_size) if t not in full)
+    assert model.generate_until(prompt, 40, absent).tolist() == full
+    # the next turn continues after the stop token with the cache kept
+    k = 9
+    head = model.generate_until(prompt, 40, full[k]).tolist()
+    n = len(head)
+    tail = model.generate([head[-1]], 40 - n, start_pos=len(prompt) + n - 1).tolist()
+    assert head + tail == full
+    model.close()
+
+
 def test_model_contract_violations(backend):
     w = synth_weights(TINY, seed=1, recipe=TINY_RECIPE)
     weights = Llama2Weights(backend, TINY, w)
