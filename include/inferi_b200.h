@@ -258,6 +258,21 @@ IB_API int32_t ib_gguf_llama_config(const ib_gguf *g, const char *arch, ib_llama
 IB_API int32_t ib_gguf_load_llama(ib_ctx *ctx, const ib_gguf *g, const char *arch, int32_t kv_dtype, uint32_t max_context, int32_t tp_rank,
                                   int32_t tp_size, ib_llama **out);
 
+/* ---- Llama tokenizer from GGUF metadata ----
+ * Replaces `LlamaTokenizer::from_gguf` / `encode` / `decode` (crates/inferi/src/models/tokenizers/llama2_tokenizer.rs:23-180):
+ * vocabulary `tokenizer.ggml.tokens`, merge scores `tokenizer.ggml.scores`, ids `tokenizer.ggml.{bos,eos,unknown}_token_id`.
+ * Same results as the reference, quirks included (see csrc/tokenizer.cu); an empty text without bos gives an empty list
+ * where the reference panics. */
+typedef struct ib_tokenizer ib_tokenizer;
+IB_API int32_t ib_tokenizer_llama_from_gguf(ib_gguf *g, ib_tokenizer **out);
+IB_API int32_t ib_tokenizer_destroy(ib_tokenizer *t);
+IB_API int32_t ib_tokenizer_info(const ib_tokenizer *t, uint32_t *vocab_size, uint32_t *bos, uint32_t *eos, uint32_t *unk);
+/* `out` may be null to ask for the count only. */
+IB_API int32_t ib_tokenizer_encode(const ib_tokenizer *t, const char *text_utf8, uint64_t text_len, int32_t add_bos, int32_t add_eos, uint32_t *out,
+                                   uint64_t cap, uint64_t *n_out);
+/* The text of `token` given the token before it (the reference strips leading whitespace after the bos token). */
+IB_API int32_t ib_tokenizer_decode(const ib_tokenizer *t, uint32_t prev_token, uint32_t token, char *out, uint64_t cap, uint64_t *len);
+
 #ifdef __cplusplus
 }
 #endif

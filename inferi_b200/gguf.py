@@ -130,6 +130,44 @@ class Gguf:
             pass
 
 
+class LlamaTokenizer:
+    """≙ `LlamaTokenizer` (crates/inferi/src/models/tokenizers/llama2_tokenizer.rs:8-180) over the C ABI."""
+
+    def __init__(self, gguf: Gguf):
+        self.lib = gguf.lib
+        h = C.c_void_p()
+        check(self.lib.ib_tokenizer_llama_from_gguf(gguf.handle, C.byref(h)))
+        self.handle = h
+        v, b, e, u = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        check(self.lib.ib_tokenizer_info(h, C.byref(v), C.byref(b), C.byref(e), C.byref(u)))
+        self.vocab_size, self.bos, self.eos, self.unk = v.value, b.value, e.value, u.value
+
+    def encode(self, text: str, bos: bool = True, eos: bool = False) -> list[int]:
+        raw = text.encode("utf-8")
+        n = C.c_uint64()
+        check(self.lib.ib_tokenizer_encode(self.handle, raw, len(raw), int(bos), int(eos), None, 0, C.byref(n)))
+        out = (C.c_uint32 * max(1, n.value))()
+        check(self.lib.ib_tokenizer_encode(self.handle, raw, len(raw), int(bos), int(eos), out, n.value, C.byref(n)))
+        return list(out[:n.value])
+
+    def decode(self, prev_token: int, token: int) -> str:
+        n = C.c_uint64()
+        buf = C.create_string_buffer(1 << 12)
+        check(self.lib.ib_tokenizer_decode(self.handle, prev_token, token, buf, 1 << 12, C.byref(n)))
+        return buf.raw[:n.value].decode("utf-8", "replace")
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.ib_tokenizer_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 # ---- writer ----
 def _s(b: bytes | str) -> bytes:
     b = b.encode() if isinstance(b, str) else b
