@@ -265,6 +265,11 @@ IB_API int32_t ib_gguf_load_llama(ib_ctx *ctx, const ib_gguf *g, const char *arc
  * where the reference panics. */
 typedef struct ib_tokenizer ib_tokenizer;
 IB_API int32_t ib_tokenizer_llama_from_gguf(ib_gguf *g, ib_tokenizer **out);
+/* GPT-2 byte-pair encoding (Llama-3 files): replaces `Gpt2Tokenizer::from_gguf` / `encode` / `decode` (crates/inferi/src/
+ * models/tokenizers/gpt2_tokenizer.rs:54-217) from `tokenizer.ggml.tokens`, `tokenizer.ggml.merges` and the bos / eos ids.
+ * "<...>" stretches of the text are looked up whole as special tokens; one that is not in the vocabulary is
+ * IB_ERR_INVALID (the reference panics).  ib_tokenizer_decode ignores prev_token for this kind. */
+IB_API int32_t ib_tokenizer_gpt2_from_gguf(ib_gguf *g, ib_tokenizer **out);
 IB_API int32_t ib_tokenizer_destroy(ib_tokenizer *t);
 IB_API int32_t ib_tokenizer_info(const ib_tokenizer *t, uint32_t *vocab_size, uint32_t *bos, uint32_t *eos, uint32_t *unk);
 /* `out` may be null to ask for the count only. */

@@ -100,6 +100,7 @@ SIGNATURES = {
     "ib_gguf_meta_array_str": (_i32, [_vp, C.c_char_p, _u64, C.c_char_p, _u64, C.POINTER(_u64)]),
     "ib_gguf_llama_config": (_i32, [_vp, C.c_char_p, C.POINTER(LlamaConfig)]),
     "ib_tokenizer_llama_from_gguf": (_i32, [_vp, C.POINTER(_vp)]),
+    "ib_tokenizer_gpt2_from_gguf": (_i32, [_vp, C.POINTER(_vp)]),
     "ib_tokenizer_destroy": (_i32, [_vp]),
     "ib_tokenizer_info": (_i32, [_vp, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
     "ib_tokenizer_encode": (_i32, [_vp, C.c_char_p, _u64, _i32, _i32, _vp, _u64, C.POINTER(_u64)]),

@@ -133,10 +133,12 @@ class Gguf:
 class LlamaTokenizer:
     """≙ `LlamaTokenizer` (crates/inferi/src/models/tokenizers/llama2_tokenizer.rs:8-180) over the C ABI."""
 
+    FROM_GGUF = "ib_tokenizer_llama_from_gguf"
+
     def __init__(self, gguf: Gguf):
         self.lib = gguf.lib
         h = C.c_void_p()
-        check(self.lib.ib_tokenizer_llama_from_gguf(gguf.handle, C.byref(h)))
+        check(getattr(self.lib, self.FROM_GGUF)(gguf.handle, C.byref(h)))
         self.handle = h
         v, b, e, u = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
         check(self.lib.ib_tokenizer_info(h, C.byref(v), C.byref(b), C.byref(e), C.byref(u)))
@@ -166,6 +168,18 @@ class LlamaTokenizer:
             self.close()
         except Exception:
             pass
+
+
+class Gpt2Tokenizer(LlamaTokenizer):
+    """≙ `Gpt2Tokenizer` (crates/inferi/src/models/tokenizers/gpt2_tokenizer.rs:37-217) over the C ABI.  `encode` adds neither
+    bos nor eos unless asked (the reference's never does)."""
+    FROM_GGUF = "ib_tokenizer_gpt2_from_gguf"
+
+    def encode(self, text: str, bos: bool = False, eos: bool = False) -> list[int]:
+        return super().encode(text, bos, eos)
+
+    def decode_tokens(self, tokens) -> str:
+        return "".join(self.decode(0, int(t)) for t in tokens)
 
 
 # ---- writer ----

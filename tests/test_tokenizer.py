@@ -104,3 +104,119 @@ def test_decode_and_round_trip(tok):
     text = "".join(t.decode(p, c) for p, c in zip(ids[:-1], ids[1:]))
     assert text == "hello world the abc"                      # leading "▁" pieces come back as spaces
     assert t.decode(0, 3 + 0xE9) == "é"                        # byte piece -> the character U+00E9 (the reference's behaviour)
+
+
+# ---- GPT-2 byte-pair encoding (crates/inferi/src/models/tokenizers/gpt2_tokenizer.rs:54-217) ----
+regex = pytest.importorskip("regex")
+PAT = regex.compile(r"'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+")
+
+
+def bytes_to_unicode():
+    bs = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return dict(zip(bs, [chr(c) for c in cs]))
+
+
+def make_bpe():
+    enc = bytes_to_unicode()
+    base = [enc[b] for b in range(256)]
+    merges, vocab = [], list(base)
+    corpus = "the quick brown fox jumps over the lazy dog hello world it's we're 123 4567 héllo wörld 日本語 " * 3
+    words = [[enc[b] for b in w.encode()] for w in PAT.findall(corpus)]
+    for _ in range(120):                                     # a small learned merge table
+        counts = {}
+        for w in words:
+            for a, b in zip(w[:-1], w[1:]):
+                counts[(a, b)] = counts.get((a, b), 0) + 1
+        if not counts:
+            break
+        (a, b), _ = max(counts.items(), key=lambda kv: (kv[1], kv[0]))
+        merges.append(f"{a} {b}")
+        vocab.append(a + b)
+        for w in words:
+            i = 0
+            while i < len(w) - 1:
+                if w[i] == a and w[i + 1] == b:
+                    w[i:i + 2] = [a + b]
+                else:
+                    i += 1
+    vocab += ["<|begin_of_text|>", "<|end_of_text|>"]
+    return vocab, merges
+
+
+def py_bpe_encode(vocab, merges, text):
+    enc = bytes_to_unicode()
+    index = {v: i for i, v in enumerate(vocab)}
+    rank = {tuple(m.split(" ")): i for i, m in enumerate(merges)}
+    out = []
+
+    def piece(sub):
+        for tok in PAT.findall(sub):
+            w = [enc[b] for b in tok.encode()]
+            while len(w) > 1:
+                pairs = {(a, b) for a, b in zip(w[:-1], w[1:])}
+                best = min(pairs, key=lambda p: rank.get(p, 1 << 60))
+                if best not in rank:
+                    break
+                a, b = best
+                nw, i = [], 0
+                while i < len(w):
+                    if w[i] == a and i + 1 < len(w) and w[i + 1] == b:
+                        nw.append(a + b)
+                        i += 2
+                    else:
+                        nw.append(w[i])
+                        i += 1
+                w = nw
+            out.extend(index[x] for x in w if x in index)
+
+    cursor = 0
+    for m in regex.finditer(r"<[^<>]*>", text):
+        if cursor != m.start():
+            piece(text[cursor:m.start()])
+        out.append(index[m.group()])
+        cursor = m.end()
+    if cursor < len(text):
+        piece(text[cursor:])
+    return out
+
+
+@pytest.fixture(scope="module")
+def bpe(tmp_path_factory):
+    vocab, merges = make_bpe()
+    path = str(tmp_path_factory.mktemp("bpe") / "t.gguf")
+    meta = [("tokenizer.ggml.tokens", G.ARRAY, (G.STRING, vocab)), ("tokenizer.ggml.merges", G.ARRAY, (G.STRING, merges)),
+            ("tokenizer.ggml.bos_token_id", G.U32, len(vocab) - 2), ("tokenizer.ggml.eos_token_id", G.U32, len(vocab) - 1)]
+    G.write_gguf(path, meta, [])
+    f = G.Gguf(path)
+    t = G.Gpt2Tokenizer(f)
+    yield t, vocab, merges
+    t.close()
+    f.close()
+
+
+@pytest.mark.parametrize("text", ["the quick brown fox", "hello world", " hello   world  ", "it's we're they'll I'd", "abc123 4567x", "héllo wörld!", "日本語 テスト",
+                                  "a\n\nb\t c", "<|begin_of_text|>the dog<|end_of_text|>", "x < y z", "a > b < c", "tabs\tand nbsp em", "", "!!! ... ???", "'", "over9000's"])
+def test_gpt2_encode_matches_the_reference_algorithm(bpe, text):
+    t, vocab, merges = bpe
+    assert t.encode(text) == py_bpe_encode(vocab, merges, text)
+
+
+def test_gpt2_decode_and_specials(bpe):
+    t, vocab, merges = bpe
+    assert (t.bos, t.eos) == (len(vocab) - 2, len(vocab) - 1)
+    ids = t.encode("the lazy dog jumps 123")
+    assert t.decode_tokens(ids) == "the lazy dog jumps 123"
+    assert t.decode_tokens(t.encode("é")) == "Ã©"            # the reference maps every byte to U+00XX: UTF-8 is not reassembled
+    assert t.encode("x", bos=True, eos=True) == [t.bos] + t.encode("x") + [t.eos]
+    from inferi_b200._lib import InferiError
+    with pytest.raises(InferiError):
+        t.encode("<nope>")                                     # a "<...>" stretch must be a vocabulary entry (the reference panics)
+    with pytest.raises(InferiError):
+        t.encode("x < y > z")
