@@ -153,6 +153,9 @@ typedef struct ib_llama_config {
     uint32_t max_position_embeddings;
     float rope_theta;
     float rms_norm_eps;
+    /* IB_ROPE_ORIGINAL (Llama: adjacent pairs) or IB_ROPE_NEOX (Qwen2: element i with i + head_size/2), as
+     * `LlamaModelType::rope_variant` selects (crates/inferi/src/models/llama2/mod.rs:24-29). */
+    uint32_t rope_variant;
 } ib_llama_config;
 
 /* = `Llama2LayerWeights` (crates/inferi/src/models/llama2/transformer.rs:176-196).  Norm weights are device
@@ -161,6 +164,8 @@ typedef struct ib_llama_layer_weights {
     const ib_qtensor *attn_q, *attn_k, *attn_v, *attn_output;
     const ib_qtensor *ffn_gate, *ffn_up, *ffn_down;
     const float *attn_norm_dev, *ffn_norm_dev;
+    /* optional f32 biases of q / k / v (Qwen2; transformer.rs:434-442), device pointers or NULL; this rank's rows */
+    const float *attn_q_bias_dev, *attn_k_bias_dev, *attn_v_bias_dev;
 } ib_llama_layer_weights;
 
 /* = `Llama2Weights` (crates/inferi/src/models/llama2/transformer.rs:176-196, 294-394).  `output == NULL`

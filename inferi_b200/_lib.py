@@ -33,12 +33,12 @@ class LlamaConfig(C.Structure):
     """= Llama2Config (crates/inferi/src/models/llama2/cpu.rs:46-66)."""
     _fields_ = [(n, C.c_uint32) for n in ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
                                           "num_key_value_heads", "vocab_size", "max_position_embeddings")] + [
-        ("rope_theta", C.c_float), ("rms_norm_eps", C.c_float)]
+        ("rope_theta", C.c_float), ("rms_norm_eps", C.c_float), ("rope_variant", C.c_uint32)]
 
 
 class LlamaLayerWeights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down",
-                                          "attn_norm_dev", "ffn_norm_dev")]
+                                          "attn_norm_dev", "ffn_norm_dev", "attn_q_bias_dev", "attn_k_bias_dev", "attn_v_bias_dev")]
 
 
 class LlamaWeights(C.Structure):

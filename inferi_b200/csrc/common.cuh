@@ -130,6 +130,7 @@ struct GemvParams {
     const float2 *rope_cs;      // [head_size/2] (cos, sin) of pos * theta_j for the current token
     uint32_t head_size, kv_dim, kv_dtype;
     void *k_cache, *v_cache;    // [max_pos, kv_dim] of this layer
+    const float *bias[3];       // optional f32 bias per segment, added before the rotation (Qwen2: transformer.rs:434-442)
     // EPI_ARGMAX
     unsigned long long *argmax_slots;  // one packed (value, ~index) per CTA
     unsigned int *argmax_counter;

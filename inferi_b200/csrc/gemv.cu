@@ -314,6 +314,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_wide_kernel(const GemvPa
             } else if (EPI == EPI_QKV) {
                 const uint32_t pos = *p.pos_ptr;
                 float a = acc[0], bb = acc[1];
+                if (p.bias[s]) {   // transformer.rs:434-442
+                    a += p.bias[s][r0];
+                    bb += p.bias[s][r0 + 1];
+                }
                 if (s < 2) {
                     // crates/inferi-shaders/src/rope.rs:75-91 (adjacent pairs)
                     const float2 cs = p.rope_cs[(r0 % p.head_size) >> 1];

@@ -390,6 +390,11 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
     } else if (EPI == EPI_RESIDUAL) {
         *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(resid_pre.x + a, resid_pre.y + b);
     } else if (EPI == EPI_QKV) {
+        if (p.bias[s]) {
+            const float2 bv = __ldg(reinterpret_cast<const float2 *>(p.bias[s] + r0));
+            a += bv.x;
+            b += bv.y;
+        }
         if (s < 2) {
             // crates/inferi-shaders/src/rope.rs:75-91 (adjacent pairs)
             const float2 cs = __ldg(p.rope_cs + ((r0 % p.head_size) >> 1));   // written by an earlier kernel: read-only here, L1 may keep it

@@ -442,6 +442,8 @@ int32_t ib_gguf_llama_config(const ib_gguf *g, const char *arch, ib_llama_config
     out->rope_theta = (fb && fb->type != MT_STRING && fb->type != MT_ARRAY) ? (float)fb->f : 10000.0f;
     const MetaValue *eps = find_meta(g, (a + ".attention.layer_norm_rms_epsilon").c_str());
     out->rms_norm_eps = (eps && eps->type != MT_STRING && eps->type != MT_ARRAY) ? (float)eps->f : 1.0e-6f;
+    // LlamaModelType::rope_variant (crates/inferi/src/models/llama2/mod.rs:24-29)
+    out->rope_variant = a == "qwen2" ? IB_ROPE_NEOX : IB_ROPE_ORIGINAL;
     return IB_OK;
 }
 
@@ -493,15 +495,18 @@ int32_t upload_part(ib_ctx *ctx, const ib_gguf_tensor_info &ti, const char *name
     return IB_OK;
 }
 
-int32_t upload_f32(const ib_gguf *g, const char *name, uint64_t n, Loaded &keep, const float **out) {
+// Uploads elements [e0, e1) of an f32 vector of `n` values.
+int32_t upload_f32(const ib_gguf *g, const char *name, uint64_t n, Loaded &keep, const float **out, uint64_t e0 = 0, uint64_t e1 = ~0ull) {
     ib_gguf_tensor_info ti;
     int32_t rc = ib_gguf_tensor_by_name(g, name, &ti);
     if (rc) return rc;
     if (ti.type != IB_F32 || ti.nbytes != n * 4) return set_error(IB_ERR_INVALID, "gguf: tensor %s must be %llu f32 values", name, (unsigned long long)n);
+    if (e1 == ~0ull) e1 = n;
+    if (e0 >= e1 || e1 > n) return set_error(IB_ERR_INVALID, "gguf: slice [%llu,%llu) of tensor %s", (unsigned long long)e0, (unsigned long long)e1, name);
     void *dev = nullptr;
-    IB_CHECK_CUDA(cudaMalloc(&dev, ti.nbytes));
+    IB_CHECK_CUDA(cudaMalloc(&dev, (e1 - e0) * 4));
     keep.device.push_back(dev);
-    IB_CHECK_CUDA(cudaMemcpy(dev, ti.data, ti.nbytes, cudaMemcpyHostToDevice));
+    IB_CHECK_CUDA(cudaMemcpy(dev, (const float *)ti.data + e0, (e1 - e0) * 4, cudaMemcpyHostToDevice));
     *out = (const float *)dev;
     return IB_OK;
 }
@@ -529,19 +534,21 @@ extern "C" int32_t ib_gguf_load_llama(ib_ctx *ctx, const ib_gguf *g, const char 
     IB_REQUIRE(c.num_key_value_heads % tp == 0 && c.vocab_size % (4 * tp) == 0 && c.intermediate_size % (256 * tp) == 0,
                "gguf: %d ranks do not divide the kv heads / vocabulary / FFN width of this model", tp_size);
     const uint64_t H = c.hidden_size, kv = (uint64_t)c.hidden_size * c.num_key_value_heads / c.num_attention_heads, F = c.intermediate_size, V = c.vocab_size;
-    if (g->by_name.count("blk.0.attn_q.bias")) return set_error(IB_ERR_UNSUPPORTED, "gguf: q/k/v bias tensors (Qwen2 variant) are not supported by the fused kernels");
 
-    Loaded keep;
+    // `keep` goes to the model; `rotated` holds q / k matrices and biases of a NeoX model, which ib_llama_create copies in
+    // its own row order and which are freed once it has
+    Loaded keep, rotated;
+    Loaded &qk = c.rope_variant == IB_ROPE_NEOX ? rotated : keep;
     std::vector<ib_llama_layer_weights> layers(c.num_hidden_layers);
-    auto fail = [&](int32_t code) { keep.release(); return code; };
+    auto fail = [&](int32_t code) { keep.release(); rotated.release(); return code; };
     auto mat = [&](const std::string &name, ib_gguf_tensor_info &ti) { return ib_gguf_tensor_by_name(g, name.c_str(), &ti); };
     for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
         const std::string p = "blk." + std::to_string(l) + ".";
         ib_llama_layer_weights &w = layers[l];
         ib_gguf_tensor_info ti;
         // rows of q / k / v (whole heads), gate / up (FFN units); columns of attn_output / ffn_down
-        if ((rc = mat(p + "attn_q.weight", ti)) || (rc = upload_part(ctx, ti, "attn_q", rk * H / tp, (rk + 1) * H / tp, 0, ti.dims[1], 0, 0, keep, &w.attn_q))) return fail(rc);
-        if ((rc = mat(p + "attn_k.weight", ti)) || (rc = upload_part(ctx, ti, "attn_k", rk * kv / tp, (rk + 1) * kv / tp, 0, ti.dims[1], 0, 0, keep, &w.attn_k))) return fail(rc);
+        if ((rc = mat(p + "attn_q.weight", ti)) || (rc = upload_part(ctx, ti, "attn_q", rk * H / tp, (rk + 1) * H / tp, 0, ti.dims[1], 0, 0, qk, &w.attn_q))) return fail(rc);
+        if ((rc = mat(p + "attn_k.weight", ti)) || (rc = upload_part(ctx, ti, "attn_k", rk * kv / tp, (rk + 1) * kv / tp, 0, ti.dims[1], 0, 0, qk, &w.attn_k))) return fail(rc);
         if ((rc = mat(p + "attn_v.weight", ti)) || (rc = upload_part(ctx, ti, "attn_v", rk * kv / tp, (rk + 1) * kv / tp, 0, ti.dims[1], 0, 0, keep, &w.attn_v))) return fail(rc);
         if ((rc = mat(p + "attn_output.weight", ti)) || (rc = upload_part(ctx, ti, "attn_output", 0, ti.dims[0], rk * H / tp, (rk + 1) * H / tp, 0, 0, keep, &w.attn_output)))
             return fail(rc);
@@ -555,6 +562,10 @@ extern "C" int32_t ib_gguf_load_llama(ib_ctx *ctx, const ib_gguf *g, const char 
         if ((rc = upload_part(ctx, dn, "ffn_down", 0, dn.dims[0], f0, f1, 0, pad, keep, &w.ffn_down))) return fail(rc);
         if ((rc = upload_f32(g, (p + "attn_norm.weight").c_str(), H, keep, &w.attn_norm_dev))) return fail(rc);
         if ((rc = upload_f32(g, (p + "ffn_norm.weight").c_str(), H, keep, &w.ffn_norm_dev))) return fail(rc);
+        // optional biases (transformer.rs:307-335), this rank's heads
+        if (g->by_name.count(p + "attn_q.bias") && (rc = upload_f32(g, (p + "attn_q.bias").c_str(), H, qk, &w.attn_q_bias_dev, rk * H / tp, (rk + 1) * H / tp))) return fail(rc);
+        if (g->by_name.count(p + "attn_k.bias") && (rc = upload_f32(g, (p + "attn_k.bias").c_str(), kv, qk, &w.attn_k_bias_dev, rk * kv / tp, (rk + 1) * kv / tp))) return fail(rc);
+        if (g->by_name.count(p + "attn_v.bias") && (rc = upload_f32(g, (p + "attn_v.bias").c_str(), kv, keep, &w.attn_v_bias_dev, rk * kv / tp, (rk + 1) * kv / tp))) return fail(rc);
     }
     ib_llama_weights W{};
     W.layers = layers.data();
@@ -572,6 +583,7 @@ extern "C" int32_t ib_gguf_load_llama(ib_ctx *ctx, const ib_gguf *g, const char 
 
     ib_llama *m = nullptr;
     if ((rc = ib_llama_create(ctx, &c, &W, kv_dtype, tp_rank, tp_size, &m))) return fail(rc);
+    rotated.release();
     llama_adopt(m, std::move(keep.tensors), std::move(keep.device));
     *out = m;
     return IB_OK;

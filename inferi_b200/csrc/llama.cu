@@ -249,6 +249,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
         p.nseg = 3; p.cols = H; p.epi = EPI_QKV; p.x = cur; p.norm_w = w.attn_norm_dev; p.eps = c.rms_norm_eps;
         p.pos_ptr = &m->ctl->pos; p.rope_cs = m->rope_cs; p.head_size = m->head_size; p.kv_dim = m->kv_dim_l; p.kv_dtype = (uint32_t)m->kv_dtype;
         p.k_cache = m->k_cache[l]; p.v_cache = m->v_cache[l]; p.pdl = pdl;
+        p.bias[0] = w.attn_q_bias_dev; p.bias[1] = w.attn_k_bias_dev; p.bias[2] = w.attn_v_bias_dev;   // transformer.rs:434-442
         if (l > 0) add_reduce(p, 1, l);   // the down partials of layer l-1: use number l of this token
         if ((rc = emit_gemv(p))) return rc;
         // attention (transformer.rs:448)
@@ -312,6 +313,66 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
     return IB_OK;
 }
 
+// NeoX rotation as a row order.  The NeoX variant rotates element j of a head with element j + head_size/2
+// (crates/inferi-shaders/src/rope.rs:96-140); the fused q/k/v epilogue rotates adjacent rows.  Reordering the rows of
+// Wq, Wk (and their biases) inside each head as [0, h/2, 1, h/2+1, ...] turns the first into the second, and the
+// attention scores do not change when q and k are permuted alike.  dst row r <- src row neox_source_row(r).
+__host__ __device__ inline uint32_t neox_source_row(uint32_t r, uint32_t head_size) {
+    const uint32_t i = r % head_size;
+    return r - i + ((i & 1u) ? head_size / 2 + i / 2 : i / 2);
+}
+
+template <typename V>
+__global__ void gather_neox_rows_kernel(const V *src, V *dst, uint32_t rows, uint32_t row_units, uint32_t head_size) {
+    for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const V *s = src + (size_t)neox_source_row(r, head_size) * row_units;
+        V *d = dst + (size_t)r * row_units;
+        for (uint32_t i = threadIdx.x; i < row_units; i += blockDim.x) d[i] = s[i];
+    }
+}
+
+static cudaError_t gather_neox_rows(const void *src, void *dst, uint32_t rows, uint64_t row_bytes, uint32_t head_size, cudaStream_t st) {
+    const uint32_t grid = rows < 4096u ? rows : 4096u;
+    if (row_bytes % 16 == 0 && ((uintptr_t)src % 16) == 0 && ((uintptr_t)dst % 16) == 0)
+        gather_neox_rows_kernel<uint4><<<grid, 128, 0, st>>>((const uint4 *)src, (uint4 *)dst, rows, (uint32_t)(row_bytes / 16), head_size);
+    else if (row_bytes % 4 == 0)
+        gather_neox_rows_kernel<uint32_t><<<grid, 128, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, rows, (uint32_t)(row_bytes / 4), head_size);
+    else
+        gather_neox_rows_kernel<uint16_t><<<grid, 128, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, rows, (uint32_t)(row_bytes / 2), head_size);
+    return cudaGetLastError();
+}
+
+// A model-owned copy of `t` with its rows in the order above (rows stay contiguous in both device layouts).
+static int32_t neox_row_copy(ib_llama *m, const ib_qtensor *t, const ib_qtensor **out) {
+    ib_qtensor *c = new (std::nothrow) ib_qtensor(*t);
+    if (!c) return set_error(IB_ERR_OOM, "host allocation failed");
+    c->dev = nullptr;
+    cudaError_t e = cudaMalloc(&c->dev, t->nbytes + 16);
+    if (e == cudaSuccess) e = gather_neox_rows(t->dev, c->dev, (uint32_t)t->rows, t->row_bytes, m->head_size, 0);
+    if (e != cudaSuccess) {
+        if (c->dev) cudaFree(c->dev);
+        delete c;
+        return set_error(e == cudaErrorMemoryAllocation ? IB_ERR_OOM : IB_ERR_CUDA, "ib_llama_create: NeoX row order of a %llux%llu matrix: %s",
+                         (unsigned long long)t->rows, (unsigned long long)t->cols, cudaGetErrorString(e));
+    }
+    m->owned_tensors.push_back(c);
+    *out = c;
+    return IB_OK;
+}
+
+static int32_t neox_bias_copy(ib_llama *m, const float *b, uint32_t rows, const float **out) {
+    float *d = nullptr;
+    cudaError_t e = cudaMalloc(&d, sizeof(float) * rows);
+    if (e == cudaSuccess) e = gather_neox_rows(b, d, rows, sizeof(float), m->head_size, 0);
+    if (e != cudaSuccess) {
+        if (d) cudaFree(d);
+        return set_error(e == cudaErrorMemoryAllocation ? IB_ERR_OOM : IB_ERR_CUDA, "ib_llama_create: NeoX order of a bias: %s", cudaGetErrorString(e));
+    }
+    m->owned_device.push_back(d);
+    *out = d;
+    return IB_OK;
+}
+
 static int32_t check_matrix(const ib_qtensor *t, const char *name, uint64_t rows, uint64_t cols, bool need_fast) {
     IB_REQUIRE(t != nullptr, "ib_llama_create: missing tensor %s", name);
     IB_REQUIRE(t->rows == rows && t->cols == cols, "ib_llama_create: %s is %llux%llu, expected %llux%llu", name, (unsigned long long)t->rows,
@@ -328,8 +389,10 @@ static int32_t check_matrix(const ib_qtensor *t, const char *name, uint64_t rows
 
 namespace ib {
 void llama_adopt(ib_llama *m, std::vector<ib_qtensor *> &&tensors, std::vector<void *> &&device) {
-    m->owned_tensors = std::move(tensors);
-    m->owned_device = std::move(device);
+    m->owned_tensors.insert(m->owned_tensors.end(), tensors.begin(), tensors.end());
+    m->owned_device.insert(m->owned_device.end(), device.begin(), device.end());
+    tensors.clear();
+    device.clear();
 }
 }  // namespace ib
 
@@ -381,6 +444,7 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
     IB_REQUIRE(c.hidden_size % c.num_attention_heads == 0 && c.num_attention_heads % c.num_key_value_heads == 0,
                "ib_llama_create: head counts do not divide the hidden size");
     IB_REQUIRE(weights->layers != nullptr, "ib_llama_create: null layer array");
+    IB_REQUIRE(c.rope_variant == IB_ROPE_ORIGINAL || c.rope_variant == IB_ROPE_NEOX, "ib_llama_create: unknown rope variant %u", c.rope_variant);
     ib_llama *m = new (std::nothrow) ib_llama();
     if (!m) return set_error(IB_ERR_OOM, "host allocation failed");
     m->ctx = ctx; m->cfg = c; m->kv_dtype = kv_dtype; m->tp_rank = tp_rank; m->tp_size = tp_size;
@@ -435,7 +499,15 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
             ib_llama_destroy(m);
             return set_error(IB_ERR_UNSUPPORTED, "ib_llama_create: layer %u gate/up types differ", l);
         }
+        if (c.rope_variant == IB_ROPE_NEOX) {
+            ib_llama_layer_weights &mw = m->layers[l];
+            FAIL_IF(neox_row_copy(m, w.attn_q, &mw.attn_q));
+            FAIL_IF(neox_row_copy(m, w.attn_k, &mw.attn_k));
+            if (w.attn_q_bias_dev) FAIL_IF(neox_bias_copy(m, w.attn_q_bias_dev, m->q_dim_l, &mw.attn_q_bias_dev));
+            if (w.attn_k_bias_dev) FAIL_IF(neox_bias_copy(m, w.attn_k_bias_dev, m->kv_dim_l, &mw.attn_k_bias_dev));
+        }
     }
+    if (c.rope_variant == IB_ROPE_NEOX) CU(cudaDeviceSynchronize());
     FAIL_IF(check_matrix(weights->token_embd, "token_embd", c.vocab_size, c.hidden_size, false));
     {
         const int tq = weights->token_embd->qtype;
@@ -537,6 +609,9 @@ static int32_t finish_graph(ib_llama *m) {
         rc = record_token(m, nullptr, 0, &phases);
         const uint32_t L = m->cfg.num_hidden_layers;
         if (rc == IB_OK && phases.size() != 5 * (size_t)L + 1) rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: unexpected phase list");
+        for (uint32_t l = 0; rc == IB_OK && l < L; l++)
+            if (m->layers[l].attn_q_bias_dev || m->layers[l].attn_k_bias_dev || m->layers[l].attn_v_bias_dev)
+                rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: q/k/v biases are only on the graph path; unset INFERI_B200_TOKEN_KERNEL");
         std::vector<PhaseDesc> table(phases.size());
         TokenProgram &P = m->prog;
         if (rc == IB_OK) {

@@ -106,7 +106,7 @@ class Gguf:
         c = LlamaConfig()
         check(self.lib.ib_gguf_llama_config(self.handle, arch.encode() if arch else None, C.byref(c)))
         return Llama2Config(c.hidden_size, c.intermediate_size, c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.vocab_size,
-                            c.max_position_embeddings, c.rope_theta, c.rms_norm_eps)
+                            c.max_position_embeddings, c.rope_theta, c.rms_norm_eps, c.rope_variant)
 
     def load_llama(self, backend: Backend, kv_f16: bool = True, max_context: int = 0, tp_rank: int = 0, tp_size: int = 1, group=None,
                    arch: str | None = None) -> Llama2:
@@ -245,6 +245,9 @@ def write_llama_gguf(path: str, cfg: Llama2Config, weights: dict, tokens: list[s
             tensors.append((f"blk.{i}.{n}.weight", lw[n][0], sh[n], raw(lw[n][1])))
         for n in ("attn_norm", "ffn_norm"):
             tensors.append((f"blk.{i}.{n}.weight", quant.F32, (cfg.hidden_size,), raw(lw[n])))
+        for n, width in (("attn_q", cfg.hidden_size), ("attn_k", cfg.kv_dim), ("attn_v", cfg.kv_dim)):   # transformer.rs:307-309
+            if lw.get(n + "_bias") is not None:
+                tensors.append((f"blk.{i}.{n}.bias", quant.F32, (width,), raw(lw[n + "_bias"])))
     tensors.append(("output_norm.weight", quant.F32, (cfg.hidden_size,), raw(weights["output_norm"])))
     if weights.get("output") is not None:
         qt, data = weights["output"]

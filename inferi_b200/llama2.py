@@ -36,6 +36,7 @@ class Llama2Config:
     max_position_embeddings: int
     rope_theta: float = 10000.0      # defaults of from_gguf (cpu.rs:95-106)
     rms_norm_eps: float = 1.0e-6
+    rope_variant: int = 0            # 0 Original (Llama), 1 NeoX (Qwen2): crates/inferi/src/models/llama2/mod.rs:24-29
 
     @property
     def head_size(self) -> int:
@@ -51,7 +52,8 @@ class Llama2Config:
 
     def to_c(self) -> LlamaConfig:
         return LlamaConfig(self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.num_attention_heads,
-                           self.num_key_value_heads, self.vocab_size, self.max_position_embeddings, self.rope_theta, self.rms_norm_eps)
+                           self.num_key_value_heads, self.vocab_size, self.max_position_embeddings, self.rope_theta, self.rms_norm_eps,
+                           self.rope_variant)
 
     def shapes(self) -> dict:
         """[out_features, in_features] of every matrix (transformer.rs:304-315)."""
@@ -75,10 +77,16 @@ LLAMA_3_2_1B = Llama2Config(2048, 8192, 16, 32, 8, 128256, 4096, 500000.0, 1e-5)
 LLAMA_3_8B = Llama2Config(4096, 14336, 32, 32, 8, 128256, 8192, 500000.0, 1e-5)
 
 
-def synth_weights(cfg: Llama2Config, seed: int, device: str = "cpu", recipe: dict = Q4_K_M, tied: bool = False, std: float = 0.02) -> dict:
+BIAS_NAMES = ("attn_q_bias", "attn_k_bias", "attn_v_bias")
+
+
+def synth_weights(cfg: Llama2Config, seed: int, device: str = "cpu", recipe: dict = Q4_K_M, tied: bool = False, std: float = 0.02,
+                  qkv_bias: bool = False) -> dict:
     """Seeded random checkpoint in GGUF block bytes: f32 N(0, std) matrices quantized with the recipe's types, norm weights
     1 + N(0, std).  Returns {'layers': [{name: (qtype, uint8 tensor [rows, row_bytes]), 'attn_norm': f32, 'ffn_norm': f32}],
-    'token_embd': (qtype, tensor), 'output': (qtype, tensor) | None, 'output_norm': f32} with tensors on `device`."""
+    'token_embd': (qtype, tensor), 'output': (qtype, tensor) | None, 'output_norm': f32} with tensors on `device`.
+    `qkv_bias` adds f32 'attn_q_bias' / 'attn_k_bias' / 'attn_v_bias' ~ N(0, 0.1) to every layer (the Qwen2 variant:
+    transformer.rs:181-183); they are drawn after everything else, so the matrices do not depend on the flag."""
     g = torch.Generator(device=device)
     g.manual_seed(seed)
     sh = cfg.shapes()
@@ -101,14 +109,20 @@ def synth_weights(cfg: Llama2Config, seed: int, device: str = "cpu", recipe: dic
         lw["attn_norm"] = norm()
         lw["ffn_norm"] = norm()
         layers.append(lw)
-    return {"layers": layers, "token_embd": mat("token_embd"), "output": None if tied else mat("output"), "output_norm": norm()}
+    out = {"layers": layers, "token_embd": mat("token_embd"), "output": None if tied else mat("output"), "output_norm": norm()}
+    if qkv_bias:
+        for lw in layers:
+            for n, width in zip(BIAS_NAMES, (cfg.hidden_size, cfg.kv_dim, cfg.kv_dim)):
+                lw[n] = torch.randn(width, generator=g, device=device, dtype=torch.float32) * 0.1
+    return out
 
 
 def weights_to_host(weights: dict) -> dict:
     """The same checkpoint as numpy arrays (for a CPU checker)."""
     def m(t):
         return (t[0], t[1].cpu().numpy())
-    return {"layers": [{**{n: m(lw[n]) for n in LAYER_MATS}, "attn_norm": lw["attn_norm"].cpu().numpy(), "ffn_norm": lw["ffn_norm"].cpu().numpy()}
+    return {"layers": [{**{n: m(lw[n]) for n in LAYER_MATS}, "attn_norm": lw["attn_norm"].cpu().numpy(), "ffn_norm": lw["ffn_norm"].cpu().numpy(),
+                        **{n: lw[n].cpu().numpy() for n in BIAS_NAMES if lw.get(n) is not None}}
                        for lw in weights["layers"]],
             "token_embd": m(weights["token_embd"]), "output": None if weights["output"] is None else m(weights["output"]),
             "output_norm": weights["output_norm"].cpu().numpy()}
@@ -126,8 +140,9 @@ class Llama2Weights:
         self._keep = []
         for lw in weights["layers"]:
             d = {n: GpuQuantTensor(backend, lw[n][0], sh[n][0], sh[n][1], lw[n][1]) for n in LAYER_MATS}
-            for n in ("attn_norm", "ffn_norm"):
-                d[n] = torch.as_tensor(lw[n]).to(dev, torch.float32).contiguous()
+            for n in ("attn_norm", "ffn_norm") + BIAS_NAMES:
+                if lw.get(n) is not None:
+                    d[n] = torch.as_tensor(lw[n]).to(dev, torch.float32).contiguous()
             self.layers.append(d)
         qt, data = weights["token_embd"]
         self.token_embd = GpuQuantTensor(backend, qt, *sh["token_embd"], data)
@@ -144,6 +159,9 @@ class Llama2Weights:
                 setattr(arr[i], n, d[n].handle)
             arr[i].attn_norm_dev = d["attn_norm"].data_ptr()
             arr[i].ffn_norm_dev = d["ffn_norm"].data_ptr()
+            for n in BIAS_NAMES:
+                if n in d:
+                    setattr(arr[i], n + "_dev", d[n].data_ptr())
         w = LlamaWeights(arr, self.token_embd.handle, self.output.handle if self.output else None, self.output_norm.data_ptr())
         return w, arr
 

@@ -77,6 +77,9 @@ def shard_weights(cfg: Llama2Config, weights: dict, rank: int, tp: int) -> dict:
             "ffn_down": cols_slice(lw["ffn_down"], f0, f1, pad),
             "attn_norm": lw["attn_norm"], "ffn_norm": lw["ffn_norm"],
         })
+        for n, (a, b) in (("attn_q_bias", (q0, q1)), ("attn_k_bias", (k0, k1)), ("attn_v_bias", (k0, k1))):
+            if lw.get(n) is not None:
+                layers[-1][n] = lw[n][a:b]
     v0, v1 = rank * cfg.vocab_size // tp, (rank + 1) * cfg.vocab_size // tp
     head = weights["output"] if weights.get("output") is not None else weights["token_embd"]
     return {"layers": layers, "token_embd": weights["token_embd"], "output": rows_slice(head, v0, v1), "output_norm": weights["output_norm"]}

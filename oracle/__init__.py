@@ -65,6 +65,8 @@ def lib():
         L.orc_llama_set_norms.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.orc_llama_set_globals.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.orc_llama_free.argtypes = [C.c_void_p]
+        L.orc_llama_set_variant.argtypes = [C.c_void_p, C.c_int]
+        L.orc_llama_set_bias.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
         L.orc_llama_set_gemv_mode.argtypes = [C.c_void_p, C.c_int]
         L.orc_llama_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
         L.orc_llama_hidden.restype = C.POINTER(C.c_float)
@@ -189,15 +191,23 @@ class Llama:
     """Whole-model CPU forward in the op order of crates/inferi/src/models/llama2/transformer.rs:418-478."""
 
     def __init__(self, cfg: dict, weights: dict, kv_f16: bool, nthreads: int | None = None):
-        """cfg keys = LlamaConfig fields; weights: {'layers': [{'attn_q': (qtype, uint8 array), ..., 'attn_norm': f32,
-        'ffn_norm': f32}], 'token_embd': (qtype, arr), 'output': (qtype, arr) | None, 'output_norm': f32}."""
+        """cfg keys = LlamaConfig fields, plus optionally 'rope_variant' (0 Original, 1 NeoX); weights: {'layers':
+        [{'attn_q': (qtype, uint8 array), ..., 'attn_norm': f32, 'ffn_norm': f32, optionally 'attn_q_bias' / 'attn_k_bias' /
+        'attn_v_bias': f32}], 'token_embd': (qtype, arr), 'output': (qtype, arr) | None, 'output_norm': f32}."""
+        cfg = dict(cfg)
+        rope_variant = int(cfg.pop("rope_variant", 0))
         self.cfg = LlamaConfig(**cfg)
         self._keep = []
         self.vocab = cfg["vocab"]
         self.hidden = cfg["hidden"]
         self.h = lib().orc_llama_create(C.byref(self.cfg), int(kv_f16), nthreads or max_threads())
+        lib().orc_llama_set_variant(self.h, rope_variant)
         names = ["attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"]
         for l, lw in enumerate(weights["layers"]):
+            biases = [(_f32(lw[n]) if lw.get(n) is not None else None) for n in ("attn_q_bias", "attn_k_bias", "attn_v_bias")]
+            if any(b is not None for b in biases):
+                self._keep += [b for b in biases if b is not None]
+                lib().orc_llama_set_bias(self.h, l, *[(_p(b) if b is not None else None) for b in biases])
             for which, n in enumerate(names):
                 qt, arr = lw[n]
                 arr = np.ascontiguousarray(arr, dtype=np.uint8)

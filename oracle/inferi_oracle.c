@@ -598,6 +598,8 @@ typedef struct orc_llama {
     uint32_t kv_dim, head_size, kv_mul;
     float *x, *xb, *xb2, *hb, *hb2, *q, *krow, *vrow;
     void **kc, **vc;           /* per layer [max_pos, kv_dim] f32 or f16 */
+    int rope_variant;          /* 0 Original (Llama), 1 NeoX (Qwen2): crates/inferi/src/models/llama2/mod.rs:24-29 */
+    const float **bias;        /* [n_layers * 3] optional q / k / v biases (transformer.rs:181-183) */
 } orc_llama;
 
 /* crates/inferi/src/models/llama2/cpu.rs:110-141 (derived sizes) and transformer.rs:46-137 (state). */
@@ -613,6 +615,7 @@ orc_llama *orc_llama_create(const orc_llama_config *c, int kv_f16, int nthreads)
     m->x = (float *)calloc(c->hidden, 4); m->xb = (float *)calloc(c->hidden, 4); m->xb2 = (float *)calloc(c->hidden, 4);
     m->hb = (float *)calloc(c->ffn, 4); m->hb2 = (float *)calloc(c->ffn, 4); m->q = (float *)calloc(c->hidden, 4);
     m->krow = (float *)calloc(m->kv_dim, 4); m->vrow = (float *)calloc(m->kv_dim, 4);
+    m->bias = (const float **)calloc((size_t)c->n_layers * 3, sizeof(float *));
     m->kc = (void **)calloc(c->n_layers, sizeof(void *)); m->vc = (void **)calloc(c->n_layers, sizeof(void *));
     size_t esz = kv_f16 ? 2 : 4;
     for (uint32_t l = 0; l < c->n_layers; l++) {
@@ -629,6 +632,11 @@ void orc_llama_set_mat(orc_llama *m, uint32_t layer, int which, int qtype, const
 void orc_llama_set_norms(orc_llama *m, uint32_t layer, const float *attn_norm, const float *ffn_norm) {
     m->attn_norm[layer] = attn_norm; m->ffn_norm[layer] = ffn_norm;
 }
+/* Qwen2 variant: NeoX rotation and q / k / v biases (any of them may be NULL). */
+void orc_llama_set_variant(orc_llama *m, int rope_variant) { m->rope_variant = rope_variant; }
+void orc_llama_set_bias(orc_llama *m, uint32_t layer, const float *q_bias, const float *k_bias, const float *v_bias) {
+    m->bias[(size_t)layer * 3 + 0] = q_bias; m->bias[(size_t)layer * 3 + 1] = k_bias; m->bias[(size_t)layer * 3 + 2] = v_bias;
+}
 /* output.data == NULL ties the classifier to token_embd (transformer.rs:376-382). */
 void orc_llama_set_globals(orc_llama *m, int embd_qtype, const void *embd, int out_qtype, const void *output, const float *output_norm) {
     m->token_embd.qtype = embd_qtype; m->token_embd.data = embd;
@@ -639,7 +647,7 @@ void orc_llama_set_globals(orc_llama *m, int embd_qtype, const void *embd, int o
 void orc_llama_free(orc_llama *m) {
     if (!m) return;
     for (uint32_t l = 0; l < m->c.n_layers; l++) { free(m->kc[l]); free(m->vc[l]); }
-    free(m->kc); free(m->vc); free(m->mats); free(m->attn_norm); free(m->ffn_norm);
+    free(m->kc); free(m->vc); free(m->mats); free(m->attn_norm); free(m->ffn_norm); free(m->bias);
     free(m->x); free(m->xb); free(m->xb2); free(m->hb); free(m->hb2); free(m->q); free(m->krow); free(m->vrow);
     free(m);
 }
@@ -669,7 +677,11 @@ void orc_llama_forward(orc_llama *m, uint32_t token, uint32_t pos, float *logits
         model_gemv(m, &w[ORC_W_Q], H, H, m->xb, m->q);
         model_gemv(m, &w[ORC_W_K], KV, H, m->xb, m->krow);
         model_gemv(m, &w[ORC_W_V], KV, H, m->xb, m->vrow);
-        orc_rope(0, m->q, H, m->krow, KV, m->head_size, pos, c->rope_theta);
+        /* biases before the rotation: transformer.rs:434-442 */
+        if (m->bias[(size_t)l * 3 + 0]) orc_add_assign(m->q, m->bias[(size_t)l * 3 + 0], H);
+        if (m->bias[(size_t)l * 3 + 1]) orc_add_assign(m->krow, m->bias[(size_t)l * 3 + 1], KV);
+        if (m->bias[(size_t)l * 3 + 2]) orc_add_assign(m->vrow, m->bias[(size_t)l * 3 + 2], KV);
+        orc_rope(m->rope_variant, m->q, H, m->krow, KV, m->head_size, pos, c->rope_theta);
         if (m->kv_f16) {
             uint16_t *kr = (uint16_t *)m->kc[l] + (size_t)pos * KV, *vr = (uint16_t *)m->vc[l] + (size_t)pos * KV;
             for (size_t i = 0; i < KV; i++) { kr[i] = orc_encode_f16(m->krow[i]); vr[i] = orc_encode_f16(m->vrow[i]); }

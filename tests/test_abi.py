@@ -29,8 +29,8 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layouts_match_the_header():
     assert C.sizeof(_lib.AttnParams) == 24
-    assert C.sizeof(_lib.LlamaConfig) == 36
-    assert C.sizeof(_lib.LlamaLayerWeights) == 9 * C.sizeof(C.c_void_p)
+    assert C.sizeof(_lib.LlamaConfig) == 40
+    assert C.sizeof(_lib.LlamaLayerWeights) == 12 * C.sizeof(C.c_void_p)
     assert C.sizeof(_lib.LlamaWeights) == 4 * C.sizeof(C.c_void_p)
 
 

@@ -17,7 +17,7 @@ RECIPE = dict(attn_q=quant.Q4_K, attn_k=quant.Q5_K, attn_v=quant.Q8_0, attn_outp
 
 
 def oracle_tokens(cfg, w, prompt, n_gen, kv_f16=True):
-    ref = oracle.Llama(dict(hidden=cfg.hidden_size, ffn=cfg.intermediate_size, n_layers=cfg.num_hidden_layers, n_heads=cfg.num_attention_heads,
+    ref = oracle.Llama(dict(rope_variant=cfg.rope_variant, hidden=cfg.hidden_size, ffn=cfg.intermediate_size, n_layers=cfg.num_hidden_layers, n_heads=cfg.num_attention_heads,
                             n_kv_heads=cfg.num_key_value_heads, vocab=cfg.vocab_size, max_pos=cfg.max_position_embeddings,
                             rope_theta=float(np.float32(cfg.rope_theta)), rms_eps=float(np.float32(cfg.rms_norm_eps))), weights_to_host(w), kv_f16=kv_f16)
     want = []
@@ -50,6 +50,26 @@ def test_model_from_file_equals_model_from_tensors(backend, tmp_path, tied):
     assert np.array_equal(la, lb)                        # same kernels on the same bytes
     from_file.close()
     direct.close()
+
+
+def test_qwen2_file_with_biases(backend, tmp_path):
+    """arch "qwen2" (crates/inferi/src/models/llama2/mod.rs:17-22): `qwen2.*` metadata keys, blk.N.attn_{q,k,v}.bias tensors
+    (transformer.rs:307-335), NeoX rotation."""
+    import dataclasses
+    cfg = dataclasses.replace(TINY, rope_variant=1)
+    w = synth_weights(cfg, seed=23, recipe=RECIPE, qkv_bias=True)
+    path = str(tmp_path / "q.gguf")
+    G.write_llama_gguf(path, cfg, w, arch="qwen2")
+    f = G.Gguf(path)
+    with pytest.raises(InferiError):
+        f.llama_config()                                 # the default model type looks for llama.* keys (cpu.rs:74-76)
+    got = f.llama_config("qwen2")
+    assert got.rope_variant == 1 and (got.hidden_size, got.num_key_value_heads, got.vocab_size) == (cfg.hidden_size, cfg.num_key_value_heads, cfg.vocab_size)
+    m = f.load_llama(backend, kv_f16=True, arch="qwen2")
+    f.close()
+    prompt, n_gen = [9, 17, 250], 20
+    assert m.generate(prompt, n_gen).tolist() == oracle_tokens(cfg, w, prompt, n_gen)
+    m.close()
 
 
 def test_context_cap_and_unsupported_tensor_types(backend, tmp_path):

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 def oracle_cfg(c: Llama2Config) -> dict:
     return dict(hidden=c.hidden_size, ffn=c.intermediate_size, n_layers=c.num_hidden_layers, n_heads=c.num_attention_heads,
                 n_kv_heads=c.num_key_value_heads, vocab=c.vocab_size, max_pos=c.max_position_embeddings, rope_theta=c.rope_theta,
-                rms_eps=c.rms_norm_eps)
+                rms_eps=c.rms_norm_eps, rope_variant=c.rope_variant)
 
 
 TINY = Llama2Config(256, 2048, 2, 4, 2, 512, 64, 500000.0, 1e-5)
@@ -109,6 +109,34 @@ def test_llama_3_2_1b_architecture_64_tokens(backend):
     prompt = np.random.default_rng(3002).integers(0, cfg.vocab_size, 32).tolist()
     worst = check_loop(backend, cfg, w, True, prompt=prompt, n_gen=TOKENS_EXACT - 32 + 1)
     print(f"1B-architecture: worst logits max-abs difference over 64 positions = {worst:.3e}")
+
+
+@pytest.mark.parametrize("cfg,recipe", [(TINY, TINY_RECIPE), (SMALL, Q4_K_M)], ids=["head64", "head128"])
+def test_qwen2_variant_neox_rotation_and_qkv_biases(backend, cfg, recipe):
+    """`LlamaModelType::Qwen2` (crates/inferi/src/models/llama2/mod.rs:11-29): NeoX rotation, q / k / v biases added before it
+    (transformer.rs:434-445).  The device model reorders the q / k rows at creation; the oracle rotates split halves."""
+    import dataclasses
+    qcfg = dataclasses.replace(cfg, rope_variant=1)
+    w = synth_weights(qcfg, seed=77, recipe=recipe, qkv_bias=True)
+    worst = check_loop(backend, qcfg, w, True, [2, 77, 300], 24)
+    assert worst <= LOGITS_MAX_ABS
+    # the biases and the rotation matter: the Llama reading of the same matrices gives other logits
+    plain = Llama2(backend, cfg, Llama2Weights(backend, cfg, {**w, "layers": [{k: v for k, v in lw.items() if not k.endswith("_bias")} for lw in w["layers"]]}))
+    qwen = Llama2(backend, qcfg, Llama2Weights(backend, qcfg, w))
+    _, a = plain.forward(5, 3, want_logits=True)
+    _, b = qwen.forward(5, 3, want_logits=True)
+    assert np.abs(a - b).max() > 1e-2
+    plain.close()
+    qwen.close()
+
+
+def test_qwen2_biases_are_refused_by_the_token_kernel(backend, monkeypatch):
+    import dataclasses
+    monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", "1")
+    qcfg = dataclasses.replace(TINY, rope_variant=1)
+    w = synth_weights(qcfg, seed=78, recipe=TINY_RECIPE, qkv_bias=True)
+    with pytest.raises(InferiError):
+        Llama2(backend, qcfg, Llama2Weights(backend, qcfg, w))
 
 
 def test_generate_until_stops_at_the_stop_token(backend):

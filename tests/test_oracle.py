@@ -163,16 +163,19 @@ def test_attention_matches_closed_form(kv_dtype):
     assert np.array_equal(got, oracle.attention(q, kc2, vc2, n_heads=n_heads, kv_mul=kv_mul, head_size=hs, pos=pos))
 
 
-def test_llama_forward_matches_numpy_restatement():
-    """Whole-model oracle vs a dequantize-everything numpy forward in the op order of transformer.rs:418-478."""
+@pytest.mark.parametrize("qwen2", [False, True])
+def test_llama_forward_matches_numpy_restatement(qwen2):
+    """Whole-model oracle vs a dequantize-everything numpy forward in the op order of transformer.rs:418-478; the Qwen2 variant
+    adds q / k / v biases before a NeoX rotation (transformer.rs:434-445, crates/inferi-shaders/src/rope.rs:97-141)."""
     import torch
     from inferi_b200.llama2 import Llama2Config, synth_weights, weights_to_host
 
     cfg = Llama2Config(256, 512, 2, 4, 2, 512, 16, 500000.0, 1e-5)
     recipe = {n: quant.Q4_K for n in ("attn_q", "attn_k", "attn_output", "ffn_gate", "ffn_up", "token_embd")}
     recipe.update(attn_v=quant.Q8_0, ffn_down=quant.Q5_K, output=quant.Q6_K)
-    w = weights_to_host(synth_weights(cfg, seed=21, recipe=recipe))
-    ocfg = dict(hidden=256, ffn=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab=512, max_pos=16, rope_theta=500000.0, rms_eps=1e-5)
+    w = weights_to_host(synth_weights(cfg, seed=21, recipe=recipe, qkv_bias=qwen2))
+    ocfg = dict(hidden=256, ffn=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab=512, max_pos=16, rope_theta=500000.0, rms_eps=1e-5,
+                rope_variant=int(qwen2))
     m = oracle.Llama(ocfg, w, kv_f16=False)
     sh = cfg.shapes()
 
@@ -192,16 +195,24 @@ def test_llama_forward_matches_numpy_restatement():
         v = v.reshape(-1, hs).copy()
         ang = pos * 500000.0 ** (-2.0 * np.arange(hs // 2) / hs)
         c, s = np.cos(ang), np.sin(ang)
-        a, b = v[:, 0::2].copy(), v[:, 1::2].copy()
-        v[:, 0::2], v[:, 1::2] = c * a - s * b, s * a + c * b
+        if qwen2:
+            a, b = v[:, :hs // 2].copy(), v[:, hs // 2:].copy()
+            v[:, :hs // 2], v[:, hs // 2:] = c * a - s * b, s * a + c * b
+        else:
+            a, b = v[:, 0::2].copy(), v[:, 1::2].copy()
+            v[:, 0::2], v[:, 1::2] = c * a - s * b, s * a + c * b
         return v.reshape(-1)
+
+    def bias(l, n):
+        return w["layers"][l][n].astype(np.float64) if qwen2 else 0.0
 
     tokens = [5, 77, 300, 12]
     for pos, tok in enumerate(tokens):
         x = E[tok].copy()
         for l in range(2):
             xb = norm(x, w["layers"][l]["attn_norm"])
-            q, k, v = rope(D[l]["attn_q"] @ xb, pos), rope(D[l]["attn_k"] @ xb, pos), D[l]["attn_v"] @ xb
+            q, k = rope(D[l]["attn_q"] @ xb + bias(l, "attn_q_bias"), pos), rope(D[l]["attn_k"] @ xb + bias(l, "attn_k_bias"), pos)
+            v = D[l]["attn_v"] @ xb + bias(l, "attn_v_bias")
             kc[l][pos], vc[l][pos] = k, v
             att = np.zeros(cfg.hidden_size)
             for h in range(4):
@@ -217,6 +228,34 @@ def test_llama_forward_matches_numpy_restatement():
         got = m.forward(tok, pos)
         assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max()), pos
     m.close()
+
+
+def test_neox_rotation_equals_adjacent_rotation_of_reordered_rows():
+    """What the device model relies on for the Qwen2 variant: reordering the rows of Wq, Wk and their biases inside each head as
+    [0, h/2, 1, h/2+1, ...] and rotating adjacent pairs gives the logits of the NeoX rotation on the original rows."""
+    from inferi_b200.llama2 import Llama2Config, synth_weights, weights_to_host
+
+    cfg = Llama2Config(256, 512, 2, 4, 2, 512, 16, 500000.0, 1e-5)
+    recipe = {n: quant.Q4_K for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down", "token_embd", "output")}
+    w = weights_to_host(synth_weights(cfg, seed=5, recipe=recipe, qkv_bias=True))
+    ocfg = dict(hidden=256, ffn=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab=512, max_pos=16, rope_theta=500000.0, rms_eps=1e-5)
+    hs = cfg.head_size
+    order = np.array([(i // 2) + (hs // 2 if i & 1 else 0) for i in range(hs)])
+
+    def reorder(a):
+        a = np.asarray(a)
+        idx = (np.arange(a.shape[0]) // hs * hs) + order[np.arange(a.shape[0]) % hs]
+        return a[idx]
+
+    w2 = dict(w, layers=[dict(lw, attn_q=(lw["attn_q"][0], reorder(lw["attn_q"][1])), attn_k=(lw["attn_k"][0], reorder(lw["attn_k"][1])),
+                              attn_q_bias=reorder(lw["attn_q_bias"]), attn_k_bias=reorder(lw["attn_k_bias"])) for lw in w["layers"]])
+    neox = oracle.Llama(dict(ocfg, rope_variant=1), w, kv_f16=False)
+    adj = oracle.Llama(dict(ocfg, rope_variant=0), w2, kv_f16=False)
+    for pos, tok in enumerate([9, 100, 31, 7, 480]):
+        a, b = neox.forward(tok, pos), adj.forward(tok, pos)
+        assert np.abs(a - b).max() <= 1e-5 * max(1.0, np.abs(a).max())
+    neox.close()
+    adj.close()
 
 
 def _np_sample(logits, temperature, topp, coin):

@@ -10,9 +10,9 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("from_gguf", [False, True])
+@pytest.mark.parametrize("from_gguf,qwen2", [(False, False), (True, False), (True, True)], ids=["tensors", "gguf", "gguf-qwen2"])
 @pytest.mark.parametrize("world", [2])
-def test_two_ranks_match_the_oracle(world, from_gguf, tmp_path):
+def test_two_ranks_match_the_oracle(world, from_gguf, qwen2, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
@@ -21,11 +21,12 @@ def test_two_ranks_match_the_oracle(world, from_gguf, tmp_path):
         sys.path.insert(0, ROOT)
         from inferi_b200.gguf import write_llama_gguf
         from inferi_b200.llama2 import Llama2Config, Q4_K_M, synth_weights
-        cfg = Llama2Config(2048, 8192, 2, 32, 8, 1024, 96, 500000.0, 1e-5)
+        cfg = Llama2Config(2048, 8192, 2, 32, 8, 1024, 96, 500000.0, 1e-5, int(qwen2))
         path = str(tmp_path / "tp.gguf")
-        write_llama_gguf(path, cfg, synth_weights(cfg, seed=4001, recipe=Q4_K_M))
+        write_llama_gguf(path, cfg, synth_weights(cfg, seed=4001, recipe=Q4_K_M, qkv_bias=qwen2), arch="qwen2" if qwen2 else "llama")
         env["TP_FROM_GGUF"] = path
-    port = 29600 + os.getpid() % 1000 + (7 if from_gguf else 0)
+    env["TP_QWEN2"] = "1" if qwen2 else "0"
+    port = 29600 + os.getpid() % 1000 + (7 if from_gguf else 0) + (13 if qwen2 else 0)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)

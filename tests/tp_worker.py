@@ -26,8 +26,9 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", rank))
     dist.init_process_group("gloo")                      # host-side hand-shake only; the data path is peer stores
     torch.cuda.set_device(local)
-    cfg = Llama2Config(2048, 8192, 2, 32, 8, 1024, 96, 500000.0, 1e-5)
-    full = synth_weights(cfg, seed=4001, recipe=Q4_K_M)   # CPU generator: identical on every rank
+    qwen2 = os.environ.get("TP_QWEN2") == "1"             # NeoX rotation + q/k/v biases (sharded by heads like the matrices)
+    cfg = Llama2Config(2048, 8192, 2, 32, 8, 1024, 96, 500000.0, 1e-5, int(qwen2))
+    full = synth_weights(cfg, seed=4001, recipe=Q4_K_M, qkv_bias=qwen2)   # CPU generator: identical on every rank
     mine = tp.shard_weights(cfg, full, rank, world)
     be = Backend(local)
     shapes = tp.shard_shapes(cfg, world, Q4_K_M["ffn_down"])
@@ -36,7 +37,7 @@ def main():
         # every rank maps the same file and uploads its slice itself (the library cuts the GGUF bytes)
         from inferi_b200.gguf import Gguf
         f = Gguf(path)
-        model = f.load_llama(be, kv_f16=True, tp_rank=rank, tp_size=world)
+        model = f.load_llama(be, kv_f16=True, tp_rank=rank, tp_size=world, arch="qwen2" if qwen2 else None)
         f.close()
     else:
         model = Llama2(be, cfg, Llama2Weights(be, cfg, mine, shapes=shapes), kv_f16=True, tp_rank=rank, tp_size=world)
@@ -50,7 +51,8 @@ def main():
     ok = True
     if rank == 0:
         assert all(p[0] == parts[0][0] and p[1] == parts[0][1] for p in parts), "ranks disagree on the greedy tokens"
-        ref = oracle.Llama(dict(hidden=2048, ffn=8192, n_layers=2, n_heads=32, n_kv_heads=8, vocab=1024, max_pos=96, rope_theta=500000.0, rms_eps=1e-5),
+        ref = oracle.Llama(dict(hidden=2048, ffn=8192, n_layers=2, n_heads=32, n_kv_heads=8, vocab=1024, max_pos=96, rope_theta=500000.0, rms_eps=1e-5,
+                                rope_variant=int(qwen2)),
                            weights_to_host(full), kv_f16=True)
         want, tok = [], None
         for pos in range(len(prompt) + n_gen - 1):
