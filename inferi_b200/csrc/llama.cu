@@ -611,7 +611,7 @@ static int32_t finish_graph(ib_llama *m) {
         if (rc == IB_OK && phases.size() != 5 * (size_t)L + 1) rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: unexpected phase list");
         for (uint32_t l = 0; rc == IB_OK && l < L; l++)
             if (m->layers[l].attn_q_bias_dev || m->layers[l].attn_k_bias_dev || m->layers[l].attn_v_bias_dev)
-                rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: q/k/v biases are only on the graph path; unset INFERI_B200_TOKEN_KERNEL");
+                rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: q/k/v biases are only on the graph path");   // falls through to the graph below
         std::vector<PhaseDesc> table(phases.size());
         TokenProgram &P = m->prog;
         if (rc == IB_OK) {

@@ -11,7 +11,8 @@
 //   top-p: candidates p_i >= (1 - topp) / (n - 1), sorted by descending p (stable: ascending index on ties), cut after
 //          the first prefix whose sum exceeds topp, then first i with coin * prefix_sum < running sum (sampler.rs:84-129)
 // Sums run in a fixed order (per-thread chunks, then a block scan): results are deterministic; they can differ from a
-// sequential f32 sum in the last bits, which changes the sampled token only when the coin falls within ~1e-6 of a boundary.
+// sequential f32 sum by rounding (of the order of sqrt(n) * 2^-24 in the running sum), which changes the sampled token only when
+// the coin falls that close to a boundary between two tokens.
 #include "common.cuh"
 
 #include <math.h>
@@ -165,9 +166,26 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float *__r
         for (uint32_t i = i0; i < i1; i++) cnt += probs[i] >= cutoff;
         uint32_t n0;
         uint32_t at = block_scan_u32(cnt, smu, &n0);
-        if (n0 == 0) {   // cannot happen for 0 < topp < 1 (the largest probability is >= 1/n); keep the arg-max semantics
-            n0 = 1;
-            if (tid == 0) keys[0] = 0ull;
+        if (n0 == 0) {
+            // No probability reaches the cut-off ((1 - topp) / (n - 1) can exceed the largest one, e.g. n = 2 with a small
+            // topp).  The reference subtracts 1 from an unsigned zero there (sampler.rs:108); defined here as the arg-max,
+            // lowest index on ties.
+            __shared__ unsigned long long amax;
+            if (tid == 0) amax = 0ull;
+            __syncthreads();
+            unsigned long long b = 0ull;
+            for (uint32_t i = i0; i < i1; i++) {
+                const unsigned long long k = ((unsigned long long)__float_as_uint(probs[i]) << 32) | (0xFFFFFFFFu - i);   // p >= 0: bits order like values
+                b = k > b ? k : b;
+            }
+            if (i0 < i1) atomicMax(&amax, b);
+            __syncthreads();
+            if (tid == 0) {
+                const uint32_t t = 0xFFFFFFFFu - (uint32_t)(amax & 0xFFFFFFFFull);
+                *out = t;
+                if (out2) *out2 = t;
+            }
+            return;
         }
         uint32_t cap = 1;
         while (cap < n0) cap <<= 1;

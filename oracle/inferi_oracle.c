@@ -503,6 +503,13 @@ uint32_t orc_sample(const float *logits, size_t n, float temperature, float topp
         const float cutoff = (1.0f - topp) / ((float)n - 1.0f);
         for (size_t i = 0; i < n; i++)
             if (p[i] >= cutoff) { pi[n0].index = (uint32_t)i; pi[n0].prob = p[i]; n0++; }
+        if (n0 == 0) {
+            /* No probability reaches the cut-off (possible when (1 - topp) / (n - 1) > max p, e.g. n = 2 with a small topp).
+             * The reference computes n0 - 1 on an unsigned zero there (sampler.rs:108: a panic in a checked build);
+             * the defined behaviour here and on the device is the arg-max. */
+            free(pi); free(p);
+            return orc_argmax(logits, n);
+        }
         qsort(pi, n0, sizeof(orc_prob_index), cmp_prob_desc);
         float cumulative = 0.0f;
         size_t last = n0 - 1;

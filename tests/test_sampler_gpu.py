@@ -18,16 +18,51 @@ def gpu_sample(backend, logits, temperature, topp, coin):
     return int(out.item())
 
 
+def valid_within_rounding(logits, temperature, topp, coin, got, tol):
+    """Is `got` what the reference algorithm picks when every running sum may be off by `tol`?  Recomputed in float64."""
+    x = logits.astype(np.float64) / temperature
+    p = np.exp(x - x.max())
+    p /= p.sum()
+    n = p.size
+    if topp <= 0.0 or topp >= 1.0:
+        cdf = np.cumsum(p)
+        lo = cdf[got - 1] if got else 0.0
+        return lo - tol <= coin < cdf[got] + tol or (got == n - 1 and coin >= cdf[-1] - tol)
+    cutoff = (1.0 - topp) / (n - 1.0)
+    cand = np.flatnonzero(p >= cutoff * (1 - 1e-6))
+    if got not in cand:
+        return False
+    pc = np.sort(p[cand])[::-1]
+    cum = np.cumsum(pc)
+    # Tokens whose f32 probabilities are equal or a few ulps apart may be ordered either way (the sort sees f32 values, ties go by
+    # index): `got` sits somewhere between the tokens clearly above it and the tokens clearly below it.
+    eps = 1e-6
+    k_min = int(np.count_nonzero(pc > p[got] * (1 + eps)))
+    k_max = int(np.count_nonzero(pc >= p[got] * (1 - eps))) - 1
+    lo_min = cum[k_min - 1] if k_min else 0.0
+    hi_max = cum[k_max]
+    # every place the nucleus may end when the comparison with topp is taken with a rounding error
+    ends = [i for i in range(cum.size) if cum[i] > topp - tol and (i == 0 or cum[i - 1] <= topp + tol)] or [cum.size - 1]
+    for last in ends:
+        if k_min > last:
+            continue
+        r = coin * cum[last]
+        if lo_min - tol <= r < hi_max + tol or (k_max >= last and r >= lo_min - tol):
+            return True
+    return False
+
+
 def check_many(backend, logits, temperature, topp, coins):
-    close_calls = 0
+    """Identical tokens, except where a running sum in another order may decide otherwise: the reference adds n probabilities
+    one by one in f32, the device adds per-thread chunks and scans them; both are within ~sqrt(n) * 2^-24 of the exact sum, and
+    a coin that close to the boundary between two tokens may fall on either side."""
+    tol = 2e-6 + 8.0 * np.sqrt(logits.size) * 2.0 ** -24
     for coin in coins:
         want, margin = oracle.sample(logits, temperature, topp, float(coin))
         got = gpu_sample(backend, logits, temperature, topp, float(coin))
         if got != want:
-            # a parallel sum differs from the sequential one in the last bits: only a coin on a boundary may decide otherwise
-            assert margin < 2e-6, f"T={temperature} topp={topp} coin={coin}: {got} vs {want} (margin {margin})"
-            close_calls += 1
-    assert close_calls <= max(1, len(coins) // 20)
+            assert margin < tol, f"T={temperature} topp={topp} coin={coin}: {got} vs {want} (margin {margin}, allowed {tol})"
+            assert valid_within_rounding(logits, temperature, topp, float(coin), got, tol), f"T={temperature} topp={topp} coin={coin}: {got} is not a neighbour of {want}"
 
 
 @pytest.mark.parametrize("n", [2, 50, 1000, 4097, 32000, 128256])
@@ -65,8 +100,8 @@ def test_model_loop_with_sampling(backend):
     """The model's own loop with a sampler: every fed-back token must be what the reference's sampler picks from the
     oracle's logits with the same coin, and a run is reproducible from its seed."""
     cfg = Llama2Config(256, 2048, 2, 4, 2, 512, 64, 500000.0, 1e-5)
-    recipe = dict(attn_q=quant.Q4_K, attn_k=quant.Q4_K, attn_v=quant.Q6_K, attn_output=quant.Q4_K, ffn_gate=quant.Q4_K, ffn_up=quant.Q4_K,
-                  ffn_down=quant.Q6_K, token_embd=quant.Q4_K, output=quant.Q6_K)
+    recipe = dict(attn_q=quant.Q4_K, attn_k=quant.Q4_K, attn_v=quant.Q8_0, attn_output=quant.Q4_K, ffn_gate=quant.Q4_K, ffn_up=quant.Q4_K,
+                  ffn_down=quant.Q6_K, token_embd=quant.Q4_K, output=quant.Q8_0)
     w = synth_weights(cfg, seed=77, recipe=recipe, std=0.1)             # larger weights: a distribution with some shape
     model = Llama2(backend, cfg, Llama2Weights(backend, cfg, w), kv_f16=True)
     temperature, topp, seed = 0.8, 0.9, 1234
