@@ -41,9 +41,30 @@ __device__ unsigned long long g_cta_end[8][160], g_cta_packed[8][160];   // per 
     do {                                                                                              \
         if (lane == 0 && warp == 0 && blockIdx.x < 160) arr[EPI][blockIdx.x] = global_ns();           \
     } while (0)
+// Where a consumer warp of CTA 0 spends its cycles, per epilogue kind: [wait for the tile, dot products, shuffle tree,
+// partials / direct epilogue, cross-warp fold, slot release, tiles, total]
+__device__ long long g_phase[8][32][8];
+#define PH_DECL long long _pc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long _t0 = clock64(); const long long _tb = _t0
+#define PH_MARK(i, dep)                                                                       \
+    do {                                                                                      \
+        long long _t;                                                                         \
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(_t) : "f"(dep) : "memory");             \
+        _pc[i] += _t - _t0;                                                                   \
+        _t0 = _t;                                                                             \
+    } while (0)
+#define PH_DUMP(warp_id)                                                                      \
+    do {                                                                                      \
+        if (lane == 0 && blockIdx.x == 0) {                                                   \
+            _pc[7] = clock64() - _tb;                                                         \
+            for (int _i = 0; _i < 8; _i++) g_phase[EPI][warp_id][_i] = _pc[_i];               \
+        }                                                                                     \
+    } while (0)
 #else
 #define TRACE(slot) do { } while (0)
 #define TRACE_CTA(arr) do { } while (0)
+#define PH_DECL do { } while (0)
+#define PH_MARK(i, dep) do { } while (0)
+#define PH_DUMP(warp_id) do { } while (0)
 #endif
 
 struct StreamGeom {
@@ -72,6 +93,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
     const uint32_t S = c.S, CG = c.CG, RG = c.RG;
     TileCursor tc;
     tc.init(sh);
+    PH_DECL;
 #pragma unroll 1
     for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
         const uint32_t st = k % S, s = tc.seg, n = tc.count(sh);
@@ -82,6 +104,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
             cur_type = qtype;
         }
         if (!mbar_wait(c.bar0 + 8 * st, (k / S) & 1, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
+        PH_MARK(0, 0.f);
         const uint8_t *tile = c.ring + (size_t)st * c.stage_bytes;
         const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
         const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
@@ -100,17 +123,20 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                 va = unit_dot<QT>(qtype, rowA, lc, ua);
                 vb = unit_dot<QT>(qtype, rowB, lc, ua);
             }
+            PH_MARK(1, va + vb);
 #pragma unroll
             for (int o = 16; o; o >>= 1) {
                 va += __shfl_xor_sync(0xffffffffu, va, o);
                 vb += __shfl_xor_sync(0xffffffffu, vb, o);
             }
+            PH_MARK(2, va + vb);
             if (CG == 1) {
                 if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p}, rpre);
             } else if (lane == 0) {
                 pt[(pr * 2 + 0) * CW + c.cg] = va;
                 pt[(pr * 2 + 1) * CW + c.cg] = vb;
             }
+            PH_MARK(3, 0.f);
         }
         if (CG > 1) {
             // the last warp of the row group to finish the tile folds the column partials in a fixed order
@@ -136,8 +162,14 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
             }
         }
         __syncwarp();
+        PH_MARK(4, 0.f);
         if (lane == 0) mbar_arrive(c.bar0 + 8 * (S + st));   // this warp is done with the stage
+        PH_MARK(5, 0.f);
+#ifdef IB_STREAM_TRACE
+        _pc[6] += 1;
+#endif
     }
+    PH_DUMP(c.cg + c.rg * c.CG);
 }
 
 // ---- the kernel ----
@@ -406,6 +438,9 @@ extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(
 extern "C" __attribute__((visibility("default"))) int32_t ib_debug_cta_times(unsigned long long *ends, unsigned long long *packed) {
     if (cudaMemcpyFromSymbol(ends, g_cta_end, sizeof(unsigned long long) * 8 * 160) != cudaSuccess) return 2;
     return cudaMemcpyFromSymbol(packed, g_cta_packed, sizeof(unsigned long long) * 8 * 160) == cudaSuccess ? 0 : 2;
+}
+extern "C" __attribute__((visibility("default"))) int32_t ib_debug_consumer_phases(long long *out) {
+    return cudaMemcpyFromSymbol(out, g_phase, sizeof(long long) * 8 * 32 * 8) == cudaSuccess ? 0 : 2;
 }
 #endif
 
