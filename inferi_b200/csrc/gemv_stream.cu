@@ -42,9 +42,9 @@ __device__ unsigned long long g_cta_end[8][160], g_cta_packed[8][160];   // per 
         if (lane == 0 && warp == 0 && blockIdx.x < 160) arr[EPI][blockIdx.x] = global_ns();           \
     } while (0)
 // Where a consumer warp of CTA 0 spends its cycles, per epilogue kind: [wait for the tile, dot products, shuffle tree,
-// partials / direct epilogue, cross-warp fold, slot release, tiles, total]
-__device__ long long g_phase[8][32][8];
-#define PH_DECL long long _pc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long _t0 = clock64(); const long long _tb = _t0
+// partials / direct epilogue, cross-warp fold, slot release, tiles, total, loop bookkeeping before the wait]
+__device__ long long g_phase[8][32][10];
+#define PH_DECL long long _pc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long _t0 = clock64(); const long long _tb = _t0
 #define PH_MARK(i, dep)                                                                       \
     do {                                                                                      \
         long long _t;                                                                         \
@@ -56,7 +56,7 @@ __device__ long long g_phase[8][32][8];
     do {                                                                                      \
         if (lane == 0 && blockIdx.x == 0) {                                                   \
             _pc[7] = clock64() - _tb;                                                         \
-            for (int _i = 0; _i < 8; _i++) g_phase[EPI][warp_id][_i] = _pc[_i];               \
+            for (int _i = 0; _i < 10; _i++) g_phase[EPI][warp_id][_i] = _pc[_i];               \
         }                                                                                     \
     } while (0)
 #else
@@ -67,6 +67,12 @@ __device__ long long g_phase[8][32][8];
 #define PH_DUMP(warp_id) do { } while (0)
 #endif
 
+#ifndef IB_COPY_PIECE_BYTES
+#define IB_COPY_PIECE_BYTES (1u << 24)   // larger than any tile: one bulk copy per tile part
+#endif
+constexpr uint32_t COPY_PIECE = IB_COPY_PIECE_BYTES;   // a multiple of 16; 32 x COPY_PIECE must fit 32 bits
+static_assert(COPY_PIECE % 16 == 0 && COPY_PIECE <= (1u << 26), "piece size");
+
 struct StreamGeom {
     uint32_t stages, stage_bytes, act_off, part_off, bar_off;
 };
@@ -75,7 +81,7 @@ struct StreamGeom {
 struct Consumer {
     const uint8_t *ring;
     float *part;          // [stages][PT_MAX][2][CW] per-warp column partials
-    uint32_t *cnt;        // [stages][CW] arrivals of a row group's warps
+    uint32_t fold0;       // mbarriers [stages][CW]: the other warps of a row group have left their partials of the tile
     uint32_t bar0, S, stage_bytes;
     uint32_t CG, RG, cg, rg, u;
     bool has_unit;
@@ -94,26 +100,30 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
     TileCursor tc;
     tc.init(sh);
     PH_DECL;
+    // stage and phase parity of the tile, and the warp of the row group that folds it (they take turns), kept as counters:
+    // a division by a run-time value per tile is a chain of ~200 cycles that nothing overlaps
+    uint32_t st = 0, par = 0, folder = c.rg % CG;
 #pragma unroll 1
-    for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
-        const uint32_t st = k % S, s = tc.seg, n = tc.count(sh);
+    for (; tc.valid(sh); tc.advance(sh), st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u, folder = (folder + 1 == CG) ? 0 : folder + 1) {
+        const uint32_t s = tc.seg, n = tc.count(sh);
         const uint32_t qtype = (QT != QT_MIXED) ? QT : p.seg[s].qtype;
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
             unit_init<QT>(qtype, c.u, lc);
             if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
             cur_type = qtype;
         }
-        if (!mbar_wait(c.bar0 + 8 * st, (k / S) & 1, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
+        PH_MARK(8, 0.f);   // loop bookkeeping since the slot release
+        if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
         PH_MARK(0, 0.f);
         const uint8_t *tile = c.ring + (size_t)st * c.stage_bytes;
         const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
         const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
         const uint32_t strideA = (EPI == EPI_SWIGLU) ? rbA : 2 * rbA, offB = (EPI == EPI_SWIGLU) ? n * rbA : rbA;
         float *pt = c.part + (size_t)st * PT_MAX * 2 * CW;
-        // residual values of the pair this lane may have to finish (CG > 1: as the last warp of the row group; CG == 1: lane 0
-        // of each pair's warp, fetched per pair below): requested now, needed after the dot products
+        // residual values of the pair this lane has to finish (CG > 1: in the warp that folds this tile; CG == 1: lane 0 of
+        // each pair's warp, fetched per pair below): requested now, needed after the dot products
         float2 rpre = make_float2(0.f, 0.f);
-        if (EPI == EPI_RESIDUAL && CG > 1 && c.rg + RG * lane < n) rpre = residual_prefetch(p.resid, tc.next + c.rg + RG * lane);
+        if (EPI == EPI_RESIDUAL && CG > 1 && c.cg == folder && c.rg + RG * lane < n) rpre = residual_prefetch(p.resid, tc.next + c.rg + RG * lane);
         for (uint32_t pr = c.rg; pr < n; pr += RG) {
             const uint8_t *rowA = tile + pr * strideA;
             const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + offB + pr * rbB : rowA + rbA;
@@ -139,15 +149,15 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
             PH_MARK(3, 0.f);
         }
         if (CG > 1) {
-            // the last warp of the row group to finish the tile folds the column partials in a fixed order
-            uint32_t last = 0;
-            if (lane == 0) {
-                __threadfence_block();
-                last = (atomicAdd(c.cnt + st * CW + c.rg, 1u) == CG - 1) ? 1u : 0u;
-            }
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence_block();
+            // The row group's warps take turns folding a tile.  The others leave their partials and arrive on the tile's
+            // fold barrier (a release) without waiting; the folding warp waits for their CG - 1 arrivals (an acquire), adds
+            // the column partials in a fixed order and runs the epilogue.
+            const uint32_t fb = c.fold0 + 8 * (st * CW + c.rg);
+            if (c.cg != folder) {
+                if (lane == 0) mbar_arrive(fb);
+            } else {
+                __syncwarp();   // lane 0's own partials, read by the other lanes below
+                if (!mbar_wait(fb, par, p.err, 5)) return;
                 const uint32_t pr = c.rg + RG * lane;
                 if (pr < n) {
                     float va = 0.f, vb = 0.f;
@@ -157,8 +167,6 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                     }
                     epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p}, rpre);
                 }
-                __syncwarp();
-                if (lane == 0) c.cnt[st * CW + c.rg] = 0;
             }
         }
         __syncwarp();
@@ -185,7 +193,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     uint8_t *ring = smem;
     uint8_t *act_sm = smem + geo.act_off;
     float *part = reinterpret_cast<float *>(smem + geo.part_off);              // [stages][PT_MAX][2][CW]
-    uint32_t *cnt = reinterpret_cast<uint32_t *>(part + geo.stages * PT_MAX * 2 * CW);   // [stages][CW]
+    const uint32_t fold0 = smem_u32(part + geo.stages * PT_MAX * 2 * CW);                // mbarriers [stages][CW]
     const uint32_t bar0 = smem_u32(smem + geo.bar_off);                         // full[stages], empty[stages]
     const uint32_t S = geo.stages;
 
@@ -204,35 +212,41 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         mbar_init(bar0 + 8 * threadIdx.x, threadIdx.x < S ? 1u : active);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     } else if (threadIdx.x >= 32 && threadIdx.x < 32 + S * CW) {
-        cnt[threadIdx.x - 32] = 0;
+        // fold barrier of (stage, row group): the arrivals of the row group's warps other than the folding one
+        mbar_init(fold0 + 8 * (threadIdx.x - 32), CG > 1 ? CG - 1 : 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     TRACE(1);
     if (p.pdl) asm volatile("griddepcontrol.launch_dependents;");
 
     if (warp == CW) {
-        // ================= producer warp: one lane streams this CTA's tiles =================
-        if (lane == 0) {
-            TileCursor tc;
-            tc.init(sh);
-            for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh)) {
-                const uint32_t st = k % S;
-                if (k >= S && !mbar_wait(bar0 + 8 * (S + st), ((k / S) - 1) & 1, p.err, 2)) break;
-                const uint32_t n = tc.count(sh), s = tc.seg;
-                const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes), full = bar0 + 8 * st;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (EPI == EPI_SWIGLU) {
-                    const uint32_t ba = n * (uint32_t)p.seg[0].row_bytes, bb = n * (uint32_t)p.seg[1].row_bytes;
-                    mbar_expect_tx(full, ba + bb);
-                    bulk_g2s(dst, p.seg[0].w + (size_t)tc.next * p.seg[0].row_bytes, ba, full);
-                    bulk_g2s(dst + ba, p.seg[1].w + (size_t)tc.next * p.seg[1].row_bytes, bb, full);
-                } else {
-                    const uint32_t bytes = n * sh.cost(s);
-                    mbar_expect_tx(full, bytes);
-                    bulk_g2s(dst, p.seg[s].w + (size_t)tc.next * sh.cost(s), bytes, full);
-                }
-                TRACE(2 + (k < 6 ? k : 6));
-            }
+        // ================= producer warp: streams this CTA's tiles =================
+        // Lane 0 waits for the slot and announces the tile's bytes; the copy itself is issued as pieces of at most
+        // COPY_PIECE bytes, one lane each: several smaller bulk copies in flight fetch faster than one large one.
+        TileCursor tc;
+        tc.init(sh);
+        uint32_t st = 0, par = 1;   // parity of the slot's previous use ("1" before the first one: nothing to wait for)
+        bool first_round = true;
+        for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh), st = (st + 1 == S) ? 0 : st + 1) {
+            if (st == 0 && k > 0) { par ^= 1u; first_round = false; }
+            uint32_t ok = 1;
+            if (!first_round && lane == 0) ok = mbar_wait(bar0 + 8 * (S + st), par, p.err, 2) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            const uint32_t n = tc.count(sh), s = tc.seg;
+            const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes), full = bar0 + 8 * st;
+            const uint32_t ba = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[0].row_bytes : n * sh.cost(s);
+            const uint32_t bb = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[1].row_bytes : 0u;
+            const uint8_t *srcA = (EPI == EPI_SWIGLU) ? p.seg[0].w + (size_t)tc.next * p.seg[0].row_bytes : p.seg[s].w + (size_t)tc.next * sh.cost(s);
+            const uint8_t *srcB = (EPI == EPI_SWIGLU) ? p.seg[1].w + (size_t)tc.next * p.seg[1].row_bytes : nullptr;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // every issuing lane: the consumers' reads of the slot come first
+            if (lane == 0) mbar_expect_tx(full, ba + bb);
+            __syncwarp();
+            for (uint32_t off = lane * COPY_PIECE; off < ba; off += 32 * COPY_PIECE) bulk_g2s(dst + off, srcA + off, min(COPY_PIECE, ba - off), full);
+            if constexpr (EPI == EPI_SWIGLU)
+                for (uint32_t off = lane * COPY_PIECE; off < bb; off += 32 * COPY_PIECE) bulk_g2s(dst + ba + off, srcB + off, min(COPY_PIECE, bb - off), full);
+            TRACE(2 + (k < 6 ? k : 6));
         }
         return;
     }
@@ -257,7 +271,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     unsigned long long best = 0ull;
     if ((uint32_t)warp < active) {
         Consumer c;
-        c.ring = ring; c.part = part; c.cnt = cnt; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
+        c.ring = ring; c.part = part; c.fold0 = fold0; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
         c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
         consume_tiles<EPI, QT>(p, sh, c, A, best);
     }
@@ -401,7 +415,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
             }
         stage = (stage + 127) & ~127u;
         for (S = 4;; S--) {
-            const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4;
+            const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 8;
             total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8;
             if (total <= STREAM_SMEM_BUDGET || S == 2) break;
         }
@@ -416,7 +430,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     geo.stage_bytes = stage;
     geo.act_off = S * stage;
     geo.part_off = (uint32_t)(geo.act_off + act);
-    geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 4 + 127) & ~(size_t)127));
+    geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 8 + 127) & ~(size_t)127));
     int grid = ctx->sm_count;       // one persistent CTA per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
     if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
@@ -440,7 +454,7 @@ extern "C" __attribute__((visibility("default"))) int32_t ib_debug_cta_times(uns
     return cudaMemcpyFromSymbol(packed, g_cta_packed, sizeof(unsigned long long) * 8 * 160) == cudaSuccess ? 0 : 2;
 }
 extern "C" __attribute__((visibility("default"))) int32_t ib_debug_consumer_phases(long long *out) {
-    return cudaMemcpyFromSymbol(out, g_phase, sizeof(long long) * 8 * 32 * 8) == cudaSuccess ? 0 : 2;
+    return cudaMemcpyFromSymbol(out, g_phase, sizeof(long long) * 8 * 32 * 10) == cudaSuccess ? 0 : 2;
 }
 #endif
 

@@ -19,12 +19,15 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+#ifndef IB_TRY_WAIT_HINT_NS
+#define IB_TRY_WAIT_HINT_NS 2000u
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(2000u)   // suspend-time hint in ns: a waiting warp sleeps instead of spinning through issue slots
+        : "r"(bar), "r"(parity), "r"(IB_TRY_WAIT_HINT_NS)   // suspend-time hint in ns: a waiting warp sleeps instead of spinning through issue slots
         : "memory");
     return ok != 0;
 }

@@ -113,16 +113,16 @@ def main() -> None:
             pk = (packed[e * 160:e * 160 + 148].astype(np.int64) - int(t[e * 16])) / 1e3
             print(f"{names[e]:18s} converted: min {pk.min():.2f} median {np.median(pk):.2f} max {pk.max():.2f} | CTA end: min {en.min():.2f} p10 {np.percentile(en, 10):.2f} "
                   f"median {np.median(en):.2f} p90 {np.percentile(en, 90):.2f} max {en.max():.2f}")
-        ph = np.zeros((8, 32, 8), dtype=np.int64)
+        ph = np.zeros((8, 32, 10), dtype=np.int64)
         lib.ib_debug_consumer_phases.argtypes = [C.c_void_p]
         lib.ib_debug_consumer_phases(ph.ctypes.data_as(C.c_void_p))
         print("consumer warps of CTA 0, SM cycles per tile: wait for the tile | dot products | shuffle tree | partials or epilogue | "
-              "cross-warp fold | slot release || tiles | cycles in the loop")
+              "cross-warp fold | slot release | loop bookkeeping || tiles | cycles in the loop")
         for e in (3, 2, 1, 4):
             rows = ph[e][ph[e][:, 6] > 0]
             if rows.size == 0:
                 continue
-            per = rows[:, :6] / rows[:, 6:7]
+            per = rows[:, [0, 1, 2, 3, 4, 5, 8]] / rows[:, 6:7]
             print(f"{names[e]:18s} median over {rows.shape[0]} warps: " + " | ".join(f"{v:7.0f}" for v in np.median(per, axis=0))
                   + f" || {np.median(rows[:, 6]):.0f} | {np.median(rows[:, 7]):.0f}")
             print(f"{'':18s} slowest warp:          " + " | ".join(f"{v:7.0f}" for v in per[np.argmax(rows[:, 7])])
