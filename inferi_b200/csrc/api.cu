@@ -80,6 +80,14 @@ int32_t ib_ctx_create(int32_t device, ib_ctx **out) {
         delete ctx;
         return set_error(IB_ERR_CUDA, "allocating the error word failed: %s", cudaGetErrorString(he));
     }
+    cudaError_t ce = cudaMalloc((void **)&ctx->stream_counters, sizeof(uint32_t) * 2 * IB_STREAM_COUNTER_PAIRS);
+    if (ce == cudaSuccess) ce = cudaMemset(ctx->stream_counters, 0, sizeof(uint32_t) * 2 * IB_STREAM_COUNTER_PAIRS);
+    if (ce != cudaSuccess) {
+        if (ctx->stream_counters) cudaFree(ctx->stream_counters);
+        cudaFreeHost(ctx->err_host);
+        delete ctx;
+        return set_error(IB_ERR_CUDA, "allocating the tile counters failed: %s", cudaGetErrorString(ce));
+    }
     *out = ctx;
     return IB_OK;
 }
@@ -92,6 +100,7 @@ int32_t ib_ctx_destroy(ib_ctx *ctx) {
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
     if (ctx->argmax_counter) cudaFree(ctx->argmax_counter);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
+    if (ctx->stream_counters) cudaFree(ctx->stream_counters);
     delete ctx;
     return IB_OK;
 }

@@ -82,7 +82,12 @@ struct ib_ctx {
     // after any synchronisation without a copy
     uint32_t *err_host = nullptr;
     uint32_t *err_dev = nullptr;
+    // (claimed, finished) counter pairs through which the CTAs of a streaming GEMV launch share out its tiles; launch i
+    // uses pair i mod IB_STREAM_COUNTER_PAIRS (only neighbouring launches overlap), its last CTA clears the pair
+    uint32_t *stream_counters = nullptr;
+    uint64_t stream_seq = 0;
 };
+constexpr uint32_t IB_STREAM_COUNTER_PAIRS = 16;
 
 struct ib_qtensor {
     ib_ctx *ctx = nullptr;
@@ -130,6 +135,7 @@ struct GemvParams {
     const float2 *rope_cs;      // [head_size/2] (cos, sin) of pos * theta_j for the current token
     uint32_t head_size, kv_dim, kv_dtype;
     void *k_cache, *v_cache;    // [max_pos, kv_dim] of this layer
+    uint32_t *tile_claim;       // streaming kernel: [claimed, finished] counters of this launch (set by its launcher)
     const float *bias[3];       // optional f32 bias per segment, added before the rotation (Qwen2: transformer.rs:434-442)
     // EPI_ARGMAX
     unsigned long long *argmax_slots;  // one packed (value, ~index) per CTA

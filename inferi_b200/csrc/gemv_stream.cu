@@ -17,6 +17,8 @@
 // Every wait on an mbarrier is bounded; a wait that gives up raises the context's error word and carries on.
 #include "gemv_stream.cuh"
 
+#include <stdlib.h>
+
 namespace ib {
 
 #ifdef IB_STREAM_TRACE
@@ -75,13 +77,29 @@ static_assert(COPY_PIECE % 16 == 0 && COPY_PIECE <= (1u << 26), "piece size");
 
 struct StreamGeom {
     uint32_t stages, stage_bytes, act_off, part_off, bar_off;
+    // the launch's tiles in hand-out order: per segment the pairs, the pairs per tile and the tiles; bytes per pair
+    uint32_t seg_pairs[3], seg_pt[3], seg_tiles[3], seg_cost[3], total_tiles, meta_off;
+    uint32_t dynamic;   // 1: tiles are claimed from a counter; 0: every CTA streams its own byte-balanced range of pairs
 };
+
+// Tile number -> (segment, first pair, pairs); pairs == 0 past the last tile.
+__device__ __forceinline__ uint4 tile_of(const StreamGeom &g, uint32_t t) {
+    uint32_t s = 0;
+    if (t >= g.seg_tiles[0]) { t -= g.seg_tiles[0]; s = 1; if (t >= g.seg_tiles[1]) { t -= g.seg_tiles[1]; s = 2; } }
+    const uint32_t np = s == 0 ? g.seg_pairs[0] : (s == 1 ? g.seg_pairs[1] : g.seg_pairs[2]);
+    const uint32_t pt = s == 0 ? g.seg_pt[0] : (s == 1 ? g.seg_pt[1] : g.seg_pt[2]);
+    const uint32_t nt = s == 0 ? g.seg_tiles[0] : (s == 1 ? g.seg_tiles[1] : g.seg_tiles[2]);
+    if (t >= nt) return make_uint4(0, 0, 0, 0);
+    const uint32_t first = t * pt;
+    return make_uint4(s, first, (np - first) < pt ? (np - first) : pt, 0);
+}
 
 // ---- consumer side ----
 struct Consumer {
     const uint8_t *ring;
     float *part;          // [stages][PT_MAX][2][CW] per-warp column partials
     uint32_t fold0;       // mbarriers [stages][CW]: the other warps of a row group have left their partials of the tile
+    const uint4 *meta;    // [stages] (segment, first pair, pairs, -) of the tile in the slot, written by the producer
     uint32_t bar0, S, stage_bytes;
     uint32_t CG, RG, cg, rg, u;
     bool has_unit;
@@ -91,30 +109,32 @@ struct Consumer {
 // Consumes this warp's share of every tile.  One loop for all formats (the format switch sits at the dot product):
 // separate inlined loops per format made the register allocator spill.
 template <uint32_t EPI, uint32_t QT>
-__device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &sh, const Consumer &c, const Act &A, unsigned long long &best) {
+__device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consumer &c, const Act &A, unsigned long long &best) {
     const int lane = c.lane;
     UnitAct ua;
     LaneConst lc;
     uint32_t cur_type = 0xFFFFFFFFu;
     const uint32_t S = c.S, CG = c.CG, RG = c.RG;
-    TileCursor tc;
-    tc.init(sh);
     PH_DECL;
     // stage and phase parity of the tile, and the warp of the row group that folds it (they take turns), kept as counters:
     // a division by a run-time value per tile is a chain of ~200 cycles that nothing overlaps
     uint32_t st = 0, par = 0, folder = c.rg % CG;
 #pragma unroll 1
-    for (; tc.valid(sh); tc.advance(sh), st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u, folder = (folder + 1 == CG) ? 0 : folder + 1) {
-        const uint32_t s = tc.seg, n = tc.count(sh);
+    for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u, folder = (folder + 1 == CG) ? 0 : folder + 1) {
+        PH_MARK(8, 0.f);   // loop bookkeeping since the slot release
+        if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
+        PH_MARK(0, 0.f);
+        // which tile the producer put into the slot (tiles are handed out through a counter: a CTA that starts late or
+        // runs slowly takes fewer of them); no pairs = no tiles left
+        const uint4 tm = c.meta[st];
+        const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
+        if (n == 0) break;
         const uint32_t qtype = (QT != QT_MIXED) ? QT : p.seg[s].qtype;
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
             unit_init<QT>(qtype, c.u, lc);
             if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
             cur_type = qtype;
         }
-        PH_MARK(8, 0.f);   // loop bookkeeping since the slot release
-        if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
-        PH_MARK(0, 0.f);
         const uint8_t *tile = c.ring + (size_t)st * c.stage_bytes;
         const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
         const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
@@ -123,25 +143,30 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
         // residual values of the pair this lane has to finish (CG > 1: in the warp that folds this tile; CG == 1: lane 0 of
         // each pair's warp, fetched per pair below): requested now, needed after the dot products
         float2 rpre = make_float2(0.f, 0.f);
-        if (EPI == EPI_RESIDUAL && CG > 1 && c.cg == folder && c.rg + RG * lane < n) rpre = residual_prefetch(p.resid, tc.next + c.rg + RG * lane);
+        if (EPI == EPI_RESIDUAL && CG > 1 && c.cg == folder && c.rg + RG * lane < n) rpre = residual_prefetch(p.resid, first_pair + c.rg + RG * lane);
         for (uint32_t pr = c.rg; pr < n; pr += RG) {
             const uint8_t *rowA = tile + pr * strideA;
             const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + offB + pr * rbB : rowA + rbA;
-            if (EPI == EPI_RESIDUAL && CG == 1 && lane == 0) rpre = residual_prefetch(p.resid, tc.next + pr);
+            if (EPI == EPI_RESIDUAL && CG == 1 && lane == 0) rpre = residual_prefetch(p.resid, first_pair + pr);
             float va = 0.f, vb = 0.f;
             if (c.has_unit) {
                 va = unit_dot<QT>(qtype, rowA, lc, ua);
                 vb = unit_dot<QT>(qtype, rowB, lc, ua);
             }
             PH_MARK(1, va + vb);
+            {
+                // one shuffle tree for both rows: after the first exchange the upper half-warp carries row B
+                // (the same pairs are added in the same order as two separate trees would: the bits do not change)
+                const bool up = lane & 16;
+                float v = (up ? vb : va) + __shfl_xor_sync(0xffffffffu, up ? va : vb, 16);
 #pragma unroll
-            for (int o = 16; o; o >>= 1) {
-                va += __shfl_xor_sync(0xffffffffu, va, o);
-                vb += __shfl_xor_sync(0xffffffffu, vb, o);
+                for (int o = 8; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                va = __shfl_sync(0xffffffffu, v, 0);
+                vb = __shfl_sync(0xffffffffu, v, 16);
             }
             PH_MARK(2, va + vb);
             if (CG == 1) {
-                if (lane == 0) epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p}, rpre);
+                if (lane == 0) epilogue<EPI>(p, s, first_pair + pr, va, vb, best, ParamCaches{p}, rpre);
             } else if (lane == 0) {
                 pt[(pr * 2 + 0) * CW + c.cg] = va;
                 pt[(pr * 2 + 1) * CW + c.cg] = vb;
@@ -165,7 +190,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Share &
                         va += pt[(pr * 2 + 0) * CW + g];
                         vb += pt[(pr * 2 + 1) * CW + g];
                     }
-                    epilogue<EPI>(p, s, tc.next + pr, va, vb, best, ParamCaches{p}, rpre);
+                    epilogue<EPI>(p, s, first_pair + pr, va, vb, best, ParamCaches{p}, rpre);
                 }
             }
         }
@@ -202,9 +227,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     const uint32_t RG = CW / CG;                 // row groups working side by side
     const uint32_t active = CG * RG;             // consumer warps with work
 
-    Share sh;
-    make_share<EPI>(p, geo.stage_bytes, RG, sh);
-
 
     // set-up spread over threads: it sits on the critical path of a CTA that starts late (its SM was the last to be freed)
     if (threadIdx.x < 2 * S) {
@@ -221,25 +243,55 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     if (p.pdl) asm volatile("griddepcontrol.launch_dependents;");
 
     if (warp == CW) {
-        // ================= producer warp: streams this CTA's tiles =================
-        // Lane 0 waits for the slot and announces the tile's bytes; the copy itself is issued as pieces of at most
-        // COPY_PIECE bytes, one lane each: several smaller bulk copies in flight fetch faster than one large one.
+        // ================= producer warp: picks tiles and streams them =================
+        // With many tiles per CTA they are handed out through a counter in global memory, so that a CTA which starts late
+        // (its SM was the last to be freed by the previous kernel) or runs slowly takes fewer of them.  With few tiles per
+        // CTA a tile is too coarse a unit for that: every CTA then streams its own byte-balanced range of row pairs, cut
+        // into tiles.  Either way the slot's descriptor tells the consumers what the tile is.  Lane 0 picks, waits for the
+        // slot and announces the tile; the copy is issued as pieces of at most COPY_PIECE bytes, one lane each.
+        uint4 *meta = reinterpret_cast<uint4 *>(smem + geo.meta_off);
+        const bool dyn = geo.dynamic != 0;
+        Share sh;
         TileCursor tc;
-        tc.init(sh);
+        if (!dyn) {
+            make_share<EPI>(p, geo.stage_bytes, RG, sh);
+            tc.init(sh);
+        }
         uint32_t st = 0, par = 1;   // parity of the slot's previous use ("1" before the first one: nothing to wait for)
         bool first_round = true;
-        for (uint32_t k = 0; tc.valid(sh); k++, tc.advance(sh), st = (st + 1 == S) ? 0 : st + 1) {
+        uint32_t t = 0, held = S;   // the ring's first S tiles come from one claim
+        if (dyn && lane == 0) t = atomicAdd(p.tile_claim, S);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        for (uint32_t k = 0;; k++, st = (st + 1 == S) ? 0 : st + 1) {
             if (st == 0 && k > 0) { par ^= 1u; first_round = false; }
+            // the tile after this one is claimed now: the counter's round trip overlaps the wait for the slot
+            uint32_t tn = 0;
+            if (dyn && held == 1 && lane == 0 && t < geo.total_tiles) tn = atomicAdd(p.tile_claim, 1u);
             uint32_t ok = 1;
             if (!first_round && lane == 0) ok = mbar_wait(bar0 + 8 * (S + st), par, p.err, 2) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            const uint32_t n = tc.count(sh), s = tc.seg;
-            const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes), full = bar0 + 8 * st;
-            const uint32_t ba = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[0].row_bytes : n * sh.cost(s);
+            const uint4 tm = dyn ? tile_of(geo, t) : (tc.valid(sh) ? make_uint4(tc.seg, tc.next, tc.count(sh), 0) : make_uint4(0, 0, 0, 0));
+            const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
+            const uint32_t full = bar0 + 8 * st;
+            if (lane == 0) meta[st] = tm;
+            if (n == 0) {
+                // no tiles left: tell the consumers, and let the last CTA to get here clear the counters for their next use
+                if (lane == 0) {
+                    mbar_arrive(full);
+                    if (dyn && atomicAdd(p.tile_claim + 1, 1u) == gridDim.x - 1) {
+                        p.tile_claim[0] = 0u;
+                        p.tile_claim[1] = 0u;
+                    }
+                }
+                break;
+            }
+            const uint32_t cost = s == 0 ? geo.seg_cost[0] : (s == 1 ? geo.seg_cost[1] : geo.seg_cost[2]);
+            const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes);
+            const uint32_t ba = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[0].row_bytes : n * cost;
             const uint32_t bb = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[1].row_bytes : 0u;
-            const uint8_t *srcA = (EPI == EPI_SWIGLU) ? p.seg[0].w + (size_t)tc.next * p.seg[0].row_bytes : p.seg[s].w + (size_t)tc.next * sh.cost(s);
-            const uint8_t *srcB = (EPI == EPI_SWIGLU) ? p.seg[1].w + (size_t)tc.next * p.seg[1].row_bytes : nullptr;
+            const uint8_t *srcA = (EPI == EPI_SWIGLU) ? p.seg[0].w + (size_t)first_pair * p.seg[0].row_bytes : p.seg[s].w + (size_t)first_pair * cost;
+            const uint8_t *srcB = (EPI == EPI_SWIGLU) ? p.seg[1].w + (size_t)first_pair * p.seg[1].row_bytes : nullptr;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // every issuing lane: the consumers' reads of the slot come first
             if (lane == 0) mbar_expect_tx(full, ba + bb);
             __syncwarp();
@@ -247,6 +299,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
             if constexpr (EPI == EPI_SWIGLU)
                 for (uint32_t off = lane * COPY_PIECE; off < bb; off += 32 * COPY_PIECE) bulk_g2s(dst + ba + off, srcB + off, min(COPY_PIECE, bb - off), full);
             TRACE(2 + (k < 6 ? k : 6));
+            if (!dyn) tc.advance(sh);
+            else if (held > 1) { t++; held--; }
+            else t = __shfl_sync(0xffffffffu, tn, 0);
         }
         return;
     }
@@ -271,9 +326,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     unsigned long long best = 0ull;
     if ((uint32_t)warp < active) {
         Consumer c;
-        c.ring = ring; c.part = part; c.fold0 = fold0; c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
+        c.ring = ring; c.part = part; c.fold0 = fold0; c.meta = reinterpret_cast<const uint4 *>(smem + geo.meta_off); c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
         c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
-        consume_tiles<EPI, QT>(p, sh, c, A, best);
+        consume_tiles<EPI, QT>(p, c, A, best);
     }
     TRACE(15);
     TRACE_CTA(g_cta_end);
@@ -382,6 +437,8 @@ static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvPar
     }
 }
 
+static int32_t launch_stream_switch(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t total);
+
 int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p) {
     uint32_t max_cost = 0, pairs = 0;
     if (p.epi == EPI_SWIGLU) {
@@ -416,14 +473,19 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
         stage = (stage + 127) & ~127u;
         for (S = 4;; S--) {
             const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 8;
-            total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8;
+            total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8 + S * 16;   // + barriers + tile descriptors
             if (total <= STREAM_SMEM_BUDGET || S == 2) break;
         }
         return total <= STREAM_SMEM_BUDGET;
     };
     uint32_t stage = 0, S = 0;
     size_t total = 0;
-    if (!layout(75776, stage, S, total) && !layout(49152, stage, S, total) && !layout(32768, stage, S, total) && !layout(max_cost, stage, S, total))
+    static const uint32_t first_try = [] {
+        const char *e = getenv("INFERI_B200_TILE_BYTES");   // experiments: the largest tile to try first
+        const long v = e ? atol(e) : 0;
+        return (uint32_t)(v >= 4096 && v <= 98304 ? v : 75776);
+    }();
+    if (!layout(first_try, stage, S, total) && !layout(49152, stage, S, total) && !layout(32768, stage, S, total) && !layout(max_cost, stage, S, total))
         return set_error(IB_ERR_UNSUPPORTED, "gemv: a row pair of %u bytes with %u columns does not fit the streaming kernel's ring", max_cost, p.cols);
     StreamGeom geo;
     geo.stages = S;
@@ -431,9 +493,37 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     geo.act_off = S * stage;
     geo.part_off = (uint32_t)(geo.act_off + act);
     geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 8 + 127) & ~(size_t)127));
+    geo.meta_off = geo.bar_off + 2 * S * 8;
+    // the tiles in hand-out order: per segment whole rounds of the row groups, as many as fit a stage
+    geo.total_tiles = 0;
+    for (uint32_t s = 0; s < 3; s++) {
+        geo.seg_pairs[s] = geo.seg_tiles[s] = 0;
+        geo.seg_pt[s] = 1;
+        geo.seg_cost[s] = 16;
+        const bool swiglu = p.epi == EPI_SWIGLU;
+        if (s >= (swiglu ? 1u : p.nseg)) continue;
+        const uint32_t cost = swiglu ? max_cost : (uint32_t)(2 * p.seg[s].row_bytes);
+        uint32_t pt = stage / cost;
+        pt = pt < 1 ? 1 : (pt > (uint32_t)PT_MAX ? (uint32_t)PT_MAX : pt);
+        if (pt > RG) pt = pt / RG * RG;
+        geo.seg_cost[s] = cost;
+        geo.seg_pt[s] = pt;
+        geo.seg_pairs[s] = swiglu ? p.seg[0].rows : p.seg[s].rows / 2;
+        geo.seg_tiles[s] = (geo.seg_pairs[s] + pt - 1) / pt;
+        geo.total_tiles += geo.seg_tiles[s];
+    }
     int grid = ctx->sm_count;       // one persistent CTA per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
     if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
+    geo.dynamic = geo.total_tiles >= 6u * (uint32_t)grid ? 1u : 0u;
+    // the counters through which this launch's CTAs share out the tiles: consecutive launches overlap (programmatic
+    // dependent launch), so they take different pairs of a small ring; the last CTA of a launch clears its pair
+    GemvParams q = p;
+    q.tile_claim = ctx->stream_counters + 2 * (ctx->stream_seq++ % IB_STREAM_COUNTER_PAIRS);
+    return launch_stream_switch(ctx, stream, q, grid, geo, total);
+}
+
+static int32_t launch_stream_switch(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t total) {
     switch (p.epi) {
     case EPI_STORE: return launch_stream_epi<EPI_STORE>(ctx, stream, p, grid, geo, total);
     case EPI_RESIDUAL: return launch_stream_epi<EPI_RESIDUAL>(ctx, stream, p, grid, geo, total);
