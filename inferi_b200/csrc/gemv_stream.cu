@@ -80,18 +80,19 @@ struct StreamGeom {
     // the launch's tiles in hand-out order: per segment the pairs, the pairs per tile and the tiles; bytes per pair
     uint32_t seg_pairs[3], seg_pt[3], seg_tiles[3], seg_cost[3], total_tiles, meta_off;
     uint32_t dynamic;   // 1: tiles are claimed from a counter; 0: every CTA streams its own byte-balanced range of pairs
+    uint32_t head_per_cta, head_tiles, tail_pt;   // counter hand-out: see tile_of
 };
 
-// Tile number -> (segment, first pair, pairs); pairs == 0 past the last tile.
+// Counter hand-out (one segment only): tile number -> (segment 0, first pair, pairs); pairs == 0 past the last tile.
+// The first `head_tiles` tiles hold `seg_pt[0]` pairs each and belong to the CTAs by position (CTA b: tiles b * head_per_cta
+// ...); the rest of the pairs follow as smaller tiles of `tail_pt` pairs, claimed from the counter.
 __device__ __forceinline__ uint4 tile_of(const StreamGeom &g, uint32_t t) {
-    uint32_t s = 0;
-    if (t >= g.seg_tiles[0]) { t -= g.seg_tiles[0]; s = 1; if (t >= g.seg_tiles[1]) { t -= g.seg_tiles[1]; s = 2; } }
-    const uint32_t np = s == 0 ? g.seg_pairs[0] : (s == 1 ? g.seg_pairs[1] : g.seg_pairs[2]);
-    const uint32_t pt = s == 0 ? g.seg_pt[0] : (s == 1 ? g.seg_pt[1] : g.seg_pt[2]);
-    const uint32_t nt = s == 0 ? g.seg_tiles[0] : (s == 1 ? g.seg_tiles[1] : g.seg_tiles[2]);
-    if (t >= nt) return make_uint4(0, 0, 0, 0);
-    const uint32_t first = t * pt;
-    return make_uint4(s, first, (np - first) < pt ? (np - first) : pt, 0);
+    const uint32_t np = g.seg_pairs[0];
+    uint32_t first, pt;
+    if (t < g.head_tiles) { pt = g.seg_pt[0]; first = t * pt; }
+    else { pt = g.tail_pt; first = g.head_tiles * g.seg_pt[0] + (t - g.head_tiles) * pt; }
+    if (first >= np) return make_uint4(0, 0, 0, 0);
+    return make_uint4(0, first, (np - first) < pt ? (np - first) : pt, 0);
 }
 
 // ---- consumer side ----
@@ -259,19 +260,19 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         }
         uint32_t st = 0, par = 1;   // parity of the slot's previous use ("1" before the first one: nothing to wait for)
         bool first_round = true;
-        uint32_t t = 0, held = S;   // the ring's first S tiles come from one claim
-        if (dyn && lane == 0) t = atomicAdd(p.tile_claim, S);
-        t = __shfl_sync(0xffffffffu, t, 0);
+        // counter hand-out: the CTA's first tiles are its own by position (no round trip before the first copy), every
+        // later one is claimed
+        uint32_t t = blockIdx.x * geo.head_per_cta, held = geo.head_per_cta;
         for (uint32_t k = 0;; k++, st = (st + 1 == S) ? 0 : st + 1) {
             if (st == 0 && k > 0) { par ^= 1u; first_round = false; }
             // the tile after this one is claimed now: the counter's round trip overlaps the wait for the slot
+            const uint4 tm = dyn ? tile_of(geo, t) : (tc.valid(sh) ? make_uint4(tc.seg, tc.next, tc.count(sh), 0) : make_uint4(0, 0, 0, 0));
             uint32_t tn = 0;
-            if (dyn && held == 1 && lane == 0 && t < geo.total_tiles) tn = atomicAdd(p.tile_claim, 1u);
+            if (dyn && held == 1 && tm.z != 0 && lane == 0) tn = geo.head_tiles + atomicAdd(p.tile_claim, 1u);
             uint32_t ok = 1;
             if (!first_round && lane == 0) ok = mbar_wait(bar0 + 8 * (S + st), par, p.err, 2) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            const uint4 tm = dyn ? tile_of(geo, t) : (tc.valid(sh) ? make_uint4(tc.seg, tc.next, tc.count(sh), 0) : make_uint4(0, 0, 0, 0));
             const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
             const uint32_t full = bar0 + 8 * st;
             if (lane == 0) meta[st] = tm;
@@ -515,7 +516,25 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     int grid = ctx->sm_count;       // one persistent CTA per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
     if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
-    geo.dynamic = geo.total_tiles >= 6u * (uint32_t)grid ? 1u : 0u;
+    // Hand-out: launches of one segment with enough tiles per CTA give every CTA its first tiles by position and let the
+    // CTAs claim the rest from a counter - whole tiles when there are many (>= 6 per CTA), one-round tiles for the last
+    // third or so when there are few (>= 2.5 per CTA, e.g. gate/up with 3.0), where a whole tile would be too coarse a
+    // unit to even out the CTAs' end times.  Everything else: static byte-balanced ranges.
+    geo.dynamic = 0;
+    geo.head_per_cta = geo.head_tiles = 0;
+    geo.tail_pt = geo.seg_pt[0];
+    const bool single = p.epi == EPI_SWIGLU || p.nseg == 1;
+    const uint32_t tiles_x2_per_cta = 2u * geo.total_tiles / (uint32_t)grid;
+    if (single && tiles_x2_per_cta >= 12u) {
+        geo.dynamic = 1;
+        geo.head_per_cta = S;
+    } else if (single && tiles_x2_per_cta >= 5u && geo.seg_pt[0] >= 2 * RG) {
+        geo.dynamic = 1;
+        const uint32_t whole = geo.total_tiles / (uint32_t)grid;
+        geo.head_per_cta = whole - 1 < S ? whole - 1 : S;
+        geo.tail_pt = RG;
+    }
+    geo.head_tiles = (uint32_t)grid * geo.head_per_cta;
     // the counters through which this launch's CTAs share out the tiles: consecutive launches overlap (programmatic
     // dependent launch), so they take different pairs of a small ring; the last CTA of a launch clears its pair
     GemvParams q = p;
