@@ -130,7 +130,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
         const uint4 tm = c.meta[st];
         const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
         if (n == 0) break;
-        const uint32_t qtype = (QT != QT_MIXED) ? QT : p.seg[s].qtype;
+        const uint32_t qtype = (QT != QT_MIXED && QT != QT_Q4_Q6) ? QT : p.seg[s].qtype;
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
             unit_init<QT>(qtype, c.u, lc);
             if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
@@ -427,8 +427,13 @@ static int32_t launch_stream_inst(ib_ctx *ctx, cudaStream_t stream, const GemvPa
 template <uint32_t EPI>
 static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
     uint32_t qt = p.seg[0].qtype;
-    for (uint32_t s = 1; s < p.nseg; s++)
+    bool only_q4_q6 = true;
+    for (uint32_t s = 0; s < p.nseg; s++) {
         if (p.seg[s].qtype != qt) qt = QT_MIXED;
+        only_q4_q6 = only_q4_q6 && (p.seg[s].qtype == IB_Q4_K || p.seg[s].qtype == IB_Q6_K);
+    }
+    if constexpr (EPI == EPI_QKV)
+        if (qt == QT_MIXED && only_q4_q6) return launch_stream_inst<EPI, QT_Q4_Q6>(ctx, stream, p, grid, geo, smem);
     switch (qt) {
     case IB_Q4_K: return launch_stream_inst<EPI, IB_Q4_K>(ctx, stream, p, grid, geo, smem);
     case IB_Q6_K: return launch_stream_inst<EPI, IB_Q6_K>(ctx, stream, p, grid, geo, smem);

@@ -343,11 +343,17 @@ template <> struct Unit<IB_Q8_0> {
 };
 
 constexpr uint32_t QT_MIXED = 0xFFu;   // kernel instance for launches whose segments differ in format
+constexpr uint32_t QT_Q4_Q6 = 0xFEu;   // ... and hold only Q4_K and Q6_K (q, k, v of the Q4_K_M recipe): two formats to switch between, not four
 
 template <uint32_t QT>
 __device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst &lc) {
     lc.o0 = lc.o1 = lc.o2 = lc.o3 = lc.k = 0;
-    if (QT != QT_MIXED) { Unit<QT == QT_MIXED ? IB_Q4_K : QT>::init(u, lc); return; }
+    if (QT == QT_Q4_Q6) {
+        if (qtype == IB_Q4_K) Unit<IB_Q4_K>::init(u, lc);
+        else Unit<IB_Q6_K>::init(u, lc);
+        return;
+    }
+    if (QT != QT_MIXED) { Unit<(QT == QT_MIXED || QT == QT_Q4_Q6) ? IB_Q4_K : QT>::init(u, lc); return; }
     switch (qtype) {
     case IB_Q4_K: Unit<IB_Q4_K>::init(u, lc); break;
     case IB_Q6_K: Unit<IB_Q6_K>::init(u, lc); break;
@@ -357,7 +363,8 @@ __device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst 
 }
 template <uint32_t QT>
 __device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
-    if (QT != QT_MIXED) return Unit<QT == QT_MIXED ? IB_Q4_K : QT>::dot(row, lc, ua);
+    if (QT == QT_Q4_Q6) return qtype == IB_Q4_K ? Unit<IB_Q4_K>::dot(row, lc, ua) : Unit<IB_Q6_K>::dot(row, lc, ua);
+    if (QT != QT_MIXED) return Unit<(QT == QT_MIXED || QT == QT_Q4_Q6) ? IB_Q4_K : QT>::dot(row, lc, ua);
     switch (qtype) {
     case IB_Q4_K: return Unit<IB_Q4_K>::dot(row, lc, ua);
     case IB_Q6_K: return Unit<IB_Q6_K>::dot(row, lc, ua);
