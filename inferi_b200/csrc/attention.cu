@@ -19,16 +19,15 @@ constexpr int ATTN_STEPS = 8;              // row steps per tile kept in registe
 template <int HS, int KVM, typename T>
 __global__ void __launch_bounds__(ATTN_THREADS) attn_kernel(const AttnArgs a) {
     __shared__ float sm[attn_block_smem_floats(HS, KVM)];
-    if (a.pdl) {
-        asm volatile("griddepcontrol.launch_dependents;");
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-    }
+    if (a.pdl) asm volatile("griddepcontrol.launch_dependents;");
+    // The position was written by the end of the previous token, many kernels ago, and not by the predecessor (which
+    // only waits for its own predecessor after it has let this kernel start): it can be read before the wait.
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t pos = a.pos_ptr ? *a.pos_ptr : a.p.pos;
     uint32_t nsplit, per;
     attn_split_plan(pos + 1, a.max_splits, nsplit, per);
     if (split >= nsplit) return;
-    attn_block<HS, KVM, T, ATTN_STEPS>(a, a.kc, a.vc, kvh, split, nsplit, per, pos + 1, (int)threadIdx.x, 1, sm);
+    attn_block<HS, KVM, T, ATTN_STEPS>(a, a.kc, a.vc, kvh, split, nsplit, per, pos + 1, (int)threadIdx.x, 1, sm, a.pdl != 0);
 }
 
 size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits) {

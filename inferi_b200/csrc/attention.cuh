@@ -72,7 +72,7 @@ __device__ __forceinline__ void attn_split_plan(uint32_t total, uint32_t max_spl
 // no block ever waits for another.  STEPS = cache-row steps per tile kept in registers.
 template <int HS, int KVM, typename T, int STEPS, bool QS = false>
 __device__ __forceinline__ void attn_block(const AttnArgs &a, const void *k_cache, const void *v_cache, uint32_t kvh, uint32_t split, uint32_t nsplit,
-                                           uint32_t per, uint32_t total, int tid, int bar, float *sm) {
+                                           uint32_t per, uint32_t total, int tid, int bar, float *sm, bool wait_inside = false) {
     constexpr int EPL = KvVec<T>::EPL;   // elements per 16-byte lane load
     constexpr int LPR = HS / EPL;        // lanes covering one cache row of this kv head
     constexpr int RPW = 32 / LPR;        // rows per warp step
@@ -91,6 +91,38 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, const void *k_cach
     const T *kc = reinterpret_cast<const T *>(k_cache) + (size_t)kvh * HS + li * EPL;
     const T *vc = reinterpret_cast<const T *>(v_cache) + (size_t)kvh * HS + li * EPL;
     const float scale = 1.0f / sqrtf((float)HS);
+
+    // `wait_inside`: the kernel was launched ahead of its predecessor's completion (programmatic dependent launch) and has
+    // not waited for it yet.  The predecessor writes this token's q and the newest cache row (position total - 1); every
+    // older cache row was written by earlier tokens.  So the first tile's older rows are requested now, the wait comes
+    // next, and q and the newest row are read after it: the cache round trip overlaps the predecessor's tail.
+    uint4 kraw[STEPS], vraw[STEPS];
+    const uint32_t base0 = t0 + warp * TILE;
+    if (wait_inside) {
+        if (base0 < t1) {
+#pragma unroll
+            for (int s = 0; s < STEPS; s++) {
+                const uint32_t t = base0 + s * RPW + g;
+                const uint32_t tc = t < t1 ? t : t1 - 1;
+                if (tc + 1 != total) {
+                    kraw[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
+                    vraw[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
+                }
+            }
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (base0 < t1) {
+#pragma unroll
+            for (int s = 0; s < STEPS; s++) {
+                const uint32_t t = base0 + s * RPW + g;
+                const uint32_t tc = t < t1 ? t : t1 - 1;
+                if (tc + 1 == total) {
+                    kraw[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
+                    vraw[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
+                }
+            }
+        }
+    }
 
     float qr[QS ? 1 : KVM][QS ? 1 : EPL];
     float *sm_q = reinterpret_cast<float *>(sm_last + 4);   // [KVM][HS], only with QS
@@ -113,14 +145,15 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, const void *k_cach
         for (int e = 0; e < EPL; e++) acc[m][e] = 0.f;
     }
 
-    for (uint32_t base = t0 + warp * TILE; base < t1; base += ATTN_WARPS * TILE) {
-        uint4 kraw[STEPS], vraw[STEPS];
+    for (uint32_t base = base0; base < t1; base += ATTN_WARPS * TILE) {
+        if (!(wait_inside && base == base0)) {
 #pragma unroll
-        for (int s = 0; s < STEPS; s++) {
-            const uint32_t t = base + s * RPW + g;
-            const uint32_t tc = t < t1 ? t : t1 - 1;
-            kraw[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
-            vraw[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
+            for (int s = 0; s < STEPS; s++) {
+                const uint32_t t = base + s * RPW + g;
+                const uint32_t tc = t < t1 ? t : t1 - 1;
+                kraw[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
+                vraw[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
+            }
         }
         float sc[STEPS][KVM];
 #pragma unroll
