@@ -162,16 +162,15 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
                 float v = (up ? vb : va) + __shfl_xor_sync(0xffffffffu, up ? va : vb, 16);
 #pragma unroll
                 for (int o = 8; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                va = __shfl_sync(0xffffffffu, v, 0);
-                vb = __shfl_sync(0xffffffffu, v, 16);
+                if (CG == 1) {
+                    va = __shfl_sync(0xffffffffu, v, 0);
+                    vb = __shfl_sync(0xffffffffu, v, 16);
+                } else if ((lane & 15) == 0) {
+                    pt[(pr * 2 + (lane >> 4)) * CW + c.cg] = v;   // lane 0 holds row A's sum, lane 16 row B's
+                }
             }
             PH_MARK(2, va + vb);
-            if (CG == 1) {
-                if (lane == 0) epilogue<EPI>(p, s, first_pair + pr, va, vb, best, ParamCaches{p}, rpre);
-            } else if (lane == 0) {
-                pt[(pr * 2 + 0) * CW + c.cg] = va;
-                pt[(pr * 2 + 1) * CW + c.cg] = vb;
-            }
+            if (CG == 1 && lane == 0) epilogue<EPI>(p, s, first_pair + pr, va, vb, best, ParamCaches{p}, rpre);
             PH_MARK(3, 0.f);
         }
         if (CG > 1) {
@@ -180,6 +179,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
             // the column partials in a fixed order and runs the epilogue.
             const uint32_t fb = c.fold0 + 8 * (st * CW + c.rg);
             if (c.cg != folder) {
+                __syncwarp();   // lane 16's partials are ordered before lane 0's arrival (a release)
                 if (lane == 0) mbar_arrive(fb);
             } else {
                 __syncwarp();   // lane 0's own partials, read by the other lanes below
