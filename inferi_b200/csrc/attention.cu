@@ -40,6 +40,9 @@ uint32_t attn_max_splits(const ib_ctx *ctx, const ib_attn_params &p) {
     uint32_t s = (uint32_t)(ctx->sm_count * 4) / (n_kv ? n_kv : 1);
     if (s < 1) s = 1;
     if (s > 256) s = 256;
+    // the merging block stages every slice's (max, sum) in its accumulator area: 2 * splits * kv_mul floats must fit the
+    // 4 * kv_mul * head_size it owns
+    if (s > 2 * p.head_size) s = 2 * p.head_size;
     return s;
 }
 
@@ -76,6 +79,8 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     const uint32_t n_kv = p.n_heads / p.kv_mul;
     IB_REQUIRE(p.kv_dim == n_kv * p.head_size, "attention: kv_dim=%u != n_kv_heads*head_size=%u", p.kv_dim, n_kv * p.head_size);
     IB_REQUIRE(a.pos_ptr || p.pos < p.seq_len, "attention: pos=%u outside the cache of %u rows", p.pos, p.seq_len);
+    IB_REQUIRE(a.max_splits >= 1 && a.max_splits <= 2 * p.head_size && a.max_splits <= 256, "attention: %u position slices exceed what the merge step holds (%u)",
+               a.max_splits, 2 * p.head_size < 256 ? 2 * p.head_size : 256);
     AttnArgs args{p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, a.pdl};
     // with a host-known position only the splits that will do work are launched
     uint32_t splits = a.max_splits;

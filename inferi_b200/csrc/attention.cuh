@@ -251,7 +251,7 @@ __device__ __forceinline__ void attn_block(const AttnArgs &a, const void *k_cach
     // merge of the kv head's partials.  Maxima and sums of all slices first go to shared memory (the block's accumulator
     // area is free by now), so that the weighted sum over slices is a loop of independent loads.
     const float *parts = a.scratch + (size_t)kvh * a.max_splits * KVM * slot;
-    float *pm = sm_acc, *pl = sm_acc + nsplit * KVM;   // [nsplit][KVM] each; fits: nsplit <= 256 <= 2 * HS
+    float *pm = sm_acc, *pl = sm_acc + nsplit * KVM;   // [nsplit][KVM] each; fits because the launcher keeps nsplit <= 2 * HS (sm_acc holds 4 * KVM * HS floats)
     for (uint32_t i = tid; i < nsplit * KVM; i += ATTN_THREADS) {
         const float *ps = parts + (size_t)i * slot;    // slice i / KVM, head i % KVM
         pm[i] = __ldcg(ps + HS);

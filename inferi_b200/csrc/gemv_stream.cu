@@ -21,59 +21,6 @@
 
 namespace ib {
 
-#ifdef IB_STREAM_TRACE
-// Timeline probes for latency studies: globaltimer stamps of CTA 0 (and of the last CTA's end), one row of 16 slots
-// per epilogue kind, read back with ib_debug_stream_trace().  Never compiled into the shipped library.
-__device__ unsigned long long g_trace[16 * 16];
-__device__ unsigned long long g_cta_end[8][160], g_cta_packed[8][160];   // per CTA: end of the kernel / activations packed
-#define TRACE(slot)                                                                                   \
-    do {                                                                                              \
-        if (lane == 0 && blockIdx.x == 0 && (warp == 0 || warp == CW)) {                              \
-            unsigned long long _t;                                                                    \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
-            g_trace[(warp == CW ? 128 : 0) + EPI * 16 + (slot)] = _t;                                 \
-        }                                                                                             \
-        if (lane == 0 && blockIdx.x == gridDim.x - 1 && warp == 0 && (slot) == 15) {                  \
-            unsigned long long _t;                                                                    \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                    \
-            g_trace[EPI * 16 + 14] = _t;                                                              \
-        }                                                                                             \
-    } while (0)
-#define TRACE_CTA(arr)                                                                                \
-    do {                                                                                              \
-        if (lane == 0 && warp == 0 && blockIdx.x < 160) arr[EPI][blockIdx.x] = global_ns();           \
-    } while (0)
-// Where a consumer warp of CTA 0 spends its cycles, per epilogue kind: [wait for the tile, dot products, shuffle tree,
-// partials / direct epilogue, cross-warp fold, slot release, tiles, total, loop bookkeeping before the wait]
-__device__ long long g_phase[8][32][10];
-#define PH_DECL long long _pc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long _t0 = clock64(); const long long _tb = _t0
-#define PH_MARK(i, dep)                                                                       \
-    do {                                                                                      \
-        long long _t;                                                                         \
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(_t) : "f"(dep) : "memory");             \
-        _pc[i] += _t - _t0;                                                                   \
-        _t0 = _t;                                                                             \
-    } while (0)
-#define PH_DUMP(warp_id)                                                                      \
-    do {                                                                                      \
-        if (lane == 0 && blockIdx.x == 0) {                                                   \
-            _pc[7] = clock64() - _tb;                                                         \
-            for (int _i = 0; _i < 10; _i++) g_phase[EPI][warp_id][_i] = _pc[_i];               \
-        }                                                                                     \
-    } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#define TRACE_CTA(arr) do { } while (0)
-#define PH_DECL do { } while (0)
-#define PH_MARK(i, dep) do { } while (0)
-#define PH_DUMP(warp_id) do { } while (0)
-#endif
-
-#ifndef IB_COPY_PIECE_BYTES
-#define IB_COPY_PIECE_BYTES (1u << 24)   // larger than any tile: one bulk copy per tile part
-#endif
-constexpr uint32_t COPY_PIECE = IB_COPY_PIECE_BYTES;   // a multiple of 16; 32 x COPY_PIECE must fit 32 bits
-static_assert(COPY_PIECE % 16 == 0 && COPY_PIECE <= (1u << 26), "piece size");
 
 struct StreamGeom {
     uint32_t stages, stage_bytes, act_off, part_off, bar_off;
@@ -97,130 +44,116 @@ __device__ __forceinline__ uint4 tile_of(const StreamGeom &g, uint32_t t) {
 
 // ---- consumer side ----
 struct Consumer {
-    const uint8_t *ring;
-    float *part;          // [stages][PT_MAX][2][CW] per-warp column partials
-    uint32_t fold0;       // mbarriers [stages][CW]: the other warps of a row group have left their partials of the tile
-    const uint4 *meta;    // [stages] (segment, first pair, pairs, -) of the tile in the slot, written by the producer
+    uint32_t ring;        // shared address of the ring
+    uint32_t part;        // shared address of the per-stage partial sums [stages][2][CW][PT_MAX]
+    uint32_t meta;        // shared address of [stages] (segment, first pair, pairs, -) descriptors written by the producer
     uint32_t bar0, S, stage_bytes;
     uint32_t CG, RG, cg, rg, u;
     bool has_unit;
     int lane;
 };
 
-// Consumes this warp's share of every tile.  One loop for all formats (the format switch sits at the dot product):
-// separate inlined loops per format made the register allocator spill.
+// Offset (in floats) of the partial of (row of the pair, column-group warp, pair of the tile) inside a stage's block:
+// pairs are the fastest index, so that the lanes of the epilogue warp (one pair each) read consecutive words.
+__device__ __forceinline__ uint32_t part_index(uint32_t row, uint32_t cg, uint32_t pr) { return (row * CW + cg) * PT_MAX + pr; }
+constexpr uint32_t PART_STAGE_FLOATS = 2 * CW * PT_MAX;
+
+// A consumer warp: its lanes' 64-column units of every row pair of every tile.  Per tile it waits for the weights, leaves
+// two partial sums per pair (its columns of the two rows) in the stage's partial block and arrives on the stage's "done"
+// barrier.  It never waits for another consumer warp: adding up the column groups and everything that follows is the
+// epilogue warp's work.
 template <uint32_t EPI, uint32_t QT>
-__device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consumer &c, const Act &A, unsigned long long &best) {
+__device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consumer &c, const Act &A) {
     const int lane = c.lane;
     UnitAct ua;
     LaneConst lc;
     uint32_t cur_type = 0xFFFFFFFFu;
-    const uint32_t S = c.S, CG = c.CG, RG = c.RG;
-    PH_DECL;
-    // stage and phase parity of the tile, and the warp of the row group that folds it (they take turns), kept as counters:
-    // a division by a run-time value per tile is a chain of ~200 cycles that nothing overlaps
-    uint32_t st = 0, par = 0, folder = c.rg % CG;
+    const uint32_t S = c.S, RG = c.RG;
+    uint32_t st = 0, par = 0;
+    constexpr bool ONE_TYPE = (QT != QT_MIXED && QT != QT_Q4_Q6);
+    const uint32_t rb0 = (uint32_t)p.seg[0].row_bytes, rb1 = (uint32_t)p.seg[1].row_bytes, rb2 = (uint32_t)p.seg[2].row_bytes;
 #pragma unroll 1
-    for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u, folder = (folder + 1 == CG) ? 0 : folder + 1) {
-        PH_MARK(8, 0.f);   // loop bookkeeping since the slot release
+    for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
         if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
-        PH_MARK(0, 0.f);
-        // which tile the producer put into the slot (tiles are handed out through a counter: a CTA that starts late or
-        // runs slowly takes fewer of them); no pairs = no tiles left
-        const uint4 tm = c.meta[st];
-        const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
-        if (n == 0) break;
-        const uint32_t qtype = (QT != QT_MIXED && QT != QT_Q4_Q6) ? QT : p.seg[s].qtype;
+        const uint4 tm = lds128(c.meta + 16 * st);
+        const uint32_t s = tm.x, n = tm.z;
+        if (n == 0) break;   // no tiles left
+        const uint32_t qtype = ONE_TYPE ? QT : (s == 0 ? p.seg[0].qtype : (s == 1 ? p.seg[1].qtype : p.seg[2].qtype));
         if (qtype != cur_type) {   // (re)load this lane's activations in the layout of the segment's format
             unit_init<QT>(qtype, c.u, lc);
             if (c.has_unit) load_unit_act(qtype, c.u, A, ua);
             cur_type = qtype;
         }
-        const uint8_t *tile = c.ring + (size_t)st * c.stage_bytes;
-        const uint32_t rbA = (uint32_t)p.seg[s].row_bytes;
-        const uint32_t rbB = (EPI == EPI_SWIGLU) ? (uint32_t)p.seg[1].row_bytes : rbA;
-        const uint32_t strideA = (EPI == EPI_SWIGLU) ? rbA : 2 * rbA, offB = (EPI == EPI_SWIGLU) ? n * rbA : rbA;
-        float *pt = c.part + (size_t)st * PT_MAX * 2 * CW;
-        // residual values of the pair this lane has to finish (CG > 1: in the warp that folds this tile; CG == 1: lane 0 of
-        // each pair's warp, fetched per pair below): requested now, needed after the dot products
-        float2 rpre = make_float2(0.f, 0.f);
-        if (EPI == EPI_RESIDUAL && CG > 1 && c.cg == folder && c.rg + RG * lane < n) rpre = residual_prefetch(p.resid, first_pair + c.rg + RG * lane);
+        const uint32_t tile = c.ring + st * c.stage_bytes;
+        const uint32_t rbA = (EPI == EPI_SWIGLU || s == 0) ? rb0 : (s == 1 ? rb1 : rb2);
+        const uint32_t strideA = (EPI == EPI_SWIGLU) ? rbA : 2 * rbA;
+        const uint32_t offB = (EPI == EPI_SWIGLU) ? n * rbA : rbA, strideB = (EPI == EPI_SWIGLU) ? rb1 : strideA;
+        const uint32_t pt = c.part + 4 * (st * PART_STAGE_FLOATS);
         for (uint32_t pr = c.rg; pr < n; pr += RG) {
-            const uint8_t *rowA = tile + pr * strideA;
-            const uint8_t *rowB = (EPI == EPI_SWIGLU) ? tile + offB + pr * rbB : rowA + rbA;
-            if (EPI == EPI_RESIDUAL && CG == 1 && lane == 0) rpre = residual_prefetch(p.resid, first_pair + pr);
             float va = 0.f, vb = 0.f;
             if (c.has_unit) {
-                va = unit_dot<QT>(qtype, rowA, lc, ua);
-                vb = unit_dot<QT>(qtype, rowB, lc, ua);
+                va = unit_dot<QT>(qtype, tile + pr * strideA, lc, ua);
+                vb = unit_dot<QT>(qtype, tile + offB + pr * strideB, lc, ua);
             }
-            PH_MARK(1, va + vb);
-            {
-                // one shuffle tree for both rows: after the first exchange the upper half-warp carries row B
-                // (the same pairs are added in the same order as two separate trees would: the bits do not change)
-                const bool up = lane & 16;
-                float v = (up ? vb : va) + __shfl_xor_sync(0xffffffffu, up ? va : vb, 16);
+            // one shuffle tree for both rows: after the first exchange the upper half-warp carries row B
+            const bool up = lane & 16;
+            float v = (up ? vb : va) + __shfl_xor_sync(0xffffffffu, up ? va : vb, 16);
 #pragma unroll
-                for (int o = 8; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (CG == 1) {
-                    va = __shfl_sync(0xffffffffu, v, 0);
-                    vb = __shfl_sync(0xffffffffu, v, 16);
-                } else if ((lane & 15) == 0) {
-                    pt[(pr * 2 + (lane >> 4)) * CW + c.cg] = v;   // lane 0 holds row A's sum, lane 16 row B's
-                }
-            }
-            PH_MARK(2, va + vb);
-            if (CG == 1 && lane == 0) epilogue<EPI>(p, s, first_pair + pr, va, vb, best, ParamCaches{p}, rpre);
-            PH_MARK(3, 0.f);
+            for (int o = 8; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((lane & 15) == 0)   // lane 0 holds row A's sum, lane 16 row B's
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(pt + 4 * part_index(lane >> 4, c.cg, pr)), "f"(v) : "memory");
         }
-        if (CG > 1) {
-            // The row group's warps take turns folding a tile.  The others leave their partials and arrive on the tile's
-            // fold barrier (a release) without waiting; the folding warp waits for their CG - 1 arrivals (an acquire), adds
-            // the column partials in a fixed order and runs the epilogue.
-            const uint32_t fb = c.fold0 + 8 * (st * CW + c.rg);
-            if (c.cg != folder) {
-                __syncwarp();   // lane 16's partials are ordered before lane 0's arrival (a release)
-                if (lane == 0) mbar_arrive(fb);
-            } else {
-                __syncwarp();   // lane 0's own partials, read by the other lanes below
-                if (!mbar_wait(fb, par, p.err, 5)) return;
-                const uint32_t pr = c.rg + RG * lane;
-                if (pr < n) {
-                    float va = 0.f, vb = 0.f;
-                    for (uint32_t g = 0; g < CG; g++) {
-                        va += pt[(pr * 2 + 0) * CW + g];
-                        vb += pt[(pr * 2 + 1) * CW + g];
-                    }
-                    epilogue<EPI>(p, s, first_pair + pr, va, vb, best, ParamCaches{p}, rpre);
-                }
+        __syncwarp();   // lane 16's partials are ordered before lane 0's arrival (a release)
+        if (lane == 0) mbar_arrive(c.bar0 + 8 * (2 * S + st));   // this warp is done with the stage: weights read, partials left
+    }
+}
+
+// The epilogue warp: per tile it waits until every consumer warp has left its partials, adds up the column groups in a
+// fixed order (bitwise deterministic results), hands the stage back to the producer and runs the epilogue of the tile's
+// row pairs, one pair per lane.
+template <uint32_t EPI>
+__device__ __forceinline__ void finish_tiles(const GemvParams &p, uint32_t part, uint32_t meta, uint32_t bar0, uint32_t S, uint32_t CG, int lane,
+                                             unsigned long long &best) {
+    uint32_t st = 0, par = 0;
+#pragma unroll 1
+    for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
+        if (!mbar_wait(bar0 + 8 * st, par, p.err, 1)) return;
+        const uint4 tm = lds128(meta + 16 * st);
+        const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
+        if (n == 0) break;
+        const bool mine = (uint32_t)lane < n;
+        // the pair's residual values are requested before the wait for the dot products: the L2 round trip overlaps it
+        float2 rpre = make_float2(0.f, 0.f);
+        if (EPI == EPI_RESIDUAL && mine) rpre = residual_prefetch(p.resid, first_pair + lane);
+        if (!mbar_wait(bar0 + 8 * (2 * S + st), par, p.err, 5)) return;
+        float va = 0.f, vb = 0.f;
+        if (mine) {
+            const uint32_t pt = part + 4 * (st * PART_STAGE_FLOATS);
+            for (uint32_t g = 0; g < CG; g++) {
+                va += __uint_as_float(lds32(pt + 4 * part_index(0, g, lane)));
+                vb += __uint_as_float(lds32(pt + 4 * part_index(1, g, lane)));
             }
         }
         __syncwarp();
-        PH_MARK(4, 0.f);
-        if (lane == 0) mbar_arrive(c.bar0 + 8 * (S + st));   // this warp is done with the stage
-        PH_MARK(5, 0.f);
-#ifdef IB_STREAM_TRACE
-        _pc[6] += 1;
-#endif
+        if (lane == 0) mbar_arrive(bar0 + 8 * (S + st));   // partials read: the producer may refill the stage
+        if (mine) epilogue<EPI>(p, s, first_pair + lane, va, vb, best, ParamCaches{p}, rpre);
     }
-    PH_DUMP(c.cg + c.rg * c.CG);
 }
 
 // ---- the kernel ----
+// Shared-memory barriers: full[S] (the producer's expect_tx arrival + the copy's bytes), empty[S] (one arrival: the
+// epilogue warp has read the stage's partials, which implies that every consumer warp is done with its weights),
+// done[S] (one arrival per working consumer warp).
 template <uint32_t EPI, uint32_t QT>
 __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const GemvParams p, const StreamGeom geo) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[PACK_THREADS / 32 + 1];
-    __shared__ unsigned long long best_sm[CW];
-    __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    TRACE(0);
 
     uint8_t *ring = smem;
     uint8_t *act_sm = smem + geo.act_off;
-    float *part = reinterpret_cast<float *>(smem + geo.part_off);              // [stages][PT_MAX][2][CW]
-    const uint32_t fold0 = smem_u32(part + geo.stages * PT_MAX * 2 * CW);                // mbarriers [stages][CW]
-    const uint32_t bar0 = smem_u32(smem + geo.bar_off);                         // full[stages], empty[stages]
+    const uint32_t part = smem_u32(smem + geo.part_off);                        // [stages][2][CW][PT_MAX] floats
+    const uint32_t bar0 = smem_u32(smem + geo.bar_off);                         // full[stages], empty[stages], done[stages]
     const uint32_t S = geo.stages;
 
     const uint32_t units = p.cols / 64;
@@ -228,28 +161,21 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     const uint32_t RG = CW / CG;                 // row groups working side by side
     const uint32_t active = CG * RG;             // consumer warps with work
 
-
-    // set-up spread over threads: it sits on the critical path of a CTA that starts late (its SM was the last to be freed)
-    if (threadIdx.x < 2 * S) {
-        // full[s]: the producer's expect_tx arrival; empty[s]: one arrival per working consumer warp
-        mbar_init(bar0 + 8 * threadIdx.x, threadIdx.x < S ? 1u : active);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    } else if (threadIdx.x >= 32 && threadIdx.x < 32 + S * CW) {
-        // fold barrier of (stage, row group): the arrivals of the row group's warps other than the folding one
-        mbar_init(fold0 + 8 * (threadIdx.x - 32), CG > 1 ? CG - 1 : 1u);
+    if (threadIdx.x < 3 * S) {
+        const uint32_t which = threadIdx.x / S;
+        mbar_init(bar0 + 8 * threadIdx.x, which == 2 ? active : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    TRACE(1);
     if (p.pdl) asm volatile("griddepcontrol.launch_dependents;");
 
-    if (warp == CW) {
+    if (warp == W_PRODUCER) {
         // ================= producer warp: picks tiles and streams them =================
         // With many tiles per CTA they are handed out through a counter in global memory, so that a CTA which starts late
         // (its SM was the last to be freed by the previous kernel) or runs slowly takes fewer of them.  With few tiles per
         // CTA a tile is too coarse a unit for that: every CTA then streams its own byte-balanced range of row pairs, cut
-        // into tiles.  Either way the slot's descriptor tells the consumers what the tile is.  Lane 0 picks, waits for the
-        // slot and announces the tile; the copy is issued as pieces of at most COPY_PIECE bytes, one lane each.
+        // into tiles.  Either way the slot's descriptor tells the other warps what the tile is.  Lane 0 picks, waits for
+        // the slot, announces the tile and issues its bulk copies.
         uint4 *meta = reinterpret_cast<uint4 *>(smem + geo.meta_off);
         const bool dyn = geo.dynamic != 0;
         Share sh;
@@ -277,7 +203,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
             const uint32_t full = bar0 + 8 * st;
             if (lane == 0) meta[st] = tm;
             if (n == 0) {
-                // no tiles left: tell the consumers, and let the last CTA to get here clear the counters for their next use
+                // no tiles left: tell the others, and let the last CTA to get here clear the counters for their next use
                 if (lane == 0) {
                     mbar_arrive(full);
                     if (dyn && atomicAdd(p.tile_claim + 1, 1u) == gridDim.x - 1) {
@@ -293,16 +219,69 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
             const uint32_t bb = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[1].row_bytes : 0u;
             const uint8_t *srcA = (EPI == EPI_SWIGLU) ? p.seg[0].w + (size_t)first_pair * p.seg[0].row_bytes : p.seg[s].w + (size_t)first_pair * cost;
             const uint8_t *srcB = (EPI == EPI_SWIGLU) ? p.seg[1].w + (size_t)first_pair * p.seg[1].row_bytes : nullptr;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // every issuing lane: the consumers' reads of the slot come first
-            if (lane == 0) mbar_expect_tx(full, ba + bb);
-            __syncwarp();
-            for (uint32_t off = lane * COPY_PIECE; off < ba; off += 32 * COPY_PIECE) bulk_g2s(dst + off, srcA + off, min(COPY_PIECE, ba - off), full);
-            if constexpr (EPI == EPI_SWIGLU)
-                for (uint32_t off = lane * COPY_PIECE; off < bb; off += 32 * COPY_PIECE) bulk_g2s(dst + ba + off, srcB + off, min(COPY_PIECE, bb - off), full);
-            TRACE(2 + (k < 6 ? k : 6));
+            if (lane == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the consumers' reads of the slot come first
+                mbar_expect_tx(full, ba + bb);
+                bulk_g2s(dst, srcA, ba, full);
+                if constexpr (EPI == EPI_SWIGLU) bulk_g2s(dst + ba, srcB, bb, full);
+            }
             if (!dyn) tc.advance(sh);
             else if (held > 1) { t++; held--; }
             else t = __shfl_sync(0xffffffffu, tn, 0);
+        }
+        return;
+    }
+
+    if (warp == W_EPILOGUE) {
+        // ================= epilogue warp =================
+        // outputs (and the residual it reads) are touched by the previous kernels of the stream: wait for them like the consumers do
+        if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+        unsigned long long best = 0ull;
+        finish_tiles<EPI>(p, part, smem_u32(smem + geo.meta_off), bar0, S, CG, lane, best);
+        if (EPI == EPI_PUSH) {
+            // All of this CTA's peer stores were issued by this warp.  Each lane fences its own stores, lane 0 then arrives on
+            // a local counter with a system-scope release; the last CTA to arrive tells every rank that this rank has
+            // delivered.  (One remote arrival per CTA instead was faster on 2 GPUs and slower on 4: hundreds of remote atomics on
+            // one word.)
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t before;
+                asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], %2;" : "=r"(before) : "l"(p.push_done), "r"(1u) : "memory");
+                if (before == gridDim.x - 1) {
+                    *p.push_done = 0u;   // next used by a later kernel
+                    for (uint32_t rk = 0; rk < p.tp; rk++) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[rk]), "r"(1u) : "memory");
+                }
+            }
+        }
+        if (EPI == EPI_ARGMAX) {
+#pragma unroll
+            for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+            uint32_t last = 0;
+            if (lane == 0) {
+                p.argmax_slots[blockIdx.x] = best;
+                __threadfence();
+                last = (atomicAdd(p.argmax_counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                // the last CTA to arrive folds every CTA's candidate; no CTA waits for another
+                __threadfence();
+                unsigned long long b = 0ull;
+                for (uint32_t i = lane; i < gridDim.x; i += 32) b = max(b, __ldcg(p.argmax_slots + i));
+#pragma unroll
+                for (int o = 16; o; o >>= 1) b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+                if (lane == 0) {
+                    *p.argmax_out = 0xFFFFFFFFu - (uint32_t)(b & 0xFFFFFFFFull);
+                    *p.argmax_counter = 0u;
+                    if (p.tp > 1) {
+                        // sharded vocabulary: every rank gets this rank's candidate; the end-of-token kernel folds them
+                        for (uint32_t rk = 0; rk < p.tp; rk++) *p.amax_dst[rk] = b;
+                        __threadfence_system();
+                        for (uint32_t rk = 0; rk < p.tp; rk++) atomicAdd_system(p.amax_flag[rk], 1u);
+                    }
+                }
+            }
         }
         return;
     }
@@ -311,7 +290,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     float4 norm_g[4];
     pack_prefetch_norm(p.norm_w, p.cols, norm_g);   // weights: fetched while the previous kernel is still running
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-    TRACE(2);
     PackReduce rd{nullptr, 0, nullptr};
     if (p.reduce_src) {
         // every rank's partial sums of the previous row-split GEMV must have landed in this rank's slots
@@ -321,69 +299,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     }
     pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g, rd, p.cols / 64);
     const Act A{act_sm, p.cols, p.cols / 64};
-    TRACE(3);
-    TRACE_CTA(g_cta_packed);
 
-    unsigned long long best = 0ull;
     if ((uint32_t)warp < active) {
         Consumer c;
-        c.ring = ring; c.part = part; c.fold0 = fold0; c.meta = reinterpret_cast<const uint4 *>(smem + geo.meta_off); c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
+        c.ring = smem_u32(ring); c.part = part; c.meta = smem_u32(smem + geo.meta_off); c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
         c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
-        consume_tiles<EPI, QT>(p, c, A, best);
-    }
-    TRACE(15);
-    TRACE_CTA(g_cta_end);
-
-    if (EPI == EPI_PUSH) {
-        // All of this CTA's peer stores are issued.  One thread per CTA arrives on a local counter with a system-scope
-        // release (the CTA barrier makes it cumulative over the other threads' stores); the last CTA to arrive tells every
-        // rank that this rank has delivered.  (One remote arrival per CTA instead was faster on 2 GPUs and slower on 4:
-        // hundreds of remote atomics on one word.)
-        named_barrier(1, PACK_THREADS);
-        if (threadIdx.x == 0) {
-            uint32_t before;
-            asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], %2;" : "=r"(before) : "l"(p.push_done), "r"(1u) : "memory");
-            if (before == gridDim.x - 1) {
-                *p.push_done = 0u;   // next used by a later kernel
-                for (uint32_t rk = 0; rk < p.tp; rk++) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[rk]), "r"(1u) : "memory");
-            }
-        }
-    }
-    if (EPI == EPI_ARGMAX) {
-#pragma unroll
-        for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
-        if (lane == 0) best_sm[warp] = best;
-        named_barrier(1, PACK_THREADS);
-        if (threadIdx.x == 0) {
-            unsigned long long b = 0ull;
-            for (int w = 0; w < CW; w++) b = max(b, best_sm[w]);
-            p.argmax_slots[blockIdx.x] = b;
-            __threadfence();
-            is_last = (atomicAdd(p.argmax_counter, 1u) == gridDim.x - 1);
-        }
-        named_barrier(1, PACK_THREADS);
-        if (is_last) {
-            // the last CTA to arrive folds every CTA's candidate; no CTA waits for another
-            __threadfence();
-            unsigned long long b = 0ull;
-            for (uint32_t i = threadIdx.x; i < gridDim.x; i += PACK_THREADS) b = max(b, __ldcg(p.argmax_slots + i));
-#pragma unroll
-            for (int o = 16; o; o >>= 1) b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
-            named_barrier(1, PACK_THREADS);
-            if (lane == 0) best_sm[warp] = b;
-            named_barrier(1, PACK_THREADS);
-            if (threadIdx.x == 0) {
-                for (int w = 0; w < CW; w++) b = max(b, best_sm[w]);
-                *p.argmax_out = 0xFFFFFFFFu - (uint32_t)(b & 0xFFFFFFFFull);
-                *p.argmax_counter = 0u;
-                if (p.tp > 1) {
-                    // sharded vocabulary: every rank gets this rank's candidate; the end-of-token kernel folds them
-                    for (uint32_t rk = 0; rk < p.tp; rk++) *p.amax_dst[rk] = b;
-                    __threadfence_system();
-                    for (uint32_t rk = 0; rk < p.tp; rk++) atomicAdd_system(p.amax_flag[rk], 1u);
-                }
-            }
-        }
+        consume_tiles<EPI, QT>(p, c, A);
     }
 }
 
@@ -457,15 +378,20 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
             pairs += p.seg[s].rows / 2;
         }
     }
-    // tile = whole "rounds" of the row groups (RG pairs each): two rounds when they fit in ~37 KB, so that the
-    // per-tile hand-offs are paid once per two pairs of a warp; at least two stages must fit beside the activations
+    // tile = whole "rounds" of the row groups (RG pairs each, one pair per consumer warp) of up to ~56 KB, in as many stages
+    // as fit beside the activations (at most 4): several copies in flight per SM keep HBM busy while one tile is consumed
     const uint32_t units = p.cols / 64, CG = (units + 31) / 32, RG = CW / CG;
     const size_t act = (act_smem_bytes(p.cols) + 127) & ~(size_t)127;
+    auto part_bytes = [](uint32_t S) { return (size_t)S * PART_STAGE_FLOATS * 4; };
+    auto bar_bytes = [](uint32_t S) { return ((size_t)3 * S * 8 + 15) & ~(size_t)15; };
+    // returns 0 if the layout does not fit, 1 if it fits, 2 if it fits and every segment's tile is whole rounds
     auto layout = [&](uint32_t max_tile_bytes, uint32_t &stage, uint32_t &S, size_t &total) {
+        bool whole = true;
         auto pairs_per_tile = [&](uint32_t cost) {
             uint32_t pt = RG;
             while (pt * 2 <= PT_MAX && pt * 2 * cost <= max_tile_bytes) pt *= 2;
             while (pt > 1 && pt * cost > max_tile_bytes) pt--;
+            if (pt % RG) whole = false;
             return pt;
         };
         stage = 0;
@@ -478,28 +404,27 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
             }
         stage = (stage + 127) & ~127u;
         for (S = 4;; S--) {
-            const size_t part = (size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 8;
-            total = (size_t)S * stage + act + ((part + 127) & ~(size_t)127) + 2 * S * 8 + S * 16;   // + barriers + tile descriptors
+            total = (size_t)S * stage + act + part_bytes(S) + bar_bytes(S) + S * 16;   // + partials + barriers + tile descriptors
             if (total <= STREAM_SMEM_BUDGET || S == 2) break;
         }
-        return total <= STREAM_SMEM_BUDGET;
+        return total <= STREAM_SMEM_BUDGET ? (whole ? 2 : 1) : 0;
     };
     uint32_t stage = 0, S = 0;
     size_t total = 0;
-    static const uint32_t first_try = [] {
-        const char *e = getenv("INFERI_B200_TILE_BYTES");   // experiments: the largest tile to try first
-        const long v = e ? atol(e) : 0;
-        return (uint32_t)(v >= 4096 && v <= 98304 ? v : 75776);
-    }();
-    if (!layout(first_try, stage, S, total) && !layout(49152, stage, S, total) && !layout(32768, stage, S, total) && !layout(max_cost, stage, S, total))
+    const uint32_t tries[5] = {57344, 75776, 49152, 32768, max_cost};
+    int chosen = -1;
+    for (int pass = 2; pass >= 1 && chosen < 0; pass--)
+        for (int i = 0; i < 5 && chosen < 0; i++)
+            if (layout(tries[i], stage, S, total) >= pass) chosen = i;
+    if (chosen < 0)
         return set_error(IB_ERR_UNSUPPORTED, "gemv: a row pair of %u bytes with %u columns does not fit the streaming kernel's ring", max_cost, p.cols);
     StreamGeom geo;
     geo.stages = S;
     geo.stage_bytes = stage;
     geo.act_off = S * stage;
     geo.part_off = (uint32_t)(geo.act_off + act);
-    geo.bar_off = (uint32_t)(geo.part_off + (((size_t)S * PT_MAX * 2 * CW * 4 + (size_t)S * CW * 8 + 127) & ~(size_t)127));
-    geo.meta_off = geo.bar_off + 2 * S * 8;
+    geo.bar_off = (uint32_t)(geo.part_off + part_bytes(S));
+    geo.meta_off = (uint32_t)(geo.bar_off + bar_bytes(S));
     // the tiles in hand-out order: per segment whole rounds of the row groups, as many as fit a stage
     geo.total_tiles = 0;
     for (uint32_t s = 0; s < 3; s++) {
@@ -518,7 +443,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
         geo.seg_tiles[s] = (geo.seg_pairs[s] + pt - 1) / pt;
         geo.total_tiles += geo.seg_tiles[s];
     }
-    int grid = ctx->sm_count;       // one persistent CTA per SM: 16 consumer warps hide the latency of the dependent dp4a / shuffle chains
+    int grid = ctx->sm_count;       // one persistent CTA per SM
     if ((uint32_t)grid > pairs) grid = (int)pairs;
     if (grid < 1) grid = 1;
     // Hand-out: launches of one segment with enough tiles per CTA give every CTA its first tiles by position and let the
@@ -558,18 +483,5 @@ static int32_t launch_stream_switch(ib_ctx *ctx, cudaStream_t stream, const Gemv
     default: return set_error(IB_ERR_INVALID, "gemv: unknown epilogue %u", p.epi);
     }
 }
-
-#ifdef IB_STREAM_TRACE
-extern "C" __attribute__((visibility("default"))) int32_t ib_debug_stream_trace(unsigned long long *out64) {
-    return cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 256) == cudaSuccess ? 0 : 2;
-}
-extern "C" __attribute__((visibility("default"))) int32_t ib_debug_cta_times(unsigned long long *ends, unsigned long long *packed) {
-    if (cudaMemcpyFromSymbol(ends, g_cta_end, sizeof(unsigned long long) * 8 * 160) != cudaSuccess) return 2;
-    return cudaMemcpyFromSymbol(packed, g_cta_packed, sizeof(unsigned long long) * 8 * 160) == cudaSuccess ? 0 : 2;
-}
-extern "C" __attribute__((visibility("default"))) int32_t ib_debug_consumer_phases(long long *out) {
-    return cudaMemcpyFromSymbol(out, g_phase, sizeof(long long) * 8 * 32 * 10) == cudaSuccess ? 0 : 2;
-}
-#endif
 
 }  // namespace ib

@@ -9,7 +9,8 @@ namespace ib {
 
 
 constexpr int CW = 16;                          // consumer warps
-constexpr int STREAM_THREADS = (CW + 1) * 32;   // + 1 producer warp
+constexpr int W_PRODUCER = CW, W_EPILOGUE = CW + 1;
+constexpr int STREAM_THREADS = (CW + 2) * 32;   // + 1 producer warp + 1 epilogue warp
 constexpr int PT_MAX = 16;                      // row pairs per tile
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait on an mbarrier or on a peer gives up after 2 s
 
@@ -19,15 +20,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-#ifndef IB_TRY_WAIT_HINT_NS
-#define IB_TRY_WAIT_HINT_NS 2000u
-#endif
+constexpr uint32_t TRY_WAIT_HINT_NS = 2000u;   // suspend-time hint of mbarrier.try_wait
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(IB_TRY_WAIT_HINT_NS)   // suspend-time hint in ns: a waiting warp sleeps instead of spinning through issue slots
+        : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS)   // suspend-time hint in ns: a waiting warp sleeps instead of spinning through issue slots
         : "memory");
     return ok != 0;
 }
@@ -76,6 +75,29 @@ __device__ __forceinline__ bool wait_counter(const uint32_t *flag, uint32_t targ
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+
+// Shared-memory loads by 32-bit shared address (no generic-address arithmetic in the inner loop).  volatile: they stay
+// between the mbarrier wait before them and the arrival after them.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
 }
 
 // ---- this CTA's share of the work: per segment a contiguous range of row pairs, balanced by bytes ----
@@ -193,79 +215,103 @@ __device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const 
         asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.x[g]) : "r"(smem_u32(SX + e16[g])) : "memory");
     }
     if (qtype == IB_Q4_K) { ua.s[2] *= (1.0f / 16.0f); ua.s[3] *= (1.0f / 16.0f); }  // high nibbles are used in place (16 q)
+    if (qtype == IB_Q4_K || qtype == IB_Q5_K) {   // groups 0,1 (and 2,3) form one 32-column sub-block: one sum each
+        ua.x[0] += ua.x[1];
+        ua.x[2] += ua.x[3];
+    }
 }
 
-__device__ __forceinline__ int dot4_ss(const uint4 &q, const uint4 &a, int d) {
-    d = dp4a_ss(q.x, a.x, d); d = dp4a_ss(q.y, a.y, d); d = dp4a_ss(q.z, a.z, d); return dp4a_ss(q.w, a.w, d);
-}
-__device__ __forceinline__ int dot4_us(const uint4 &q, const uint4 &a, int d) {
-    d = dp4a_us(q.x, a.x, d); d = dp4a_us(q.y, a.y, d); d = dp4a_us(q.z, a.z, d); return dp4a_us(q.w, a.w, d);
-}
-__device__ __forceinline__ uint4 and4(const uint4 &q, uint32_t m) { return make_uint4(q.x & m, q.y & m, q.z & m, q.w & m); }
-
-// One row (in shared memory) x one unit -> the lane's partial dot product.  Everything that depends only on the
-// lane (byte offsets inside a row, shift amounts) is computed once in init().
-struct LaneConst { uint32_t o0, o1, o2, o3, k; };
+// One row (in shared memory, 32-bit shared address) x one unit -> the lane's partial dot product.  Everything that
+// depends only on the lane (byte offsets inside a row, shift amounts, masks) is computed once in init().
+struct LaneConst { uint32_t o0, o1, o2, o3, k, ma, mb, mc; };
+// component w of a 128-bit register group; w is a compile-time constant wherever this is used (unrolled loops)
+__device__ __forceinline__ uint32_t comp(const uint4 &v, int w) { return w == 0 ? v.x : (w == 1 ? v.y : (w == 2 ? v.z : v.w)); }
 template <uint32_t QT> struct Unit;
 
+// 6-bit (scale, min) pairs of sub-blocks 2c and 2c+1 of a Q4_K / Q5_K header without a branch on c (the lanes of a warp
+// differ in c): lanes with c < 2 carry masks (0x3F3F, 0, 0), the others (0, 0x3030, 0x0F0F), and both read the same three
+// half-words (crates/inferi/src/quantization.rs:394-402).
+__device__ __forceinline__ void kquant_scales_lane(const uint4 &hdr, const LaneConst &lc, uint32_t &sc2, uint32_t &m2) {
+    const uint32_t y2 = hdr.y >> lc.o2, z2 = hdr.z >> lc.o2, w2 = hdr.w >> lc.o2;   // o2 = 16 * (c & 1); the masks drop the upper half
+    sc2 = (y2 & lc.ma) | ((y2 >> 2) & lc.mb) | (w2 & lc.mc);
+    m2 = (z2 & lc.ma) | ((z2 >> 2) & lc.mb) | ((w2 >> 4) & lc.mc);
+}
+__device__ __forceinline__ void kquant_lane_init(uint32_t c, LaneConst &lc) {
+    lc.k = c;
+    lc.o2 = 16 * (c & 1);
+    lc.ma = c < 2 ? 0x3F3Fu : 0u;
+    lc.mb = c < 2 ? 0u : 0x3030u;
+    lc.mc = c < 2 ? 0u : 0x0F0Fu;
+}
+// d * (sc_lo * lo + sc_hi * hi) - dmin * (m_lo * x_lo + m_hi * x_hi) for one 64-column chunk of a Q4_K / Q5_K block
+__device__ __forceinline__ float kquant_finish(const uint4 &hdr, uint32_t sc2, uint32_t m2, float lo, float hi, float x_lo, float x_hi) {
+    const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+    const float a = (float)(sc2 & 0xFFu) * lo + (float)(sc2 >> 8) * hi;
+    const float b = (float)(m2 & 0xFFu) * x_lo + (float)(m2 >> 8) * x_hi;
+    return dm.x * a - dm.y * b;
+}
+
 template <> struct Unit<IB_Q4_K> {
-    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) { lc.k = u & 3; lc.o0 = (u >> 2) * 144; lc.o1 = lc.o0 + 16 + 32 * lc.k; }
-    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
-        const uint32_t off_hdr = lc.o0, off_q = lc.o1, c = lc.k;
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + off_hdr);
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
-        const uint4 l0 = and4(q0, 0x0F0F0F0Fu), l1 = and4(q1, 0x0F0F0F0Fu), h0 = and4(q0, 0xF0F0F0F0u), h1 = and4(q1, 0xF0F0F0F0u);
-        int D[4][3];
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) {
+        kquant_lane_init(u & 3, lc);
+        lc.o0 = (u >> 2) * 144;
+        lc.o1 = lc.o0 + 16 + 32 * lc.k;
+    }
+    static __device__ __forceinline__ float dot(uint32_t row, const LaneConst &lc, const UnitAct &ua) {
+        const uint4 hdr = lds128(row + lc.o0), q0 = lds128(row + lc.o1), q1 = lds128(row + lc.o1 + 16);
+        const uint32_t qa[4] = {q0.x, q0.y, q0.z, q0.w}, qb[4] = {q1.x, q1.y, q1.z, q1.w};
+        int L[3] = {0, 0, 0}, H[3] = {0, 0, 0};   // low nibbles = sub-block 2c (groups 0,1), high nibbles = sub-block 2c+1 (groups 2,3)
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            D[0][k] = dot4_ss(l0, ua.l[k][0], 0);
-            D[1][k] = dot4_ss(l1, ua.l[k][1], 0);
-            D[2][k] = dot4_us(h0, ua.l[k][2], 0);
-            D[3][k] = dot4_us(h1, ua.l[k][3], 0);
+        for (int w = 0; w < 4; w++) {
+            const uint32_t lo = qa[w] & 0x0F0F0F0Fu, hi = qa[w] & 0xF0F0F0F0u;
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                L[k] = dp4a_ss(lo, comp(ua.l[k][0], w), L[k]);
+                H[k] = dp4a_us(hi, comp(ua.l[k][2], w), H[k]);
+            }
+        }
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const uint32_t lo = qb[w] & 0x0F0F0F0Fu, hi = qb[w] & 0xF0F0F0F0u;
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                L[k] = dp4a_ss(lo, comp(ua.l[k][1], w), L[k]);
+                H[k] = dp4a_us(hi, comp(ua.l[k][3], w), H[k]);
+            }
         }
         uint32_t sc2, m2;
-        kquant_scales(hdr, c, sc2, m2);
-        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-        // groups 0,1 (and 2,3) share the activation scale and the sub-block scale: add them as integers
-        const float lo = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
-        const float hi = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
-        return (dm.x * (float)(sc2 & 0xFFu)) * lo - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi -
-               (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
+        kquant_scales_lane(hdr, lc, sc2, m2);
+        return kquant_finish(hdr, sc2, m2, ua.s[0] * limb_combine(L[0], L[1], L[2]), ua.s[2] * limb_combine(H[0], H[1], H[2]), ua.x[0], ua.x[2]);
     }
 };
 
 template <> struct Unit<IB_Q5_K> {
-    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) { lc.k = u & 3; lc.o0 = (u >> 2) * 176; lc.o1 = lc.o0 + 48 + 32 * lc.k; }
-    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
-        const uint32_t off_hdr = lc.o0, off_q = lc.o1, c = lc.k;
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + off_hdr);
-        const uint4 hA = *reinterpret_cast<const uint4 *>(row + off_hdr + 16), hB = *reinterpret_cast<const uint4 *>(row + off_hdr + 32);
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q), q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
+    static __device__ __forceinline__ void init(uint32_t u, LaneConst &lc) {
+        kquant_lane_init(u & 3, lc);
+        lc.o0 = (u >> 2) * 176;
+        lc.o1 = lc.o0 + 48 + 32 * lc.k;
+        lc.o3 = 2 * lc.k;
+    }
+    static __device__ __forceinline__ float dot(uint32_t row, const LaneConst &lc, const UnitAct &ua) {
+        const uint4 hdr = lds128(row + lc.o0), hA = lds128(row + lc.o0 + 16), hB = lds128(row + lc.o0 + 32);
+        const uint4 q0 = lds128(row + lc.o1), q1 = lds128(row + lc.o1 + 16);
         const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const uint32_t hw[8] = {hA.x, hA.y, hA.z, hA.w, hB.x, hB.y, hB.z, hB.w};
-        uint32_t lo[8], hi[8];
+        int L[3] = {0, 0, 0}, H[3] = {0, 0, 0};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const uint32_t t = hw[i] >> (2 * c);  // bit 0 of each byte: flag of the low-nibble element, bit 1: of the high-nibble element
-            lo[i] = (qw[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
-            hi[i] = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
-        }
-        int D[4][3];
+            const uint32_t t = hw[i] >> lc.o3;  // bit 0 of each byte: fifth bit of the low-nibble element, bit 1: of the high-nibble element
+            const uint32_t lo = (qw[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
+            const uint32_t hi = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            D[0][k] = dot4_ss(make_uint4(lo[0], lo[1], lo[2], lo[3]), ua.l[k][0], 0);
-            D[1][k] = dot4_ss(make_uint4(lo[4], lo[5], lo[6], lo[7]), ua.l[k][1], 0);
-            D[2][k] = dot4_ss(make_uint4(hi[0], hi[1], hi[2], hi[3]), ua.l[k][2], 0);
-            D[3][k] = dot4_ss(make_uint4(hi[4], hi[5], hi[6], hi[7]), ua.l[k][3], 0);
+            for (int k = 0; k < 3; k++) {
+                L[k] = dp4a_ss(lo, comp(ua.l[k][i >> 2], i & 3), L[k]);
+                H[k] = dp4a_ss(hi, comp(ua.l[k][2 + (i >> 2)], i & 3), H[k]);
+            }
         }
         uint32_t sc2, m2;
-        kquant_scales(hdr, c, sc2, m2);
-        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-        const float lo_f = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
-        const float hi_f = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
-        return (dm.x * (float)(sc2 & 0xFFu)) * lo_f - (dm.y * (float)(m2 & 0xFFu)) * (ua.x[0] + ua.x[1]) + (dm.x * (float)(sc2 >> 8)) * hi_f -
-               (dm.y * (float)(m2 >> 8)) * (ua.x[2] + ua.x[3]);
+        kquant_scales_lane(hdr, lc, sc2, m2);
+        return kquant_finish(hdr, sc2, m2, ua.s[0] * limb_combine(L[0], L[1], L[2]), ua.s[2] * limb_combine(H[0], H[1], H[2]), ua.x[0], ua.x[2]);
     }
 };
 
@@ -278,34 +324,31 @@ template <> struct Unit<IB_Q6_K> {
         lc.o2 = grp + 1536 + 16 * bb + 8 * i;
         lc.o3 = grp + 1664 + 2 * bb;
         lc.k = 8 * h;
+        lc.ma = lc.mb = lc.mc = 0;
     }
-    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
-        const uint32_t off_qa = lc.o0, off_qh = lc.o1, off_sc = lc.o2, off_d = lc.o3, sh = lc.k;
-        const uint4 qa = *reinterpret_cast<const uint4 *>(row + off_qa);
-        const uint4 qb = *reinterpret_cast<const uint4 *>(row + off_qa + 32);
-        const uint4 qh = *reinterpret_cast<const uint4 *>(row + off_qh);
-        const uint2 scw = *reinterpret_cast<const uint2 *>(row + off_sc);   // scales[8i .. 8i+7]
-        const float d = h2f(*reinterpret_cast<const unsigned short *>(row + off_d));
+    static __device__ __forceinline__ float dot(uint32_t row, const LaneConst &lc, const UnitAct &ua) {
+        const uint4 qa = lds128(row + lc.o0), qb = lds128(row + lc.o0 + 32), qh = lds128(row + lc.o1);
+        const uint2 scw = lds64(row + lc.o2);   // scales[8i .. 8i+7]
+        const float d = h2f(lds16(row + lc.o3));
         const uint32_t la[4] = {qa.x, qa.y, qa.z, qa.w}, lb[4] = {qb.x, qb.y, qb.z, qb.w}, hh[4] = {qh.x, qh.y, qh.z, qh.w};
-        uint32_t g0[4], g1[4], g2[4], g3[4];
+        int D[4][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
 #pragma unroll
         for (int w = 0; w < 4; w++) {
             // crates/inferi/src/quantization.rs:237-246: 4 low bits from ql, 2 high bits from qh
-            g0[w] = (la[w] & 0x0F0F0F0Fu) | ((hh[w] << 4) & 0x30303030u);
-            g1[w] = (lb[w] & 0x0F0F0F0Fu) | ((hh[w] << 2) & 0x30303030u);
-            g2[w] = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
-            g3[w] = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
-        }
-        int D[4][3];
+            const uint32_t g0 = (la[w] & 0x0F0F0F0Fu) | ((hh[w] << 4) & 0x30303030u);
+            const uint32_t g1 = (lb[w] & 0x0F0F0F0Fu) | ((hh[w] << 2) & 0x30303030u);
+            const uint32_t g2 = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
+            const uint32_t g3 = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            D[0][k] = dot4_ss(make_uint4(g0[0], g0[1], g0[2], g0[3]), ua.l[k][0], 0);
-            D[1][k] = dot4_ss(make_uint4(g1[0], g1[1], g1[2], g1[3]), ua.l[k][1], 0);
-            D[2][k] = dot4_ss(make_uint4(g2[0], g2[1], g2[2], g2[3]), ua.l[k][2], 0);
-            D[3][k] = dot4_ss(make_uint4(g3[0], g3[1], g3[2], g3[3]), ua.l[k][3], 0);
+            for (int k = 0; k < 3; k++) {
+                D[0][k] = dp4a_ss(g0, comp(ua.l[k][0], w), D[0][k]);
+                D[1][k] = dp4a_ss(g1, comp(ua.l[k][1], w), D[1][k]);
+                D[2][k] = dp4a_ss(g2, comp(ua.l[k][2], w), D[2][k]);
+                D[3][k] = dp4a_ss(g3, comp(ua.l[k][3], w), D[3][k]);
+            }
         }
         // scale of group g is byte 2g + h of the 8 loaded: bytes {h, 2+h} of word x, {h, 2+h} of word y
-        const uint32_t sx = scw.x >> sh, sy = scw.y >> sh;
+        const uint32_t sx = scw.x >> lc.k, sy = scw.y >> lc.k;
         const float s0 = (float)(int)(int8_t)(sx & 0xFF), s1 = (float)(int)(int8_t)((sx >> 16) & 0xFF);
         const float s2 = (float)(int)(int8_t)(sy & 0xFF), s3 = (float)(int)(int8_t)((sy >> 16) & 0xFF);
         float v = s0 * (ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) - 32.0f * ua.x[0]);
@@ -322,23 +365,23 @@ template <> struct Unit<IB_Q8_0> {
         const uint32_t b0 = 2 * u, grp = (b0 >> 3) * 272, bb = b0 & 7;
         lc.o0 = grp + 32 * bb;
         lc.o1 = grp + 256 + 2 * bb;
+        lc.o2 = lc.o3 = lc.k = lc.ma = lc.mb = lc.mc = 0;
     }
-    static __device__ __forceinline__ float dot(const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
-        const uint32_t off_q = lc.o0, off_d = lc.o1;
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(row + off_q), q1 = *reinterpret_cast<const uint4 *>(row + off_q + 16);
-        const uint4 q2 = *reinterpret_cast<const uint4 *>(row + off_q + 32), q3 = *reinterpret_cast<const uint4 *>(row + off_q + 48);
-        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(row + off_d));   // scales of the two blocks
-        int D[4][3];
+    static __device__ __forceinline__ float dot(uint32_t row, const LaneConst &lc, const UnitAct &ua) {
+        const uint4 q[4] = {lds128(row + lc.o0), lds128(row + lc.o0 + 16), lds128(row + lc.o0 + 32), lds128(row + lc.o0 + 48)};
+        const uint32_t dbits = lds32(row + lc.o1);   // f16 scales of the two blocks
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&dbits));
+        int A[3] = {0, 0, 0}, B[3] = {0, 0, 0};   // block 2u (groups 0,1), block 2u+1 (groups 2,3)
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            D[0][k] = dot4_ss(q0, ua.l[k][0], 0);
-            D[1][k] = dot4_ss(q1, ua.l[k][1], 0);
-            D[2][k] = dot4_ss(q2, ua.l[k][2], 0);
-            D[3][k] = dot4_ss(q3, ua.l[k][3], 0);
-        }
-        const float a = ua.s[0] * limb_combine(D[0][0] + D[1][0], D[0][1] + D[1][1], D[0][2] + D[1][2]);
-        const float c = ua.s[2] * limb_combine(D[2][0] + D[3][0], D[2][1] + D[3][1], D[2][2] + D[3][2]);
-        return dd.x * a + dd.y * c;
+        for (int g = 0; g < 4; g++)
+#pragma unroll
+            for (int w = 0; w < 4; w++)
+#pragma unroll
+                for (int k = 0; k < 3; k++) {
+                    if (g < 2) A[k] = dp4a_ss(comp(q[g], w), comp(ua.l[k][g], w), A[k]);
+                    else B[k] = dp4a_ss(comp(q[g], w), comp(ua.l[k][g], w), B[k]);
+                }
+        return dd.x * (ua.s[0] * limb_combine(A[0], A[1], A[2])) + dd.y * (ua.s[2] * limb_combine(B[0], B[1], B[2]));
     }
 };
 
@@ -347,7 +390,7 @@ constexpr uint32_t QT_Q4_Q6 = 0xFEu;   // ... and hold only Q4_K and Q6_K (q, k,
 
 template <uint32_t QT>
 __device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst &lc) {
-    lc.o0 = lc.o1 = lc.o2 = lc.o3 = lc.k = 0;
+    lc.o0 = lc.o1 = lc.o2 = lc.o3 = lc.k = lc.ma = lc.mb = lc.mc = 0;
     if (QT == QT_Q4_Q6) {
         if (qtype == IB_Q4_K) Unit<IB_Q4_K>::init(u, lc);
         else Unit<IB_Q6_K>::init(u, lc);
@@ -362,7 +405,7 @@ __device__ __forceinline__ void unit_init(uint32_t qtype, uint32_t u, LaneConst 
     }
 }
 template <uint32_t QT>
-__device__ __forceinline__ float unit_dot(uint32_t qtype, const uint8_t *row, const LaneConst &lc, const UnitAct &ua) {
+__device__ __forceinline__ float unit_dot(uint32_t qtype, uint32_t row, const LaneConst &lc, const UnitAct &ua) {
     if (QT == QT_Q4_Q6) return qtype == IB_Q4_K ? Unit<IB_Q4_K>::dot(row, lc, ua) : Unit<IB_Q6_K>::dot(row, lc, ua);
     if (QT != QT_MIXED) return Unit<(QT == QT_MIXED || QT == QT_Q4_Q6) ? IB_Q4_K : QT>::dot(row, lc, ua);
     switch (qtype) {

@@ -124,12 +124,6 @@ struct ib_llama {
     cudaGraphExec_t graph_exec = nullptr;
     cudaStream_t own_stream = nullptr;
     uint64_t launches_per_token = 0;
-    // whole-token kernel (single GPU): the phase list on the device, the grid-barrier counter, the launch plan
-    ib::PhaseDesc *phases_dev = nullptr;
-    uint32_t *grid_bar = nullptr, *tile_ctr = nullptr;
-    ib::TokenProgram prog{};
-    ib::TokenKernelPlan plan{};
-    bool use_token_kernel = false;
     // sampling beyond greedy (ib_llama_set_sampler): parameters, scratch, and the graph that carries the sampler node
     float temperature = 0.f, topp = 0.f;
     uint64_t sample_seed = 0;
@@ -168,41 +162,17 @@ static void set_pdl(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, uint32_t
     cfg.numAttrs = pdl ? 1 : 0;
 }
 
-// Issues the kernels of one token into `s`, or - with `collect` - appends them as phases of the whole-token kernel
-// (which does the begin / end book-keeping itself).
-struct HostPhase {
-    bool attn;
-    GemvParams g;
-    AttnLaunch a;
-};
-
-static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vector<HostPhase> *collect = nullptr) {
+// Issues the kernels of one token into `s`.
+static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     ib_ctx *ctx = m->ctx;
     const ib_llama_config &c = m->cfg;
     const int tp = m->tp_size, rank = m->tp_rank;
     const uint32_t H = c.hidden_size, L = c.num_hidden_layers;
     const CommLayout cl(H, tp);
     int32_t rc;
-    auto emit_gemv = [&](const GemvParams &p) -> int32_t {
-        if (!collect) return launch_gemv(ctx, s, p);
-        HostPhase ph;
-        memset(&ph, 0, sizeof ph);
-        ph.g = p;
-        ph.g.err = ctx->err_dev;
-        ph.g.pdl = 0;
-        collect->push_back(ph);
-        return IB_OK;
-    };
-    auto emit_attn = [&](const AttnLaunch &a) -> int32_t {
-        if (!collect) return launch_attention(ctx, s, a);
-        HostPhase ph;
-        memset(&ph, 0, sizeof ph);
-        ph.attn = true;
-        ph.a = a;
-        collect->push_back(ph);
-        return IB_OK;
-    };
-    if (!collect) {
+    auto emit_gemv = [&](const GemvParams &p) -> int32_t { return launch_gemv(ctx, s, p); };
+    auto emit_attn = [&](const AttnLaunch &a) -> int32_t { return launch_attention(ctx, s, a); };
+    {
         QDesc e{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((H + 255) / 256);
@@ -291,14 +261,14 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl, std::vect
         }
     if ((rc = emit_gemv(p))) return rc;
     m->x_final = cur;
-    if (!collect && m->temperature > 0.f) {
+    if (m->temperature > 0.f) {
         // temperature / top-p sampling replaces the greedy token (models/sampler.rs:32-52); the coin is a function of
         // (seed, position)
         if ((rc = launch_sample(ctx, s, m->logits, c.vocab_size, m->temperature, m->topp, m->sample_seed, &m->ctl->pos, 0.f, m->sample_probs, m->sample_keys,
                                 &m->ctl->next, nullptr, pdl)))
             return rc;
     }
-    if (!collect) {
+    {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(32);
@@ -414,7 +384,7 @@ int32_t ib_llama_destroy(ib_llama *m) {
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
         if (m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch, m->phases_dev, m->grid_bar, m->tile_ctr};
+                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -592,80 +562,7 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
 
 // Records the token graph (once every pointer it needs is known) and instantiates it.
 static int32_t finish_graph(ib_llama *m) {
-    ib_ctx *ctx = m->ctx;
-    int32_t rc;
-#define CU(expr)                                                                                                        \
-    do {                                                                                                                \
-        cudaError_t _e = (expr);                                                                                        \
-        if (_e != cudaSuccess) return set_error(IB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));           \
-    } while (0)
-    CU(cudaDeviceSynchronize());
-    // Single GPU with INFERI_B200_TOKEN_KERNEL=1: the whole token as one cooperative kernel (token_kernel.cu), if the
-    // model's shapes fit its shared-memory plan.  The default is the graph of separate kernels, which is the faster of the
-    // two at present.
-    const char *tk = getenv("INFERI_B200_TOKEN_KERNEL");
-    if (m->tp_size == 1 && tk && tk[0] == '1') {
-        std::vector<HostPhase> phases;
-        rc = record_token(m, nullptr, 0, &phases);
-        const uint32_t L = m->cfg.num_hidden_layers;
-        if (rc == IB_OK && phases.size() != 5 * (size_t)L + 1) rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: unexpected phase list");
-        for (uint32_t l = 0; rc == IB_OK && l < L; l++)
-            if (m->layers[l].attn_q_bias_dev || m->layers[l].attn_k_bias_dev || m->layers[l].attn_v_bias_dev)
-                rc = set_error(IB_ERR_UNSUPPORTED, "token kernel: q/k/v biases are only on the graph path");   // falls through to the graph below
-        std::vector<PhaseDesc> table(phases.size());
-        TokenProgram &P = m->prog;
-        if (rc == IB_OK) {
-            memset(table.data(), 0, sizeof(PhaseDesc) * table.size());
-            void *kc = nullptr, *vc = nullptr;
-            for (size_t i = 0; i < phases.size(); i++) {
-                const HostPhase &h = phases[i];
-                PhaseDesc &d = table[i];
-                if (h.attn) {
-                    d.kind = PH_ATTN;
-                    d.k_cache = (void *)h.a.k_cache; d.v_cache = (void *)h.a.v_cache;
-                    continue;
-                }
-                d.kind = PH_GEMV;
-                for (uint32_t sg = 0; sg < h.g.nseg; sg++) {
-                    d.m[sg] = LayerMat{h.g.seg[sg].w, (uint32_t)h.g.seg[sg].row_bytes, h.g.seg[sg].qtype};
-                    d.rows[sg] = h.g.seg[sg].rows;
-                }
-                d.x = h.g.x; d.norm_w = h.g.norm_w; d.eps = h.g.eps;
-                d.nseg = h.g.nseg; d.epi = h.g.epi; d.cols = h.g.cols;
-                if (h.g.epi == EPI_QKV) { kc = h.g.k_cache; vc = h.g.v_cache; }
-                d.k_cache = kc; d.v_cache = vc;
-            }
-            P.phases = nullptr; P.n_phases = (uint32_t)phases.size();
-            P.qkv = phases[0].g; P.res = phases[2].g; P.gu = phases[3].g; P.cls = phases[5 * (size_t)L].g;
-            const AttnLaunch &a0 = phases[1].a;
-            P.attn = AttnArgs{a0.p, a0.pos_ptr, a0.q, a0.k_cache, a0.v_cache, a0.out, a0.scratch, a0.counters, a0.max_splits, 0};
-            P.ctl = m->ctl; P.seq = m->seq; P.seq_cap = m->seq_cap;
-            P.embd = QDesc{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
-            P.hidden = m->cfg.hidden_size; P.vocab = m->cfg.vocab_size; P.half_head = m->head_size / 2;
-            P.x = m->x; P.theta = m->theta; P.rope_cs = m->rope_cs;
-            P.epoch = m->epoch; P.barriers_per_token = (uint32_t)phases.size() + 1;
-            P.err = ctx->err_dev;
-            P.head_size = m->head_size; P.kv_mul = m->cfg.num_attention_heads / m->cfg.num_key_value_heads; P.kv_dtype = (uint32_t)m->kv_dtype;
-            rc = plan_token_kernel(ctx, P, table.data(), m->plan);
-        }
-        if (rc == IB_OK) {
-            CU(cudaMalloc(&m->phases_dev, sizeof(PhaseDesc) * table.size()));
-            CU(cudaMemcpy(m->phases_dev, table.data(), sizeof(PhaseDesc) * table.size(), cudaMemcpyHostToDevice));
-            CU(cudaMalloc(&m->grid_bar, sizeof(uint32_t)));
-            CU(cudaMemset(m->grid_bar, 0, sizeof(uint32_t)));
-            CU(cudaMalloc(&m->tile_ctr, sizeof(uint32_t) * table.size()));
-            CU(cudaMemset(m->tile_ctr, 0, sizeof(uint32_t) * table.size()));
-            P.phases = m->phases_dev;
-            P.grid_bar = m->grid_bar;
-            P.tile_ctr = m->tile_ctr;
-            P.geo = m->plan.geo;
-            m->use_token_kernel = true;
-            m->launches_per_token = 1;
-            return IB_OK;
-        }
-        if (rc != IB_ERR_UNSUPPORTED) return rc;   // shapes outside the kernel's plan: the graph of separate kernels serves them
-    }
-#undef CU
+    IB_CHECK_CUDA(cudaDeviceSynchronize());
     return capture_graph(m, &m->graph_exec, &m->launches_per_token);
 }
 
@@ -674,9 +571,7 @@ static int32_t capture_graph(ib_llama *m, cudaGraphExec_t *exec, uint64_t *launc
     ib_ctx *ctx = m->ctx;
     const uint64_t before = ctx->launches;
     IB_CHECK_CUDA(cudaStreamBeginCapture(m->own_stream, cudaStreamCaptureModeThreadLocal));
-    // INFERI_B200_NO_PDL=1 records the graph with plain kernel-to-kernel dependencies (for comparisons)
-    const char *no_pdl = getenv("INFERI_B200_NO_PDL");
-    const int32_t rc = record_token(m, m->own_stream, (no_pdl && no_pdl[0] == '1') ? 0 : 1);
+    const int32_t rc = record_token(m, m->own_stream, 1);
     cudaGraph_t graph = nullptr;
     cudaError_t ce = cudaStreamEndCapture(m->own_stream, &graph);
     *launches_per_token = ctx->launches - before;
@@ -701,7 +596,6 @@ int32_t ib_llama_set_sampler(ib_llama *m, float temperature, float topp, uint64_
     IB_REQUIRE(temperature >= 0.f, "ib_llama_set_sampler: negative temperature");
     if (temperature > 0.f) {
         if (m->tp_size > 1) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_set_sampler: sampling needs the whole vocabulary on one GPU (tensor-parallel models are greedy)");
-        if (m->use_token_kernel) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_set_sampler: the whole-token kernel is greedy; unset INFERI_B200_TOKEN_KERNEL");
     }
     IB_CHECK_CUDA(cudaDeviceSynchronize());
     if (m->graph_exec_sample) { cudaGraphExecDestroy(m->graph_exec_sample); m->graph_exec_sample = nullptr; }
@@ -748,7 +642,7 @@ int32_t ib_llama_tp_connect(ib_llama *m, const void *handles) {
 }
 
 static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, uint32_t n_prompt, uint32_t start_pos, uint32_t n_steps) {
-    if (!m->graph_exec && !m->use_token_kernel) return set_error(IB_ERR_COMM, "the tensor-parallel model is not connected yet: call ib_llama_tp_connect on every rank first");
+    if (!m->graph_exec) return set_error(IB_ERR_COMM, "the tensor-parallel model is not connected yet: call ib_llama_tp_connect on every rank first");
     // control block + given tokens in one pinned staging buffer -> two small async copies
     uint32_t *h = m->h_pinned;
     IB_CHECK_CUDA(cudaEventSynchronize(m->staged));  // an earlier call's copies out of the staging buffer are done
@@ -757,13 +651,6 @@ static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, u
     IB_CHECK_CUDA(cudaMemcpyAsync(m->ctl, h, sizeof(TokenCtl), cudaMemcpyHostToDevice, s));
     IB_CHECK_CUDA(cudaMemcpyAsync(m->seq, h + 4, sizeof(uint32_t) * n_prompt, cudaMemcpyHostToDevice, s));
     IB_CHECK_CUDA(cudaEventRecord(m->staged, s));
-    if (m->use_token_kernel) {
-        for (uint32_t i = 0; i < n_steps; i++) {
-            int32_t rc = launch_token_kernel(m->ctx, s, m->prog, m->plan);
-            if (rc) return rc;
-        }
-        return IB_OK;
-    }
     const bool sampled = m->temperature > 0.f && m->graph_exec_sample;
     for (uint32_t i = 0; i < n_steps; i++) {
         IB_CHECK_CUDA(cudaGraphLaunch(sampled ? m->graph_exec_sample : m->graph_exec, s));

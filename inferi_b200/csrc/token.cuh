@@ -1,5 +1,4 @@
-// The token loop's device control block, the quantized-row descriptor of the embedding table, and the program of the
-// whole-token kernel (one cooperative launch per token: token_kernel.cu).
+// The token loop's device control block and the quantized-row descriptor of the embedding table.
 #pragma once
 
 #include "attention.cuh"
@@ -64,70 +63,5 @@ __device__ inline float dequant_at(const QDesc &q, const uint8_t *row, uint32_t 
     const int qv = (int)(((g & 2) ? (lo >> 4) : (lo & 0xF)) | (((h >> (2 * g)) & 3) << 4)) - 32;
     return half_at(dp) * (float)(int8_t)sc[8 * i + 2 * g + l / 16] * (float)qv;
 }
-
-
-// ---- whole-token kernel ----
-constexpr uint32_t TK_SLOTS = 4;            // tiles in flight per CTA (mbarrier pairs of the byte ring)
-constexpr uint32_t TK_TILE_MAX = 75776;     // largest tile in bytes
-
-enum TokenPhaseKind : uint32_t { PH_GEMV = 0, PH_ATTN = 1 };
-
-// One matrix of a phase: what may differ from layer to layer (GGUF mixes give some layers wider formats).
-struct __align__(16) LayerMat {
-    const uint8_t *w;
-    uint32_t row_bytes, qtype;
-};
-
-// One phase of the token, in global memory.  The producer warp and the consumer warps read it at the start of the
-// phase; what the inner loops need all the time (outputs, cache geometry) is the same for every layer and travels as
-// kernel parameters (constant bank) instead.
-struct __align__(16) PhaseDesc {
-    LayerMat m[3];            // PH_GEMV: 1-3 row segments streamed back to back (q|k|v, gate|up, or a single matrix)
-    const float *x;           // input vector [cols]
-    const float *norm_w;      // RMSNorm weights applied to x first, or null
-    void *k_cache, *v_cache;  // this layer's cache (qkv epilogue, attention)
-    uint32_t rows[3];
-    uint32_t nseg, epi, cols;
-    float eps;
-    uint32_t kind;
-};
-static_assert(sizeof(PhaseDesc) % 16 == 0, "descriptors are read in 16-byte pieces");
-
-struct TokenGeom {
-    uint32_t ring_bytes, act_off, act_bytes, part_off, bar_off, tile_max;
-};
-
-struct TokenProgram {
-    const PhaseDesc *phases;
-    uint32_t n_phases;
-    GemvParams qkv, res, gu, cls;       // epilogue parameters by kind: q/k/v, residual (o_proj and down), gate/up, classifier
-    AttnArgs attn;                      // kc / vc come from the phase
-    TokenCtl *ctl;
-    uint32_t *seq;
-    uint32_t seq_cap;
-    QDesc embd;
-    uint32_t hidden, vocab, half_head;
-    float *x;
-    const float *theta;
-    float2 *rope_cs;
-    uint32_t *grid_bar;                 // arrival counter of the grid barriers (only ever grows)
-    uint32_t *epoch;                    // completed tokens
-    uint32_t *tile_ctr;                 // [n_phases] tile hand-out counters, zero between tokens
-    uint32_t barriers_per_token;
-    uint32_t *err;
-    uint32_t head_size, kv_mul, kv_dtype;
-    TokenGeom geo;
-};
-
-struct TokenKernelPlan {
-    TokenGeom geo;
-    size_t smem_bytes;
-    int grid;
-    int variant;          // which instance of the kernel serves the model's attention shape
-};
-
-// Shared-memory layout for a model, or IB_ERR_UNSUPPORTED if some matrix does not fit the kernel.
-int32_t plan_token_kernel(ib_ctx *ctx, const TokenProgram &prog, const PhaseDesc *phases_host, TokenKernelPlan &plan);
-int32_t launch_token_kernel(ib_ctx *ctx, cudaStream_t stream, const TokenProgram &prog, const TokenKernelPlan &plan);
 
 }  // namespace ib

@@ -61,29 +61,23 @@ def check_loop(backend, cfg, weights, kv_f16, prompt, n_gen, tied=False):
     return worst
 
 
-@pytest.mark.parametrize("token_kernel", ["0", "1"])
 @pytest.mark.parametrize("kv_f16", [False, True])
-def test_tiny_model_all_quant_types(backend, kv_f16, token_kernel, monkeypatch):
-    monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", token_kernel)   # 1: the whole token as one cooperative kernel
+def test_tiny_model_all_quant_types(backend, kv_f16):
     w = synth_weights(TINY, seed=3001, recipe=TINY_RECIPE)
     check_loop(backend, TINY, w, kv_f16, prompt=[3, 500, 41, 7], n_gen=24)
 
 
-def test_token_kernel_and_kernel_graph_give_the_same_tokens(backend, monkeypatch):
-    """INFERI_B200_TOKEN_KERNEL=1 selects one cooperative kernel per token; the default is the graph of separate kernels
-    (5 per layer + 3: begin, classifier, end).  Both must reproduce the oracle's greedy tokens, and the launch counter tells them apart."""
+def test_token_graph_launch_count_and_oracle_tokens(backend):
+    """A token is a graph of 5 kernels per layer + 3 (begin, classifier, end); the launch counter must say so, and the
+    greedy tokens must be the oracle's."""
     w = synth_weights(SMALL, seed=3005, device="cuda")
     prompt, n_gen = [5, 77, 1001], 10
     steps = len(prompt) + n_gen - 1
-    outs = {}
-    for mode, per_token in (("1", 1), ("0", 5 * SMALL.num_hidden_layers + 3)):
-        monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", mode)
-        model = Llama2(backend, SMALL, Llama2Weights(backend, SMALL, w), kv_f16=True)
-        backend.reset_launch_count()
-        outs[mode] = model.generate(prompt, n_gen).tolist()
-        assert backend.launch_count() == steps * per_token
-        model.close()
-    assert outs["0"] == outs["1"]
+    model = Llama2(backend, SMALL, Llama2Weights(backend, SMALL, w), kv_f16=True)
+    backend.reset_launch_count()
+    got = model.generate(prompt, n_gen).tolist()
+    assert backend.launch_count() == steps * (5 * SMALL.num_hidden_layers + 3)
+    model.close()
     ref = oracle.Llama(oracle_cfg(SMALL), weights_to_host(w), kv_f16=True)
     want, tok = [], None
     for pos in range(steps):
@@ -92,7 +86,7 @@ def test_token_kernel_and_kernel_graph_give_the_same_tokens(backend, monkeypatch
         if pos >= len(prompt) - 1:
             want.append(oracle.argmax(lg))
     ref.close()
-    assert outs["1"] == want
+    assert got == want
 
 
 def test_small_model_tied_classifier(backend):
@@ -128,16 +122,6 @@ def test_qwen2_variant_neox_rotation_and_qkv_biases(backend, cfg, recipe):
     assert np.abs(a - b).max() > 1e-2
     plain.close()
     qwen.close()
-
-
-def test_qwen2_biases_with_the_token_kernel_requested(backend, monkeypatch):
-    """The whole-token kernel has no bias input: a model with biases is served by the graph of separate kernels even when the
-    token kernel is asked for, with the same results."""
-    import dataclasses
-    monkeypatch.setenv("INFERI_B200_TOKEN_KERNEL", "1")
-    qcfg = dataclasses.replace(TINY, rope_variant=1)
-    w = synth_weights(qcfg, seed=78, recipe=TINY_RECIPE, qkv_bias=True)
-    assert check_loop(backend, qcfg, w, True, [4, 9], 12) <= LOGITS_MAX_ABS
 
 
 def test_generate_until_stops_at_the_stop_token(backend):
