@@ -143,6 +143,7 @@ struct GemvParams {
     uint32_t *argmax_out;
     uint32_t row_offset;               // added to the row index (tensor-parallel vocabulary shard)
     uint32_t pdl;                      // 1: launched with programmatic dependent launch
+    uint32_t pair_instance;            // 1: run Q4_K-only / Q6_K-only launches on the two-format instance too (shared code across a token graph)
     uint32_t *err;                     // device view of the context's error word (set by launch_gemv)
     // ---- tensor parallel (tp > 1): one-shot push all-reduce fused into epilogue and prologue ----
     uint32_t tp;                                // number of ranks; 0 or 1 = single GPU

@@ -45,15 +45,6 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t idx) 
     return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - idx);  // ties -> lowest index
 }
 
-// 6-bit (scale, min) pairs of sub-blocks 2c and 2c+1 of a Q4_K / Q5_K block header (crates/inferi/src/quantization.rs:394-402):
-// returns sc_lo | sc_hi << 8 and m_lo | m_hi << 8.
-__device__ __forceinline__ void kquant_scales(const uint4 &hdr, uint32_t c, uint32_t &sc2, uint32_t &m2) {
-    const uint32_t sh = 16 * (c & 1);
-    const uint32_t y2 = (hdr.y >> sh) & 0xFFFFu, z2 = (hdr.z >> sh) & 0xFFFFu, w2 = (hdr.w >> sh) & 0xFFFFu;
-    if (c < 2) { sc2 = y2 & 0x3F3Fu; m2 = z2 & 0x3F3Fu; }
-    else { sc2 = (w2 & 0x0F0Fu) | ((y2 >> 2) & 0x3030u); m2 = ((w2 >> 4) & 0x0F0Fu) | ((z2 >> 2) & 0x3030u); }
-}
-
 // -------------------------------------------------------------------------------------------------
 // prologue: (optional RMSNorm) + conversion of x into the limb form in shared memory.
 // Called by the first PACK_THREADS threads of the CTA; synchronises them on named barrier 1.
@@ -223,67 +214,6 @@ __device__ __forceinline__ void pack_activation(uint8_t *smem, uint32_t cols, co
             if (norm_w && ok) {
                 const float4 w = __ldg(w4 + 4 * run + j);
                 v[j].x = (v[j].x * rms) * w.x; v[j].y = (v[j].y * rms) * w.y; v[j].z = (v[j].z * rms) * w.z; v[j].w = (v[j].w * rms) * w.w;
-            }
-        }
-        pack_run(v, run, cols, smem, ok, nq);
-    }
-    named_barrier(1, NT);
-}
-
-// The same conversion with a small register footprint, for kernels that keep other state alive across it (the
-// whole-token kernel): one run of 16 columns per thread is held in registers at a time; with RMSNorm the runs beyond the
-// first are read twice (sum of squares, then conversion).  Result bit-identical to pack_activation.
-template <int NT = PACK_THREADS>
-__device__ __forceinline__ void pack_activation_lean(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                     float *red /* [NT/32 + 1] */, uint32_t nq = 0) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t nruns = cols / 16;
-    const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    const float4 *w4 = reinterpret_cast<const float4 *>(norm_w);
-    float4 v[4], g[4];
-    const bool have0 = (uint32_t)tid < nruns;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        v[j] = have0 ? __ldcg(x4 + 4 * tid + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        g[j] = (norm_w && have0) ? __ldg(w4 + 4 * tid + j) : make_float4(1.f, 1.f, 1.f, 1.f);
-    }
-    float rms = 1.0f;
-    if (norm_w) {
-        // crates/inferi-shaders/src/rms_norm.rs:112-120
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; j++) ss += (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
-#pragma unroll 1
-        for (uint32_t run = tid + NT; run < nruns; run += NT)
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float4 t = __ldcg(x4 + 4 * run + j);
-                ss += (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
-            }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp] = ss;
-        named_barrier(1, NT);
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < NT / 32; w++) t += red[w];
-        rms = 1.0f / sqrtf(t / (float)cols + eps);
-    }
-#pragma unroll 1
-    for (uint32_t base = warp * 32; base < nruns; base += NT) {   // warp-uniform: both lanes of a 32-column group are present
-        const uint32_t run = base + lane;
-        const bool ok = run < nruns;
-        if (base != (uint32_t)(warp * 32)) {   // runs beyond the first: fetched here
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                v[j] = ok ? __ldcg(x4 + 4 * run + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-                g[j] = (norm_w && ok) ? __ldg(w4 + 4 * run + j) : make_float4(1.f, 1.f, 1.f, 1.f);
-            }
-        }
-        if (norm_w && ok) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                v[j].x = (v[j].x * rms) * g[j].x; v[j].y = (v[j].y * rms) * g[j].y; v[j].z = (v[j].z * rms) * g[j].z; v[j].w = (v[j].w * rms) * g[j].w;
             }
         }
         pack_run(v, run, cols, smem, ok, nq);

@@ -62,7 +62,7 @@ constexpr uint32_t PART_STAGE_FLOATS = 2 * CW * PT_MAX;
 // two partial sums per pair (its columns of the two rows) in the stage's partial block and arrives on the stage's "done"
 // barrier.  It never waits for another consumer warp: adding up the column groups and everything that follows is the
 // epilogue warp's work.
-template <uint32_t EPI, uint32_t QT>
+template <uint32_t QT>
 __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consumer &c, const Act &A) {
     const int lane = c.lane;
     UnitAct ua;
@@ -72,6 +72,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
     uint32_t st = 0, par = 0;
     constexpr bool ONE_TYPE = (QT != QT_MIXED && QT != QT_Q4_Q6);
     const uint32_t rb0 = (uint32_t)p.seg[0].row_bytes, rb1 = (uint32_t)p.seg[1].row_bytes, rb2 = (uint32_t)p.seg[2].row_bytes;
+    const bool swiglu = p.epi == EPI_SWIGLU;   // gate rows, then up rows, in one tile: a "pair" is gate row r + up row r
 #pragma unroll 1
     for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
         if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
@@ -85,9 +86,9 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
             cur_type = qtype;
         }
         const uint32_t tile = c.ring + st * c.stage_bytes;
-        const uint32_t rbA = (EPI == EPI_SWIGLU || s == 0) ? rb0 : (s == 1 ? rb1 : rb2);
-        const uint32_t strideA = (EPI == EPI_SWIGLU) ? rbA : 2 * rbA;
-        const uint32_t offB = (EPI == EPI_SWIGLU) ? n * rbA : rbA, strideB = (EPI == EPI_SWIGLU) ? rb1 : strideA;
+        const uint32_t rbA = (swiglu || s == 0) ? rb0 : (s == 1 ? rb1 : rb2);
+        const uint32_t strideA = swiglu ? rbA : 2 * rbA;
+        const uint32_t offB = swiglu ? n * rbA : rbA, strideB = swiglu ? rb1 : strideA;
         const uint32_t pt = c.part + 4 * (st * PART_STAGE_FLOATS);
         for (uint32_t pr = c.rg; pr < n; pr += RG) {
             float va = 0.f, vb = 0.f;
@@ -111,10 +112,12 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
 // The epilogue warp: per tile it waits until every consumer warp has left its partials, adds up the column groups in a
 // fixed order (bitwise deterministic results), hands the stage back to the producer and runs the epilogue of the tile's
 // row pairs, one pair per lane.
-template <uint32_t EPI>
 __device__ __forceinline__ void finish_tiles(const GemvParams &p, uint32_t part, uint32_t meta, uint32_t bar0, uint32_t S, uint32_t CG, int lane,
-                                             unsigned long long &best) {
+                                             const float *red, unsigned long long &best) {
     uint32_t st = 0, par = 0;
+    float rms = 1.0f;
+    bool rms_known = p.norm_w == nullptr;
+    const bool residual = p.epi == EPI_RESIDUAL;
 #pragma unroll 1
     for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
         if (!mbar_wait(bar0 + 8 * st, par, p.err, 1)) return;
@@ -124,7 +127,17 @@ __device__ __forceinline__ void finish_tiles(const GemvParams &p, uint32_t part,
         const bool mine = (uint32_t)lane < n;
         // the pair's residual values are requested before the wait for the dot products: the L2 round trip overlaps it
         float2 rpre = make_float2(0.f, 0.f);
-        if (EPI == EPI_RESIDUAL && mine) rpre = residual_prefetch(p.resid, first_pair + lane);
+        if (residual && mine) rpre = residual_prefetch(p.resid, first_pair + lane);
+        if (!rms_known) {
+            // RMSNorm factor of the input vector (crates/inferi-shaders/src/rms_norm.rs:112-120): the consumer warps left
+            // their parts of the sum of squares in `red`; added in a fixed order
+            if (!mbar_wait(bar0 + 8 * (3 * S), 0, p.err, 6)) return;
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < PACK_THREADS / 32; w++) t += red[w];
+            rms = 1.0f / sqrtf(t / (float)p.cols + p.eps);
+            rms_known = true;
+        }
         if (!mbar_wait(bar0 + 8 * (2 * S + st), par, p.err, 5)) return;
         float va = 0.f, vb = 0.f;
         if (mine) {
@@ -136,15 +149,17 @@ __device__ __forceinline__ void finish_tiles(const GemvParams &p, uint32_t part,
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar0 + 8 * (S + st));   // partials read: the producer may refill the stage
-        if (mine) epilogue<EPI>(p, s, first_pair + lane, va, vb, best, ParamCaches{p}, rpre);
+        if (mine) epilogue(p, s, first_pair + lane, va * rms, vb * rms, best, rpre);
     }
 }
 
 // ---- the kernel ----
 // Shared-memory barriers: full[S] (the producer's expect_tx arrival + the copy's bytes), empty[S] (one arrival: the
 // epilogue warp has read the stage's partials, which implies that every consumer warp is done with its weights),
-// done[S] (one arrival per working consumer warp).
-template <uint32_t EPI, uint32_t QT>
+// done[S] (one arrival per working consumer warp), ss (one arrival per consumer warp: its part of the input's sum of squares).
+// One instance per weight format (or format pair); what the launch does with the row sums is a run-time switch in the
+// epilogue warp, so that the launches of a token graph share their code.
+template <uint32_t QT>
 __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const GemvParams p, const StreamGeom geo) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[PACK_THREADS / 32 + 1];
@@ -161,9 +176,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     const uint32_t RG = CW / CG;                 // row groups working side by side
     const uint32_t active = CG * RG;             // consumer warps with work
 
-    if (threadIdx.x < 3 * S) {
+    if (threadIdx.x <= 3 * S) {
         const uint32_t which = threadIdx.x / S;
-        mbar_init(bar0 + 8 * threadIdx.x, which == 2 ? active : 1u);
+        mbar_init(bar0 + 8 * threadIdx.x, which == 2 ? active : (which == 3 ? (uint32_t)CW : 1u));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -180,8 +195,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         const bool dyn = geo.dynamic != 0;
         Share sh;
         TileCursor tc;
+        const bool swiglu = p.epi == EPI_SWIGLU;
         if (!dyn) {
-            make_share<EPI>(p, geo.stage_bytes, RG, sh);
+            make_share(p, geo.stage_bytes, RG, sh);
             tc.init(sh);
         }
         uint32_t st = 0, par = 1;   // parity of the slot's previous use ("1" before the first one: nothing to wait for)
@@ -215,15 +231,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
             }
             const uint32_t cost = s == 0 ? geo.seg_cost[0] : (s == 1 ? geo.seg_cost[1] : geo.seg_cost[2]);
             const uint32_t dst = smem_u32(ring + (size_t)st * geo.stage_bytes);
-            const uint32_t ba = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[0].row_bytes : n * cost;
-            const uint32_t bb = (EPI == EPI_SWIGLU) ? n * (uint32_t)p.seg[1].row_bytes : 0u;
-            const uint8_t *srcA = (EPI == EPI_SWIGLU) ? p.seg[0].w + (size_t)first_pair * p.seg[0].row_bytes : p.seg[s].w + (size_t)first_pair * cost;
-            const uint8_t *srcB = (EPI == EPI_SWIGLU) ? p.seg[1].w + (size_t)first_pair * p.seg[1].row_bytes : nullptr;
+            const uint32_t ba = swiglu ? n * (uint32_t)p.seg[0].row_bytes : n * cost;
+            const uint32_t bb = swiglu ? n * (uint32_t)p.seg[1].row_bytes : 0u;
+            const uint8_t *srcA = swiglu ? p.seg[0].w + (size_t)first_pair * p.seg[0].row_bytes : p.seg[s].w + (size_t)first_pair * cost;
+            const uint8_t *srcB = swiglu ? p.seg[1].w + (size_t)first_pair * p.seg[1].row_bytes : nullptr;
             if (lane == 0) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the consumers' reads of the slot come first
                 mbar_expect_tx(full, ba + bb);
                 bulk_g2s(dst, srcA, ba, full);
-                if constexpr (EPI == EPI_SWIGLU) bulk_g2s(dst + ba, srcB, bb, full);
+                if (swiglu) bulk_g2s(dst + ba, srcB, bb, full);
             }
             if (!dyn) tc.advance(sh);
             else if (held > 1) { t++; held--; }
@@ -237,8 +253,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         // outputs (and the residual it reads) are touched by the previous kernels of the stream: wait for them like the consumers do
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
         unsigned long long best = 0ull;
-        finish_tiles<EPI>(p, part, smem_u32(smem + geo.meta_off), bar0, S, CG, lane, best);
-        if (EPI == EPI_PUSH) {
+        finish_tiles(p, part, smem_u32(smem + geo.meta_off), bar0, S, CG, lane, red, best);
+        if (p.epi == EPI_PUSH) {
             // All of this CTA's peer stores were issued by this warp.  Each lane fences its own stores, lane 0 then arrives on
             // a local counter with a system-scope release; the last CTA to arrive tells every rank that this rank has
             // delivered.  (One remote arrival per CTA instead was faster on 2 GPUs and slower on 4: hundreds of remote atomics on
@@ -254,7 +270,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
                 }
             }
         }
-        if (EPI == EPI_ARGMAX) {
+        if (p.epi == EPI_ARGMAX) {
 #pragma unroll
             for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
             uint32_t last = 0;
@@ -287,6 +303,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     }
 
     // ================= consumer warps =================
+    Consumer c;
+    c.ring = smem_u32(ring); c.part = part; c.meta = smem_u32(smem + geo.meta_off); c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
+    c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
+    const Act A{act_sm, p.cols, p.cols / 64};
     float4 norm_g[4];
     pack_prefetch_norm(p.norm_w, p.cols, norm_g);   // weights: fetched while the previous kernel is still running
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -297,15 +317,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         named_barrier(1, PACK_THREADS);
         rd = PackReduce{p.reduce_src, p.tp, p.x_out};
     }
-    pack_activation(act_sm, p.cols, p.x, p.norm_w, p.eps, red, norm_g, rd, p.cols / 64);
-    const Act A{act_sm, p.cols, p.cols / 64};
-
-    if ((uint32_t)warp < active) {
-        Consumer c;
-        c.ring = smem_u32(ring); c.part = part; c.meta = smem_u32(smem + geo.meta_off); c.bar0 = bar0; c.S = S; c.stage_bytes = geo.stage_bytes;
-        c.CG = CG; c.RG = RG; c.cg = warp % CG; c.rg = warp / CG; c.u = c.cg * 32 + lane; c.has_unit = c.u < units; c.lane = lane;
-        consume_tiles<EPI, QT>(p, c, A);
-    }
+    pack_stream(act_sm, p.cols, p.x, p.norm_w, red, bar0 + 8 * (3 * S), norm_g, rd, p.cols / 64);
+    if ((uint32_t)warp < active) consume_tiles<QT>(p, c, A);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -323,11 +336,11 @@ bool gemv_stream_eligible(const GemvParams &p) {
     return true;
 }
 
-template <uint32_t EPI, uint32_t QT>
+template <uint32_t QT>
 static int32_t launch_stream_inst(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
-        IB_CHECK_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<EPI, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM_BUDGET));
+        IB_CHECK_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM_BUDGET));
         attr_set[ctx->device & 15] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -340,31 +353,29 @@ static int32_t launch_stream_inst(ib_ctx *ctx, cudaStream_t stream, const GemvPa
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl ? 1 : 0;
-    IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<EPI, QT>, p, geo));
+    IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<QT>, p, geo));
     ctx->launches++;
     return IB_OK;
 }
 
-template <uint32_t EPI>
-static int32_t launch_stream_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
+// Which instance serves a launch: the one of its format; launches that mix Q4_K and Q6_K segments - or that ask for it
+// (`pair_instance`: the launches of a Q4_K_M token graph, so that all of them run the same code) - the two-format one.
+static int32_t launch_stream_format(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t smem) {
     uint32_t qt = p.seg[0].qtype;
     bool only_q4_q6 = true;
     for (uint32_t s = 0; s < p.nseg; s++) {
         if (p.seg[s].qtype != qt) qt = QT_MIXED;
         only_q4_q6 = only_q4_q6 && (p.seg[s].qtype == IB_Q4_K || p.seg[s].qtype == IB_Q6_K);
     }
-    if constexpr (EPI == EPI_QKV)
-        if (qt == QT_MIXED && only_q4_q6) return launch_stream_inst<EPI, QT_Q4_Q6>(ctx, stream, p, grid, geo, smem);
+    if (only_q4_q6 && (qt == QT_MIXED || p.pair_instance)) return launch_stream_inst<QT_Q4_Q6>(ctx, stream, p, grid, geo, smem);
     switch (qt) {
-    case IB_Q4_K: return launch_stream_inst<EPI, IB_Q4_K>(ctx, stream, p, grid, geo, smem);
-    case IB_Q6_K: return launch_stream_inst<EPI, IB_Q6_K>(ctx, stream, p, grid, geo, smem);
-    case IB_Q5_K: return launch_stream_inst<EPI, IB_Q5_K>(ctx, stream, p, grid, geo, smem);
-    case IB_Q8_0: return launch_stream_inst<EPI, IB_Q8_0>(ctx, stream, p, grid, geo, smem);
-    default: return launch_stream_inst<EPI, QT_MIXED>(ctx, stream, p, grid, geo, smem);
+    case IB_Q4_K: return launch_stream_inst<IB_Q4_K>(ctx, stream, p, grid, geo, smem);
+    case IB_Q6_K: return launch_stream_inst<IB_Q6_K>(ctx, stream, p, grid, geo, smem);
+    case IB_Q5_K: return launch_stream_inst<IB_Q5_K>(ctx, stream, p, grid, geo, smem);
+    case IB_Q8_0: return launch_stream_inst<IB_Q8_0>(ctx, stream, p, grid, geo, smem);
+    default: return launch_stream_inst<QT_MIXED>(ctx, stream, p, grid, geo, smem);
     }
 }
-
-static int32_t launch_stream_switch(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t total);
 
 int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p) {
     uint32_t max_cost = 0, pairs = 0;
@@ -383,7 +394,7 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     const uint32_t units = p.cols / 64, CG = (units + 31) / 32, RG = CW / CG;
     const size_t act = (act_smem_bytes(p.cols) + 127) & ~(size_t)127;
     auto part_bytes = [](uint32_t S) { return (size_t)S * PART_STAGE_FLOATS * 4; };
-    auto bar_bytes = [](uint32_t S) { return ((size_t)3 * S * 8 + 15) & ~(size_t)15; };
+    auto bar_bytes = [](uint32_t S) { return ((size_t)(3 * S + 1) * 8 + 15) & ~(size_t)15; };
     // returns 0 if the layout does not fit, 1 if it fits, 2 if it fits and every segment's tile is whole rounds
     auto layout = [&](uint32_t max_tile_bytes, uint32_t &stage, uint32_t &S, size_t &total) {
         bool whole = true;
@@ -469,19 +480,8 @@ int32_t launch_gemv_stream(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p
     // dependent launch), so they take different pairs of a small ring; the last CTA of a launch clears its pair
     GemvParams q = p;
     q.tile_claim = ctx->stream_counters + 2 * (ctx->stream_seq++ % IB_STREAM_COUNTER_PAIRS);
-    return launch_stream_switch(ctx, stream, q, grid, geo, total);
-}
-
-static int32_t launch_stream_switch(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p, int grid, const StreamGeom &geo, size_t total) {
-    switch (p.epi) {
-    case EPI_STORE: return launch_stream_epi<EPI_STORE>(ctx, stream, p, grid, geo, total);
-    case EPI_RESIDUAL: return launch_stream_epi<EPI_RESIDUAL>(ctx, stream, p, grid, geo, total);
-    case EPI_SWIGLU: return launch_stream_epi<EPI_SWIGLU>(ctx, stream, p, grid, geo, total);
-    case EPI_QKV: return launch_stream_epi<EPI_QKV>(ctx, stream, p, grid, geo, total);
-    case EPI_ARGMAX: return launch_stream_epi<EPI_ARGMAX>(ctx, stream, p, grid, geo, total);
-    case EPI_PUSH: return launch_stream_epi<EPI_PUSH>(ctx, stream, p, grid, geo, total);
-    default: return set_error(IB_ERR_INVALID, "gemv: unknown epilogue %u", p.epi);
-    }
+    IB_REQUIRE(q.epi <= EPI_PUSH, "gemv: unknown epilogue %u", q.epi);
+    return launch_stream_format(ctx, stream, q, grid, geo, total);
 }
 
 }  // namespace ib

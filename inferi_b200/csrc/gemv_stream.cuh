@@ -153,9 +153,8 @@ __device__ __forceinline__ void make_share_rt(bool swiglu, uint32_t nseg, uint32
     sh.t2 = tile_pairs(stage_bytes, sh.c2, RG);
 }
 
-template <uint32_t EPI>
 __device__ __forceinline__ void make_share(const GemvParams &p, uint32_t stage_bytes, uint32_t RG, Share &sh) {
-    make_share_rt(EPI == EPI_SWIGLU, p.nseg, p.seg[0].rows, p.seg[1].rows, p.seg[2].rows, (uint32_t)p.seg[0].row_bytes, (uint32_t)p.seg[1].row_bytes,
+    make_share_rt(p.epi == EPI_SWIGLU, p.nseg, p.seg[0].rows, p.seg[1].rows, p.seg[2].rows, (uint32_t)p.seg[0].row_bytes, (uint32_t)p.seg[1].row_bytes,
                   (uint32_t)p.seg[2].row_bytes, stage_bytes, RG, gridDim.x, blockIdx.x, sh);
 }
 
@@ -189,7 +188,6 @@ struct UnitAct {
 //   Q6_K       : block u>>2, half i = (u>>1)&1, 16-byte half h = u&1: groups g = 0..3 at 256b + 128i + 32g + 16h
 //   Q8_0       : blocks 2u, 2u+1: columns 64u .. +63
 __device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const Act &A, UnitAct &ua) {
-    const float *SC = A.sc(), *SX = A.sx16();
     uint32_t e16[4];
     if (qtype == IB_Q6_K) {
         const uint32_t b = u >> 2, i = (u >> 1) & 1, h = u & 1, base = 16 * b + 8 * i + h;
@@ -199,20 +197,17 @@ __device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const 
 #pragma unroll
         for (int g = 0; g < 4; g++) e16[g] = 4 * u + g;
     }
-    // asm volatile loads: they must stay where they are.  As ordinary loads they are loop-invariant and the compiler
-    // hoists the copies of every format's consumer loop to one place, where they all stay live at once.
+    // 32-bit shared addresses, computed once; volatile loads: they must stay where they are (as ordinary loads they are
+    // loop-invariant and would be hoisted to one place where every format's copies stay live at once)
+    const uint32_t base = smem_u32(A.base), ls = A.lstride();
+    const uint32_t sc0 = base + 3 * ls, sx0 = sc0 + A.cols / 8;   // f32 scale per 32 columns, then f32 sum per 16 columns
 #pragma unroll
     for (int g = 0; g < 4; g++) {
+        const uint32_t at = base + 16 * A.pos(e16[g]);
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const uint32_t addr = smem_u32(A.limb(k) + A.pos(e16[g]));
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(ua.l[k][g].x), "=r"(ua.l[k][g].y), "=r"(ua.l[k][g].z), "=r"(ua.l[k][g].w)
-                         : "r"(addr)
-                         : "memory");
-        }
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.s[g]) : "r"(smem_u32(SC + (e16[g] >> 1))) : "memory");
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ua.x[g]) : "r"(smem_u32(SX + e16[g])) : "memory");
+        for (int k = 0; k < 3; k++) ua.l[k][g] = lds128(at + k * ls);
+        ua.s[g] = __uint_as_float(lds32(sc0 + 4 * (e16[g] >> 1)));
+        ua.x[g] = __uint_as_float(lds32(sx0 + 4 * e16[g]));
     }
     if (qtype == IB_Q4_K) { ua.s[2] *= (1.0f / 16.0f); ua.s[3] *= (1.0f / 16.0f); }  // high nibbles are used in place (16 q)
     if (qtype == IB_Q4_K || qtype == IB_Q5_K) {   // groups 0,1 (and 2,3) form one 32-column sub-block: one sum each
@@ -416,33 +411,98 @@ __device__ __forceinline__ float unit_dot(uint32_t qtype, uint32_t row, const La
     }
 }
 
-// Where EPI_QKV appends the k / v rows: taken from the launch parameters ...
-struct ParamCaches {
-    const GemvParams &p;
-    __device__ __forceinline__ void *k() const { return p.k_cache; }
-    __device__ __forceinline__ void *v() const { return p.v_cache; }
-};
+// -------------------------------------------------------------------------------------------------
+// Prologue of the streaming kernel, run by the 16 consumer warps: y = (x [+ the ranks' partial sums]) * w -> limb form in
+// shared memory.  The RMS factor is NOT applied here: it is one scalar for the whole vector, the GEMV is linear, so the
+// epilogue warp multiplies the finished row sums by it.  That takes the sum-of-squares reduction off the consumers'
+// critical path: every warp leaves its part of the sum in red[warp], arrives on `ss_bar` and carries on; only the
+// epilogue warp waits there.
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pack_stream(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float *red,
+                                            uint32_t ss_bar, const float4 (&g)[4], const PackReduce rd, uint32_t nq) {
+    constexpr int NT = PACK_THREADS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t nruns = cols / 16;    // cols is a multiple of 64: runs pair up inside a warp; at most 2 * NT of them (cols <= 16384)
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    const float4 *w4 = reinterpret_cast<const float4 *>(norm_w);
+    PackRegs r;
+#pragma unroll
+    for (int i = 0; i < PACK_RUNS; i++) {
+        const uint32_t run = tid + NT * i;
+#pragma unroll
+        for (int j = 0; j < 4; j++) r.x[i][j] = run < nruns ? __ldcg(x4 + 4 * run + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (rd.src) {
+#pragma unroll
+        for (int i = 0; i < PACK_RUNS; i++) {
+            const uint32_t run = tid + NT * i;
+            if (run < nruns) {
+                for (uint32_t rk = 0; rk < rd.tp; rk++) {
+                    const float4 *s4 = reinterpret_cast<const float4 *>(rd.src + (size_t)rk * cols) + 4 * run;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float4 a = __ldcg(s4 + j);
+                        r.x[i][j].x += a.x; r.x[i][j].y += a.y; r.x[i][j].z += a.z; r.x[i][j].w += a.w;
+                    }
+                }
+                if (rd.x_out && blockIdx.x == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) reinterpret_cast<float4 *>(rd.x_out)[4 * run + j] = r.x[i][j];
+                }
+            }
+        }
+    }
+    if (norm_w) {
+        // crates/inferi-shaders/src/rms_norm.rs:112-120: the sum of squares; the factor itself is applied by the epilogue warp
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PACK_RUNS; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) ss += (r.x[i][j].x * r.x[i][j].x + r.x[i][j].y * r.x[i][j].y) + (r.x[i][j].z * r.x[i][j].z + r.x[i][j].w * r.x[i][j].w);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) {
+            red[warp] = ss;
+            mbar_arrive(ss_bar);   // a release: the epilogue warp's wait sees red[warp]
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < PACK_RUNS; i++) {
+        const uint32_t run = tid + NT * i;
+        if ((uint32_t)(warp * 32 + NT * i) < nruns) {   // warp-uniform: both lanes of a 32-column group are present
+            const bool ok = run < nruns;
+            if (norm_w && ok) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 w = (i == 0) ? g[j] : __ldg(w4 + 4 * run + j);
+                    float4 &v = r.x[i][j];
+                    v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+                }
+            }
+            pack_run(r.x[i], run, cols, smem, ok, nq);
+        }
+    }
+    named_barrier(1, NT);
+}
 
 __device__ __forceinline__ float2 residual_prefetch(const float *resid, uint32_t pair) { return __ldcg(reinterpret_cast<const float2 *>(resid + 2 * pair)); }
 
-// ---- epilogue of one row pair ----
-// `caches`: where the k / v rows of EPI_QKV go; any type with k() and v() (the launch parameters, or a layer-table entry).
-// `resid_pre`: the pair's residual values (EPI_RESIDUAL), fetched by the caller ahead of the dot product so that the L2
-// round trip is off the tile's critical path (see residual_prefetch).
-template <uint32_t EPI, typename Caches>
-__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best, const Caches &caches,
-                                         float2 resid_pre) {
-    if (EPI == EPI_SWIGLU) {
+// ---- epilogue of one row pair (run by the epilogue warp only, so the kind of epilogue is a run-time switch: one kernel
+// instance per weight format serves every role in the token graph and stays in the instruction cache) ----
+// `resid_pre`: the pair's residual values (EPI_RESIDUAL), fetched by the caller ahead of the wait for the dot products.
+__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32_t pair, float a, float b, unsigned long long &best, float2 resid_pre) {
+    const uint32_t epi = p.epi;
+    if (epi == EPI_SWIGLU) {
         // crates/inferi-shaders/src/silu.rs:16-19,46-52: a = gate row, b = up row
         p.seg[0].out[pair] = b * (a / (1.0f + expf(-a)));
         return;
     }
     const uint32_t r0 = 2 * pair;
-    if (EPI == EPI_STORE) {
+    if (epi == EPI_STORE) {
         *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(a, b);
-    } else if (EPI == EPI_RESIDUAL) {
+    } else if (epi == EPI_RESIDUAL) {
         *reinterpret_cast<float2 *>(p.seg[s].out + r0) = make_float2(resid_pre.x + a, resid_pre.y + b);
-    } else if (EPI == EPI_QKV) {
+    } else if (epi == EPI_QKV) {
         if (p.bias[s]) {
             const float2 bv = __ldg(reinterpret_cast<const float2 *>(p.bias[s] + r0));
             a += bv.x;
@@ -450,7 +510,7 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
         }
         if (s < 2) {
             // crates/inferi-shaders/src/rope.rs:75-91 (adjacent pairs)
-            const float2 cs = __ldg(p.rope_cs + ((r0 % p.head_size) >> 1));   // written by an earlier kernel: read-only here, L1 may keep it
+            const float2 cs = __ldcg(p.rope_cs + ((r0 % p.head_size) >> 1));
             const float x = a, y = b;
             a = cs.x * x - cs.y * y;
             b = cs.y * x + cs.x * y;
@@ -458,19 +518,18 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
         if (s == 0) {
             *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
         } else {
-            void *cache = (s == 1) ? caches.k() : caches.v();
+            void *cache = (s == 1) ? p.k_cache : p.v_cache;
             const size_t off = (size_t)(*p.pos_ptr) * p.kv_dim + r0;
             if (p.kv_dtype == IB_KV_F16) reinterpret_cast<__half2 *>(cache)[off >> 1] = __floats2half2_rn(a, b);
             else reinterpret_cast<float2 *>(cache)[off >> 1] = make_float2(a, b);
         }
-    } else if (EPI == EPI_PUSH) {
+    } else if (epi == EPI_PUSH) {
         // row-split matrix of a tensor-parallel model: this rank's partial goes straight into every rank's memory
         for (uint32_t rk = 0; rk < p.tp; rk++) *reinterpret_cast<float2 *>(p.push_dst[rk] + r0) = make_float2(a, b);
-    } else if (EPI == EPI_ARGMAX) {
+    } else if (epi == EPI_ARGMAX) {
         if (p.seg[0].out) *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
         best = max(best, max(argmax_key(a, p.row_offset + r0), argmax_key(b, p.row_offset + r0 + 1)));
     }
 }
-
 
 }  // namespace ib

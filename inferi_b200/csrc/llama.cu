@@ -170,7 +170,11 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     const uint32_t H = c.hidden_size, L = c.num_hidden_layers;
     const CommLayout cl(H, tp);
     int32_t rc;
-    auto emit_gemv = [&](const GemvParams &p) -> int32_t { return launch_gemv(ctx, s, p); };
+    // every launch of the graph asks for the shared two-format instance where its formats allow (Q4_K_M models: all of them)
+    auto emit_gemv = [&](GemvParams p) -> int32_t {
+        p.pair_instance = 1;
+        return launch_gemv(ctx, s, p);
+    };
     auto emit_attn = [&](const AttnLaunch &a) -> int32_t { return launch_attention(ctx, s, a); };
     {
         QDesc e{m->token_embd->dev, m->token_embd->row_bytes, (uint32_t)m->token_embd->qtype, m->token_embd->layout, m->token_embd->nb};
