@@ -10,9 +10,12 @@ path) are followed by exactly K timed tokens.  One JSON line is printed by rank 
   e2e       tok/s through `ib_llama_forward` with host buffers: every step copies the token id in from pinned host
             memory, reads the next token id back and synchronises (the reference's per-token loop)
   roofline  per token (one graph launch): algorithmic bytes = every weight byte once + the KV rows read and written,
-            divided by the measured time per token; `kernels` holds the dominant GEMV launches timed alone
-  cpu_baseline  the CPU port of the reference's shader arithmetic (oracle/, lane-structured f32 GEMVs, all host threads)
-            on one 8B-shaped layer + classifier, extrapolated to 32 layers
+            divided by the measured time per token; `kernels` holds the dominant launches timed alone as replays of a
+            CUDA graph over rotating buffers
+  configs   the other benchmark configurations, each measured in the same run (single GEMVs, the 1B-architecture
+            model, long-context attention); single-GPU runs only
+  cpu_baseline  the CPU port of the reference's shader arithmetic (oracle/, lane-structured f32 GEMVs, all host threads):
+            whole tokens of the full model
 
 `--impl reference` times only that CPU port (the reference is Rust and cannot be built here).
 """
@@ -33,7 +36,7 @@ import numpy as np  # noqa: E402
 METRIC = "batch-1 decode tok/s, Llama-3-8B-arch Q4_K_M"
 UNIT = "tok/s"
 PROMPT_SEED, WEIGHT_SEED = 4002, 4001
-DRAM_TRAFFIC_RATIO = 1.0003   # dram__bytes_read+write / algorithmic bytes of the streaming GEMV (33.11 MB moved for a 33.10 MB matrix)
+DRAM_TRAFFIC_RATIO = 1.0003   # dram__bytes_read+write / algorithmic bytes of the streaming GEMV (33.12 MB moved for a 33.10 MB matrix)
 
 
 def measured_peaks():
@@ -42,6 +45,15 @@ def measured_peaks():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def host_threads() -> int:
+    """Threads the CPU arm may use: the cores this process is allowed on (torch.distributed.run exports OMP_NUM_THREADS=1,
+    which is not the size of the machine)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 class ClockSampler:
@@ -88,96 +100,220 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------------------------
-# CPU baseline: the oracle's lane-structured port of the reference shaders on the host cores
+# CPU arm: the oracle's lane-structured port of the reference shaders on the host cores, whole tokens of the full model
 # ------------------------------------------------------------------------------------------------------------------
-def cpu_baseline(cfg, tokens: int = 3, pos0: int = 384):
+def cpu_model(cfg, threads: int, max_pos: int):
+    """The full-depth model for the CPU arm.  Four distinct layers' worth of random blocks are cycled over the layers
+    (generating 4.9 GB of random blocks would take longer than the measurement; 4 x 139 MB + the 431 MB classifier
+    still exceed every host cache, so each token streams its weights from DRAM as a real checkpoint would)."""
     import oracle
     from inferi_b200 import quant
     from inferi_b200.llama2 import LAYER_MATS, Q4_K_M
 
     sh = cfg.shapes()
-    seed = 90
-    layer = {}
-    for n in LAYER_MATS:
-        seed += 1
-        layer[n] = (Q4_K_M[n], quant.random_blocks(Q4_K_M[n], *sh[n], seed=seed, scale=0.002))
-    rng = np.random.default_rng(5)
-    layer["attn_norm"] = np.ones(cfg.hidden_size, np.float32)
-    layer["ffn_norm"] = np.ones(cfg.hidden_size, np.float32)
-    # the embedding table is only indexed (one row per token): a short one keeps the sample small
-    vocab_s = 1024
-    w = {"layers": [layer], "token_embd": (Q4_K_M["token_embd"], quant.random_blocks(Q4_K_M["token_embd"], vocab_s, cfg.hidden_size, seed=77, scale=0.002)),
+    distinct = []
+    for i in range(min(4, cfg.num_hidden_layers)):
+        layer = {n: (Q4_K_M[n], quant.random_blocks(Q4_K_M[n], *sh[n], seed=90 + 16 * i + j, scale=0.002)) for j, n in enumerate(LAYER_MATS)}
+        layer["attn_norm"] = np.ones(cfg.hidden_size, np.float32)
+        layer["ffn_norm"] = np.ones(cfg.hidden_size, np.float32)
+        distinct.append(layer)
+    vocab_s = 1024   # the embedding table is only indexed (one row per token): a short one keeps the set-up small
+    w = {"layers": [distinct[l % len(distinct)] for l in range(cfg.num_hidden_layers)],
+         "token_embd": (Q4_K_M["token_embd"], quant.random_blocks(Q4_K_M["token_embd"], vocab_s, cfg.hidden_size, seed=77, scale=0.002)),
          "output": (Q4_K_M["output"], quant.random_blocks(Q4_K_M["output"], *sh["output"], seed=78, scale=0.002)),
          "output_norm": np.ones(cfg.hidden_size, np.float32)}
-    ocfg = dict(hidden=cfg.hidden_size, ffn=cfg.intermediate_size, n_layers=1, n_heads=cfg.num_attention_heads, n_kv_heads=cfg.num_key_value_heads,
-                vocab=cfg.vocab_size, max_pos=pos0 + tokens + 1, rope_theta=cfg.rope_theta, rms_eps=cfg.rms_norm_eps)
-    threads = oracle.max_threads()
+    ocfg = dict(hidden=cfg.hidden_size, ffn=cfg.intermediate_size, n_layers=cfg.num_hidden_layers, n_heads=cfg.num_attention_heads,
+                n_kv_heads=cfg.num_key_value_heads, vocab=cfg.vocab_size, max_pos=max_pos, rope_theta=cfg.rope_theta, rms_eps=cfg.rms_norm_eps)
     m = oracle.Llama(ocfg, w, kv_f16=True, nthreads=threads)
-    m.set_gemv_mode(True)
-    # fill the cache rows below pos0 with something finite: attention cost at pos0 is what is sampled
-    m.forward(1, 0, want_logits=False)
-    t_layer, t_full = [], []
-    for i in range(tokens):
-        tok = int(rng.integers(0, vocab_s))
-        t0 = time.perf_counter()
-        m.forward(tok, pos0 + i, want_logits=False)
-        t1 = time.perf_counter()
-        m.forward(tok, pos0 + i, want_logits=True)
-        t2 = time.perf_counter()
-        t_layer.append(t1 - t0)
-        t_full.append(t2 - t1)
+    m.set_gemv_mode(True)   # every GEMV through the lane-structured shader port
+    return m, vocab_s
+
+
+def cpu_tokens(cfg, steps: int, warmup: int, pos0: int = 128):
+    """Times `steps` whole tokens (after `warmup` untimed ones) of the full model on the host cores."""
+    threads = host_threads()
+    m, vocab_s = cpu_model(cfg, threads, pos0 + steps + warmup + 1)
+    rng = np.random.default_rng(5)
+    m.forward(1, 0, want_logits=False)   # something finite in the cache rows (attention cost is what matters, not its values)
+    pos = pos0
+    for _ in range(warmup):
+        m.forward(int(rng.integers(0, vocab_s)), pos, want_logits=True)
+        pos += 1
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        m.forward(int(rng.integers(0, vocab_s)), pos, want_logits=True)
+        pos += 1
+    dt = time.perf_counter() - t0
     m.close()
-    tl = min(t_layer)
-    th = max(min(t_full) - tl, 0.0)
-    per_token = cfg.num_hidden_layers * tl + th
-    return {"value": 1.0 / per_token, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"1 of {cfg.num_hidden_layers} layers + classifier at position {pos0}, best of {tokens} tokens, "
-                      f"extrapolated: {cfg.num_hidden_layers} x {tl * 1e3:.1f} ms + {th * 1e3:.1f} ms per token"}
+    return {"value": steps / dt, "unit": UNIT, "cores": threads, "kind": "port", "ms_per_step": dt / steps * 1e3,
+            "sample": f"{steps} whole tokens of the {cfg.num_hidden_layers}-layer model at positions {pos0 + warmup}..{pos - 1} after {warmup} warm-up token(s), "
+                      f"all {threads} host threads, every GEMV through the lane-structured port of the reference shaders"}
 
 
 def run_reference(args, cfg, rank):
-    """The reference arm: the CPU port timed alone (rank 0 only)."""
+    """The reference arm: the CPU port timed alone (rank 0 only), whole tokens of the full model.  A CPU token takes about a
+    second, so at most 16 timed steps and 2 warm-up steps are run whatever was asked for; the line says how many."""
     if rank != 0:
         return
-    vals = []
-    for _ in range(max(1, min(args.steps, 3))):
-        vals.append(cpu_baseline(cfg, tokens=2))
-    best = max(vals, key=lambda v: v["value"])
-    line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1e3 / best["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": workload_name(cfg), "note": "reference is Rust (no toolchain here): CPU port of its shader arithmetic, "
-                                            "all host threads, one layer + classifier sampled per step and extrapolated"},
+    steps, warmup = max(1, min(args.steps, 16)), max(1, min(args.warmup, 2))
+    best = cpu_tokens(cfg, steps, warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": workload_name(cfg), "parallelism": "host threads",
+                                            "l2": "weights per token (4.9 GB) exceed every host cache"},
             "cpu_baseline": best, "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+            "gpu_launches": 0,
+            "note": "the reference is Rust with un-vendored dependencies (no toolchain here): this arm is the CPU port of its shader arithmetic"}
     print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# single kernels: timed as replays of a CUDA graph that rotates over distinct buffers (together larger than L2)
+# ------------------------------------------------------------------------------------------------------------------
+def graph_time_us(launches, replays: int = 20):
+    """`launches`: callables that each issue one kernel on the current stream.  They are captured once, in order, into
+    a CUDA graph; the graph is replayed `replays` times between two events.  Returns microseconds per launch."""
+    import torch
+    for f in launches:      # outside the capture first: lazy allocations and function attributes happen here
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in launches:
+            f()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        g.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) * 1e3 / (replays * len(launches))
+
+
+def gemv_case(backend, qt, rows, cols, seed, copies, peak, replays=20):
+    import torch
+    from inferi_b200 import quant
+    from inferi_b200.ops import GemvQuant, GpuQuantTensor
+    mats = [GpuQuantTensor(backend, qt, rows, cols, quant.random_blocks(qt, rows, cols, seed=seed + i)) for i in range(copies)]
+    v, o = torch.randn(cols, device="cuda"), torch.empty(rows, device="cuda")
+    g = GemvQuant(backend)
+    us = graph_time_us([(lambda m=m: g.launch(o, m, v)) for m in mats] * max(1, 8 // copies), replays)
+    b = mats[0].nbytes + 4 * (rows + cols)
+    for m in mats:
+        m.close()
+    return {"shape": f"{quant.NAMES[qt]} {rows}x{cols}", "us": round(us, 2), "algorithmic_bytes": b, "gbs": round(b / us / 1e3, 1), "frac": round(b / us / 1e3 / peak, 3),
+            "timing": f"CUDA-graph replays over {copies} distinct matrices ({copies * mats[0].nbytes >> 20} MiB)"}
+
+
+def attention_case(backend, ctx_len, peak, replays=20):
+    """Long-context decode attention: 32 query / 8 kv heads of 128, f16 cache from N(0,1), one query at the last position."""
+    import torch
+    from inferi_b200.ops import AttnParams, FusedAttention
+    hs, nh, kvm = 128, 32, 4
+    kv_dim = nh // kvm * hs
+    copies = max(2, (160 << 20) // (2 * ctx_len * kv_dim * 2) + 1)    # rotate over more than L2
+    caches = [(torch.randn(ctx_len, kv_dim, device="cuda").half(), torch.randn(ctx_len, kv_dim, device="cuda").half()) for _ in range(copies)]
+    q, o = torch.randn(nh * hs, device="cuda"), torch.empty(nh * hs, device="cuda")
+    att = FusedAttention(backend)
+    p = AttnParams(ctx_len, kv_dim, kvm, nh, hs, ctx_len - 1)
+    us = graph_time_us([(lambda kc=kc, vc=vc: att.launch(p, q, kc, vc, o)) for kc, vc in caches], replays)
+    b = 2 * ctx_len * kv_dim * 2
+    return {"context": ctx_len, "us": round(us, 2), "algorithmic_bytes": b, "gbs": round(b / us / 1e3, 1), "frac": round(b / us / 1e3 / peak, 3),
+            "timing": f"CUDA-graph replays over {copies} distinct caches"}
+
+
+def config_1b(backend, peak):
+    """The Llama-3.2-1B-architecture configuration: 32 random prompt tokens through the decode path, then 256 greedy tokens."""
+    import torch
+    from inferi_b200.llama2 import LLAMA_3_2_1B, Llama2, Llama2Weights, synth_weights
+    cfg = LLAMA_3_2_1B
+    w = synth_weights(cfg, seed=3001, device="cuda")
+    dw = Llama2Weights(backend, cfg, w)
+    del w
+    model = Llama2(backend, cfg, dw, kv_f16=True)
+    prompt = np.random.default_rng(3002).integers(0, cfg.vocab_size, 32).astype(np.uint32)
+    first = model.generate(prompt, 1, start_pos=0)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    out = model.generate(first, 256, start_pos=32)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    bytes_per_token = cfg.weight_bytes() + cfg.kv_bytes_per_position(True) * (32 + 255 / 2.0 + 2)
+    gbs = bytes_per_token / (ms * 1e-3 / 256) / 1e9
+    model.close()
+    dw.close()
+    torch.cuda.empty_cache()
+    return {"workload": "Llama-3.2-1B-arch, Q4_K_M, f16 KV, 32 prompt + 256 greedy tokens", "tok_s": round(256 / (ms * 1e-3), 1), "ms_per_token": round(ms / 256, 4),
+            "algorithmic_bytes_per_token": int(bytes_per_token), "gbs": round(gbs, 1), "frac": round(gbs / peak, 3), "first_ids": out[:8].tolist()}
+
+
+def other_configs(backend, peak):
+    """BASELINE.json's other configurations, measured in the same run (single GPU)."""
+    import oracle
+    from inferi_b200 import quant
+    out = {}
+    # config 1: single Q8_0 GEMV 4096 x 4096, GPU and CPU
+    c1 = gemv_case(backend, quant.Q8_0, 4096, 4096, 1001, 8, peak)
+    blocks = quant.random_blocks(quant.Q8_0, 4096, 4096, seed=1001)
+    v = np.random.default_rng(1002).standard_normal(4096).astype(np.float32)
+    cpu = {}
+    for name, nt in (("cpu_us_1_thread", 1), ("cpu_us_all_threads", host_threads())):
+        oracle.gemv_shader(quant.Q8_0, 4096, 4096, blocks, v, nthreads=nt)
+        t0 = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            oracle.gemv_shader(quant.Q8_0, 4096, 4096, blocks, v, nthreads=nt)
+        cpu[name] = round((time.perf_counter() - t0) / reps * 1e6, 1)
+    c1.update(cpu)
+    c1["cpu_threads"] = host_threads()
+    out["1_q8_0_gemv_4096x4096"] = c1
+    # config 2: the K-quant sweep
+    out["2_kquant_gemv"] = [gemv_case(backend, quant.Q4_K, 4096, 4096, 2001, 16, peak), gemv_case(backend, quant.Q4_K, 14336, 4096, 2002, 6, peak),
+                            gemv_case(backend, quant.Q5_K, 4096, 14336, 2003, 4, peak), gemv_case(backend, quant.Q6_K, 128256, 4096, 2004, 1, peak, replays=5)]
+    # config 3: the 1B-architecture model
+    out["3_llama_3_2_1b"] = config_1b(backend, peak)
+    # config 5: long-context attention
+    out["5_long_context_attention"] = [attention_case(backend, n, peak) for n in (8192, 16384, 32768)]
+    return out
 
 
 def kernel_case(name: str):
     """A small stand-alone loop over one kernel, for `ncu` captures: a few launches, rotating over buffers that together
-    exceed L2.  Cases: gate_q4k, q_q4k, down_q6k, lmhead_q6k, q5k, q8_0, attn_8k, attn_32k."""
+    exceed L2.  Cases: gate_q4k, q_q4k, down_q6k, lmhead_q6k, q5k, q8_0, gate_up, attn_8k, attn_32k."""
     import torch
     from inferi_b200 import quant
-    from inferi_b200.ops import AttnParams, Backend, FusedAttention, GemvQuant, GpuQuantTensor
+    from inferi_b200.ops import AttnParams, Backend, FfnGateUp, FusedAttention, GemvQuant, GpuQuantTensor
     torch.cuda.set_device(0)
     backend = Backend(0)
     shapes = {"gate_q4k": (quant.Q4_K, 14336, 4096, 6), "q_q4k": (quant.Q4_K, 4096, 4096, 16), "down_q6k": (quant.Q6_K, 4096, 14336, 4),
               "lmhead_q6k": (quant.Q6_K, 128256, 4096, 1), "q5k": (quant.Q5_K, 4096, 14336, 4), "q8_0": (quant.Q8_0, 4096, 4096, 8)}
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if name in shapes:
-        qt, rows, cols, copies = shapes[name]
-        mats = [GpuQuantTensor(backend, qt, rows, cols, quant.random_blocks(qt, rows, cols, seed=10 + i)) for i in range(copies)]
+    if name in shapes or name == "gate_up":
+        qt, rows, cols, copies = shapes.get(name, (quant.Q4_K, 14336, 4096, 3))
+        mats = [GpuQuantTensor(backend, qt, rows, cols, quant.random_blocks(qt, rows, cols, seed=10 + i)) for i in range(copies * (2 if name == "gate_up" else 1))]
         v, o = torch.randn(cols, device="cuda"), torch.empty(rows, device="cuda")
-        g = GemvQuant(backend)
+        w = torch.ones(cols, device="cuda")
+        g, f = GemvQuant(backend), FfnGateUp(backend)
         n = 0
         for rep in range(3):
             if rep == 2:
                 start.record()
-            for m in mats:
-                g.launch(o, m, v)
-                n += rep == 2
+            if name == "gate_up":
+                for i in range(copies):
+                    f.launch(o, mats[2 * i], mats[2 * i + 1], v, w)
+                    n += rep == 2
+            else:
+                for m in mats:
+                    g.launch(o, m, v)
+                    n += rep == 2
         end.record()
         torch.cuda.synchronize()
-        b = mats[0].nbytes + 4 * (rows + cols)
+        b = (2 if name == "gate_up" else 1) * mats[0].nbytes + 4 * (rows + cols)
     elif name.startswith("attn_"):
         ctx = {"attn_8k": 8192, "attn_32k": 32768}[name]
         hs, nh, kvm = 128, 32, 4
@@ -215,6 +351,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (the result is then not the benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the other benchmark configurations (single GEMVs, 1B model, long-context attention)")
     ap.add_argument("--kernel-case", default="", help="run a small loop over one kernel instead of the benchmark (for ncu captures)")
     args = ap.parse_args()
     if args.kernel_case:
@@ -234,8 +371,9 @@ def main():
         return
 
     import torch
+    from inferi_b200 import quant
     from inferi_b200.llama2 import Llama2, Llama2Weights, synth_weights
-    from inferi_b200.ops import Backend, GemvQuant
+    from inferi_b200.ops import Backend, FfnGateUp, GemvQuant
 
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run); got {world}")
@@ -302,31 +440,29 @@ def main():
     e2e_tok_s = K / e2e_s
 
     # ---- roofline --------------------------------------------------------------------------------------------
-    peak, peak_src = measured_peaks()
-    peak *= world                                            # aggregate HBM bandwidth of the ranks
+    peak1, peak_src = measured_peaks()
+    peak = peak1 * world                                     # aggregate HBM bandwidth of the ranks
     avg_pos = W + (K - 1) / 2.0
     bytes_per_token = cfg.weight_bytes() + cfg.kv_bytes_per_position(True) * (avg_pos + 1) + cfg.kv_bytes_per_position(True)
     achieved = bytes_per_token / (ms * 1e-3 / K) / 1e9
     kernels = []
-    gemv = GemvQuant(backend)
-    for name, mats in () if world > 1 else (("ffn_gate Q4_K 14336x4096", [l["ffn_gate"] for l in dev_w.layers]), ("ffn_down Q6_K 4096x14336", [l["ffn_down"] for l in dev_w.layers]),
-                       ("attn_q Q4_K 4096x4096", [l["attn_q"] for l in dev_w.layers]), ("output Q6_K 128256x4096", [dev_w.output])):
-        v = torch.randn(mats[0].cols, device="cuda")
-        o = torch.empty(mats[0].rows, device="cuda")
-        reps = max(3, 96 // len(mats))
-        for m_ in mats[:4]:
-            gemv.launch(o, m_, v)
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(reps):
-            for m_ in mats:                                  # rotate over distinct buffers (> L2 in total)
-                gemv.launch(o, m_, v)
-        end.record()
-        torch.cuda.synchronize()
-        us = start.elapsed_time(end) * 1e3 / (reps * len(mats))
-        b = mats[0].nbytes + 4 * (mats[0].rows + mats[0].cols)
-        kernels.append({"kernel": f"gemv_stream_kernel {name}", "us_per_launch": round(us, 2), "algorithmic_bytes": b, "gbs": round(b / us / 1e3, 1),
-                        "frac": round(b / us / 1e3 / peak, 3)})
+    if world == 1:
+        gemv, ffn = GemvQuant(backend), FfnGateUp(backend)
+        L = dev_w.layers
+        v = torch.randn(cfg.hidden_size, device="cuda")
+        vf = torch.randn(cfg.intermediate_size, device="cuda")
+        of, oh, ov = torch.empty(cfg.intermediate_size, device="cuda"), torch.empty(cfg.hidden_size, device="cuda"), torch.empty(cfg.vocab_size, device="cuda")
+        sets = [
+            ("ffn gate+up+SwiGLU fused Q4_K 2x14336x4096", [(lambda l=l: ffn.launch(of, l["ffn_gate"], l["ffn_up"], v, l["ffn_norm"], cfg.rms_norm_eps)) for l in L[:8]],
+             2 * L[0]["ffn_gate"].nbytes + 4 * (2 * cfg.hidden_size + cfg.intermediate_size)),
+            ("ffn_down Q6_K 4096x14336", [(lambda l=l: gemv.launch(oh, l["ffn_down"], vf)) for l in L[:8]], L[0]["ffn_down"].nbytes + 4 * (cfg.hidden_size + cfg.intermediate_size)),
+            ("attn_q Q4_K 4096x4096", [(lambda l=l: gemv.launch(oh, l["attn_q"], v)) for l in L], L[0]["attn_q"].nbytes + 8 * cfg.hidden_size),
+            ("output Q6_K 128256x4096", [lambda: gemv.launch(ov, dev_w.output, v)], dev_w.output.nbytes + 4 * (cfg.hidden_size + cfg.vocab_size)),
+        ]
+        for name, fns, b in sets:
+            us = graph_time_us(fns, replays=5 if len(fns) == 1 else 10)
+            kernels.append({"kernel": f"gemv_stream_kernel {name}", "us_per_launch": round(us, 2), "algorithmic_bytes": b, "gbs": round(b / us / 1e3, 1),
+                            "frac": round(b / us / 1e3 / peak, 3), "timing": f"CUDA-graph replays over {len(fns)} distinct launches"})
 
     line = {
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
@@ -344,12 +480,19 @@ def main():
                      "frac_of_8TBs": achieved / (8000.0 * world), "kernels": kernels},
         "clocks": clocks.summary(),
         "checksum": int(np.bitwise_xor.reduce(out.astype(np.uint64))),
+        "first_ids": out[:16].tolist(),     # the same at every N: tensor-parallel runs must generate the single-GPU tokens
     }
-    if not args.no_cpu_baseline and rank == 0 and world == 1:
-        line["cpu_baseline"] = cpu_baseline(cfg)
+    model.close()
+    if rank == 0 and world == 1:
+        dev_w.close()
+        del dev_w
+        torch.cuda.empty_cache()
+        if not args.no_configs:
+            line["configs"] = other_configs(backend, peak1)
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_tokens(cfg, steps=3, warmup=1)
     if rank == 0:
         print(json.dumps(line))
-    model.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -61,6 +61,11 @@ IB_API int32_t ib_ctx_destroy(ib_ctx *ctx);
 /* Number of kernels this context has launched since creation (or since the last reset). */
 IB_API int32_t ib_ctx_launch_count(ib_ctx *ctx, uint64_t *out);
 IB_API int32_t ib_ctx_reset_launch_count(ib_ctx *ctx);
+/* Every wait inside a kernel (on a shared-memory barrier, on another rank's arrival) is bounded; a wait that gives up makes
+ * the next synchronising call return IB_ERR_TIMEOUT while the context stays usable (the reference has no such waits: its
+ * errors are `GpuBackendError`s and panics, crates/inferi/src/ops/gemv_quant.rs:113-122).  The limit, 2 s by default,
+ * applies to launches issued or recorded into a model's token graph after this call. */
+IB_API int32_t ib_ctx_set_wait_limit(ib_ctx *ctx, uint64_t nanoseconds);
 
 /* Raw device memory for callers without a CUDA runtime of their own (the reference allocates through
  * `Tensor::vector` / `TensorBuilder`, crates/inferi/src/ops/gemv_quant.rs:459-490). */
@@ -85,6 +90,12 @@ IB_API int32_t ib_qtensor_info(const ib_qtensor *qt, int32_t *qtype, uint64_t *r
 IB_API int32_t ib_gemv_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *m, const float *v_dev);
 /* The same call for host buffers: copies v in, runs the kernel, copies out back, synchronises. */
 IB_API int32_t ib_gemv_quant_host(ib_ctx *ctx, float *out_host, const ib_qtensor *m, const float *v_host);
+/* The feed-forward input half of a layer as one launch: out[r] = (up . x')[r] * silu((gate . x')[r]) with x' = RMSNorm(x) * w
+ * when `norm_w_dev` is given (x' = x when it is null).  Replaces the op sequence `rms_norm_assign`, `matmul_quant_assign`
+ * (gate), `matmul_quant_assign` (up), `silu` of crates/inferi/src/models/llama2/transformer.rs:454-464.  gate and up must have
+ * the same shape and type and meet the alignment rules of the streaming kernel. */
+IB_API int32_t ib_ffn_gate_up(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *gate, const ib_qtensor *up, const float *x_dev,
+                              const float *norm_w_dev, float eps);
 
 /* Replaces `RmsNorm::launch` (crates/inferi/src/ops/rms_norm.rs:16-69; shader
  * crates/inferi-shaders/src/rms_norm.rs:78-121): out = (x * rsqrt(mean(x^2) + eps)) * w. */
@@ -208,6 +219,12 @@ IB_API int32_t ib_llama_generate(ib_llama *model, void *stream, const uint32_t *
 #define IB_TP_HANDLE_BYTES 64
 IB_API int32_t ib_llama_tp_export(ib_llama *model, void *handle_out);
 IB_API int32_t ib_llama_tp_connect(ib_llama *model, const void *handles_by_rank);
+/* The same set-up for a host that runs all ranks in ONE process (one thread or context per GPU, peer access enabled by the
+ * host): ib_llama_tp_area gives the device pointer and size of this rank's exchange area, ib_llama_tp_connect_ptrs takes
+ * every rank's area as a device pointer valid on this model's GPU, ordered by rank (the entry of the model's own rank is
+ * ignored).  No counterpart in the reference. */
+IB_API int32_t ib_llama_tp_area(ib_llama *model, void **area_dev, uint64_t *nbytes);
+IB_API int32_t ib_llama_tp_connect_ptrs(ib_llama *model, void *const *areas_by_rank);
 
 /* Device pointer of the last forward's logits (f32[vocab / tp_size]) and of the residual stream x (f32[hidden]);
  * for parity checks (the reference exposes `Llama2State::logits`, transformer.rs:15-43). */

@@ -59,6 +59,7 @@ SIGNATURES = {
     "ib_ctx_destroy": (_i32, [_vp]),
     "ib_ctx_launch_count": (_i32, [_vp, C.POINTER(_u64)]),
     "ib_ctx_reset_launch_count": (_i32, [_vp]),
+    "ib_ctx_set_wait_limit": (_i32, [_vp, _u64]),
     "ib_malloc": (_i32, [_vp, _u64, C.POINTER(_vp)]),
     "ib_free": (_i32, [_vp, _vp]),
     "ib_memcpy_h2d": (_i32, [_vp, _vp, _vp, _vp, _u64]),
@@ -69,6 +70,7 @@ SIGNATURES = {
     "ib_qtensor_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
     "ib_gemv_quant": (_i32, [_vp, _vp, _vp, _vp, _vp]),
     "ib_gemv_quant_host": (_i32, [_vp, _vp, _vp, _vp]),
+    "ib_ffn_gate_up": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
     "ib_rms_norm": (_i32, [_vp, _vp, _vp, _vp, _vp, _u32, _f]),
     "ib_rope": (_i32, [_vp, _vp, _i32, _vp, _u32, _vp, _u32, _u32, _u32, _f]),
     "ib_silu_mul": (_i32, [_vp, _vp, _vp, _vp, _u32]),
@@ -86,6 +88,8 @@ SIGNATURES = {
     "ib_llama_state": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "ib_llama_tp_export": (_i32, [_vp, _vp]),
     "ib_llama_tp_connect": (_i32, [_vp, _vp]),
+    "ib_llama_tp_area": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_u64)]),
+    "ib_llama_tp_connect_ptrs": (_i32, [_vp, C.POINTER(_vp)]),
     "ib_gguf_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
     "ib_gguf_open_memory": (_i32, [_vp, _u64, C.POINTER(_vp)]),
     "ib_gguf_close": (_i32, [_vp]),

@@ -35,8 +35,11 @@ int32_t check_device_error(ib_ctx *ctx) {
     const uint32_t e = *(volatile uint32_t *)ctx->err_host;
     if (e == 0) return IB_OK;
     *(volatile uint32_t *)ctx->err_host = 0;
-    return set_error(IB_ERR_TIMEOUT, "a kernel gave up waiting on a shared-memory barrier (%s); results of that launch are invalid",
-                     e == 1 ? "weights never arrived" : e == 2 ? "ring stage never released" : "unknown wait");
+    static const char *const what[] = {"", "a tile of weights never arrived in shared memory", "a ring stage was never handed back to the producer",
+                                       "another rank's partial sums never arrived", "another rank's arg-max candidate never arrived",
+                                       "the consumer warps never finished a tile", "the input's sum of squares never completed",
+                                       "this rank's reduction of the partial sums never completed"};
+    return set_error(IB_ERR_TIMEOUT, "a kernel gave up waiting (%s); results of that launch are invalid", e < sizeof(what) / sizeof(what[0]) ? what[e] : "unknown wait");
 }
 
 }  // namespace ib
@@ -113,6 +116,13 @@ int32_t ib_ctx_launch_count(ib_ctx *ctx, uint64_t *out) {
 int32_t ib_ctx_reset_launch_count(ib_ctx *ctx) {
     IB_REQUIRE(ctx, "null context");
     ctx->launches = 0;
+    return IB_OK;
+}
+
+int32_t ib_ctx_set_wait_limit(ib_ctx *ctx, uint64_t nanoseconds) {
+    IB_REQUIRE(ctx, "null context");
+    IB_REQUIRE(nanoseconds >= 1000 && nanoseconds <= 600000000000ull, "ib_ctx_set_wait_limit: %llu ns is outside 1 us .. 600 s", (unsigned long long)nanoseconds);
+    ctx->wait_limit_ns = nanoseconds;
     return IB_OK;
 }
 
@@ -232,6 +242,20 @@ int32_t ib_gemv_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtenso
     GemvParams p = {};
     fill_seg(p.seg[0], m, out_dev);
     p.nseg = 1; p.cols = (uint32_t)m->cols; p.epi = EPI_STORE; p.x = v_dev;
+    return launch_gemv(ctx, (cudaStream_t)stream, p);
+}
+
+int32_t ib_ffn_gate_up(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *gate, const ib_qtensor *up, const float *x_dev, const float *norm_w_dev,
+                       float eps) {
+    IB_ENTER(ctx);
+    IB_REQUIRE(gate && up && out_dev && x_dev, "ib_ffn_gate_up: null argument");
+    IB_REQUIRE(gate->ctx->device == ctx->device && up->ctx->device == ctx->device, "ib_ffn_gate_up: tensors live on another device");
+    IB_REQUIRE(gate->rows == up->rows && gate->cols == up->cols && gate->qtype == up->qtype, "ib_ffn_gate_up: gate and up differ in shape or type");
+    IB_REQUIRE(gate->fast && up->fast, "ib_ffn_gate_up: the matrices do not meet the alignment rules of the fused kernel");
+    GemvParams p = {};
+    fill_seg(p.seg[0], gate, out_dev);
+    fill_seg(p.seg[1], up, nullptr);
+    p.nseg = 2; p.cols = (uint32_t)gate->cols; p.epi = EPI_SWIGLU; p.x = x_dev; p.norm_w = norm_w_dev; p.eps = eps;
     return launch_gemv(ctx, (cudaStream_t)stream, p);
 }
 

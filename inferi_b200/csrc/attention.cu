@@ -11,6 +11,7 @@
 // ever waits for another.  The split count is derived from the position on the device, so the same launch (and
 // the same CUDA graph node) serves every context length.
 #include "attention.cuh"
+#include "attention_gqa4.cuh"
 
 namespace ib {
 
@@ -37,7 +38,7 @@ size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits) {
 
 uint32_t attn_max_splits(const ib_ctx *ctx, const ib_attn_params &p) {
     const uint32_t n_kv = p.n_heads / p.kv_mul;
-    uint32_t s = (uint32_t)(ctx->sm_count * 4) / (n_kv ? n_kv : 1);
+    uint32_t s = (uint32_t)(ctx->sm_count * 3) / (n_kv ? n_kv : 1);   // three CTAs of either kernel fit one SM: one wave
     if (s < 1) s = 1;
     if (s > 256) s = 256;
     // the merging block stages every slice's (max, sum) in its accumulator area: 2 * splits * kv_mul floats must fit the
@@ -82,14 +83,33 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     IB_REQUIRE(a.max_splits >= 1 && a.max_splits <= 2 * p.head_size && a.max_splits <= 256, "attention: %u position slices exceed what the merge step holds (%u)",
                a.max_splits, 2 * p.head_size < 256 ? 2 * p.head_size : 256);
     AttnArgs args{p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, a.pdl};
+    const bool f16 = a.kv_dtype == IB_KV_F16;
+    // the Llama-3 shape (f16 cache, 4 query heads per kv head) has a kernel of its own
+    const bool gqa4 = f16 && p.kv_mul == 4 && (p.head_size == 64 || p.head_size == 128) && ((uintptr_t)a.q % 16) == 0 && ((uintptr_t)a.k_cache % 16) == 0 &&
+                      ((uintptr_t)a.v_cache % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && ((uintptr_t)a.scratch % 16) == 0;
     // with a host-known position only the splits that will do work are launched
     uint32_t splits = a.max_splits;
     if (!a.pos_ptr) {
-        uint32_t need = (p.pos + 1 + ATTN_MIN_PER_SPLIT - 1) / ATTN_MIN_PER_SPLIT;
+        const uint32_t min_per = gqa4 ? GQA4_MIN_PER_SPLIT : ATTN_MIN_PER_SPLIT;
+        uint32_t need = (p.pos + 1 + min_per - 1) / min_per;
         if (need < splits) splits = need;
     }
     const dim3 grid(n_kv, splits);
-    const bool f16 = a.kv_dtype == IB_KV_F16;
+    if (gqa4) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(ATTN_THREADS);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = args.pdl ? 1 : 0;
+        if (p.head_size == 128) IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, attn_gqa4_kernel<128>, args));
+        else IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, attn_gqa4_kernel<64>, args));
+        ctx->launches++;
+        return IB_OK;
+    }
     if (p.head_size == 128) return f16 ? launch_kvm<128, __half>(ctx, s, args, grid) : launch_kvm<128, float>(ctx, s, args, grid);
     if (p.head_size == 64) return f16 ? launch_kvm<64, __half>(ctx, s, args, grid) : launch_kvm<64, float>(ctx, s, args, grid);
     return set_error(IB_ERR_UNSUPPORTED, "attention: head_size=%u (supported: 64, 128)", p.head_size);

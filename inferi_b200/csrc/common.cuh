@@ -86,6 +86,8 @@ struct ib_ctx {
     // uses pair i mod IB_STREAM_COUNTER_PAIRS (only neighbouring launches overlap), its last CTA clears the pair
     uint32_t *stream_counters = nullptr;
     uint64_t stream_seq = 0;
+    // limit of every wait inside a kernel (on a shared-memory barrier, on another rank's arrival); ib_ctx_set_wait_limit
+    uint64_t wait_limit_ns = 2000000000ull;
 };
 constexpr uint32_t IB_STREAM_COUNTER_PAIRS = 16;
 
@@ -145,6 +147,7 @@ struct GemvParams {
     uint32_t pdl;                      // 1: launched with programmatic dependent launch
     uint32_t pair_instance;            // 1: run Q4_K-only / Q6_K-only launches on the two-format instance too (shared code across a token graph)
     uint32_t *err;                     // device view of the context's error word (set by launch_gemv)
+    unsigned long long wait_ns;        // how long a wait inside the kernel may last before it gives up (set by launch_gemv)
     // ---- tensor parallel (tp > 1): one-shot push all-reduce fused into epilogue and prologue ----
     uint32_t tp;                                // number of ranks; 0 or 1 = single GPU
     const uint32_t *epoch_ptr;                  // device scalar: completed token-graph launches (arrival counters only ever grow)
@@ -152,12 +155,16 @@ struct GemvParams {
     float *push_dst[IB_MAX_TP];
     uint32_t *push_flag[IB_MAX_TP];
     unsigned int *push_done;                    // local CTA arrival counter (self-resetting)
-    // prologue: x + sum over ranks of reduce_src[r][cols] once reduce_flag has reached ((*epoch) * per_epoch + use) * arrivals,
-    // arrivals = one per rank
+    // prologue: x_out = x + sum over ranks of reduce_src[r][cols] once reduce_flag has reached ((*epoch) * per_epoch + use) * arrivals
+    // (arrivals = one per rank).  The sum is formed once per rank: the CTAs share out the vector in groups of 32 columns,
+    // add their groups' count to reduce_done, and every CTA reads x_out once reduce_done has reached
+    // ((*epoch) * done_per_epoch + done_use) * (cols / 32).
     const float *reduce_src;
     const uint32_t *reduce_flag;
     uint32_t reduce_use, reduce_per_epoch, reduce_arrivals;
-    float *x_out;                               // CTA 0 stores the reduced residual stream here
+    float *x_out;                               // the reduced residual stream (the other of two buffers)
+    uint32_t *reduce_done;
+    uint32_t done_use, done_per_epoch;
     // EPI_ARGMAX with a sharded vocabulary: this rank's candidate goes to amax_dst[p] of every rank
     unsigned long long *amax_dst[IB_MAX_TP];
     uint32_t *amax_flag[IB_MAX_TP];

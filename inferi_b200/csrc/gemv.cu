@@ -547,6 +547,7 @@ static int32_t launch_epi(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p,
 int32_t launch_gemv(ib_ctx *ctx, cudaStream_t stream, const GemvParams &p_in) {
     GemvParams p = p_in;
     p.err = ctx->err_dev;
+    p.wait_ns = ctx->wait_limit_ns;
     IB_REQUIRE(p.nseg >= 1 && p.nseg <= 3, "gemv: bad segment count %u", p.nseg);
     if (gemv_stream_eligible(p)) return launch_gemv_stream(ctx, stream, p);
     if (p.tp > 1 || p.epi == EPI_PUSH)   // the cross-GPU exchange exists only in the streaming kernel

@@ -75,7 +75,7 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
     const bool swiglu = p.epi == EPI_SWIGLU;   // gate rows, then up rows, in one tile: a "pair" is gate row r + up row r
 #pragma unroll 1
     for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
-        if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1)) return;   // the error word is raised; give up on this CTA's rows
+        if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1, p.wait_ns)) return;   // the error word is raised; give up on this CTA's rows
         const uint4 tm = lds128(c.meta + 16 * st);
         const uint32_t s = tm.x, n = tm.z;
         if (n == 0) break;   // no tiles left
@@ -120,7 +120,7 @@ __device__ __forceinline__ void finish_tiles(const GemvParams &p, uint32_t part,
     const bool residual = p.epi == EPI_RESIDUAL;
 #pragma unroll 1
     for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
-        if (!mbar_wait(bar0 + 8 * st, par, p.err, 1)) return;
+        if (!mbar_wait(bar0 + 8 * st, par, p.err, 1, p.wait_ns)) return;
         const uint4 tm = lds128(meta + 16 * st);
         const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
         if (n == 0) break;
@@ -131,14 +131,14 @@ __device__ __forceinline__ void finish_tiles(const GemvParams &p, uint32_t part,
         if (!rms_known) {
             // RMSNorm factor of the input vector (crates/inferi-shaders/src/rms_norm.rs:112-120): the consumer warps left
             // their parts of the sum of squares in `red`; added in a fixed order
-            if (!mbar_wait(bar0 + 8 * (3 * S), 0, p.err, 6)) return;
+            if (!mbar_wait(bar0 + 8 * (3 * S), 0, p.err, 6, p.wait_ns)) return;
             float t = 0.f;
 #pragma unroll
             for (int w = 0; w < PACK_THREADS / 32; w++) t += red[w];
             rms = 1.0f / sqrtf(t / (float)p.cols + p.eps);
             rms_known = true;
         }
-        if (!mbar_wait(bar0 + 8 * (2 * S + st), par, p.err, 5)) return;
+        if (!mbar_wait(bar0 + 8 * (2 * S + st), par, p.err, 5, p.wait_ns)) return;
         float va = 0.f, vb = 0.f;
         if (mine) {
             const uint32_t pt = part + 4 * (st * PART_STAGE_FLOATS);
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
             uint32_t tn = 0;
             if (dyn && held == 1 && tm.z != 0 && lane == 0) tn = geo.head_tiles + atomicAdd(p.tile_claim, 1u);
             uint32_t ok = 1;
-            if (!first_round && lane == 0) ok = mbar_wait(bar0 + 8 * (S + st), par, p.err, 2) ? 1u : 0u;
+            if (!first_round && lane == 0) ok = mbar_wait(bar0 + 8 * (S + st), par, p.err, 2, p.wait_ns) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             const uint32_t s = tm.x, first_pair = tm.y, n = tm.z;
@@ -252,6 +252,28 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         // ================= epilogue warp =================
         // outputs (and the residual it reads) are touched by the previous kernels of the stream: wait for them like the consumers do
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (p.reduce_src) {
+            // Tensor parallel: the previous row-split GEMV of every rank left its partial sums in this rank's slots.  The sum
+            // (x + the partials in rank order, so every rank gets the same bits) is formed once per rank: this warp adds up
+            // the groups of 32 columns that fall to its CTA and stores them as the new residual stream; the consumer warps of
+            // all CTAs wait until every group is there.  (Each CTA adding up the whole vector for itself was N x 16 KiB of L2
+            // reads per CTA: at 8 ranks more than its share of the weights.)
+            uint32_t ok = 1;
+            if (lane == 0) ok = wait_counter(p.reduce_flag, ((*p.epoch_ptr) * p.reduce_per_epoch + p.reduce_use) * p.reduce_arrivals, p.err, 3, p.wait_ns) ? 1u : 0u;
+            __syncwarp();
+            (void)ok;   // on a time-out the error word is raised; the launch runs to its end on whatever is there
+            uint32_t cnt = 0;
+            for (uint32_t grp = blockIdx.x; grp < p.cols / 32; grp += gridDim.x) {
+                const uint32_t col = grp * 32 + lane;
+                float v = __ldcg(p.x + col);
+                for (uint32_t rk = 0; rk < p.tp; rk++) v += __ldcg(p.reduce_src + (size_t)rk * p.cols + col);
+                p.x_out[col] = v;
+                cnt++;
+            }
+            __threadfence();
+            __syncwarp();
+            if (lane == 0 && cnt) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.reduce_done), "r"(cnt) : "memory");
+        }
         unsigned long long best = 0ull;
         finish_tiles(p, part, smem_u32(smem + geo.meta_off), bar0, S, CG, lane, red, best);
         if (p.epi == EPI_PUSH) {
@@ -310,14 +332,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     float4 norm_g[4];
     pack_prefetch_norm(p.norm_w, p.cols, norm_g);   // weights: fetched while the previous kernel is still running
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-    PackReduce rd{nullptr, 0, nullptr};
     if (p.reduce_src) {
-        // every rank's partial sums of the previous row-split GEMV must have landed in this rank's slots
-        if (threadIdx.x == 0) wait_counter(p.reduce_flag, ((*p.epoch_ptr) * p.reduce_per_epoch + p.reduce_use) * p.reduce_arrivals, p.err, 3);
+        // tensor parallel: the reduced residual stream is complete once the epilogue warps of all CTAs have stored their groups
+        if (threadIdx.x == 0) wait_counter_gpu(p.reduce_done, ((*p.epoch_ptr) * p.done_per_epoch + p.done_use) * (p.cols / 32), p.err, 7, p.wait_ns);
         named_barrier(1, PACK_THREADS);
-        rd = PackReduce{p.reduce_src, p.tp, p.x_out};
     }
-    pack_stream(act_sm, p.cols, p.x, p.norm_w, red, bar0 + 8 * (3 * S), norm_g, rd, p.cols / 64);
+    pack_stream(act_sm, p.cols, p.reduce_src ? p.x_out : p.x, p.norm_w, red, bar0 + 8 * (3 * S), norm_g, p.cols / 64);
     if ((uint32_t)warp < active) consume_tiles<QT>(p, c, A);
 }
 

@@ -12,7 +12,6 @@ constexpr int CW = 16;                          // consumer warps
 constexpr int W_PRODUCER = CW, W_EPILOGUE = CW + 1;
 constexpr int STREAM_THREADS = (CW + 2) * 32;   // + 1 producer warp + 1 epilogue warp
 constexpr int PT_MAX = 16;                      // row pairs per tile
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait on an mbarrier or on a peer gives up after 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
@@ -30,19 +29,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false (and raises *err) if the phase never completes.
+// Bounded wait: returns false (and raises *err) if the phase does not complete within `limit_ns` (a context setting).
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+        if (global_ns() - t0 > limit_ns) break;
     }
     if (err) {
         *(volatile uint32_t *)err = code;   // mapped host memory: a plain store, made visible system-wide
@@ -57,13 +56,34 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ bool wait_counter(const uint32_t *flag, uint32_t target, uint32_t *err, uint32_t code) {
+__device__ __forceinline__ bool wait_counter(const uint32_t *flag, uint32_t target, uint32_t *err, uint32_t code, unsigned long long limit_ns) {
     if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         for (int i = 0; i < 64; i++)
             if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+        if (global_ns() - t0 > limit_ns) break;
+    }
+    if (err) {
+        *(volatile uint32_t *)err = code;
+        __threadfence_system();
+    }
+    return false;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// the same bounded wait on a counter that only this GPU's CTAs advance
+__device__ __forceinline__ bool wait_counter_gpu(const uint32_t *flag, uint32_t target, uint32_t *err, uint32_t code, unsigned long long limit_ns) {
+    if ((int32_t)(ld_acquire_gpu(flag) - target) >= 0) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if ((int32_t)(ld_acquire_gpu(flag) - target) >= 0) return true;
+        if (global_ns() - t0 > limit_ns) break;
     }
     if (err) {
         *(volatile uint32_t *)err = code;
@@ -412,14 +432,14 @@ __device__ __forceinline__ float unit_dot(uint32_t qtype, uint32_t row, const La
 }
 
 // -------------------------------------------------------------------------------------------------
-// Prologue of the streaming kernel, run by the 16 consumer warps: y = (x [+ the ranks' partial sums]) * w -> limb form in
+// Prologue of the streaming kernel, run by the 16 consumer warps: y = x * w -> limb form in
 // shared memory.  The RMS factor is NOT applied here: it is one scalar for the whole vector, the GEMV is linear, so the
 // epilogue warp multiplies the finished row sums by it.  That takes the sum-of-squares reduction off the consumers'
 // critical path: every warp leaves its part of the sum in red[warp], arrives on `ss_bar` and carries on; only the
 // epilogue warp waits there.
 // -------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pack_stream(uint8_t *smem, uint32_t cols, const float *__restrict__ x, const float *__restrict__ norm_w, float *red,
-                                            uint32_t ss_bar, const float4 (&g)[4], const PackReduce rd, uint32_t nq) {
+                                            uint32_t ss_bar, const float4 (&g)[4], uint32_t nq) {
     constexpr int NT = PACK_THREADS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nruns = cols / 16;    // cols is a multiple of 64: runs pair up inside a warp; at most 2 * NT of them (cols <= 16384)
@@ -431,26 +451,6 @@ __device__ __forceinline__ void pack_stream(uint8_t *smem, uint32_t cols, const 
         const uint32_t run = tid + NT * i;
 #pragma unroll
         for (int j = 0; j < 4; j++) r.x[i][j] = run < nruns ? __ldcg(x4 + 4 * run + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    if (rd.src) {
-#pragma unroll
-        for (int i = 0; i < PACK_RUNS; i++) {
-            const uint32_t run = tid + NT * i;
-            if (run < nruns) {
-                for (uint32_t rk = 0; rk < rd.tp; rk++) {
-                    const float4 *s4 = reinterpret_cast<const float4 *>(rd.src + (size_t)rk * cols) + 4 * run;
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float4 a = __ldcg(s4 + j);
-                        r.x[i][j].x += a.x; r.x[i][j].y += a.y; r.x[i][j].z += a.z; r.x[i][j].w += a.w;
-                    }
-                }
-                if (rd.x_out && blockIdx.x == 0) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) reinterpret_cast<float4 *>(rd.x_out)[4 * run + j] = r.x[i][j];
-                }
-            }
-        }
     }
     if (norm_w) {
         // crates/inferi-shaders/src/rms_norm.rs:112-120: the sum of squares; the factor itself is applied by the epilogue warp

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) begin_token_kernel(const TokenCtl *ctl, c
 // (crates/inferi-chat/src/sampler.rs:102-110, chat_llama2.rs:137-171).  With a sharded vocabulary the ranks' candidates
 // (packed value / ~index keys, pushed by the classifier kernels) are folded here, on every rank alike.
 __global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap, uint32_t *epoch, uint32_t tp, const unsigned long long *amax_slots,
-                                 const uint32_t *amax_flag, uint32_t *err, uint32_t pdl) {
+                                 const uint32_t *amax_flag, uint32_t *err, unsigned long long wait_ns, uint32_t pdl) {
     if (pdl) {
         asm volatile("griddepcontrol.launch_dependents;");
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -67,7 +67,7 @@ __global__ void end_token_kernel(TokenCtl *ctl, uint32_t *seq, uint32_t seq_cap,
                 if ((int32_t)(v - target) >= 0) break;
                 unsigned long long t1;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                if (t1 - t0 > 2000000000ull) {
+                if (t1 - t0 > wait_ns) {
                     *(volatile uint32_t *)err = 4;
                     __threadfence_system();
                     break;
@@ -116,8 +116,10 @@ struct ib_llama {
     uint8_t *comm = nullptr;
     uint8_t *comm_peer[IB_MAX_TP] = {nullptr};
     bool connected = false;
+    bool peers_mapped_by_ipc = false;    // the peers' areas were opened with cudaIpcOpenMemHandle (and are closed with the model)
     float *x_final = nullptr;            // buffer that holds the residual stream after the last layer
     unsigned int *push_done = nullptr;   // [2]
+    uint32_t *reduce_done = nullptr;     // groups of the reduced residual stream stored so far (only ever grows)
     uint32_t *epoch = nullptr;
     uint32_t *h_pinned = nullptr;  // [4 + seq_cap] staging for control block and token ids
     cudaEvent_t staged = nullptr;  // the last copy out of h_pinned has been issued and finished
@@ -193,8 +195,10 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     // order) and CTA 0 stores the sum into the other residual buffer, so the stream alternates between x and x2:
     //   qkv(l) reads cur (+ set 1 of layer l-1) ; gate/up(l) reads cur (+ set 0) ; classifier reads cur (+ set 1)
     float *cur = m->x, *other = m->x2;
+    uint32_t done_use = 0;   // running number of the reductions inside one token (2 per layer)
     auto add_reduce = [&](GemvParams &p, int set, uint32_t use) {
         if (tp <= 1) return;
+        p.reduce_done = m->reduce_done; p.done_use = ++done_use; p.done_per_epoch = 2 * L;
         p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch;
         p.reduce_src = cl.part(m->comm, set, 0, H);
         p.reduce_flag = cl.flag(m->comm, set);
@@ -281,7 +285,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         set_pdl(cfg, attr, pdl);
         IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, end_token_kernel, m->ctl, m->seq, m->seq_cap, m->epoch, (uint32_t)tp,
                                          (const unsigned long long *)(tp > 1 ? cl.amax(m->comm, 0) : nullptr),
-                                         (const uint32_t *)(tp > 1 ? cl.flag(m->comm, 2) : nullptr), ctx->err_dev, pdl));
+                                         (const uint32_t *)(tp > 1 ? cl.flag(m->comm, 2) : nullptr), ctx->err_dev, (unsigned long long)ctx->wait_limit_ns, pdl));
         ctx->launches++;
     }
     return IB_OK;
@@ -386,9 +390,9 @@ int32_t ib_llama_destroy(ib_llama *m) {
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
     if (m->staged) cudaEventDestroy(m->staged);
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
-        if (m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
+        if (m->peers_mapped_by_ipc && m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch};
+                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch, m->reduce_done};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -549,6 +553,8 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
         CU(cudaMalloc(&m->x2, sizeof(float) * c.hidden_size));
         CU(cudaMalloc(&m->push_done, 2 * sizeof(unsigned int)));
         CU(cudaMemset(m->push_done, 0, 2 * sizeof(unsigned int)));
+        CU(cudaMalloc(&m->reduce_done, sizeof(uint32_t)));
+        CU(cudaMemset(m->reduce_done, 0, sizeof(uint32_t)));
         CU(cudaDeviceSynchronize());
         *out = m;
         return IB_OK;
@@ -640,8 +646,31 @@ int32_t ib_llama_tp_connect(ib_llama *m, const void *handles) {
         cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
         if (e != cudaSuccess) return set_error(IB_ERR_COMM, "cudaIpcOpenMemHandle for rank %d failed: %s (are the GPUs NVLink/P2P peers?)", r, cudaGetErrorString(e));
         m->comm_peer[r] = (uint8_t *)ptr;
+        m->peers_mapped_by_ipc = true;
     }
     m->connected = true;
+    return finish_graph(m);
+}
+
+int32_t ib_llama_tp_area(ib_llama *m, void **area_dev, uint64_t *nbytes) {
+    IB_REQUIRE(m && area_dev && nbytes, "ib_llama_tp_area: null argument");
+    IB_REQUIRE(m->tp_size > 1 && m->comm, "ib_llama_tp_area: the model is not tensor parallel");
+    *area_dev = m->comm;
+    *nbytes = CommLayout(m->cfg.hidden_size, m->tp_size).total;
+    return IB_OK;
+}
+
+int32_t ib_llama_tp_connect_ptrs(ib_llama *m, void *const *areas) {
+    IB_REQUIRE(m && areas, "ib_llama_tp_connect_ptrs: null argument");
+    IB_REQUIRE(m->tp_size > 1 && m->comm, "ib_llama_tp_connect_ptrs: the model is not tensor parallel");
+    IB_REQUIRE(!m->connected, "ib_llama_tp_connect_ptrs: already connected");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    for (int r = 0; r < m->tp_size; r++) {
+        if (r != m->tp_rank) IB_REQUIRE(areas[r] != nullptr, "ib_llama_tp_connect_ptrs: null area for rank %d", r);
+        m->comm_peer[r] = r == m->tp_rank ? m->comm : (uint8_t *)areas[r];
+    }
+    m->connected = true;
+    m->peers_mapped_by_ipc = false;
     return finish_graph(m);
 }
 

@@ -152,6 +152,17 @@ class Llama2Weights:
             self.output = GpuQuantTensor(backend, qt, *sh["output"], data)
         self.output_norm = torch.as_tensor(weights["output_norm"]).to(dev, torch.float32).contiguous()
 
+    def close(self) -> None:
+        """Frees the device tensors (a model created from them must be closed first)."""
+        for d in self.layers:
+            for n in LAYER_MATS:
+                d[n].close()
+        self.layers = []
+        for t in (self.token_embd, self.output):
+            if t is not None:
+                t.close()
+        self.token_embd = self.output = None
+
     def to_c(self):
         arr = (LlamaLayerWeights * len(self.layers))()
         for i, d in enumerate(self.layers):
@@ -171,9 +182,11 @@ class Llama2:
     `ChatLlama2` (crates/inferi-chat/src/chat_llama2.rs:92-255)."""
 
     def __init__(self, backend: Backend, cfg: Llama2Config, weights: Llama2Weights, kv_f16: bool = True, tp_rank: int = 0, tp_size: int = 1,
-                 group=None):
+                 group=None, connect: bool = True):
         """With tp_size > 1, `weights` holds this rank's shard (tp.shard_weights) and torch.distributed must be initialised:
-        the ranks exchange the handles of their exchange areas here.  `forward` then returns this rank's slice of the logits."""
+        the ranks exchange the handles of their exchange areas here.  `forward` then returns this rank's slice of the logits.
+        `connect=False` leaves the hand-shake to the caller: a host that runs all ranks in one process calls `tp_area` on
+        every rank and then `connect_areas` with the device pointers."""
         self.backend, self.cfg, self.weights = backend, cfg, weights
         self.lib = backend.lib
         c_cfg = cfg.to_c()
@@ -183,9 +196,21 @@ class Llama2:
         self.handle = h
         self.tp_rank, self.tp_size = tp_rank, tp_size
         self.vocab_local = cfg.vocab_size // tp_size
-        if tp_size > 1:
+        if tp_size > 1 and connect:
             from . import tp
             tp.connect(self, group)      # every rank of the group must get here
+
+    def connect_areas(self, areas) -> None:
+        """Tensor-parallel set-up inside one process: `areas[r]` = device pointer of rank r's exchange area (`tp_area`), valid on
+        this model's GPU; the model's own entry is ignored."""
+        arr = (C.c_void_p * self.tp_size)(*[C.c_void_p(int(a) if a else 0) for a in areas])
+        check(self.lib.ib_llama_tp_connect_ptrs(self.handle, arr))
+
+    def tp_area(self):
+        """(device pointer, bytes) of this rank's exchange area (tensor-parallel models)."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        check(self.lib.ib_llama_tp_area(self.handle, C.byref(ptr), C.byref(n)))
+        return int(ptr.value), int(n.value)
 
     @classmethod
     def from_handle(cls, backend: Backend, cfg: Llama2Config, handle, tp_rank: int = 0, tp_size: int = 1, group=None) -> "Llama2":

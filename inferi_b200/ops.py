@@ -46,6 +46,11 @@ class Backend:
     def reset_launch_count(self) -> None:
         check(self.lib.ib_ctx_reset_launch_count(self.handle))
 
+    def set_wait_limit(self, nanoseconds: int) -> None:
+        """How long a wait inside a kernel may last before the kernel gives up and the next synchronising call returns
+        IB_ERR_TIMEOUT (default 2 s).  Applies to launches issued, and token graphs recorded, after the call."""
+        check(self.lib.ib_ctx_set_wait_limit(self.handle, int(nanoseconds)))
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.lib.ib_ctx_destroy(self.handle)
@@ -116,6 +121,20 @@ class GemvQuant:
         out = np.empty(m.rows, dtype=np.float32)
         check(self.backend.lib.ib_gemv_quant_host(self.backend.handle, out.ctypes.data_as(C.c_void_p), m.handle, v.ctypes.data_as(C.c_void_p)))
         return out
+
+
+class FfnGateUp:
+    """`rms_norm_assign` + `matmul_quant_assign` (gate) + `matmul_quant_assign` (up) + `silu` of
+    crates/inferi/src/models/llama2/transformer.rs:454-464 as one launch."""
+
+    def __init__(self, backend: Backend):
+        self.backend = backend
+
+    def launch(self, out: torch.Tensor, gate: GpuQuantTensor, up: GpuQuantTensor, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-5) -> None:
+        if x.numel() != gate.cols or out.numel() != gate.rows:
+            raise InferiError(1, f"ffn gate/up: matrices are {gate.rows}x{gate.cols} but x has {x.numel()} and out {out.numel()} elements")
+        check(self.backend.lib.ib_ffn_gate_up(self.backend.handle, _stream_ptr(), _f32_dev(out, "out"), gate.handle, up.handle, _f32_dev(x, "x"),
+                                              _f32_dev(norm_w, "norm_w") if norm_w is not None else None, float(eps)))
 
 
 @dataclass

@@ -166,3 +166,42 @@ def test_model_contract_violations(backend):
     with pytest.raises(InferiError) as e:
         Llama2(backend, TINY, Llama2Weights(backend, TINY, w2))
     assert "alignment" in str(e.value)
+
+
+def test_bounded_wait_expires_when_a_rank_never_arrives(backend):
+    """A tensor-parallel rank whose peer never delivers: every wait inside the kernels is bounded, so the forward returns
+    IB_ERR_TIMEOUT instead of hanging, the kernels have ended, and the context goes on serving other calls.
+    The "peer" is a zeroed buffer in this GPU's own memory that nobody writes to (rank 1 does not exist), and the limit of
+    the waits is set to a few milliseconds; nothing faults and no kernel is left waiting."""
+    from inferi_b200 import tp
+    from inferi_b200.ops import Backend, GemvQuant
+    be = Backend(0)
+    be.set_wait_limit(3_000_000)   # 3 ms per wait instead of the default 2 s
+    cfg = Llama2Config(512, 2048, 2, 4, 2, 512, 32, 500000.0, 1e-5)
+    recipe = {k: quant.Q4_K for k in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down", "token_embd", "output")}
+    full = synth_weights(cfg, seed=11, recipe=recipe)
+    mine = tp.shard_weights(cfg, full, 0, 2)
+    shapes = tp.shard_shapes(cfg, 2, quant.Q4_K)
+    # the exchange area of the rank that never comes: same size as ours, all zeros, never written by anyone else
+    dev_w = Llama2Weights(be, cfg, mine, shapes=shapes)
+    model = Llama2(be, cfg, dev_w, kv_f16=True, tp_rank=0, tp_size=2, connect=False)
+    _, nbytes = model.tp_area()
+    ghost = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    model.connect_areas([None, ghost.data_ptr()])
+    with pytest.raises(InferiError) as e:
+        model.forward(5, 0)
+    assert e.value.code == 5 and "gave up waiting" in e.value.message     # IB_ERR_TIMEOUT
+    torch.cuda.synchronize()                                              # the kernels have returned
+    model.close()
+    dev_w.close()
+    # the context is still usable: a GEMV through it gives the oracle's result
+    blocks = quant.random_blocks(quant.Q4_K, 64, 512, seed=3)
+    v = np.random.default_rng(4).standard_normal(512).astype(np.float32)
+    m = GpuQuantTensor(be, quant.Q4_K, 64, 512, blocks)
+    out = torch.empty(64, device="cuda")
+    GemvQuant(be).launch(out, m, torch.from_numpy(v).cuda())
+    torch.cuda.synchronize()
+    ref = oracle.gemv_ref(quant.Q4_K, 64, 512, blocks, v)
+    assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * np.abs(ref).max()
+    m.close()
+    be.close()   # every tensor and model of this context is gone by now

@@ -5,7 +5,7 @@ import torch
 
 import oracle
 from helpers import assert_close
-from inferi_b200 import ops
+from inferi_b200 import ops, quant
 from inferi_b200.ops import AttnParams, FusedAttention, InferiError, RmsNorm, RmsNormConfig, RoPE, RoPEConfig, Silu
 
 pytestmark = pytest.mark.gpu
@@ -79,6 +79,9 @@ ATTN_CASES = [
     (64, 32, 4, 0, 64), (64, 32, 4, 33, 64), (64, 32, 4, 2047, 2048), (64, 32, 4, 2048, 4096),
     (128, 32, 4, 1, 16), (128, 32, 4, 640, 1024), (128, 32, 4, 4095, 4096),
     (128, 8, 1, 100, 128), (128, 16, 2, 300, 512), (64, 16, 8, 77, 128), (128, 4, 4, 513, 1024),
+    (128, 32, 4, 31, 64), (128, 32, 4, 32, 64), (128, 32, 4, 190, 256), (64, 32, 4, 7, 16), (64, 32, 4, 255, 256),
+    # head size 64 with few kv heads and long contexts: the slice count meets its cap (2 * head_size), the merge step's staging is full
+    (64, 8, 4, 16500, 16640), (64, 16, 4, 9000, 9216), (64, 4, 1, 16384, 16400), (64, 4, 2, 8600, 8704), (128, 4, 4, 20000, 20480),
 ]
 
 
@@ -140,3 +143,24 @@ def test_attention_contract(backend):
         FusedAttention(backend).launch(AttnParams(16, 64, 1, 1, 64, 16), z, kc, kc, torch.zeros(64, device="cuda"))
     with pytest.raises(InferiError):   # mixed cache types
         FusedAttention(backend).launch(AttnParams(16, 64, 1, 1, 64, 3), z, kc, kc.half(), torch.zeros(64, device="cuda"))
+
+
+@pytest.mark.parametrize("qt,rows,cols,norm", [(quant.Q4_K, 1024, 2048, True), (quant.Q4_K, 14336, 4096, True), (quant.Q6_K, 512, 4096, False), (quant.Q8_0, 256, 1024, True)])
+def test_ffn_gate_up_is_norm_two_gemvs_and_silu(backend, qt, rows, cols, norm):
+    """`ib_ffn_gate_up` against the op sequence it replaces (transformer.rs:454-464): rms_norm, two quantized GEMVs, silu."""
+    from inferi_b200.ops import FfnGateUp, GpuQuantTensor
+    rng = np.random.default_rng(rows + cols)
+    gate_b = quant.random_blocks(qt, rows, cols, seed=rows, scale=0.05)
+    up_b = quant.random_blocks(qt, rows, cols, seed=rows + 1, scale=0.05)
+    x = rng.standard_normal(cols).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    gate, up = GpuQuantTensor(backend, qt, rows, cols, gate_b), GpuQuantTensor(backend, qt, rows, cols, up_b)
+    out = torch.full((rows,), float("nan"), device="cuda")
+    FfnGateUp(backend).launch(out, gate, up, dev(x), dev(w) if norm else None, 1e-5)
+    torch.cuda.synchronize()
+    xn = oracle.rms_norm(x, w, 1e-5) if norm else x
+    h1 = oracle.gemv_ref(qt, rows, cols, gate_b, xn)
+    h2 = oracle.gemv_ref(qt, rows, cols, up_b, xn)
+    assert_close(out.cpu().numpy(), oracle.silu_mul(h1, h2), what="ffn gate/up")
+    gate.close()
+    up.close()

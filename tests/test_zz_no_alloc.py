@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from helpers import assert_close
 from inferi_b200 import _lib
 from inferi_b200.ops import AttnParams, FusedAttention
@@ -36,6 +37,9 @@ def test_static_scratch_attention_matches_allocating_entry_point(backend, hs, n_
         _lib.check(lib.ib_attention_static(stream, C.byref(p), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), kv, got.data_ptr()))
         torch.cuda.synchronize()
         assert_close(got.cpu().numpy(), want.cpu().numpy(), what=f"static-scratch attention, call {call}")
+        # and against the CPU oracle directly: the two entry points split the positions differently
+        ref = oracle.attention(q.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), n_heads=n_heads, kv_mul=kv_mul, head_size=hs, pos=pos)
+        assert_close(got.cpu().numpy(), ref, what=f"static-scratch attention vs oracle, call {call}")
 
 
 def test_static_scratch_attention_rejects_what_does_not_fit(backend):
