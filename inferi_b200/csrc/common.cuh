@@ -149,22 +149,22 @@ struct GemvParams {
     uint32_t *err;                     // device view of the context's error word (set by launch_gemv)
     unsigned long long wait_ns;        // how long a wait inside the kernel may last before it gives up (set by launch_gemv)
     // ---- tensor parallel (tp > 1): one-shot push all-reduce fused into epilogue and prologue ----
+    // Every value travels as an 8-byte word {f32 value, u32 tag}: the tag names the exchange ((*epoch) * exchanges per token
+    // + number of the exchange inside the token, never 0), 8-byte stores and loads are single transactions, so a reader that
+    // sees the tag it expects has the value - no fence and no separate flag between the ranks.
     uint32_t tp;                                // number of ranks; 0 or 1 = single GPU
-    const uint32_t *epoch_ptr;                  // device scalar: completed token-graph launches (arrival counters only ever grow)
-    // EPI_PUSH: rank p keeps this rank's partial at push_dst[p]; the last CTA adds 1 to every rank's counter
-    float *push_dst[IB_MAX_TP];
-    uint32_t *push_flag[IB_MAX_TP];
-    unsigned int *push_done;                    // local CTA arrival counter (self-resetting)
-    // prologue: x_out = x + sum over ranks of reduce_src[r][cols] once reduce_flag has reached ((*epoch) * per_epoch + use) * arrivals
-    // (arrivals = one per rank).  The sum is formed once per rank: the CTAs share out the vector in groups of 32 columns,
-    // add their groups' count to reduce_done, and every CTA reads x_out once reduce_done has reached
-    // ((*epoch) * done_per_epoch + done_use) * (cols / 32).
-    const float *reduce_src;
-    const uint32_t *reduce_flag;
-    uint32_t reduce_use, reduce_per_epoch, reduce_arrivals;
+    const uint32_t *epoch_ptr;                  // device scalar: completed token-graph launches
+    uint32_t xchg_per_epoch;                    // exchanges per token (2 per layer)
+    // EPI_PUSH: rank p keeps this rank's partial sums at push_dst[p] ([hidden] words); push_use = number of the exchange
+    uint2 *push_dst[IB_MAX_TP];
+    uint32_t push_use;
+    // prologue: x_out = x + sum over ranks of reduce_src[r][cols] (words tagged with exchange number reduce_use).  The sum is
+    // formed once per rank: the CTAs share out the vector in groups of 32 columns, add their groups' count to reduce_done,
+    // and every CTA reads x_out once reduce_done has reached ((*epoch) * xchg_per_epoch + reduce_use) * (cols / 32).
+    const uint2 *reduce_src;
+    uint32_t reduce_use;
     float *x_out;                               // the reduced residual stream (the other of two buffers)
     uint32_t *reduce_done;
-    uint32_t done_use, done_per_epoch;
     // EPI_ARGMAX with a sharded vocabulary: this rank's candidate goes to amax_dst[p] of every rank
     unsigned long long *amax_dst[IB_MAX_TP];
     uint32_t *amax_flag[IB_MAX_TP];

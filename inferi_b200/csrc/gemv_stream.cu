@@ -253,20 +253,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         // outputs (and the residual it reads) are touched by the previous kernels of the stream: wait for them like the consumers do
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (p.reduce_src) {
-            // Tensor parallel: the previous row-split GEMV of every rank left its partial sums in this rank's slots.  The sum
+            // Tensor parallel: the previous row-split GEMV of every rank leaves its partial sums in this rank's slots.  The sum
             // (x + the partials in rank order, so every rank gets the same bits) is formed once per rank: this warp adds up
             // the groups of 32 columns that fall to its CTA and stores them as the new residual stream; the consumer warps of
             // all CTAs wait until every group is there.  (Each CTA adding up the whole vector for itself was N x 16 KiB of L2
             // reads per CTA: at 8 ranks more than its share of the weights.)
-            uint32_t ok = 1;
-            if (lane == 0) ok = wait_counter(p.reduce_flag, ((*p.epoch_ptr) * p.reduce_per_epoch + p.reduce_use) * p.reduce_arrivals, p.err, 3, p.wait_ns) ? 1u : 0u;
-            __syncwarp();
-            (void)ok;   // on a time-out the error word is raised; the launch runs to its end on whatever is there
+            const uint32_t tag = (*p.epoch_ptr) * p.xchg_per_epoch + p.reduce_use;
             uint32_t cnt = 0;
             for (uint32_t grp = blockIdx.x; grp < p.cols / 32; grp += gridDim.x) {
                 const uint32_t col = grp * 32 + lane;
                 float v = __ldcg(p.x + col);
-                for (uint32_t rk = 0; rk < p.tp; rk++) v += __ldcg(p.reduce_src + (size_t)rk * p.cols + col);
+                // on a time-out the error word is raised and the launch runs to its end on whatever is there
+                for (uint32_t rk = 0; rk < p.tp; rk++) v += wait_tagged(p.reduce_src + (size_t)rk * p.cols + col, tag, p.err, p.wait_ns);
                 p.x_out[col] = v;
                 cnt++;
             }
@@ -276,22 +274,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
         }
         unsigned long long best = 0ull;
         finish_tiles(p, part, smem_u32(smem + geo.meta_off), bar0, S, CG, lane, red, best);
-        if (p.epi == EPI_PUSH) {
-            // All of this CTA's peer stores were issued by this warp.  Each lane fences its own stores, lane 0 then arrives on
-            // a local counter with a system-scope release; the last CTA to arrive tells every rank that this rank has
-            // delivered.  (One remote arrival per CTA instead was faster on 2 GPUs and slower on 4: hundreds of remote atomics on
-            // one word.)
-            __threadfence_system();
-            __syncwarp();
-            if (lane == 0) {
-                uint32_t before;
-                asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], %2;" : "=r"(before) : "l"(p.push_done), "r"(1u) : "memory");
-                if (before == gridDim.x - 1) {
-                    *p.push_done = 0u;   // next used by a later kernel
-                    for (uint32_t rk = 0; rk < p.tp; rk++) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[rk]), "r"(1u) : "memory");
-                }
-            }
-        }
         if (p.epi == EPI_ARGMAX) {
 #pragma unroll
             for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -334,7 +316,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.reduce_src) {
         // tensor parallel: the reduced residual stream is complete once the epilogue warps of all CTAs have stored their groups
-        if (threadIdx.x == 0) wait_counter_gpu(p.reduce_done, ((*p.epoch_ptr) * p.done_per_epoch + p.done_use) * (p.cols / 32), p.err, 7, p.wait_ns);
+        if (threadIdx.x == 0) wait_counter_gpu(p.reduce_done, ((*p.epoch_ptr) * p.xchg_per_epoch + p.reduce_use) * (p.cols / 32), p.err, 7, p.wait_ns);
         named_barrier(1, PACK_THREADS);
     }
     pack_stream(act_sm, p.cols, p.reduce_src ? p.x_out : p.x, p.norm_w, red, bar0 + 8 * (3 * S), norm_g, p.cols / 64);

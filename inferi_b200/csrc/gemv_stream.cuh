@@ -49,8 +49,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     }
     return false;
 }
-// ---- cross-GPU arrival counters (tensor parallel).  Counters only grow; a rank waits until its own counter has
-// reached the value that the current use implies.  The wait is bounded like every other wait here. ----
+// ---- waits on words that another GPU (or another CTA) writes.  Counters only grow; a reader waits until the counter has
+// reached the value that the current use implies.  Bounded like every other wait here. ----
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -69,6 +69,27 @@ __device__ __forceinline__ bool wait_counter(const uint32_t *flag, uint32_t targ
         __threadfence_system();
     }
     return false;
+}
+
+// A tagged word of the tensor-parallel exchange: waits (bounded) until the word carries `tag`, returns its value.
+__device__ __forceinline__ float wait_tagged(const uint2 *w, uint32_t tag, uint32_t *err, unsigned long long limit_ns) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(w) : "memory");
+    if (v.y != tag) {
+        const unsigned long long t0 = global_ns();
+        for (;;) {
+            for (int i = 0; i < 64 && v.y != tag; i++) asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(w) : "memory");
+            if (v.y == tag) break;
+            if (global_ns() - t0 > limit_ns) {
+                if (err) {
+                    *(volatile uint32_t *)err = 3;
+                    __threadfence_system();
+                }
+                break;
+            }
+        }
+    }
+    return __uint_as_float(v.x);
 }
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
@@ -525,7 +546,10 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t s, uint32
         }
     } else if (epi == EPI_PUSH) {
         // row-split matrix of a tensor-parallel model: this rank's partial goes straight into every rank's memory
-        for (uint32_t rk = 0; rk < p.tp; rk++) *reinterpret_cast<float2 *>(p.push_dst[rk] + r0) = make_float2(a, b);
+        // ({value, tag} words: see GemvParams)
+        const uint32_t tag = (*p.epoch_ptr) * p.xchg_per_epoch + p.push_use;
+        const uint4 w = make_uint4(__float_as_uint(a), tag, __float_as_uint(b), tag);
+        for (uint32_t rk = 0; rk < p.tp; rk++) *reinterpret_cast<uint4 *>(p.push_dst[rk] + r0) = w;
     } else if (epi == EPI_ARGMAX) {
         if (p.seg[0].out) *reinterpret_cast<float2 *>(p.seg[0].out + r0) = make_float2(a, b);
         best = max(best, max(argmax_key(a, p.row_offset + r0), argmax_key(b, p.row_offset + r0 + 1)));

@@ -118,7 +118,6 @@ struct ib_llama {
     bool connected = false;
     bool peers_mapped_by_ipc = false;    // the peers' areas were opened with cudaIpcOpenMemHandle (and are closed with the model)
     float *x_final = nullptr;            // buffer that holds the residual stream after the last layer
-    unsigned int *push_done = nullptr;   // [2]
     uint32_t *reduce_done = nullptr;     // groups of the reduced residual stream stored so far (only ever grows)
     uint32_t *epoch = nullptr;
     uint32_t *h_pinned = nullptr;  // [4 + seq_cap] staging for control block and token ids
@@ -147,12 +146,12 @@ namespace ib {
 struct CommLayout {
     size_t part_bytes, amax_off, flag_off, total;
     CommLayout(uint32_t hidden, int tp) {
-        part_bytes = (size_t)tp * hidden * sizeof(float);
+        part_bytes = (size_t)tp * hidden * sizeof(uint2);   // {value, tag} words
         amax_off = 2 * part_bytes;
         flag_off = amax_off + (size_t)IB_MAX_TP * sizeof(unsigned long long);
         total = flag_off + 256;
     }
-    float *part(uint8_t *base, int set, int rank, uint32_t hidden) const { return reinterpret_cast<float *>(base + set * part_bytes) + (size_t)rank * hidden; }
+    uint2 *part(uint8_t *base, int set, int rank, uint32_t hidden) const { return reinterpret_cast<uint2 *>(base + set * part_bytes) + (size_t)rank * hidden; }
     unsigned long long *amax(uint8_t *base, int rank) const { return reinterpret_cast<unsigned long long *>(base + amax_off) + rank; }
     uint32_t *flag(uint8_t *base, int i) const { return reinterpret_cast<uint32_t *>(base + flag_off) + i; }
 };
@@ -195,25 +194,22 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     // order) and CTA 0 stores the sum into the other residual buffer, so the stream alternates between x and x2:
     //   qkv(l) reads cur (+ set 1 of layer l-1) ; gate/up(l) reads cur (+ set 0) ; classifier reads cur (+ set 1)
     float *cur = m->x, *other = m->x2;
-    uint32_t done_use = 0;   // running number of the reductions inside one token (2 per layer)
-    auto add_reduce = [&](GemvParams &p, int set, uint32_t use) {
+    // Exchanges of a token are numbered 1 .. 2L in the order they happen: o_proj of layer l is number 2l + 1 (added up by the
+    // gate/up kernel of the layer), down of layer l is number 2l + 2 (added up by the next layer's qkv kernel, or by the
+    // classifier); the number is part of the tag every exchanged word carries.
+    auto add_reduce = [&](GemvParams &p, int set, uint32_t number) {
         if (tp <= 1) return;
-        p.reduce_done = m->reduce_done; p.done_use = ++done_use; p.done_per_epoch = 2 * L;
-        p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch;
+        p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch; p.xchg_per_epoch = 2 * L;
         p.reduce_src = cl.part(m->comm, set, 0, H);
-        p.reduce_flag = cl.flag(m->comm, set);
-        p.reduce_use = use; p.reduce_per_epoch = L;
-        p.reduce_arrivals = (uint32_t)tp;
+        p.reduce_use = number;
+        p.reduce_done = m->reduce_done;
         p.x_out = other;
         float *t = cur; cur = other; other = t;
     };
-    auto add_push = [&](GemvParams &p, int set) {
-        p.epi = EPI_PUSH; p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch; p.resid = nullptr;
-        for (int r = 0; r < tp; r++) {
-            p.push_dst[r] = cl.part(m->comm_peer[r], set, rank, H);
-            p.push_flag[r] = cl.flag(m->comm_peer[r], set);
-        }
-        p.push_done = m->push_done + set;
+    auto add_push = [&](GemvParams &p, int set, uint32_t number) {
+        p.epi = EPI_PUSH; p.tp = (uint32_t)tp; p.epoch_ptr = m->epoch; p.xchg_per_epoch = 2 * L; p.resid = nullptr;
+        for (int r = 0; r < tp; r++) p.push_dst[r] = cl.part(m->comm_peer[r], set, rank, H);
+        p.push_use = number;
         p.seg[0].out = nullptr;
     };
     ib_attn_params ap{c.max_position_embeddings, m->kv_dim_l, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
@@ -228,7 +224,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         p.pos_ptr = &m->ctl->pos; p.rope_cs = m->rope_cs; p.head_size = m->head_size; p.kv_dim = m->kv_dim_l; p.kv_dtype = (uint32_t)m->kv_dtype;
         p.k_cache = m->k_cache[l]; p.v_cache = m->v_cache[l]; p.pdl = pdl;
         p.bias[0] = w.attn_q_bias_dev; p.bias[1] = w.attn_k_bias_dev; p.bias[2] = w.attn_v_bias_dev;   // transformer.rs:434-442
-        if (l > 0) add_reduce(p, 1, l);   // the down partials of layer l-1: use number l of this token
+        if (l > 0) add_reduce(p, 1, 2 * l);   // the down partials of layer l-1
         if ((rc = emit_gemv(p))) return rc;
         // attention (transformer.rs:448)
         AttnLaunch a = {};
@@ -239,20 +235,20 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         p = GemvParams{};
         fill_seg(p.seg[0], w.attn_output, cur);
         p.nseg = 1; p.cols = m->q_dim_l; p.epi = EPI_RESIDUAL; p.x = m->xb; p.resid = cur; p.pdl = pdl;
-        if (tp > 1) add_push(p, 0);
+        if (tp > 1) add_push(p, 0, 2 * l + 1);
         if ((rc = emit_gemv(p))) return rc;
         // gate/up + SwiGLU (transformer.rs:454-464)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_gate, m->hb);
         fill_seg(p.seg[1], w.ffn_up, nullptr);
         p.nseg = 2; p.cols = H; p.epi = EPI_SWIGLU; p.x = cur; p.norm_w = w.ffn_norm_dev; p.eps = c.rms_norm_eps; p.pdl = pdl;
-        add_reduce(p, 0, l + 1);          // the o_proj partials of this layer
+        add_reduce(p, 0, 2 * l + 1);      // the o_proj partials of this layer
         if ((rc = emit_gemv(p))) return rc;
         // down + residual (transformer.rs:465-468)
         p = GemvParams{};
         fill_seg(p.seg[0], w.ffn_down, cur);
         p.nseg = 1; p.cols = m->ffn_l; p.epi = EPI_RESIDUAL; p.x = m->hb; p.resid = cur; p.pdl = pdl;
-        if (tp > 1) add_push(p, 1);
+        if (tp > 1) add_push(p, 1, 2 * l + 2);
         if ((rc = emit_gemv(p))) return rc;
     }
     // classifier + greedy arg-max (transformer.rs:471-478, models/sampler.rs:54-56)
@@ -261,7 +257,7 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
     p.nseg = 1; p.cols = H; p.epi = EPI_ARGMAX; p.x = cur; p.norm_w = m->output_norm; p.eps = c.rms_norm_eps;
     p.argmax_slots = m->argmax_slots; p.argmax_counter = m->argmax_counter; p.argmax_out = &m->ctl->next; p.pdl = pdl;
     p.row_offset = (uint32_t)rank * m->vocab_l;
-    add_reduce(p, 1, L);                  // the down partials of the last layer
+    add_reduce(p, 1, 2 * L);              // the down partials of the last layer
     if (tp > 1)
         for (int r = 0; r < tp; r++) {
             p.amax_dst[r] = cl.amax(m->comm_peer[r], rank);
@@ -392,7 +388,7 @@ int32_t ib_llama_destroy(ib_llama *m) {
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
         if (m->peers_mapped_by_ipc && m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
-                    m->argmax_counter, m->x2, m->comm, m->push_done, m->epoch, m->reduce_done};
+                    m->argmax_counter, m->x2, m->comm, m->epoch, m->reduce_done};
     for (void *b : bufs)
         if (b) cudaFree(b);
     for (void *b : m->k_cache)
@@ -551,8 +547,6 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
         CU(cudaMalloc(&m->comm, cl.total));
         CU(cudaMemset(m->comm, 0, cl.total));
         CU(cudaMalloc(&m->x2, sizeof(float) * c.hidden_size));
-        CU(cudaMalloc(&m->push_done, 2 * sizeof(unsigned int)));
-        CU(cudaMemset(m->push_done, 0, 2 * sizeof(unsigned int)));
         CU(cudaMalloc(&m->reduce_done, sizeof(uint32_t)));
         CU(cudaMemset(m->reduce_done, 0, sizeof(uint32_t)));
         CU(cudaDeviceSynchronize());
