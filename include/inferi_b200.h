@@ -90,6 +90,11 @@ IB_API int32_t ib_qtensor_info(const ib_qtensor *qt, int32_t *qtype, uint64_t *r
 IB_API int32_t ib_gemv_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *m, const float *v_dev);
 /* The same call for host buffers: copies v in, runs the kernel, copies out back, synchronises. */
 IB_API int32_t ib_gemv_quant_host(ib_ctx *ctx, float *out_host, const ib_qtensor *m, const float *v_host);
+/* out[t][r] = sum_c W[r][c] * x[t][c] for n input vectors at once (row-major x [n][cols] and out [n][rows]) on the tensor
+ * cores: the building block of prompt prefill.  The reference has no batched form: it repeats `GemvQuant::launch`
+ * (crates/inferi/src/ops/gemv_quant.rs:183-341) per token.  Takes Q8_0/Q4_K/Q5_K/Q6_K matrices with rows % 128 == 0 and
+ * cols % 256 == 0 (IB_ERR_UNSUPPORTED otherwise); results agree with n GEMVs to ~1e-6 relative. */
+IB_API int32_t ib_gemm_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *m, const float *x_dev, uint32_t n);
 /* The feed-forward input half of a layer as one launch: out[r] = (up . x')[r] * silu((gate . x')[r]) with x' = RMSNorm(x) * w
  * when `norm_w_dev` is given (x' = x when it is null).  Replaces the op sequence `rms_norm_assign`, `matmul_quant_assign`
  * (gate), `matmul_quant_assign` (up), `silu` of crates/inferi/src/models/llama2/transformer.rs:454-464.  gate and up must have

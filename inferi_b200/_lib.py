@@ -70,6 +70,7 @@ SIGNATURES = {
     "ib_qtensor_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
     "ib_gemv_quant": (_i32, [_vp, _vp, _vp, _vp, _vp]),
     "ib_gemv_quant_host": (_i32, [_vp, _vp, _vp, _vp]),
+    "ib_gemm_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _u32]),
     "ib_ffn_gate_up": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
     "ib_rms_norm": (_i32, [_vp, _vp, _vp, _vp, _vp, _u32, _f]),
     "ib_rope": (_i32, [_vp, _vp, _i32, _vp, _u32, _vp, _u32, _u32, _u32, _f]),

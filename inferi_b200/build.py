@@ -12,7 +12,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libinferi_b200.so")
-SOURCES = ["api.cu", "gemv.cu", "gemv_stream.cu", "ops.cu", "attention.cu", "llama.cu", "gguf.cu", "sampler.cu", "tokenizer.cu"]
+SOURCES = ["api.cu", "gemv.cu", "gemv_stream.cu", "ops.cu", "attention.cu", "prefill.cu", "llama.cu", "gguf.cu", "sampler.cu", "tokenizer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -38,7 +38,8 @@ int32_t check_device_error(ib_ctx *ctx) {
     static const char *const what[] = {"", "a tile of weights never arrived in shared memory", "a ring stage was never handed back to the producer",
                                        "another rank's partial sums never arrived", "another rank's arg-max candidate never arrived",
                                        "the consumer warps never finished a tile", "the input's sum of squares never completed",
-                                       "this rank's reduction of the partial sums never completed"};
+                                       "this rank's reduction of the partial sums never completed", "a GEMM stage was never released by the tensor core",
+                                       "a GEMM stage was never filled", "the GEMM accumulator never completed"};
     return set_error(IB_ERR_TIMEOUT, "a kernel gave up waiting (%s); results of that launch are invalid", e < sizeof(what) / sizeof(what[0]) ? what[e] : "unknown wait");
 }
 
@@ -104,6 +105,7 @@ int32_t ib_ctx_destroy(ib_ctx *ctx) {
     if (ctx->argmax_counter) cudaFree(ctx->argmax_counter);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
     if (ctx->stream_counters) cudaFree(ctx->stream_counters);
+    if (ctx->tc_scratch) cudaFree(ctx->tc_scratch);
     delete ctx;
     return IB_OK;
 }

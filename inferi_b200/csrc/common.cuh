@@ -86,6 +86,9 @@ struct ib_ctx {
     // uses pair i mod IB_STREAM_COUNTER_PAIRS (only neighbouring launches overlap), its last CTA clears the pair
     uint32_t *stream_counters = nullptr;
     uint64_t stream_seq = 0;
+    // scratch of the tensor-core GEMM entry point (input halves + partial planes), grown on demand
+    void *tc_scratch = nullptr;
+    size_t tc_scratch_bytes = 0;
     // limit of every wait inside a kernel (on a shared-memory barrier, on another rank's arrival); ib_ctx_set_wait_limit
     uint64_t wait_limit_ns = 2000000000ull;
 };

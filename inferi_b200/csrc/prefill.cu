@@ -1,0 +1,402 @@
+// Prompt prefill: the prompt's tokens go through every matrix together, as GEMMs on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory), instead of one by one through the decode path.
+//
+// The reference has no prefill: `ChatLlama2::forward` forces the prompt through the decode path token by token
+// (crates/inferi-chat/src/chat_llama2.rs:137-155, crates/inferi-chat/src/sampler.rs:102-107), which reads every weight
+// once per prompt token.  Here the weights are read once per prompt.
+//
+// gemm_quant_tc_kernel: out^T tile = W tile (128 rows of the quantized matrix) x X^T (the tokens' input vectors).
+//  * four producer warps, one thread per weight row: dequantize 64 columns of the row per stage to f32, split the value
+//    into two f16 (w = hi + lo, exact to ~2^-22) and store both into shared memory in the K-major core-matrix layout the
+//    tensor core reads (8 rows x 16 bytes per core matrix, no swizzle); the same threads copy the tokens' inputs (already
+//    split into f16 hi / lo by the kernel that produced them) into tiles of the same layout;
+//  * one thread issues, per 16 columns, three tcgen05.mma (hi x hi, hi x lo, lo x hi; lo x lo is below f32 resolution)
+//    that accumulate in f32 in tensor memory: the result matches the f32 arithmetic of the decode path to ~1e-6;
+//  * shared-memory stages cycle through mbarriers (filled by the producers, released by tcgen05.commit);
+//  * when the K range is done the producer warps read the accumulator (tcgen05.ld: TMEM lane = weight row, column =
+//    token) and store it transposed, [token][row], coalesced over the rows.
+// Matrices with few row tiles split K over several CTAs; each writes its own partial plane and the element-wise kernel
+// that follows (RoPE + cache append, residual add, SwiGLU) adds the planes in a fixed order.
+// Every wait is bounded; a wait that gives up raises the context's error word and the kernel returns after freeing its
+// tensor memory.
+#include "prefill.cuh"
+
+namespace ib {
+
+constexpr int TC_ROWS = 128;              // weight rows per CTA = M of the MMA
+constexpr int TC_KSTAGE = 64;             // columns per stage
+constexpr int TC_STAGES = 3;
+constexpr int TC_THREADS = 5 * 32;        // 4 producer / epilogue warps + 1 MMA warp
+constexpr uint32_t TC_TILE_BYTES = TC_ROWS * TC_KSTAGE * 2;                  // one f16 tile of 128 x 64
+constexpr uint32_t TC_STAGE_BYTES = 4 * TC_TILE_BYTES;                        // W hi, W lo, X hi, X lo
+constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 + 1024;  // + barriers and TMEM address, + slack to align the tiles to 1 KiB
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long tc_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns, uint32_t *err, uint32_t code) {
+    uint32_t ok = 0;
+    const unsigned long long t0 = tc_ns();
+    for (;;) {
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (tc_ns() - t0 > limit_ns) break;
+    }
+    if (err) {
+        *(volatile uint32_t *)err = code;
+        __threadfence_system();
+    }
+    return false;
+}
+
+// Shared-memory matrix descriptor of a K-major tile without swizzle: core matrices of 8 rows x 16 bytes, `lbo` bytes
+// between core matrices that are neighbours along K, `sbo` bytes between 8-row groups.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // bits 0-13: start address / 16
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;           // bits 16-29: leading-dimension byte offset / 16
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;           // bits 32-45: stride-dimension byte offset / 16
+    d |= (uint64_t)1 << 46;                                 // bits 46-47: descriptor version of this architecture
+    return d;                                               // base offset 0, layout type 0 = no swizzle
+}
+// Instruction descriptor of kind::f16: f16 A and B (both K-major), f32 accumulator, M x N.
+__device__ __forceinline__ uint32_t tc_idesc_f16(uint32_t M, uint32_t N) {
+    return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24);   // c_format = f32; a/b format 0 = f16; no negation, no transposition
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;   // no output lane is masked off
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem), "l"(a_desc),
+        "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Element (row, k) of a 64-column K-major tile in the core-matrix layout: byte offset.  LBO = 128, SBO = 1024.
+constexpr uint32_t TC_LBO = 128, TC_SBO = (TC_KSTAGE / 8) * 128;
+__device__ __forceinline__ uint32_t tc_chunk_off(uint32_t row, uint32_t k8) { return (row >> 3) * TC_SBO + k8 * TC_LBO + (row & 7) * 16; }
+
+struct GemmTcParams {
+    QDesc w;                    // the quantized matrix, device layout
+    uint32_t rows, cols;        // rows % 128 == 0, cols % 256 == 0
+    const __half *x_hi, *x_lo;  // [n_pad][cols] row-major: the tokens' inputs split into two f16
+    uint32_t n_tokens, n_pad;   // n_pad = n_tokens rounded up to 16, <= 128; rows n_tokens .. n_pad-1 of x_* are zero
+    float *out;                 // [ksplit][n_tokens][rows] partial planes
+    uint32_t ksplit;            // gridDim.y; cols / ksplit is a multiple of 256
+    uint32_t *err;
+    unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const GemmTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES);   // full[S], empty[S], acc
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t bar0 = tc_smem_u32(bars);
+    const uint32_t row0 = blockIdx.x * TC_ROWS;
+    const uint32_t kspan = p.cols / p.ksplit, kbeg = blockIdx.y * kspan, nstage = kspan / TC_KSTAGE;
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(4 * 32));          // full: every producer thread
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (TC_STAGES + s)), "r"(1));  // empty: one tcgen05.commit
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (2 * TC_STAGES)), "r"(1));       // accumulator complete
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        // tensor memory for the 128 x n_pad f32 accumulator: 128 columns (a power of two >= 32), allocated by one warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(128u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    bool ok = true;
+
+    if (warp < 4) {
+        // ===== producers: thread = weight row (and token row) `tid` =====
+        const uint8_t *wrow = p.w.w + (size_t)(row0 + tid) * p.w.row_bytes;
+        const bool has_token = (uint32_t)tid < p.n_pad;
+        const __half *xh = p.x_hi + (size_t)(has_token ? tid : 0) * p.cols, *xl = p.x_lo + (size_t)(has_token ? tid : 0) * p.cols;
+        for (uint32_t it = 0; it < nstage && ok; it++) {
+            const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
+            if (round > 0) ok = tc_wait(bar0 + 8 * (TC_STAGES + s), (round - 1) & 1, p.wait_ns, p.err, 8);
+            if (!ok) break;
+            uint8_t *st = smem + s * TC_STAGE_BYTES;
+            const uint32_t k0 = kbeg + it * TC_KSTAGE;
+#pragma unroll 1
+            for (uint32_t k8 = 0; k8 < TC_KSTAGE / 8; k8++) {
+                __align__(16) __half hi[8], lo[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float w = dequant_at(p.w, wrow, k0 + 8 * k8 + e);
+                    hi[e] = __float2half_rn(w);
+                    lo[e] = __float2half_rn(w - __half2float(hi[e]));
+                }
+                const uint32_t off = tc_chunk_off(tid, k8);
+                *reinterpret_cast<uint4 *>(st + off) = *reinterpret_cast<const uint4 *>(hi);
+                *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = *reinterpret_cast<const uint4 *>(lo);
+                uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+                if (has_token) {
+                    a = __ldg(reinterpret_cast<const uint4 *>(xh + k0 + 8 * k8));
+                    b = __ldg(reinterpret_cast<const uint4 *>(xl + k0 + 8 * k8));
+                }
+                *reinterpret_cast<uint4 *>(st + 2 * TC_TILE_BYTES + off) = a;
+                *reinterpret_cast<uint4 *>(st + 3 * TC_TILE_BYTES + off) = b;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
+        }
+    } else if (lane == 0) {
+        // ===== MMA issue: one thread =====
+        const uint32_t idesc = tc_idesc_f16(TC_ROWS, p.n_pad);
+        for (uint32_t it = 0; it < nstage && ok; it++) {
+            const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
+            ok = tc_wait(bar0 + 8 * s, round & 1, p.wait_ns, p.err, 9);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t st = tc_smem_u32(smem + s * TC_STAGE_BYTES);
+#pragma unroll
+            for (uint32_t kk = 0; kk < TC_KSTAGE / 16; kk++) {
+                const uint32_t koff = kk * 2 * TC_LBO;   // 16 columns = two core matrices along K
+                const uint64_t w_hi = tc_smem_desc(st + koff, TC_LBO, TC_SBO), w_lo = tc_smem_desc(st + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
+                const uint64_t x_hi = tc_smem_desc(st + 2 * TC_TILE_BYTES + koff, TC_LBO, TC_SBO), x_lo = tc_smem_desc(st + 3 * TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
+                tc_mma_f16(tmem_base, w_hi, x_hi, idesc, (it | kk) != 0);
+                tc_mma_f16(tmem_base, w_hi, x_lo, idesc, 1);
+                tc_mma_f16(tmem_base, w_lo, x_hi, idesc, 1);
+            }
+            tc_commit(bar0 + 8 * (TC_STAGES + s));   // the stage is free again once these MMAs have read it
+        }
+        if (ok) tc_commit(bar0 + 8 * (2 * TC_STAGES));   // ... and the accumulator is complete when all of them are done
+    }
+
+    if (warp < 4) {
+        // ===== epilogue: TMEM lane = weight row, column = token; stored as [token][row] =====
+        if (ok) ok = tc_wait(bar0 + 8 * (2 * TC_STAGES), 0, p.wait_ns, p.err, 10);
+        ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-wide instructions
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            float *out = p.out + (size_t)blockIdx.y * p.n_tokens * p.rows + row0 + tid;
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+            for (uint32_t c0 = 0; c0 < p.n_pad; c0 += 16) {
+                uint32_t r[16];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                               "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                             : "r"(taddr + c0)
+                             : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    if (c0 + j < p.n_tokens) out[(size_t)(c0 + j) * p.rows] = __uint_as_float(r[j]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------------
+// element-wise kernels around the GEMMs (one thread per element or pair; rows = tokens)
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split_store(__half *hi, __half *lo, size_t i, float v) {
+    const __half h = __float2half_rn(v);
+    hi[i] = h;
+    lo[i] = __float2half_rn(v - __half2float(h));
+}
+
+// X[t][c] = dequantized embedding row of token t (crates/inferi/src/models/llama2/transformer.rs:367-374, chat_llama2.rs:217-220)
+__global__ void prefill_embed_kernel(QDesc embd, const uint32_t *tokens, uint32_t n, uint32_t hidden, uint32_t vocab, float *X) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n * hidden; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / hidden), c = (uint32_t)(i % hidden);
+        uint32_t tok = tokens[t];
+        if (tok >= vocab) tok = vocab - 1;
+        X[i] = dequant_at(embd, embd.w + (size_t)tok * embd.row_bytes, c);
+    }
+}
+
+// One CTA per token row: y = (x * rsqrt(mean(x^2) + eps)) * w (crates/inferi-shaders/src/rms_norm.rs:112-120; `w` null: y = x),
+// stored as the two f16 halves the GEMM reads.  Rows n .. n_pad-1 are zero-filled.
+__global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X, const float *w, float eps, uint32_t n, uint32_t cols, __half *hi, __half *lo) {
+    __shared__ float red[8];
+    const uint32_t t = blockIdx.x;
+    if (t >= n) {
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { hi[(size_t)t * cols + c] = __float2half_rn(0.f); lo[(size_t)t * cols + c] = __float2half_rn(0.f); }
+        return;
+    }
+    const float *x = X + (size_t)t * cols;
+    float rms = 1.0f;
+    if (w) {
+        float ss = 0.f;
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) ss += x[c] * x[c];
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int i = 0; i < 8; i++) tot += red[i];
+        rms = 1.0f / sqrtf(tot / (float)cols + eps);
+    }
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) split_store(hi, lo, (size_t)t * cols + c, w ? (x[c] * rms) * w[c] : x[c]);
+}
+
+__device__ __forceinline__ float plane_sum(const float *planes, uint32_t ksplit, size_t plane_elems, size_t i) {
+    float v = 0.f;
+    for (uint32_t s = 0; s < ksplit; s++) v += planes[s * plane_elems + i];   // fixed order: deterministic
+    return v;
+}
+
+// One thread per pair of neighbouring rows (the rotation acts on pairs).
+__global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
+    const size_t plane = (size_t)p.n * p.rows, pairs = plane / 2;
+    for (size_t pi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pi < pairs; pi += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = 2 * pi;
+        const uint32_t t = (uint32_t)(i / p.rows), r = (uint32_t)(i % p.rows);
+        float a = plane_sum(p.planes, p.ksplit, plane, i), b = plane_sum(p.planes, p.ksplit, plane, i + 1);
+        if (p.mode == PE_SWIGLU) {
+            // crates/inferi-shaders/src/silu.rs:16-19,46-52
+            const float ua = plane_sum(p.planes2, p.ksplit, plane, i), ub = plane_sum(p.planes2, p.ksplit, plane, i + 1);
+            split_store(p.hi, p.lo, i, ua * (a / (1.0f + expf(-a))));
+            split_store(p.hi, p.lo, i + 1, ub * (b / (1.0f + expf(-b))));
+            continue;
+        }
+        if (p.mode == PE_RESIDUAL) { p.out[i] += a; p.out[i + 1] += b; continue; }
+        if (p.mode == PE_STORE) { p.out[i] = a; p.out[i + 1] = b; continue; }
+        if (p.bias) { a += p.bias[r]; b += p.bias[r + 1]; }   // crates/inferi/src/models/llama2/transformer.rs:434-442
+        if (p.mode != PE_V) {
+            // crates/inferi-shaders/src/rope.rs:75-91 (adjacent pairs), the angle as the decode path forms it
+            float sn, cs;
+            sincosf((float)(p.pos0 + t) * p.theta[(r % p.head_size) >> 1], &sn, &cs);
+            const float x = a, y = b;
+            a = cs * x - sn * y;
+            b = sn * x + cs * y;
+        }
+        if (p.mode == PE_Q) { p.out[i] = a; p.out[i + 1] = b; continue; }
+        const size_t off = (size_t)(p.pos0 + t) * p.kv_dim + r;
+        if (p.kv_dtype == IB_KV_F16) reinterpret_cast<__half2 *>(p.cache)[off >> 1] = __floats2half2_rn(a, b);
+        else reinterpret_cast<float2 *>(p.cache)[off >> 1] = make_float2(a, b);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------------
+// K split of a matrix: enough CTAs to fill the GPU, a divisor of the number of 256-column blocks
+uint32_t prefill_ksplit(const ib_ctx *ctx, uint32_t rows, uint32_t cols) {
+    const uint32_t tiles = rows / TC_ROWS, blocks = cols / 256;
+    uint32_t want = ((uint32_t)ctx->sm_count + tiles - 1) / tiles, ks = 1;
+    if (want > 16) want = 16;
+    for (uint32_t d = 1; d <= blocks && d <= 16; d++)
+        if (blocks % d == 0) { ks = d; if (d >= want) break; }
+    return ks;
+}
+
+bool prefill_gemm_eligible(const ib_qtensor *m) {
+    return m->rows % TC_ROWS == 0 && m->cols % 256 == 0 && (m->qtype == IB_Q4_K || m->qtype == IB_Q5_K || m->qtype == IB_Q6_K || m->qtype == IB_Q8_0);
+}
+
+int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, const __half *x_hi, const __half *x_lo, uint32_t n, float *planes, uint32_t ksplit) {
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_quant_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+        attr_set[ctx->device & 15] = true;
+    }
+    GemmTcParams p;
+    p.w = QDesc{m->dev, m->row_bytes, (uint32_t)m->qtype, m->layout, m->nb};
+    p.rows = (uint32_t)m->rows; p.cols = (uint32_t)m->cols;
+    p.x_hi = x_hi; p.x_lo = x_lo; p.n_tokens = n; p.n_pad = (n + 15) & ~15u;
+    p.out = planes; p.ksplit = ksplit; p.err = ctx->err_dev; p.wait_ns = ctx->wait_limit_ns;
+    gemm_quant_tc_kernel<<<dim3(p.rows / TC_ROWS, ksplit), TC_THREADS, TC_SMEM_BYTES, s>>>(p);
+    ctx->launches++;
+    IB_CHECK_CUDA(cudaGetLastError());
+    return IB_OK;
+}
+
+int32_t launch_prefill_embed(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *embd, const uint32_t *tokens_dev, uint32_t n, uint32_t vocab, float *X) {
+    QDesc e{embd->dev, embd->row_bytes, (uint32_t)embd->qtype, embd->layout, embd->nb};
+    const uint32_t hidden = (uint32_t)embd->cols;
+    prefill_embed_kernel<<<(unsigned)(((size_t)n * hidden + 255) / 256), 256, 0, s>>>(e, tokens_dev, n, hidden, vocab, X);
+    ctx->launches++;
+    IB_CHECK_CUDA(cudaGetLastError());
+    return IB_OK;
+}
+
+int32_t launch_prefill_norm_split(ib_ctx *ctx, cudaStream_t s, const float *X, const float *w, float eps, uint32_t n, uint32_t cols, __half *hi, __half *lo) {
+    prefill_norm_split_kernel<<<(n + 15) & ~15u, 256, 0, s>>>(X, w, eps, n, cols, hi, lo);
+    ctx->launches++;
+    IB_CHECK_CUDA(cudaGetLastError());
+    return IB_OK;
+}
+
+int32_t launch_prefill_epilogue(ib_ctx *ctx, cudaStream_t s, const PrefillEpiParams &p) {
+    const size_t pairs = (size_t)p.n * p.rows / 2;
+    unsigned grid = (unsigned)((pairs + 255) / 256);
+    if (grid > 4096) grid = 4096;
+    if (p.mode == PE_SWIGLU) {
+        // the padding rows of the split product must be zero for the GEMM that follows
+        const uint32_t n_pad = (p.n + 15) & ~15u;
+        if (n_pad > p.n) {
+            IB_CHECK_CUDA(cudaMemsetAsync(p.hi + (size_t)p.n * p.rows, 0, (size_t)(n_pad - p.n) * p.rows * sizeof(__half), s));
+            IB_CHECK_CUDA(cudaMemsetAsync(p.lo + (size_t)p.n * p.rows, 0, (size_t)(n_pad - p.n) * p.rows * sizeof(__half), s));
+        }
+    }
+    prefill_epilogue_kernel<<<grid, 256, 0, s>>>(p);
+    ctx->launches++;
+    IB_CHECK_CUDA(cudaGetLastError());
+    return IB_OK;
+}
+
+}  // namespace ib
+
+using namespace ib;
+
+extern "C" int32_t ib_gemm_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *m, const float *x_dev, uint32_t n) {
+    IB_REQUIRE(ctx && m && out_dev && x_dev, "ib_gemm_quant: null argument");
+    IB_REQUIRE(m->ctx->device == ctx->device, "ib_gemm_quant: tensor lives on device %d, context on %d", m->ctx->device, ctx->device);
+    IB_REQUIRE(n >= 1, "ib_gemm_quant: no rows");
+    if (!prefill_gemm_eligible(m))
+        return set_error(IB_ERR_UNSUPPORTED, "ib_gemm_quant: %llux%llu of type %d (the tensor-core path takes Q8_0/Q4_K/Q5_K/Q6_K with rows %% 128 == 0 and cols %% 256 == 0)",
+                         (unsigned long long)m->rows, (unsigned long long)m->cols, m->qtype);
+    int prev = -1;
+    cudaGetDevice(&prev);
+    IB_REQUIRE(cudaSetDevice(ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t rows = (uint32_t)m->rows, cols = (uint32_t)m->cols, ks = prefill_ksplit(ctx, rows, cols);
+    const size_t half_bytes = (size_t)TC_ROWS * cols * sizeof(__half), plane_bytes = (size_t)ks * TC_ROWS * rows * sizeof(float);
+    const size_t need = 2 * half_bytes + plane_bytes;
+    int32_t rc = IB_OK;
+    if (need > ctx->tc_scratch_bytes) {
+        // growing the scratch: wait for work that may still use the old one
+        cudaError_t e = cudaDeviceSynchronize();
+        if (e == cudaSuccess && ctx->tc_scratch) e = cudaFree(ctx->tc_scratch);
+        ctx->tc_scratch = nullptr;
+        ctx->tc_scratch_bytes = 0;
+        if (e == cudaSuccess) e = cudaMalloc(&ctx->tc_scratch, need);
+        if (e != cudaSuccess) rc = set_error(e == cudaErrorMemoryAllocation ? IB_ERR_OOM : IB_ERR_CUDA, "ib_gemm_quant: scratch of %llu bytes: %s", (unsigned long long)need, cudaGetErrorString(e));
+        else ctx->tc_scratch_bytes = need;
+    }
+    __half *hi = reinterpret_cast<__half *>(ctx->tc_scratch), *lo = reinterpret_cast<__half *>((uint8_t *)ctx->tc_scratch + half_bytes);
+    float *planes = reinterpret_cast<float *>((uint8_t *)ctx->tc_scratch + 2 * half_bytes);
+    for (uint32_t t0 = 0; rc == IB_OK && t0 < n; t0 += TC_ROWS) {
+        const uint32_t nc = n - t0 < (uint32_t)TC_ROWS ? n - t0 : (uint32_t)TC_ROWS;
+        rc = launch_prefill_norm_split(ctx, s, x_dev + (size_t)t0 * cols, nullptr, 0.f, nc, cols, hi, lo);
+        if (rc == IB_OK) rc = launch_prefill_gemm(ctx, s, m, hi, lo, nc, planes, ks);
+        if (rc == IB_OK) {
+            PrefillEpiParams e = {};
+            e.planes = planes; e.ksplit = ks; e.n = nc; e.rows = rows; e.mode = PE_STORE; e.out = out_dev + (size_t)t0 * rows;
+            rc = launch_prefill_epilogue(ctx, s, e);
+        }
+    }
+    if (prev >= 0 && prev != ctx->device) cudaSetDevice(prev);
+    return rc;
+}

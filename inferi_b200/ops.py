@@ -123,6 +123,21 @@ class GemvQuant:
         return out
 
 
+class GemmQuant:
+    """n quantized GEMVs as one GEMM on the tensor cores (prompt prefill); no counterpart in the reference, which repeats
+    `GemvQuant::launch` per token."""
+
+    def __init__(self, backend: Backend):
+        self.backend = backend
+
+    def launch(self, out: torch.Tensor, m: GpuQuantTensor, x: torch.Tensor) -> None:
+        """out[n, rows] = x[n, cols] . m^T on the current stream."""
+        n = x.shape[0]
+        if x.dim() != 2 or x.shape[1] != m.cols or tuple(out.shape) != (n, m.rows) or not x.is_contiguous() or not out.is_contiguous():
+            raise InferiError(1, f"gemm: matrix is {m.rows}x{m.cols}, x {tuple(x.shape)}, out {tuple(out.shape)}")
+        check(self.backend.lib.ib_gemm_quant(self.backend.handle, _stream_ptr(), _f32_dev(out, "out"), m.handle, _f32_dev(x, "x"), n))
+
+
 class FfnGateUp:
     """`rms_norm_assign` + `matmul_quant_assign` (gate) + `matmul_quant_assign` (up) + `silu` of
     crates/inferi/src/models/llama2/transformer.rs:454-464 as one launch."""
