@@ -213,6 +213,17 @@ IB_API int32_t ib_llama_forward(ib_llama *model, void *stream, uint32_t token, u
 IB_API int32_t ib_llama_generate(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos,
                           uint32_t n_gen, uint32_t *out_tokens_host);
 
+/* Prompt prefill: the n prompt tokens at positions start_pos .. start_pos + n - 1 go through every matrix together, as GEMMs
+ * on the tensor cores, instead of one by one.  Fills the KV cache for those positions, leaves the logits of the last
+ * prompt position in the model state and returns the greedy token that follows the prompt (`next_token_host` may be
+ * null); decoding continues with ib_llama_generate(model, stream, &next, 1, start_pos + n, ...).
+ * The reference has no prefill - `ChatLlama2::forward` forces prompt tokens through the decode path one at a time
+ * (crates/inferi-chat/src/chat_llama2.rs:137-155, crates/inferi-chat/src/sampler.rs:102-107) - and that loop is what this call
+ * must agree with: same cache contents and logits to ~1e-5, same greedy tokens afterwards.
+ * Takes single-GPU models with an f16 cache, 4 query heads per kv head and matrices of 128-row / 256-column multiples
+ * (the Llama-3 family); IB_ERR_UNSUPPORTED otherwise, and the prompt then goes through ib_llama_generate. */
+IB_API int32_t ib_llama_prefill(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n, uint32_t start_pos, uint32_t *next_token_host);
+
 /* Tensor parallelism inside one NVLink/NVSwitch box (no counterpart in the reference, which is single-GPU): one process
  * per GPU, each creating its model with (tp_rank, tp_size > 1) and ITS SHARD of every matrix — q/k/v, gate/up and the
  * classifier split by rows (heads, FFN units, vocabulary), attn_output and ffn_down split by columns at block

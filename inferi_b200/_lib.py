@@ -88,6 +88,7 @@ SIGNATURES = {
     "ib_llama_generate": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "ib_llama_state": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "ib_llama_tp_export": (_i32, [_vp, _vp]),
+    "ib_llama_prefill": (_i32, [_vp, _vp, _vp, _u32, _u32, C.POINTER(_u32)]),
     "ib_llama_tp_connect": (_i32, [_vp, _vp]),
     "ib_llama_tp_area": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_u64)]),
     "ib_llama_tp_connect_ptrs": (_i32, [_vp, C.POINTER(_vp)]),

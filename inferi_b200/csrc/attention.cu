@@ -74,6 +74,12 @@ static int32_t launch_kvm(ib_ctx *ctx, cudaStream_t s, const AttnArgs &args, dim
     }
 }
 
+// the Llama-3 shape (f16 cache, 4 query heads per kv head, head size 64 or 128, 16-byte aligned buffers) has a kernel of its own
+bool attn_gqa4_eligible(const AttnLaunch &a) {
+    return a.kv_dtype == IB_KV_F16 && a.p.kv_mul == 4 && (a.p.head_size == 64 || a.p.head_size == 128) && ((uintptr_t)a.q % 16) == 0 &&
+           ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && ((uintptr_t)a.scratch % 16) == 0;
+}
+
 int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     const ib_attn_params &p = a.p;
     IB_REQUIRE(p.kv_mul >= 1 && p.n_heads % p.kv_mul == 0, "attention: n_heads=%u is not a multiple of kv_mul=%u", p.n_heads, p.kv_mul);
@@ -82,19 +88,19 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     IB_REQUIRE(a.pos_ptr || p.pos < p.seq_len, "attention: pos=%u outside the cache of %u rows", p.pos, p.seq_len);
     IB_REQUIRE(a.max_splits >= 1 && a.max_splits <= 2 * p.head_size && a.max_splits <= 256, "attention: %u position slices exceed what the merge step holds (%u)",
                a.max_splits, 2 * p.head_size < 256 ? 2 * p.head_size : 256);
-    AttnArgs args{p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, a.pdl};
+    AttnArgs args{p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, a.pdl, a.q_step, a.out_step, a.counter_step, a.scratch_step};
     const bool f16 = a.kv_dtype == IB_KV_F16;
-    // the Llama-3 shape (f16 cache, 4 query heads per kv head) has a kernel of its own
-    const bool gqa4 = f16 && p.kv_mul == 4 && (p.head_size == 64 || p.head_size == 128) && ((uintptr_t)a.q % 16) == 0 && ((uintptr_t)a.k_cache % 16) == 0 &&
-                      ((uintptr_t)a.v_cache % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && ((uintptr_t)a.scratch % 16) == 0;
+    const bool gqa4 = attn_gqa4_eligible(a);
+    const uint32_t nq = a.n_queries > 1 ? a.n_queries : 1;
+    IB_REQUIRE(nq == 1 || (gqa4 && !a.pos_ptr && p.pos + nq <= p.seq_len), "attention: a batched launch needs the f16 / 4-heads-per-kv-head kernel and host-known positions inside the cache");
     // with a host-known position only the splits that will do work are launched
     uint32_t splits = a.max_splits;
     if (!a.pos_ptr) {
         const uint32_t min_per = gqa4 ? GQA4_MIN_PER_SPLIT : ATTN_MIN_PER_SPLIT;
-        uint32_t need = (p.pos + 1 + min_per - 1) / min_per;
+        uint32_t need = (p.pos + nq + min_per - 1) / min_per;
         if (need < splits) splits = need;
     }
-    const dim3 grid(n_kv, splits);
+    const dim3 grid(n_kv, splits, nq);
     if (gqa4) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;

@@ -25,6 +25,10 @@ struct AttnArgs {
     unsigned int *counters;
     uint32_t max_splits;
     uint32_t pdl;
+    // Several queries in one launch (prompt prefill; gridDim.z = number of queries, only in the kernel for the Llama-3
+    // shape): query z sits at position p.pos + z, its vectors, scratch and counters `*_step` elements after query 0's.
+    uint32_t q_step, out_step, counter_step;
+    size_t scratch_step;
 };
 
 template <typename T> struct KvVec;

@@ -48,7 +48,14 @@ __device__ __forceinline__ void halve_exchange(float (&v)[N], int lane, int o) {
 }
 
 template <int HS>
-__global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnArgs a_in) {
+    // query blockIdx.z of a batched launch (prompt prefill); z = 0 and steps of 0 otherwise
+    AttnArgs a = a_in;
+    a.q += (size_t)blockIdx.z * a_in.q_step;
+    a.out += (size_t)blockIdx.z * a_in.out_step;
+    a.scratch += (size_t)blockIdx.z * a_in.scratch_step;
+    a.counters += (size_t)blockIdx.z * a_in.counter_step;
+    a.p.pos += blockIdx.z;
     constexpr int KVM = 4, EPL = 8;
     constexpr int L = HS / EPL;          // lanes per cache row
     constexpr int RPW = 32 / L;          // rows per warp step

@@ -208,7 +208,12 @@ struct AttnLaunch {
     unsigned int *counters;    // [n_kv_heads], zero before the first launch; the kernel re-zeroes them
     uint32_t max_splits;
     uint32_t pdl;
+    // batched launch (prompt prefill): n_queries > 1 queries at positions p.pos, p.pos + 1, ...; steps in elements between
+    // consecutive queries' q / out / scratch / counters.  Only the kernel for the Llama-3 shape takes it.
+    uint32_t n_queries, q_step, out_step, counter_step;
+    size_t scratch_step;
 };
+bool attn_gqa4_eligible(const AttnLaunch &a);
 size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits);
 uint32_t attn_max_splits(const ib_ctx *ctx, const ib_attn_params &p);
 int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a);

@@ -14,7 +14,7 @@
 // All of it is captured once into a CUDA graph whose kernels read the token, the position and the step from a
 // device control block, so that generation replays the same graph with no host round trip; kernels are chained
 // with programmatic dependent launch.
-#include "token.cuh"
+#include "prefill.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -132,6 +132,16 @@ struct ib_llama {
     unsigned long long *sample_keys = nullptr;
     cudaGraphExec_t graph_exec_sample = nullptr;
     uint64_t launches_per_token_sample = 0;
+    // prompt prefill (ib_llama_prefill): buffers for up to PREFILL_MAX_TOKENS tokens at a time, allocated at the first call
+    struct PrefillBuffers {
+        float *X = nullptr, *q = nullptr, *att = nullptr, *planes = nullptr, *planes2 = nullptr, *attn_scratch = nullptr;
+        __half *hi = nullptr, *lo = nullptr;
+        uint32_t *tokens = nullptr;
+        unsigned int *attn_counters = nullptr;
+        uint32_t attn_splits = 0;
+        size_t attn_scratch_step = 0;
+        bool ready = false;
+    } pf;
     // tensors and device vectors the model owns (a model loaded from a GGUF file frees its weights with itself)
     std::vector<ib_qtensor *> owned_tensors;
     std::vector<void *> owned_device;
@@ -387,6 +397,9 @@ int32_t ib_llama_destroy(ib_llama *m) {
     if (m->staged) cudaEventDestroy(m->staged);
     for (int r = 0; r < m->tp_size && r < IB_MAX_TP; r++)
         if (m->peers_mapped_by_ipc && m->comm_peer[r] && m->comm_peer[r] != m->comm) cudaIpcCloseMemHandle(m->comm_peer[r]);
+    void *pbufs[] = {m->pf.X, m->pf.q, m->pf.att, m->pf.planes, m->pf.planes2, m->pf.attn_scratch, m->pf.hi, m->pf.lo, m->pf.tokens, m->pf.attn_counters};
+    for (void *b : pbufs)
+        if (b) cudaFree(b);
     void *bufs[] = {m->x, m->xb, m->q, m->hb, m->logits, m->theta, m->rope_cs, m->ctl, m->seq, m->attn_scratch, m->attn_counters, m->argmax_slots,
                     m->argmax_counter, m->x2, m->comm, m->epoch, m->reduce_done};
     for (void *b : bufs)
@@ -701,6 +714,126 @@ int32_t ib_llama_forward(ib_llama *m, void *stream, uint32_t token, uint32_t pos
         return check_device_error(m->ctx);
     }
     return IB_OK;
+}
+
+// ---- prompt prefill on the tensor cores ----
+static int32_t prefill_prepare(ib_llama *m) {
+    if (m->pf.ready) return IB_OK;
+    const ib_llama_config &c = m->cfg;
+    const uint32_t H = c.hidden_size, F = m->ffn_l, Q = m->q_dim_l, KV = m->kv_dim_l, N = PREFILL_MAX_TOKENS;
+    const uint32_t widest = F > H ? (F > Q ? F : Q) : (H > Q ? H : Q);
+    size_t plane_elems = 0;   // largest ksplit * rows over the matrices (per token)
+    const ib_llama_layer_weights &w = m->layers[0];
+    const ib_qtensor *mats[] = {w.attn_q, w.attn_k, w.attn_v, w.attn_output, w.ffn_gate, w.ffn_up, w.ffn_down};
+    for (const ib_qtensor *t : mats) {
+        const size_t e = (size_t)prefill_ksplit(m->ctx, (uint32_t)t->rows, (uint32_t)t->cols) * t->rows;
+        if (e > plane_elems) plane_elems = e;
+    }
+    ib_attn_params ap{c.max_position_embeddings, KV, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
+    m->pf.attn_splits = 16;   // per query; the queries of a prompt fill the GPU between them
+    m->pf.attn_scratch_step = attn_scratch_bytes(ap, m->pf.attn_splits) / sizeof(float);
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.X, sizeof(float) * N * H));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.q, sizeof(float) * N * Q));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.att, sizeof(float) * N * Q));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.hi, sizeof(__half) * N * widest));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.lo, sizeof(__half) * N * widest));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.planes, sizeof(float) * N * plane_elems));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.planes2, sizeof(float) * N * plane_elems));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.tokens, sizeof(uint32_t) * N));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.attn_scratch, sizeof(float) * N * m->pf.attn_scratch_step));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.attn_counters, sizeof(unsigned int) * N * m->n_kv_l));
+    IB_CHECK_CUDA(cudaMemset(m->pf.attn_counters, 0, sizeof(unsigned int) * N * m->n_kv_l));
+    m->pf.ready = true;
+    return IB_OK;
+}
+
+int32_t ib_llama_prefill(ib_llama *m, void *stream, const uint32_t *tokens_host, uint32_t n, uint32_t start_pos, uint32_t *next_token_host) {
+    IB_REQUIRE(m && tokens_host, "ib_llama_prefill: null argument");
+    IB_REQUIRE(cudaSetDevice(m->ctx->device) == cudaSuccess, "cudaSetDevice failed");
+    IB_REQUIRE(n >= 1, "ib_llama_prefill: empty prompt");
+    const ib_llama_config &c = m->cfg;
+    IB_REQUIRE((uint64_t)start_pos + n <= c.max_position_embeddings, "ib_llama_prefill: %u positions from %u exceed the context of %u", n, start_pos, c.max_position_embeddings);
+    for (uint32_t i = 0; i < n; i++) IB_REQUIRE(tokens_host[i] < c.vocab_size, "ib_llama_prefill: token %u outside the vocabulary", tokens_host[i]);
+    ib_ctx *ctx = m->ctx;
+    // what the tensor-core path takes; everything else goes through ib_llama_generate (the prompt through the decode path)
+    if (m->tp_size > 1) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_prefill: tensor-parallel models feed their prompt through the decode path (ib_llama_generate)");
+    const uint32_t kv_mul = c.num_attention_heads / c.num_key_value_heads;
+    if (m->kv_dtype != IB_KV_F16 || kv_mul != 4)
+        return set_error(IB_ERR_UNSUPPORTED, "ib_llama_prefill: needs the f16 cache and 4 query heads per kv head (have kv_mul=%u); use ib_llama_generate", kv_mul);
+    for (const ib_llama_layer_weights &w : m->layers) {
+        const ib_qtensor *mats[] = {w.attn_q, w.attn_k, w.attn_v, w.attn_output, w.ffn_gate, w.ffn_up, w.ffn_down};
+        for (const ib_qtensor *t : mats)
+            if (!prefill_gemm_eligible(t))
+                return set_error(IB_ERR_UNSUPPORTED, "ib_llama_prefill: a %llux%llu matrix of type %d is outside the tensor-core path; use ib_llama_generate",
+                                 (unsigned long long)t->rows, (unsigned long long)t->cols, t->qtype);
+    }
+    int32_t rc = prefill_prepare(m);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t H = c.hidden_size, F = m->ffn_l, Q = m->q_dim_l, KV = m->kv_dim_l;
+    auto &B = m->pf;
+    auto gemm = [&](const ib_qtensor *w, uint32_t nc, float *planes, uint32_t &ks) -> int32_t {
+        ks = prefill_ksplit(ctx, (uint32_t)w->rows, (uint32_t)w->cols);
+        return launch_prefill_gemm(ctx, s, w, B.hi, B.lo, nc, planes, ks);
+    };
+#define PF(expr) do { if ((rc = (expr)) != IB_OK) return rc; } while (0)
+    for (uint32_t t0 = 0; t0 < n; t0 += PREFILL_MAX_TOKENS) {
+        const uint32_t nc = n - t0 < PREFILL_MAX_TOKENS ? n - t0 : PREFILL_MAX_TOKENS, pos0 = start_pos + t0;
+        IB_CHECK_CUDA(cudaMemcpyAsync(B.tokens, tokens_host + t0, sizeof(uint32_t) * nc, cudaMemcpyHostToDevice, s));
+        PF(launch_prefill_embed(ctx, s, m->token_embd, B.tokens, nc, c.vocab_size, B.X));
+        for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
+            const ib_llama_layer_weights &w = m->layers[l];
+            uint32_t ks = 1;
+            PrefillEpiParams e = {};
+            e.n = nc; e.theta = m->theta; e.head_size = m->head_size; e.pos0 = pos0; e.kv_dim = KV; e.kv_dtype = (uint32_t)m->kv_dtype;
+            // q, k, v: RMSNorm, GEMM, bias, RoPE, cache append (transformer.rs:420-445)
+            PF(launch_prefill_norm_split(ctx, s, B.X, w.attn_norm_dev, c.rms_norm_eps, nc, H, B.hi, B.lo));
+            PF(gemm(w.attn_q, nc, B.planes, ks));
+            e.planes = B.planes; e.ksplit = ks; e.rows = Q; e.mode = PE_Q; e.bias = w.attn_q_bias_dev; e.out = B.q;
+            PF(launch_prefill_epilogue(ctx, s, e));
+            PF(gemm(w.attn_k, nc, B.planes, ks));
+            e.ksplit = ks; e.rows = KV; e.mode = PE_K; e.bias = w.attn_k_bias_dev; e.cache = m->k_cache[l];
+            PF(launch_prefill_epilogue(ctx, s, e));
+            PF(gemm(w.attn_v, nc, B.planes, ks));
+            e.ksplit = ks; e.mode = PE_V; e.bias = w.attn_v_bias_dev; e.cache = m->v_cache[l];
+            PF(launch_prefill_epilogue(ctx, s, e));
+            // causal attention: query t over positions 0 .. pos0 + t (transformer.rs:448), all queries in one launch
+            AttnLaunch a = {};
+            a.p = ib_attn_params{c.max_position_embeddings, KV, kv_mul, m->n_heads_l, m->head_size, pos0};
+            a.q = B.q; a.k_cache = m->k_cache[l]; a.v_cache = m->v_cache[l]; a.kv_dtype = m->kv_dtype; a.out = B.att;
+            a.scratch = B.attn_scratch; a.counters = B.attn_counters; a.max_splits = B.attn_splits;
+            a.n_queries = nc; a.q_step = Q; a.out_step = Q; a.counter_step = m->n_kv_l; a.scratch_step = B.attn_scratch_step;
+            if (nc > 1 && !attn_gqa4_eligible(a)) return set_error(IB_ERR_UNSUPPORTED, "ib_llama_prefill: head size %u is outside the batched attention kernel; use ib_llama_generate", m->head_size);
+            PF(launch_attention(ctx, s, a));
+            // o_proj + residual (transformer.rs:450-453)
+            PF(launch_prefill_norm_split(ctx, s, B.att, nullptr, 0.f, nc, Q, B.hi, B.lo));
+            PF(gemm(w.attn_output, nc, B.planes, ks));
+            e.ksplit = ks; e.rows = H; e.mode = PE_RESIDUAL; e.bias = nullptr; e.out = B.X;
+            PF(launch_prefill_epilogue(ctx, s, e));
+            // gate, up, SwiGLU (transformer.rs:454-464)
+            PF(launch_prefill_norm_split(ctx, s, B.X, w.ffn_norm_dev, c.rms_norm_eps, nc, H, B.hi, B.lo));
+            PF(gemm(w.ffn_gate, nc, B.planes, ks));
+            PF(gemm(w.ffn_up, nc, B.planes2, ks));
+            e.planes2 = B.planes2; e.ksplit = ks; e.rows = F; e.mode = PE_SWIGLU; e.hi = B.hi; e.lo = B.lo;
+            PF(launch_prefill_epilogue(ctx, s, e));
+            // down + residual (transformer.rs:465-468)
+            PF(gemm(w.ffn_down, nc, B.planes, ks));
+            e.ksplit = ks; e.rows = H; e.mode = PE_RESIDUAL; e.out = B.X;
+            PF(launch_prefill_epilogue(ctx, s, e));
+        }
+        if (t0 + nc == n) IB_CHECK_CUDA(cudaMemcpyAsync(m->x, B.X + (size_t)(nc - 1) * H, sizeof(float) * H, cudaMemcpyDeviceToDevice, s));
+    }
+#undef PF
+    // classifier + greedy arg-max of the last prompt token (transformer.rs:471-478, models/sampler.rs:54-56): the decode kernel
+    GemvParams p = {};
+    fill_seg(p.seg[0], m->output, m->logits);
+    p.nseg = 1; p.cols = H; p.epi = EPI_ARGMAX; p.x = m->x; p.norm_w = m->output_norm; p.eps = c.rms_norm_eps;
+    p.argmax_slots = m->argmax_slots; p.argmax_counter = m->argmax_counter; p.argmax_out = &m->ctl->next; p.pair_instance = 1;
+    if ((rc = launch_gemv(ctx, s, p))) return rc;
+    m->x_final = m->x;
+    if (next_token_host) IB_CHECK_CUDA(cudaMemcpyAsync(next_token_host, &m->ctl->next, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    IB_CHECK_CUDA(cudaStreamSynchronize(s));
+    return check_device_error(ctx);
 }
 
 int32_t ib_llama_generate(ib_llama *m, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos, uint32_t n_gen,

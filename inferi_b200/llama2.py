@@ -255,6 +255,24 @@ class Llama2:
                                                start_pos, max_gen, eos_token, out.ctypes.data_as(C.c_void_p), C.byref(n)))
         return out[:n.value]
 
+    def prefill(self, prompt, start_pos: int = 0) -> int:
+        """The whole prompt at once on the tensor cores (no counterpart in the reference, whose `ChatLlama2::forward` feeds the
+        prompt token by token, chat_llama2.rs:137-155): fills the cache for positions start_pos .. start_pos + len(prompt) - 1
+        and returns the greedy token that follows.  Continue with generate([token], n, start_pos=start_pos + len(prompt))."""
+        toks = np.ascontiguousarray(prompt, dtype=np.uint32)
+        nxt = C.c_uint32()
+        check(self.lib.ib_llama_prefill(self.handle, torch.cuda.current_stream().cuda_stream, toks.ctypes.data_as(C.c_void_p), toks.size, start_pos, C.byref(nxt)))
+        return int(nxt.value)
+
+    def last_logits(self) -> np.ndarray:
+        """Logits of the last forward (this rank's slice of the vocabulary)."""
+        lg = C.c_void_p()
+        check(self.lib.ib_llama_state(self.handle, C.byref(lg), None))
+        out = np.empty(self.vocab_local, dtype=np.float32)
+        check(self.lib.ib_memcpy_d2h(self.backend.handle, None, out.ctypes.data_as(C.c_void_p), lg, out.nbytes))
+        check(self.lib.ib_stream_sync(self.backend.handle, None))
+        return out
+
     def hidden_state(self) -> np.ndarray:
         x = C.c_void_p()
         check(self.lib.ib_llama_state(self.handle, None, C.byref(x)))
