@@ -47,6 +47,10 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def peak_hbm() -> float:
+    return measured_peaks()[0]
+
+
 def host_threads() -> int:
     """Threads the CPU arm may use: the cores this process is allowed on (torch.distributed.run exports OMP_NUM_THREADS=1,
     which is not the size of the machine)."""
@@ -439,6 +443,27 @@ def main():
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_tok_s = K / e2e_s
 
+    # ---- prefill: the 128-token prompt through the tensor-core GEMMs (single GPU; not part of `value`) ---------
+    prefill = None
+    if world == 1:
+        pp = np.random.default_rng(PROMPT_SEED).integers(0, cfg.vocab_size, 128).astype(np.uint32)
+        model.prefill(pp)                                    # first call allocates its buffers
+        rank_sync()
+        start.record()
+        reps = 3
+        for _ in range(reps):
+            nxt_p = model.prefill(pp)
+        end.record()
+        rank_sync()
+        p_ms = start.elapsed_time(end) / reps
+        loop_first = int(model.generate(pp, 1)[0])           # the same prompt through the decode path
+        flops = 2.0 * cfg.matrix_params() * 128
+        prefill = {"tokens": 128, "ms": round(p_ms, 3), "tok_s": round(128 / (p_ms * 1e-3), 1), "tflops": round(flops / (p_ms * 1e-3) / 1e12, 1),
+                   "frac_of_bf16_sustained_peak": round(flops / (p_ms * 1e-3) / 1e12 / 1385.0, 4),
+                   "weight_stream_bound_ms": round(cfg.weight_bytes() / (peak_hbm() * 1e9) * 1e3, 3),
+                   "decode_path_ms_for_the_same_prompt": round(128 * ms / K, 1), "next_token_matches_decode_path": bool(nxt_p == loop_first),
+                   "note": "f16 hi/lo operand pairs, 3 tcgen05.mma per 16 columns, f32 accumulation in tensor memory; flops counted once (2 x matrix parameters x tokens, classifier excluded)"}
+
     # ---- roofline --------------------------------------------------------------------------------------------
     peak1, peak_src = measured_peaks()
     peak = peak1 * world                                     # aggregate HBM bandwidth of the ranks
@@ -482,6 +507,8 @@ def main():
         "checksum": int(np.bitwise_xor.reduce(out.astype(np.uint64))),
         "first_ids": out[:16].tolist(),     # the same at every N: tensor-parallel runs must generate the single-GPU tokens
     }
+    if prefill:
+        line["prefill"] = prefill
     model.close()
     if rank == 0 and world == 1:
         dev_w.close()

@@ -6,7 +6,7 @@
 // once per prompt token.  Here the weights are read once per prompt.
 //
 // gemm_quant_tc_kernel: out^T tile = W tile (128 rows of the quantized matrix) x X^T (the tokens' input vectors).
-//  * four producer warps, one thread per weight row: dequantize 64 columns of the row per stage to f32, split the value
+//  * eight producer warps, two threads per weight row: dequantize 64 columns of the row per stage to f32, split the value
 //    into two f16 (w = hi + lo, exact to ~2^-22) and store both into shared memory in the K-major core-matrix layout the
 //    tensor core reads (8 rows x 16 bytes per core matrix, no swizzle); the same threads copy the tokens' inputs (already
 //    split into f16 hi / lo by the kernel that produced them) into tiles of the same layout;
@@ -26,7 +26,8 @@ namespace ib {
 constexpr int TC_ROWS = 128;              // weight rows per CTA = M of the MMA
 constexpr int TC_KSTAGE = 64;             // columns per stage
 constexpr int TC_STAGES = 3;
-constexpr int TC_THREADS = 5 * 32;        // 4 producer / epilogue warps + 1 MMA warp
+constexpr int TC_PRODUCER_WARPS = 8;       // two threads per weight row, 32 columns each per stage
+constexpr int TC_THREADS = (TC_PRODUCER_WARPS + 1) * 32;   // + 1 MMA warp
 constexpr uint32_t TC_TILE_BYTES = TC_ROWS * TC_KSTAGE * 2;                  // one f16 tile of 128 x 64
 constexpr uint32_t TC_STAGE_BYTES = 4 * TC_TILE_BYTES;                        // W hi, W lo, X hi, X lo
 constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 + 1024;  // + barriers and TMEM address, + slack to align the tiles to 1 KiB
@@ -81,6 +82,70 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 constexpr uint32_t TC_LBO = 128, TC_SBO = (TC_KSTAGE / 8) * 128;
 __device__ __forceinline__ uint32_t tc_chunk_off(uint32_t row, uint32_t k8) { return (row >> 3) * TC_SBO + k8 * TC_LBO + (row & 7) * 16; }
 
+// ---- 32 consecutive weights of a row (k0 a multiple of 32) as f32, from the device layout of the matrix ----
+__device__ __forceinline__ float tc_h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
+
+// crates/inferi/src/quantization.rs:364-402 (Q4_K) and :287-329 (Q5_K): sub-block j of the block, low or high nibbles of a
+// 32-byte chunk, w = d * sc * q - dmin * m
+template <bool Q5>
+__device__ __forceinline__ void tc_dequant32_q45k(const uint8_t *row, uint32_t k0, float (&w)[32]) {
+    const uint8_t *blk = row + (size_t)(k0 >> 8) * (Q5 ? 176 : 144);
+    const uint32_t j = (k0 & 255) >> 5, c = j >> 1, high = j & 1;
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+    const uint4 *qs = reinterpret_cast<const uint4 *>(blk + (Q5 ? 48 : 16) + 32 * c);
+    const uint4 q0 = __ldg(qs), q1 = __ldg(qs + 1);
+    uint4 h0 = make_uint4(0, 0, 0, 0), h1 = h0;
+    if (Q5) { h0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16)); h1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32)); }
+    // get_scale_min_k4 (quantization.rs:394-402) on the 12 scale bytes held in hdr.y, hdr.z, hdr.w
+    const uint32_t sb[3] = {hdr.y, hdr.z, hdr.w};
+    auto byte_at = [&](uint32_t i) { return (sb[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+    uint32_t sc, mn;
+    if (j < 4) { sc = byte_at(j) & 63; mn = byte_at(j + 4) & 63; }
+    else { sc = (byte_at(j + 4) & 0xF) | ((byte_at(j - 4) >> 6) << 4); mn = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4); }
+    const float dsc = tc_h2f(hdr.x & 0xFFFFu) * (float)sc, dm = tc_h2f(hdr.x >> 16) * (float)mn;
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        uint32_t nib = high ? (qw[i] >> 4) & 0x0F0F0F0Fu : qw[i] & 0x0F0F0F0Fu;
+        if (Q5) nib |= ((hw[i] >> (2 * c + high)) & 0x01010101u) << 4;
+#pragma unroll
+        for (int b = 0; b < 4; b++) w[4 * i + b] = (float)((nib >> (8 * b)) & 0xFFu) * dsc - dm;
+    }
+}
+
+// crates/inferi/src/quantization.rs:227-256, rows stored as groups of 8 blocks [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d]
+__device__ __forceinline__ void tc_dequant32_q6k_soa(const uint8_t *row, uint32_t k0, float (&w)[32]) {
+    const uint32_t b = k0 >> 8, bb = b & 7, e0 = k0 & 255, i = e0 >> 7, g = (e0 >> 5) & 3;
+    const uint8_t *grp = row + (size_t)(b >> 3) * 1680;
+    const uint4 *ql = reinterpret_cast<const uint4 *>(grp + 128 * bb + 64 * i + 32 * (g & 1));
+    const uint4 *qh = reinterpret_cast<const uint4 *>(grp + 1024 + 64 * bb + 32 * i);
+    const uint4 l0 = __ldg(ql), l1 = __ldg(ql + 1), h0 = __ldg(qh), h1 = __ldg(qh + 1);
+    const uint32_t scw = *reinterpret_cast<const unsigned short *>(grp + 1536 + 16 * bb + 8 * i + 2 * g);   // scales of l < 16 and l >= 16
+    const float d = tc_h2f(*reinterpret_cast<const unsigned short *>(grp + 1664 + 2 * bb));
+    const float s0 = d * (float)(int)(int8_t)(scw & 0xFF), s1 = d * (float)(int)(int8_t)(scw >> 8);
+    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+    for (int wi = 0; wi < 8; wi++) {
+        const uint32_t nib = (g & 2) ? (lw[wi] >> 4) & 0x0F0F0F0Fu : lw[wi] & 0x0F0F0F0Fu;
+        const uint32_t q = nib | (((hw[wi] >> (2 * g)) & 0x03030303u) << 4);
+        const float sc = wi < 4 ? s0 : s1;
+#pragma unroll
+        for (int bt = 0; bt < 4; bt++) w[4 * wi + bt] = sc * (float)((int)((q >> (8 * bt)) & 0xFFu) - 32);
+    }
+}
+
+__device__ __forceinline__ void tc_dequant32(const QDesc &q, const uint8_t *row, uint32_t k0, float (&w)[32]) {
+    if (q.qtype == IB_Q4_K) tc_dequant32_q45k<false>(row, k0, w);
+    else if (q.qtype == IB_Q5_K) tc_dequant32_q45k<true>(row, k0, w);
+    else if (q.qtype == IB_Q6_K && q.layout == LAYOUT_SOA) tc_dequant32_q6k_soa(row, k0, w);
+    else {
+#pragma unroll
+        for (int e = 0; e < 32; e++) w[e] = dequant_at(q, row, k0 + e);   // other layouts: element by element (unrolled: w stays in registers)
+    }
+}
+
 struct GemmTcParams {
     QDesc w;                    // the quantized matrix, device layout
     uint32_t rows, cols;        // rows % 128 == 0, cols % 256 == 0
@@ -104,13 +169,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(4 * 32));          // full: every producer thread
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(TC_PRODUCER_WARPS * 32));   // full: every producer thread
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (TC_STAGES + s)), "r"(1));  // empty: one tcgen05.commit
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (2 * TC_STAGES)), "r"(1));       // accumulator complete
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == TC_PRODUCER_WARPS) {
         // tensor memory for the 128 x n_pad f32 accumulator: 128 columns (a power of two >= 32), allocated by one warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(128u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -121,36 +186,45 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     bool ok = true;
 
-    if (warp < 4) {
-        // ===== producers: thread = weight row (and token row) `tid` =====
-        const uint8_t *wrow = p.w.w + (size_t)(row0 + tid) * p.w.row_bytes;
-        const bool has_token = (uint32_t)tid < p.n_pad;
-        const __half *xh = p.x_hi + (size_t)(has_token ? tid : 0) * p.cols, *xl = p.x_lo + (size_t)(has_token ? tid : 0) * p.cols;
+    if (warp < TC_PRODUCER_WARPS) {
+        // ===== producers: thread = (weight row and token row `tid & 127`, half `tid >> 7` of the stage's 64 columns) =====
+        const uint32_t row = tid & (TC_ROWS - 1), kh = tid >> 7;
+        const uint8_t *wrow = p.w.w + (size_t)(row0 + row) * p.w.row_bytes;
+        const bool has_token = row < p.n_pad;
+        const __half *xh = p.x_hi + (size_t)(has_token ? row : 0) * p.cols, *xl = p.x_lo + (size_t)(has_token ? row : 0) * p.cols;
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
+            const uint32_t k0 = kbeg + it * TC_KSTAGE + 32 * kh;
+            // weights and inputs do not depend on the stage being free: fetch and convert first, wait for the stage after
+            float w[32];
+            tc_dequant32(p.w, wrow, k0, w);
+            uint4 xa[4], xb[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                xa[j] = has_token ? __ldg(reinterpret_cast<const uint4 *>(xh + k0 + 8 * j)) : make_uint4(0, 0, 0, 0);
+                xb[j] = has_token ? __ldg(reinterpret_cast<const uint4 *>(xl + k0 + 8 * j)) : make_uint4(0, 0, 0, 0);
+            }
             if (round > 0) ok = tc_wait(bar0 + 8 * (TC_STAGES + s), (round - 1) & 1, p.wait_ns, p.err, 8);
             if (!ok) break;
             uint8_t *st = smem + s * TC_STAGE_BYTES;
-            const uint32_t k0 = kbeg + it * TC_KSTAGE;
-#pragma unroll 1
-            for (uint32_t k8 = 0; k8 < TC_KSTAGE / 8; k8++) {
-                __align__(16) __half hi[8], lo[8];
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float w = dequant_at(p.w, wrow, k0 + 8 * k8 + e);
-                    hi[e] = __float2half_rn(w);
-                    lo[e] = __float2half_rn(w - __half2float(hi[e]));
+            for (int j = 0; j < 4; j++) {
+                uint4 hi, lo;
+                uint32_t *hp = &hi.x, *lp = &lo.x;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float a = w[8 * j + 2 * e], b = w[8 * j + 2 * e + 1];
+                    const __half2 h = __floats2half2_rn(a, b);
+                    const float2 back = __half22float2(h);
+                    const __half2 l = __floats2half2_rn(a - back.x, b - back.y);
+                    hp[e] = *reinterpret_cast<const uint32_t *>(&h);
+                    lp[e] = *reinterpret_cast<const uint32_t *>(&l);
                 }
-                const uint32_t off = tc_chunk_off(tid, k8);
-                *reinterpret_cast<uint4 *>(st + off) = *reinterpret_cast<const uint4 *>(hi);
-                *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = *reinterpret_cast<const uint4 *>(lo);
-                uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-                if (has_token) {
-                    a = __ldg(reinterpret_cast<const uint4 *>(xh + k0 + 8 * k8));
-                    b = __ldg(reinterpret_cast<const uint4 *>(xl + k0 + 8 * k8));
-                }
-                *reinterpret_cast<uint4 *>(st + 2 * TC_TILE_BYTES + off) = a;
-                *reinterpret_cast<uint4 *>(st + 3 * TC_TILE_BYTES + off) = b;
+                const uint32_t off = tc_chunk_off(row, 4 * kh + j);
+                *reinterpret_cast<uint4 *>(st + off) = hi;
+                *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = lo;
+                *reinterpret_cast<uint4 *>(st + 2 * TC_TILE_BYTES + off) = xa[j];
+                *reinterpret_cast<uint4 *>(st + 3 * TC_TILE_BYTES + off) = xb[j];
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
@@ -178,15 +252,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
         if (ok) tc_commit(bar0 + 8 * (2 * TC_STAGES));   // ... and the accumulator is complete when all of them are done
     }
 
-    if (warp < 4) {
-        // ===== epilogue: TMEM lane = weight row, column = token; stored as [token][row] =====
+    if (warp < TC_PRODUCER_WARPS) {
+        // ===== epilogue: TMEM lane = weight row, column = token; stored as [token][row].  A warp reaches the 32 lanes
+        // 32 * (warp % 4); warps 0-3 take the first half of the token columns, warps 4-7 the second =====
         if (ok) ok = tc_wait(bar0 + 8 * (2 * TC_STAGES), 0, p.wait_ns, p.err, 10);
         ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-wide instructions
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            float *out = p.out + (size_t)blockIdx.y * p.n_tokens * p.rows + row0 + tid;
-            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-            for (uint32_t c0 = 0; c0 < p.n_pad; c0 += 16) {
+            const uint32_t row = tid & (TC_ROWS - 1), groups = p.n_pad / 16, gsplit = (groups + 1) / 2;
+            const uint32_t g_beg = (warp < 4) ? 0 : gsplit, g_end = (warp < 4) ? gsplit : groups;
+            float *out = p.out + (size_t)blockIdx.y * p.n_tokens * p.rows + row0 + row;
+            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            for (uint32_t c0 = 16 * g_beg; c0 < 16 * g_end; c0 += 16) {
                 uint32_t r[16];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
@@ -202,7 +279,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    if (warp == TC_PRODUCER_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
 }
 
 

@@ -69,6 +69,11 @@ class Llama2Config:
         norms = (2 * self.num_hidden_layers + 1) * self.hidden_size * 4
         return per_layer * self.num_hidden_layers + head + norms
 
+    def matrix_params(self) -> int:
+        """Weights of the layer matrices (what a prompt's GEMMs multiply with; classifier and embedding excluded)."""
+        sh = self.shapes()
+        return self.num_hidden_layers * sum(sh[n][0] * sh[n][1] for n in LAYER_MATS)
+
     def kv_bytes_per_position(self, kv_f16: bool = True) -> int:
         return 2 * self.num_hidden_layers * self.kv_dim * (2 if kv_f16 else 4)
 
