@@ -288,7 +288,7 @@ def other_configs(backend, peak):
 
 def kernel_case(name: str):
     """A small stand-alone loop over one kernel, for `ncu` captures: a few launches, rotating over buffers that together
-    exceed L2.  Cases: gate_q4k, q_q4k, down_q6k, lmhead_q6k, q5k, q8_0, gate_up, attn_8k, attn_32k."""
+    exceed L2.  Cases: gate_q4k, q_q4k, down_q6k, lmhead_q6k, q5k, q8_0, gate_up, gemm_gate, attn_8k, attn_32k."""
     import torch
     from inferi_b200 import quant
     from inferi_b200.ops import AttnParams, Backend, FfnGateUp, FusedAttention, GemvQuant, GpuQuantTensor
@@ -318,6 +318,23 @@ def kernel_case(name: str):
         end.record()
         torch.cuda.synchronize()
         b = (2 if name == "gate_up" else 1) * mats[0].nbytes + 4 * (rows + cols)
+    elif name == "gemm_gate":
+        # the prefill GEMM: 128 tokens through a Q4_K 14336 x 4096 matrix (tensor cores)
+        from inferi_b200.ops import GemmQuant
+        rows, cols, ntok = 14336, 4096, 128
+        mats = [GpuQuantTensor(backend, quant.Q4_K, rows, cols, quant.random_blocks(quant.Q4_K, rows, cols, seed=10 + i)) for i in range(4)]
+        x, o = torch.randn(ntok, cols, device="cuda"), torch.empty(ntok, rows, device="cuda")
+        g = GemmQuant(backend)
+        n = 0
+        for rep in range(3):
+            if rep == 2:
+                start.record()
+            for m in mats:
+                g.launch(o, m, x)
+                n += rep == 2
+        end.record()
+        torch.cuda.synchronize()
+        b = mats[0].nbytes + 4 * ntok * (rows + cols)
     elif name.startswith("attn_"):
         ctx = {"attn_8k": 8192, "attn_32k": 32768}[name]
         hs, nh, kvm = 128, 32, 4

@@ -85,17 +85,28 @@ __device__ __forceinline__ uint32_t tc_chunk_off(uint32_t row, uint32_t k8) { re
 // ---- 32 consecutive weights of a row (k0 a multiple of 32) as f32, from the device layout of the matrix ----
 __device__ __forceinline__ float tc_h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
 
+// The bytes a thread needs for its 32 weights, fetched one stage ahead of their conversion.
+struct TcRaw {
+    uint4 v[5];       // Q4_K: header, 32 quant bytes; Q5_K: + the 32 high-bit bytes; Q6_K: 32 low and 32 high bytes
+    uint32_t s, d;    // Q6_K: the two scales, the block's f16 scale
+};
+
 // crates/inferi/src/quantization.rs:364-402 (Q4_K) and :287-329 (Q5_K): sub-block j of the block, low or high nibbles of a
 // 32-byte chunk, w = d * sc * q - dmin * m
 template <bool Q5>
-__device__ __forceinline__ void tc_dequant32_q45k(const uint8_t *row, uint32_t k0, float (&w)[32]) {
+__device__ __forceinline__ void tc_load32_q45k(const uint8_t *row, uint32_t k0, TcRaw &r) {
     const uint8_t *blk = row + (size_t)(k0 >> 8) * (Q5 ? 176 : 144);
-    const uint32_t j = (k0 & 255) >> 5, c = j >> 1, high = j & 1;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+    const uint32_t c = (k0 & 255) >> 6;
+    r.v[0] = __ldg(reinterpret_cast<const uint4 *>(blk));
     const uint4 *qs = reinterpret_cast<const uint4 *>(blk + (Q5 ? 48 : 16) + 32 * c);
-    const uint4 q0 = __ldg(qs), q1 = __ldg(qs + 1);
-    uint4 h0 = make_uint4(0, 0, 0, 0), h1 = h0;
-    if (Q5) { h0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16)); h1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32)); }
+    r.v[1] = __ldg(qs);
+    r.v[2] = __ldg(qs + 1);
+    if (Q5) { r.v[3] = __ldg(reinterpret_cast<const uint4 *>(blk + 16)); r.v[4] = __ldg(reinterpret_cast<const uint4 *>(blk + 32)); }
+}
+template <bool Q5>
+__device__ __forceinline__ void tc_convert32_q45k(const TcRaw &r, uint32_t k0, float (&w)[32]) {
+    const uint32_t j = (k0 & 255) >> 5, c = j >> 1, high = j & 1;
+    const uint4 hdr = r.v[0];
     // get_scale_min_k4 (quantization.rs:394-402) on the 12 scale bytes held in hdr.y, hdr.z, hdr.w
     const uint32_t sb[3] = {hdr.y, hdr.z, hdr.w};
     auto byte_at = [&](uint32_t i) { return (sb[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
@@ -103,8 +114,8 @@ __device__ __forceinline__ void tc_dequant32_q45k(const uint8_t *row, uint32_t k
     if (j < 4) { sc = byte_at(j) & 63; mn = byte_at(j + 4) & 63; }
     else { sc = (byte_at(j + 4) & 0xF) | ((byte_at(j - 4) >> 6) << 4); mn = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4); }
     const float dsc = tc_h2f(hdr.x & 0xFFFFu) * (float)sc, dm = tc_h2f(hdr.x >> 16) * (float)mn;
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    const uint32_t qw[8] = {r.v[1].x, r.v[1].y, r.v[1].z, r.v[1].w, r.v[2].x, r.v[2].y, r.v[2].z, r.v[2].w};
+    const uint32_t hw[8] = {r.v[3].x, r.v[3].y, r.v[3].z, r.v[3].w, r.v[4].x, r.v[4].y, r.v[4].z, r.v[4].w};
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         uint32_t nib = high ? (qw[i] >> 4) & 0x0F0F0F0Fu : qw[i] & 0x0F0F0F0Fu;
@@ -115,17 +126,21 @@ __device__ __forceinline__ void tc_dequant32_q45k(const uint8_t *row, uint32_t k
 }
 
 // crates/inferi/src/quantization.rs:227-256, rows stored as groups of 8 blocks [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d]
-__device__ __forceinline__ void tc_dequant32_q6k_soa(const uint8_t *row, uint32_t k0, float (&w)[32]) {
+__device__ __forceinline__ void tc_load32_q6k_soa(const uint8_t *row, uint32_t k0, TcRaw &r) {
     const uint32_t b = k0 >> 8, bb = b & 7, e0 = k0 & 255, i = e0 >> 7, g = (e0 >> 5) & 3;
     const uint8_t *grp = row + (size_t)(b >> 3) * 1680;
     const uint4 *ql = reinterpret_cast<const uint4 *>(grp + 128 * bb + 64 * i + 32 * (g & 1));
     const uint4 *qh = reinterpret_cast<const uint4 *>(grp + 1024 + 64 * bb + 32 * i);
-    const uint4 l0 = __ldg(ql), l1 = __ldg(ql + 1), h0 = __ldg(qh), h1 = __ldg(qh + 1);
-    const uint32_t scw = *reinterpret_cast<const unsigned short *>(grp + 1536 + 16 * bb + 8 * i + 2 * g);   // scales of l < 16 and l >= 16
-    const float d = tc_h2f(*reinterpret_cast<const unsigned short *>(grp + 1664 + 2 * bb));
-    const float s0 = d * (float)(int)(int8_t)(scw & 0xFF), s1 = d * (float)(int)(int8_t)(scw >> 8);
-    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    r.v[0] = __ldg(ql); r.v[1] = __ldg(ql + 1); r.v[2] = __ldg(qh); r.v[3] = __ldg(qh + 1);
+    r.s = __ldg(reinterpret_cast<const unsigned short *>(grp + 1536 + 16 * bb + 8 * i + 2 * g));   // scales of l < 16 and l >= 16
+    r.d = __ldg(reinterpret_cast<const unsigned short *>(grp + 1664 + 2 * bb));
+}
+__device__ __forceinline__ void tc_convert32_q6k_soa(const TcRaw &r, uint32_t k0, float (&w)[32]) {
+    const uint32_t g = ((k0 & 255) >> 5) & 3;
+    const float d = tc_h2f(r.d);
+    const float s0 = d * (float)(int)(int8_t)(r.s & 0xFF), s1 = d * (float)(int)(int8_t)(r.s >> 8);
+    const uint32_t lw[8] = {r.v[0].x, r.v[0].y, r.v[0].z, r.v[0].w, r.v[1].x, r.v[1].y, r.v[1].z, r.v[1].w};
+    const uint32_t hw[8] = {r.v[2].x, r.v[2].y, r.v[2].z, r.v[2].w, r.v[3].x, r.v[3].y, r.v[3].z, r.v[3].w};
 #pragma unroll
     for (int wi = 0; wi < 8; wi++) {
         const uint32_t nib = (g & 2) ? (lw[wi] >> 4) & 0x0F0F0F0Fu : lw[wi] & 0x0F0F0F0Fu;
@@ -136,13 +151,22 @@ __device__ __forceinline__ void tc_dequant32_q6k_soa(const uint8_t *row, uint32_
     }
 }
 
-__device__ __forceinline__ void tc_dequant32(const QDesc &q, const uint8_t *row, uint32_t k0, float (&w)[32]) {
-    if (q.qtype == IB_Q4_K) tc_dequant32_q45k<false>(row, k0, w);
-    else if (q.qtype == IB_Q5_K) tc_dequant32_q45k<true>(row, k0, w);
-    else if (q.qtype == IB_Q6_K && q.layout == LAYOUT_SOA) tc_dequant32_q6k_soa(row, k0, w);
+// 0: Q4_K, 1: Q5_K, 2: Q6_K in the 8-block row layout, 3: everything else (converted element by element, no prefetch)
+__device__ __forceinline__ uint32_t tc_path(const QDesc &q) {
+    return q.qtype == IB_Q4_K ? 0u : (q.qtype == IB_Q5_K ? 1u : ((q.qtype == IB_Q6_K && q.layout == LAYOUT_SOA) ? 2u : 3u));
+}
+__device__ __forceinline__ void tc_load32(uint32_t path, const uint8_t *row, uint32_t k0, TcRaw &r) {
+    if (path == 0) tc_load32_q45k<false>(row, k0, r);
+    else if (path == 1) tc_load32_q45k<true>(row, k0, r);
+    else if (path == 2) tc_load32_q6k_soa(row, k0, r);
+}
+__device__ __forceinline__ void tc_convert32(uint32_t path, const QDesc &q, const uint8_t *row, const TcRaw &r, uint32_t k0, float (&w)[32]) {
+    if (path == 0) tc_convert32_q45k<false>(r, k0, w);
+    else if (path == 1) tc_convert32_q45k<true>(r, k0, w);
+    else if (path == 2) tc_convert32_q6k_soa(r, k0, w);
     else {
 #pragma unroll
-        for (int e = 0; e < 32; e++) w[e] = dequant_at(q, row, k0 + e);   // other layouts: element by element (unrolled: w stays in registers)
+        for (int e = 0; e < 32; e++) w[e] = dequant_at(q, row, k0 + e);   // unrolled: w stays in registers
     }
 }
 
@@ -190,20 +214,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
         // ===== producers: thread = (weight row and token row `tid & 127`, half `tid >> 7` of the stage's 64 columns) =====
         const uint32_t row = tid & (TC_ROWS - 1), kh = tid >> 7;
         const uint8_t *wrow = p.w.w + (size_t)(row0 + row) * p.w.row_bytes;
-        const bool has_token = row < p.n_pad;
-        const __half *xh = p.x_hi + (size_t)(has_token ? row : 0) * p.cols, *xl = p.x_lo + (size_t)(has_token ? row : 0) * p.cols;
+        // The tokens' inputs are copied by all producer threads together, in an order that keeps the global loads dense: the
+        // 32 lanes of a warp take 8 token rows x 4 consecutive 16-byte chunks (64 contiguous bytes per row), not one row
+        // each (that was 32 cache lines per load instruction and made the L1 the limiter of the whole kernel).
+        uint32_t xrow[4], xk8[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t id = i * (TC_PRODUCER_WARPS * 32) + tid;   // chunk number: 128 rows x 8 chunks per tile
+            xrow[i] = ((id >> 6) << 3) | (id & 7);
+            xk8[i] = (id >> 3) & 7;
+        }
+        // the bytes of a stage are requested one stage ahead of their use: the conversion of stage i overlaps the loads of
+        // stage i + 1 (weights and inputs do not depend on a stage of shared memory being free)
+        const uint32_t path = tc_path(p.w);
+        TcRaw raw;
+        uint4 xa[4], xb[4];
+        auto fetch = [&](uint32_t it) {
+            const uint32_t kst = kbeg + it * TC_KSTAGE;
+            tc_load32(path, wrow, kst + 32 * kh, raw);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const bool has = xrow[j] < p.n_pad;
+                const size_t at = (size_t)(has ? xrow[j] : 0) * p.cols + kst + 8 * xk8[j];
+                xa[j] = has ? __ldg(reinterpret_cast<const uint4 *>(p.x_hi + at)) : make_uint4(0, 0, 0, 0);
+                xb[j] = has ? __ldg(reinterpret_cast<const uint4 *>(p.x_lo + at)) : make_uint4(0, 0, 0, 0);
+            }
+        };
+        if (nstage) fetch(0);
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
             const uint32_t k0 = kbeg + it * TC_KSTAGE + 32 * kh;
-            // weights and inputs do not depend on the stage being free: fetch and convert first, wait for the stage after
             float w[32];
-            tc_dequant32(p.w, wrow, k0, w);
-            uint4 xa[4], xb[4];
+            tc_convert32(path, p.w, wrow, raw, k0, w);
+            uint4 ca[4], cb[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                xa[j] = has_token ? __ldg(reinterpret_cast<const uint4 *>(xh + k0 + 8 * j)) : make_uint4(0, 0, 0, 0);
-                xb[j] = has_token ? __ldg(reinterpret_cast<const uint4 *>(xl + k0 + 8 * j)) : make_uint4(0, 0, 0, 0);
-            }
+            for (int j = 0; j < 4; j++) { ca[j] = xa[j]; cb[j] = xb[j]; }
+            if (it + 1 < nstage) fetch(it + 1);
             if (round > 0) ok = tc_wait(bar0 + 8 * (TC_STAGES + s), (round - 1) & 1, p.wait_ns, p.err, 8);
             if (!ok) break;
             uint8_t *st = smem + s * TC_STAGE_BYTES;
@@ -223,8 +269,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
                 const uint32_t off = tc_chunk_off(row, 4 * kh + j);
                 *reinterpret_cast<uint4 *>(st + off) = hi;
                 *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = lo;
-                *reinterpret_cast<uint4 *>(st + 2 * TC_TILE_BYTES + off) = xa[j];
-                *reinterpret_cast<uint4 *>(st + 3 * TC_TILE_BYTES + off) = xb[j];
+                const uint32_t xoff = tc_chunk_off(xrow[j], xk8[j]);
+                *reinterpret_cast<uint4 *>(st + 2 * TC_TILE_BYTES + xoff) = ca[j];
+                *reinterpret_cast<uint4 *>(st + 3 * TC_TILE_BYTES + xoff) = cb[j];
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
