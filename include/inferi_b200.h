@@ -140,10 +140,14 @@ IB_API int32_t ib_attention(ib_ctx *ctx, void *stream, const ib_attn_params *par
  * the memory budget): it takes no context and calls no cudaMalloc/cudaFree.  The split-K scratch is a fixed array inside
  * the library, so every GPU that loads the library holds about 1 MiB for it until the process exits.
  * Limits: n_heads * (head_size + 2) <= 262144 and at most 256 kv heads, else IB_ERR_UNSUPPORTED with a message.
- * The device that is current when it is called is used.  The first call on each device looks the array's address up
- * (cudaGetSymbolAddress); make that first call during set-up, before any stream capture.
+ * The device that is current when it is called is used, and `stream` must belong to it.  The first call on each device
+ * looks the array's address up (cudaGetSymbolAddress) and, where the driver loads modules lazily, is also when the module
+ * holding the array is loaded (the driver may allocate and synchronise then): make that first call during set-up, before
+ * any stream capture.  The addresses are remembered per device ordinal for the life of the process (cudaDeviceReset
+ * invalidates them).
  * All calls share the one array: two calls whose kernels may overlap on the GPU (different streams) race; calls on one
- * stream are safe, each call leaves the array's counters at zero for the next. */
+ * stream are safe, each call leaves the array's counters at zero for the next.  After a failed launch or a race the
+ * counters are in an undefined state. */
 IB_API int32_t ib_attention_static(void *stream, const ib_attn_params *params, const float *q_dev, const void *k_cache_dev,
                                    const void *v_cache_dev, int32_t kv_dtype, float *out_dev);
 

@@ -170,7 +170,8 @@ extern "C" int32_t ib_attention_static(void *stream, const ib_attn_params *param
     IB_CHECK_CUDA(cudaGetDevice(&dev));
     IB_REQUIRE(dev >= 0 && dev < STATIC_ATTN_MAX_DEVICES, "ib_attention_static: device ordinal %d not supported", dev);
     if (!g_static_scratch_addr[dev]) {
-        // first call on this device: resolve the symbols (no allocation takes place; the arrays already exist)
+        // first call on this device: resolve the symbols.  With lazy module loading this is also the moment the driver loads
+        // the module that holds the arrays (which may allocate and synchronise): make this call during set-up.
         float *s = nullptr;
         unsigned int *c = nullptr;
         IB_CHECK_CUDA(cudaGetSymbolAddress((void **)&s, g_static_attn_scratch));

@@ -244,6 +244,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
             if (!dyn) tc.advance(sh);
             else if (held > 1) { t++; held--; }
             else t = __shfl_sync(0xffffffffu, tn, 0);
+            // The CTA's first tile travels alone: with a ring-full of copies in flight at once the copy engine interleaves
+            // them and all of them - the first one too - arrive when the last byte does, which is later than the consumers
+            // are ready for the first tile.  The others follow as soon as the first has landed.
+            if (k == 0) {
+                uint32_t ok0 = 1;
+                if (lane == 0) ok0 = mbar_wait(bar0, 0, p.err, 1, p.wait_ns) ? 1u : 0u;
+                if (!__shfl_sync(0xffffffffu, ok0, 0)) break;
+            }
         }
         return;
     }

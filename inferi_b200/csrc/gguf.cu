@@ -220,8 +220,15 @@ int32_t parse(ib_gguf *g) {
     for (size_t i = 0; i < g->tensors.size(); i++) {
         TensorRec &t = g->tensors[i];
         uint32_t bb, be;
+        // element count: every factor and every running product is bounded by what the file could hold (a product of four
+        // 64-bit dims can wrap even 128 bits; largest block length is 256, smallest block one byte)
         unsigned __int128 n = 1;
-        for (int d = 0; d < 4; d++) n *= t.dims[d];
+        const unsigned __int128 most = (unsigned __int128)g->size * 256u;
+        for (int d = 0; d < 4; d++) {
+            if (t.dims[d] == 0 || t.dims[d] > most) return set_error(IB_ERR_INVALID, "gguf: tensor %s has a dimension of %llu", t.name.c_str(), (unsigned long long)t.dims[d]);
+            n *= t.dims[d];
+            if (n > most) return set_error(IB_ERR_INVALID, "gguf: tensor %s is larger than the file", t.name.c_str());
+        }
         if (type_size(t.type, bb, be)) {
             if (n % be) return set_error(IB_ERR_INVALID, "gguf: tensor %s has %llu elements, not a multiple of its block length %u", t.name.c_str(), (unsigned long long)n, be);
             const unsigned __int128 bytes = n / be * bb;

@@ -257,12 +257,12 @@ extern "C" int32_t ib_sample(ib_ctx *ctx, void *stream, const float *logits_dev,
     IB_REQUIRE(coin >= 0.f && coin < 1.f, "ib_sample: coin=%f outside [0, 1)", (double)coin);
     IB_REQUIRE(temperature >= 0.f, "ib_sample: negative temperature");
     if (temperature == 0.f) return launch_argmax(ctx, (cudaStream_t)stream, logits_dev, n, out_dev);   // sampler.rs:33-35
-    float *probs = nullptr;
-    unsigned long long *keys = nullptr;
-    IB_CHECK_CUDA(cudaMallocAsync((void **)&probs, sizeof(float) * n, (cudaStream_t)stream));
-    IB_CHECK_CUDA(cudaMallocAsync((void **)&keys, sizeof(unsigned long long) * sample_keys_capacity(n), (cudaStream_t)stream));
-    const int32_t rc = launch_sample(ctx, (cudaStream_t)stream, logits_dev, n, temperature, topp, 0, nullptr, coin, probs, keys, out_dev, nullptr, 0);
-    cudaFreeAsync(probs, (cudaStream_t)stream);
-    cudaFreeAsync(keys, (cudaStream_t)stream);
+    // one stream-ordered allocation for both scratch arrays (probabilities, then the sort keys, 8-byte aligned)
+    const size_t probs_bytes = (sizeof(float) * n + 7) & ~(size_t)7;
+    uint8_t *scratch = nullptr;
+    IB_CHECK_CUDA(cudaMallocAsync((void **)&scratch, probs_bytes + sizeof(unsigned long long) * sample_keys_capacity(n), (cudaStream_t)stream));
+    const int32_t rc = launch_sample(ctx, (cudaStream_t)stream, logits_dev, n, temperature, topp, 0, nullptr, coin, reinterpret_cast<float *>(scratch),
+                                     reinterpret_cast<unsigned long long *>(scratch + probs_bytes), out_dev, nullptr, 0);
+    cudaFreeAsync(scratch, (cudaStream_t)stream);
     return rc;
 }
