@@ -232,8 +232,9 @@ IB_API int32_t ib_llama_prefill(ib_llama *model, void *stream, const uint32_t *t
  * per GPU, each creating its model with (tp_rank, tp_size > 1) and ITS SHARD of every matrix — q/k/v, gate/up and the
  * classifier split by rows (heads, FFN units, vocabulary), attn_output and ffn_down split by columns at block
  * granularity (Q6_K: multiples of 2048 columns), token_embd and the norm vectors replicated.  Partial sums of the two
- * row-split GEMVs are exchanged by a one-shot push all-reduce fused into the kernels (peer stores into each rank's
- * exchange area + arrival counters, every wait bounded).  Set-up: every rank calls ib_llama_tp_export, the hosts exchange
+ * row-split GEMVs are exchanged by a one-shot push all-reduce fused into the kernels (peer stores of 8-byte {value, tag}
+ * words into each rank's exchange area - the tag names the token and the exchange, so the data is its own arrival signal
+ * - every wait bounded).  Set-up: every rank calls ib_llama_tp_export, the hosts exchange
  * the IB_TP_HANDLE_BYTES-byte handles (any transport), every rank calls ib_llama_tp_connect with all handles ordered by
  * rank; only then can the model run.  All ranks must then issue the same forward/generate calls. */
 #define IB_TP_HANDLE_BYTES 64
@@ -254,6 +255,20 @@ IB_API int32_t ib_llama_tp_connect_ptrs(ib_llama *model, void *const *areas_by_r
  * start_pos + n_prompt + *n_out - 1 with the last token as its prompt (KV reuse). */
 IB_API int32_t ib_llama_generate_until(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos,
                                        uint32_t max_gen, uint32_t eos_token, uint32_t *out_tokens_host, uint32_t *n_out);
+/* The token loop of `ChatLlama2::forward` (crates/inferi-chat/src/chat_llama2.rs:92-189) with its event callback.  `out` is
+ * called once per generated token with what `ChatEvent::Token` carries (chat_llama2.rs:173-178): the token and its
+ * predecessor (the pair `tokenizer.decode(prev, token)` turns into the event's string), `next_pos` = the position whose
+ * forward produced it, `token_count` = next_pos - start_pos - 1 and `token_time` = seconds since the forward at
+ * start_pos + 1 began - the reference leaves the first forward out of its tok/s (`timing_delay = 1`, :131), so the first
+ * event of a one-token prompt carries (0, 0.0).  A non-zero return from `out` ends the turn early (the reference stops when
+ * its callback returns Err, :180-183); the stop token ends it without an event (:158-160).  Prompt positions are forced,
+ * not sampled.  The device loop runs in chunks of 16 tokens, so the callback sees up to 16 events at once, their times
+ * spread evenly over the chunk; prompts of 10 tokens and more go through ib_llama_prefill when the model qualifies.
+ * *n_out (may be NULL) receives the number of events delivered; the next turn starts at start_pos + n_prompt + *n_out - 1
+ * with the last delivered token as the head of its prompt. */
+typedef int32_t (*ib_token_event_fn)(void *user, uint32_t prev_token, uint32_t token, uint32_t next_pos, uint32_t token_count, double token_time);
+IB_API int32_t ib_llama_chat(ib_llama *model, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos, uint32_t max_gen,
+                             uint32_t eos_token, ib_token_event_fn out, void *user, uint32_t *n_out);
 /* ≙ `Sampler::new(vocab, temperature, topp)` (models/sampler.rs:22-30) for the model's own token loop: after this,
  * ib_llama_forward / ib_llama_generate feed back sampled tokens instead of the arg-max (temperature 0 = greedy again).
  * The coin of a position is splitmix64(seed, position) -> [0, 1), so a run can be reproduced.  Single GPU only. */

@@ -53,6 +53,8 @@ class GgufTensorInfo(C.Structure):
 
 # name -> (restype, argtypes); every symbol include/inferi_b200.h declares
 _vp, _u32, _u64, _i32, _f = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float
+# ib_token_event_fn: (user, prev_token, token, next_pos, token_count, token_time) -> non-zero to stop
+TOKEN_EVENT_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_double)
 SIGNATURES = {
     "ib_last_error_string": (C.c_char_p, []),
     "ib_ctx_create": (_i32, [_i32, C.POINTER(_vp)]),
@@ -82,6 +84,7 @@ SIGNATURES = {
     "ib_sample": (_i32, [_vp, _vp, _vp, _u32, _f, _f, _f, _vp]),
     "ib_llama_set_sampler": (_i32, [_vp, _f, _f, _u64]),
     "ib_llama_generate_until": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, C.POINTER(_u32)]),
+    "ib_llama_chat": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, TOKEN_EVENT_FN, _vp, C.POINTER(_u32)]),
     "ib_llama_create": (_i32, [_vp, C.POINTER(LlamaConfig), C.POINTER(LlamaWeights), _i32, _i32, _i32, C.POINTER(_vp)]),
     "ib_llama_destroy": (_i32, [_vp]),
     "ib_llama_forward": (_i32, [_vp, _vp, _u32, _u32, _vp, _vp]),

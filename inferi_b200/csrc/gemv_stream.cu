@@ -73,6 +73,14 @@ __device__ __forceinline__ void consume_tiles(const GemvParams &p, const Consume
     constexpr bool ONE_TYPE = (QT != QT_MIXED && QT != QT_Q4_Q6);
     const uint32_t rb0 = (uint32_t)p.seg[0].row_bytes, rb1 = (uint32_t)p.seg[1].row_bytes, rb2 = (uint32_t)p.seg[2].row_bytes;
     const bool swiglu = p.epi == EPI_SWIGLU;   // gate rows, then up rows, in one tile: a "pair" is gate row r + up row r
+    {
+        // The lane's activations go into registers in the layout of the first segment's format before the first tile is
+        // waited for: the copy of that tile and this load overlap.
+        const uint32_t q0 = ONE_TYPE ? QT : p.seg[0].qtype;
+        unit_init<QT>(q0, c.u, lc);
+        if (c.has_unit) load_unit_act(q0, c.u, A, ua);
+        cur_type = q0;
+    }
 #pragma unroll 1
     for (;; st = (st + 1 == S) ? 0 : st + 1, par ^= (st == 0) ? 1u : 0u) {
         if (!mbar_wait(c.bar0 + 8 * st, par, p.err, 1, p.wait_ns)) return;   // the error word is raised; give up on this CTA's rows
@@ -321,6 +329,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_stream_kernel(const Ge
     const Act A{act_sm, p.cols, p.cols / 64};
     float4 norm_g[4];
     pack_prefetch_norm(p.norm_w, p.cols, norm_g);   // weights: fetched while the previous kernel is still running
+    {
+        // The launch parameters the tile loop reads, touched while the previous kernel is still running: their first read
+        // misses the constant cache, and that round trip would otherwise sit between the activations and the first tile.
+        const uint32_t touch = (uint32_t)p.seg[0].row_bytes ^ (uint32_t)p.seg[1].row_bytes ^ (uint32_t)p.seg[2].row_bytes ^ p.seg[0].qtype ^
+                               p.seg[1].qtype ^ p.seg[2].qtype ^ p.epi ^ (uint32_t)p.wait_ns ^ (uint32_t)(uintptr_t)p.err;
+        asm volatile("" ::"r"(touch));
+    }
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.reduce_src) {
         // tensor parallel: the reduced residual stream is complete once the epilogue warps of all CTAs have stored their groups

@@ -20,6 +20,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <new>
+#include <chrono>
 #include <vector>
 
 using namespace ib;
@@ -881,6 +882,74 @@ int32_t ib_llama_generate_until(ib_llama *m, void *stream, const uint32_t *token
         cur_n = 1;
     }
     *n_out = done;
+    return IB_OK;
+}
+
+int32_t ib_llama_chat(ib_llama *m, void *stream, const uint32_t *tokens_host, uint32_t n_prompt, uint32_t start_pos, uint32_t max_gen,
+                      uint32_t eos_token, ib_token_event_fn out, void *user, uint32_t *n_out) {
+    IB_REQUIRE(m && tokens_host && out, "ib_llama_chat: null argument");
+    IB_REQUIRE(n_prompt >= 1 && max_gen >= 1, "ib_llama_chat: empty prompt or nothing to generate");
+    if (n_out) *n_out = 0;
+    const uint64_t ctx_len = m->cfg.max_position_embeddings;
+    IB_REQUIRE((uint64_t)start_pos + n_prompt <= ctx_len, "ib_llama_chat: %u prompt positions from %u exceed the context of %llu", n_prompt, start_pos,
+               (unsigned long long)ctx_len);
+    // The turn also ends when the context is full: the forward at the last position still yields a token.
+    if ((uint64_t)max_gen > ctx_len - start_pos - n_prompt + 1) max_gen = (uint32_t)(ctx_len - start_pos - n_prompt + 1);
+    using clock = std::chrono::steady_clock;
+    auto seconds_since = [](clock::time_point t0) { return std::chrono::duration<double>(clock::now() - t0).count(); };
+    // chat_llama2.rs:131-140: the forward at start_pos is outside the timed span (`timing_delay = 1`), so it runs alone.
+    uint32_t first_next = 0;
+    int32_t rc = ib_llama_forward(m, stream, tokens_host[0], start_pos, nullptr, &first_next);
+    if (rc) return rc;
+    const clock::time_point t_start = clock::now();
+    uint32_t pos = start_pos + 1;            // next position to feed
+    uint32_t emitted = 0;
+    uint32_t prev = tokens_host[n_prompt - 1];
+    uint32_t last = first_next;              // the token the model produced for position pos - 1
+    if (n_prompt == 1) {
+        // The only prompt token was the untimed one: its successor is the first event, with no rate yet (chat_llama2.rs:168-177).
+        if (last == eos_token) return IB_OK;
+        if (out(user, prev, last, start_pos, 0, 0.0)) return IB_OK;
+        emitted = 1;
+        if (n_out) *n_out = emitted;
+        prev = last;
+    } else {
+        // The rest of the prompt: positions start_pos + 1 .. start_pos + n_prompt - 2 only fill the cache (the tensor-core
+        // prefill when the model qualifies, the decode loop otherwise); the last prompt token then goes through the token loop.
+        const uint32_t mid = n_prompt - 2;
+        if (mid >= 8) {
+            rc = ib_llama_prefill(m, stream, tokens_host + 1, mid, pos, nullptr);
+            if (rc == IB_OK) pos += mid;
+            else if (rc != IB_ERR_UNSUPPORTED) return rc;
+        }
+    }
+    constexpr uint32_t CHUNK = 16;
+    std::vector<uint32_t> buf(CHUNK);
+    // What is still to feed: the prompt tokens from index pos - start_pos on, or (after the prompt) the last produced token.
+    while (emitted < max_gen) {
+        const uint32_t fed = pos - start_pos;
+        const uint32_t *cur = fed < n_prompt ? tokens_host + fed : &last;
+        const uint32_t cur_n = fed < n_prompt ? n_prompt - fed : 1;
+        const uint32_t g = max_gen - emitted < CHUNK ? max_gen - emitted : CHUNK;
+        const double t_before = seconds_since(t_start);
+        rc = ib_llama_generate(m, stream, cur, cur_n, pos, g, buf.data());
+        if (rc) return rc;
+        const double t_after = seconds_since(t_start);
+        const uint32_t first_gen_pos = pos + cur_n - 1;   // the forward at this position produced buf[0]
+        for (uint32_t i = 0; i < g; i++) {
+            const uint32_t tok = buf[i];
+            if (tok == eos_token) return IB_OK;           // chat_llama2.rs:158-160: the stop token ends the turn unreported
+            // The host sees a chunk's tokens together; their times are spread evenly over the chunk's forwards.
+            const double t = t_before + (t_after - t_before) * double(cur_n + i) / double(cur_n + g - 1);
+            const uint32_t at = first_gen_pos + i;
+            if (out(user, prev, tok, at, at - start_pos - 1, t)) { if (n_out) *n_out = emitted + 1; return IB_OK; }
+            emitted++;
+            if (n_out) *n_out = emitted;
+            prev = tok;
+        }
+        last = buf[g - 1];
+        pos = first_gen_pos + g;
+    }
     return IB_OK;
 }
 

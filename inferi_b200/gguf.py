@@ -222,9 +222,11 @@ def write_gguf(path: str, metadata: list[tuple[str, int, object]], tensors: list
             f.write(b"\0" * ((-len(raw)) % alignment))
 
 
-def write_llama_gguf(path: str, cfg: Llama2Config, weights: dict, tokens: list[str] | None = None, arch: str = "llama") -> None:
+def write_llama_gguf(path: str, cfg: Llama2Config, weights: dict, tokens: list[str] | None = None, arch: str = "llama",
+                     scores=None, special: tuple[int, int, int] | None = None, chat_template: str | None = None) -> None:
     """A checkpoint in the layout of `llama2.synth_weights` as a GGUF v3 file (tensor names of transformer.rs:304-315,
-    metadata keys of cpu.rs:81-88).  Without `tokens` the file carries no tokenizer and the vocabulary is read off token_embd."""
+    metadata keys of cpu.rs:81-88).  Without `tokens` the file carries no tokenizer and the vocabulary is read off token_embd;
+    `scores` and `special` = (bos, eos, unk) ids complete what `LlamaTokenizer::from_gguf` reads (llama2_tokenizer.rs:23-40)."""
     meta = [("general.architecture", STRING, arch), (f"{arch}.embedding_length", U32, cfg.hidden_size),
             (f"{arch}.feed_forward_length", U32, cfg.intermediate_size), (f"{arch}.block_count", U32, cfg.num_hidden_layers),
             (f"{arch}.attention.head_count", U32, cfg.num_attention_heads), (f"{arch}.attention.head_count_kv", U32, cfg.num_key_value_heads),
@@ -232,6 +234,12 @@ def write_llama_gguf(path: str, cfg: Llama2Config, weights: dict, tokens: list[s
             (f"{arch}.attention.layer_norm_rms_epsilon", F32, cfg.rms_norm_eps)]
     if tokens is not None:
         meta.append(("tokenizer.ggml.tokens", ARRAY, (STRING, tokens)))
+    if scores is not None:
+        meta.append(("tokenizer.ggml.scores", ARRAY, (F32, list(scores))))
+    if special is not None:
+        meta += [(f"tokenizer.ggml.{n}_token_id", U32, v) for n, v in zip(("bos", "eos", "unknown"), special)]
+    if chat_template is not None:
+        meta.append(("tokenizer.chat_template", STRING, chat_template))
     sh = cfg.shapes()
 
     def raw(t) -> bytes:

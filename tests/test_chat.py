@@ -1,0 +1,81 @@
+"""Chat template and prompt hand-off (host side; no GPU): `ChatTemplate` against renderings of the reference's bundled default
+template (tests/golden/chat_template.json) and against hand-written expectations of the published Llama-2 layout."""
+import json
+import os
+import re
+
+import pytest
+
+from inferi_b200.chat import LLAMA2_CHAT_TEMPLATE, ChatTemplate, Prompt
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "chat_template.json")
+
+
+def prompt_of(entries) -> Prompt:
+    p = Prompt()
+    for role, text in entries:
+        {"user": p.append_user, "assistant": p.append_assistant, "system": p.append_system}[role](text)
+    return p
+
+
+def squeeze(s: str) -> str:
+    return re.sub(r"\s+", "", s)
+
+
+@pytest.mark.parametrize("case", json.load(open(GOLDEN)), ids=lambda c: f"{len(c['entries'])}-entries")
+def test_default_template_renders_what_the_reference_default_renders(case):
+    # The reference's file leaves its own indentation between the turns; everything but white space must agree, and the
+    # rendering here carries no white space the conversation did not contain.
+    mine = ChatTemplate(LLAMA2_CHAT_TEMPLATE).apply(prompt_of(case["entries"]), case["bos"], case["eos"])
+    assert squeeze(mine) == squeeze(case["rendered"])
+    assert "  " not in mine and not mine.startswith((" ", "\n")) and not mine.endswith("\n")
+
+
+def test_default_template_layout():
+    p = prompt_of([["system", " be brief "], ["user", "hi there"], ["assistant", "hello"], ["user", "bye"]])
+    got = ChatTemplate(LLAMA2_CHAT_TEMPLATE).apply(p, "<s>", "</s>")
+    assert got == "<s>[INST] <<SYS>>\nbe brief\n<</SYS>>\n\nhi there [/INST] hello </s><s>[INST] bye [/INST]"
+
+
+def test_roles_must_alternate():
+    import jinja2
+    with pytest.raises(jinja2.TemplateError):
+        ChatTemplate(LLAMA2_CHAT_TEMPLATE).apply(prompt_of([["user", "a"], ["user", "b"]]), "<s>", "</s>")
+
+
+def test_template_globals_and_python_style_expressions():
+    # The globals of chat_template.rs:30-32 and the two constructs the reference rewrites for its engine (:12-16).
+    t = ChatTemplate("{{ bos_token }}{% for m in messages %}{{ m['content'].split(':')[-1] }}|{% endfor %}"
+                     "{% if add_generation_prompt %}<gen>{% endif %}{{ eos_token }}")
+    assert t.apply(prompt_of([["user", "a:b:c"], ["assistant", "x"]]), "<B>", "<E>") == "<B>c|x|<gen><E>"
+
+
+def test_block_trimming_is_on():
+    t = ChatTemplate("{% for m in messages %}\n{{ m['role'] }}\n{% endfor %}\n")
+    assert t.apply(prompt_of([["user", "a"], ["assistant", "b"]]), "", "") == "user\nassistant\n"
+
+
+def test_from_gguf_reads_the_metadata_template_or_falls_back(tmp_path):
+    from inferi_b200 import gguf as G
+    from inferi_b200.llama2 import Llama2Config
+    try:
+        G.load()
+    except Exception as e:      # the shared library is the parser; without it there is nothing to test
+        pytest.skip(f"shared library not built: {e}")
+    path = str(tmp_path / "m.gguf")
+    G.write_gguf(path, [("tokenizer.chat_template", G.STRING, "{{ bos_token }}X")], [])
+    g = G.Gguf(path)
+    assert ChatTemplate.from_gguf(g).template == "{{ bos_token }}X"
+    g.close()
+    G.write_gguf(path, [("general.name", G.STRING, "m")], [])
+    g = G.Gguf(path)
+    assert ChatTemplate.from_gguf(g).template == LLAMA2_CHAT_TEMPLATE
+    g.close()
+
+
+def test_prompt_display_and_jinja_input():
+    p = prompt_of([["system", "s"], ["user", "u"]])
+    assert str(p) == "[System] s\n[User] u\n"
+    assert p.to_jinja_input() == {"messages": [{"role": "system", "content": "s"}, {"role": "user", "content": "u"}]}
+    p.clear()
+    assert p.entries == []
