@@ -96,8 +96,9 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     // with a host-known position only the splits that will do work are launched
     uint32_t splits = a.max_splits;
     if (!a.pos_ptr) {
-        const uint32_t min_per = gqa4 ? GQA4_MIN_PER_SPLIT : ATTN_MIN_PER_SPLIT;
-        uint32_t need = (p.pos + nq + min_per - 1) / min_per;
+        uint32_t need, per;
+        if (gqa4) attn_split_plan(p.pos + nq, a.max_splits, need, per, GQA4_MIN_PER_SPLIT, GQA4_KNEE, GQA4_KNEE_PER);
+        else attn_split_plan(p.pos + nq, a.max_splits, need, per);
         if (need < splits) splits = need;
     }
     const dim3 grid(n_kv, splits, nq);

@@ -60,9 +60,16 @@ __device__ __forceinline__ void attn_bar(int id) { asm volatile("bar.sync %0, %1
 __host__ __device__ constexpr uint32_t attn_block_smem_floats(uint32_t hs, uint32_t kvm) { return ATTN_WARPS * kvm * hs + 2 * ATTN_WARPS * kvm + 4; }
 
 // The split of `total` positions: number of non-empty slices and positions per slice.
-__device__ __forceinline__ void attn_split_plan(uint32_t total, uint32_t max_splits, uint32_t &nsplit, uint32_t &per,
-                                                uint32_t min_per_split = ATTN_MIN_PER_SPLIT) {
+// With `knee` > 0 the slices stop multiplying at `knee` until each holds `knee_per` positions: the merge reads every
+// slice's partial (eight per L2 round trip), so beyond a dozen slices more of them only pay once they shorten the row loop
+// by more than they lengthen the merge.
+__host__ __device__ __forceinline__ void attn_split_plan(uint32_t total, uint32_t max_splits, uint32_t &nsplit, uint32_t &per,
+                                                         uint32_t min_per_split = ATTN_MIN_PER_SPLIT, uint32_t knee = 0, uint32_t knee_per = 0) {
     nsplit = (total + min_per_split - 1) / min_per_split;
+    if (knee && nsplit > knee) {
+        const uint32_t by_len = (total + knee_per - 1) / knee_per;
+        nsplit = by_len > knee ? by_len : knee;
+    }
     if (nsplit > max_splits) nsplit = max_splits;
     per = (total + nsplit - 1) / nsplit;
     nsplit = (total + per - 1) / per;  // every remaining split is non-empty

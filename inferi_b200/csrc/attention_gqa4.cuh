@@ -20,7 +20,11 @@
 namespace ib {
 
 constexpr uint32_t GQA4_ROWS_PER_WARP_STEP = 8;
-constexpr uint32_t GQA4_MIN_PER_SPLIT = ATTN_WARPS * GQA4_ROWS_PER_WARP_STEP;   // one step of every warp
+// Slices: one warp step of every warp (32 positions) each while there are at most 16 of them, then 16 slices that grow to
+// 128 positions, then slices of 128 positions up to the launch's maximum, then longer ones.  Measured on a B200 (us per
+// launch at 128 / 512 / 2048 / 8192 positions): 32 per slice throughout 4.6 / 6.1 / 12.6 / 17.1; 128 per slice 5.4 / 7.6 /
+// 9.1 / 17.1; 256 per slice 5.4 / 10.6 / 11.3 / 16.1.
+constexpr uint32_t GQA4_MIN_PER_SPLIT = ATTN_WARPS * GQA4_ROWS_PER_WARP_STEP, GQA4_KNEE = 16, GQA4_KNEE_PER = 128;
 
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
     unsigned long long ra, rb, rc, rd;
@@ -73,7 +77,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnAr
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t total = (a.pos_ptr ? *a.pos_ptr : a.p.pos) + 1;
     uint32_t nsplit, per;
-    attn_split_plan(total, a.max_splits, nsplit, per, GQA4_MIN_PER_SPLIT);
+    attn_split_plan(total, a.max_splits, nsplit, per, GQA4_MIN_PER_SPLIT, GQA4_KNEE, GQA4_KNEE_PER);
     if (split >= nsplit) return;
     const uint32_t t0 = split * per, t1 = min(total, t0 + per);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -129,14 +133,18 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnAr
 #pragma unroll
         for (int j = 0; j < EPL / 2; j++) acc[m][j] = make_float2(0.f, 0.f);
 
+    // The rows of the next iteration are requested before the current ones are used: a slice is then one cache round
+    // trip plus arithmetic, however many iterations it has, and twice the bytes are in flight per warp.
+    uint4 knext[STEPS], vnext[STEPS];
 #pragma unroll 1
     for (uint32_t base = base0; base < t1; base += ATTN_WARPS * ROWS) {
-        if (base != base0) {
+        const uint32_t nbase = base + ATTN_WARPS * ROWS;
+        if (nbase < t1) {
 #pragma unroll
             for (int s = 0; s < STEPS; s++) {
-                const uint32_t t = base + s * RPW + g, tc = t < t1 ? t : t1 - 1;
-                kraw[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
-                vraw[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
+                const uint32_t t = nbase + s * RPW + g, tc = t < t1 ? t : t1 - 1;
+                knext[s] = __ldcg(reinterpret_cast<const uint4 *>(kc + (size_t)tc * kv_dim));
+                vnext[s] = __ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)tc * kv_dim));
             }
         }
         // partial scores of the lane's 8 elements: v[s * KVM + m]
@@ -195,6 +203,10 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnAr
             for (int m = 0; m < KVM; m++)
 #pragma unroll
                 for (int j = 0; j < EPL / 2; j++) acc[m][j] = ffma2(make_float2(pv[m], pv[m]), v2[j], acc[m][j]);
+        }
+        if (nbase < t1) {
+#pragma unroll
+            for (int s = 0; s < STEPS; s++) { kraw[s] = knext[s]; vraw[s] = vnext[s]; }
         }
     }
 
@@ -258,12 +270,17 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnAr
         if (d_out == 0) *reinterpret_cast<float2 *>(part + m_out * slot + HS) = make_float2(mx, ls);
     }
 
-    __threadfence();
+    // The block's partial is published by one release/acquire arrival of thread 0: the barrier before it orders the other
+    // threads' stores ahead of the release, the barrier after it orders their reads of the other blocks' partials (from
+    // L2) behind the acquire.
     __syncthreads();
-    if (tid == 0) sm_last = (atomicAdd(a.counters + kvh, 1u) == nsplit - 1) ? 1u : 0u;
+    if (tid == 0) {
+        uint32_t old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(a.counters + kvh) : "memory");
+        sm_last = (old == nsplit - 1) ? 1u : 0u;
+    }
     __syncthreads();
     if (sm_last == 0u) return;
-    __threadfence();
     // merge of the kv head's partials: every thread adds up its outputs over the slices, eight slices at a time - their
     // (max, sum) pairs and their accumulator values are requested together (one round trip to L2 per eight slices), then
     // folded into a running (max, sum, accumulator) the way the main loop folds cache rows.

@@ -6,10 +6,14 @@
 // once per prompt token.  Here the weights are read once per prompt.
 //
 // gemm_quant_tc_kernel: out^T tile = W tile (128 rows of the quantized matrix) x X^T (the tokens' input vectors).
-//  * eight producer warps, two threads per weight row: dequantize 64 columns of the row per stage to f32, split the value
-//    into two f16 (w = hi + lo, exact to ~2^-22) and store both into shared memory in the K-major core-matrix layout the
-//    tensor core reads (8 rows x 16 bytes per core matrix, no swizzle); the same threads copy the tokens' inputs (already
-//    split into f16 hi / lo by the kernel that produced them) into tiles of the same layout;
+//  * the quantized blocks of the tile's 128 rows travel to shared memory by bulk copies (cp.async.bulk, one 256-column
+//    block per row and step, a ring of steps ahead of their use) - no thread-per-row global loads, which were 32 cache
+//    lines per load instruction and kept the L1 busy 91 % of the time;
+//  * eight producer warps, two threads per weight row: read the row's block from shared memory, dequantize 64 columns of
+//    the row per stage to f32, split the value into two f16 (w = hi + lo, exact to ~2^-22) and store both into shared
+//    memory in the K-major core-matrix layout the tensor core reads (8 rows x 16 bytes per core matrix, no swizzle);
+//  * the tokens' inputs (already split into f16 hi / lo by the kernel that produced them, and laid out in global memory
+//    as tiles of that same layout) arrive by one bulk copy per tile;
 //  * one thread issues, per 16 columns, three tcgen05.mma (hi x hi, hi x lo, lo x hi; lo x lo is below f32 resolution)
 //    that accumulate in f32 in tensor memory: the result matches the f32 arithmetic of the decode path to ~1e-6;
 //  * shared-memory stages cycle through mbarriers (filled by the producers, released by tcgen05.commit);
@@ -25,12 +29,14 @@ namespace ib {
 
 constexpr int TC_ROWS = 128;              // weight rows per CTA = M of the MMA
 constexpr int TC_KSTAGE = 64;             // columns per stage
-constexpr int TC_STAGES = 3;
+constexpr int TC_STAGES = 2;                // stages of split f16 tiles (W hi, W lo, X hi, X lo: 64 KiB each)
+constexpr uint32_t TC_RAW_MAX = 4;         // most stages of raw blocks (as many as fit are used)
 constexpr int TC_PRODUCER_WARPS = 8;       // two threads per weight row, 32 columns each per stage
 constexpr int TC_THREADS = (TC_PRODUCER_WARPS + 1) * 32;   // + 1 MMA warp
 constexpr uint32_t TC_TILE_BYTES = TC_ROWS * TC_KSTAGE * 2;                  // one f16 tile of 128 x 64
 constexpr uint32_t TC_STAGE_BYTES = 4 * TC_TILE_BYTES;                        // W hi, W lo, X hi, X lo
-constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 + 1024;  // + barriers and TMEM address, + slack to align the tiles to 1 KiB
+constexpr uint32_t TC_SMEM_FIXED = TC_STAGES * TC_STAGE_BYTES + 1024 + 1024;  // + barriers and TMEM address, + slack to align the tiles to 1 KiB
+constexpr uint32_t TC_SMEM_LIMIT = 227 * 1024;
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ unsigned long long tc_ns() {
@@ -82,27 +88,87 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 constexpr uint32_t TC_LBO = 128, TC_SBO = (TC_KSTAGE / 8) * 128;
 __device__ __forceinline__ uint32_t tc_chunk_off(uint32_t row, uint32_t k8) { return (row >> 3) * TC_SBO + k8 * TC_LBO + (row & 7) * 16; }
 
-// ---- 32 consecutive weights of a row (k0 a multiple of 32) as f32, from the device layout of the matrix ----
+// ---- 32 consecutive weights of a row (k0 a multiple of 32) as f32 ----
 __device__ __forceinline__ float tc_h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
 
-// The bytes a thread needs for its 32 weights, fetched one stage ahead of their conversion.
+// The bytes a thread needs for its 32 weights, read from the stage of raw blocks in shared memory.
 struct TcRaw {
     uint4 v[5];       // Q4_K: header, 32 quant bytes; Q5_K: + the 32 high-bit bytes; Q6_K: 32 low and 32 high bytes
     uint32_t s, d;    // Q6_K: the two scales, the block's f16 scale
 };
 
+// How a matrix reaches the producers.  0: Q4_K, 1: Q5_K, 2: Q6_K in the 8-block row layout - their blocks are copied into
+// shared memory by bulk copies, one 256-column block of every row of the tile per step; 3: everything else (read from
+// global memory element by element).
+constexpr int TC_PATH_Q4K = 0, TC_PATH_Q5K = 1, TC_PATH_Q6K = 2, TC_PATH_OTHER = 3;
+__host__ __device__ inline int tc_path(uint32_t qtype, uint32_t layout) {
+    return qtype == IB_Q4_K ? TC_PATH_Q4K : (qtype == IB_Q5_K ? TC_PATH_Q5K : ((qtype == IB_Q6_K && layout == LAYOUT_SOA) ? TC_PATH_Q6K : TC_PATH_OTHER));
+}
+// A raw stage holds one block of each of the tile's 128 rows.  Row strides are odd multiples of 16 bytes, so that the 16-byte
+// reads of 8 consecutive rows fall into different bank groups.  Q6_K: four arrays (low bits, high bits, scales, d).
+constexpr uint32_t TC_Q6_QL = 0, TC_Q6_QH = TC_ROWS * 144, TC_Q6_SC = TC_Q6_QH + TC_ROWS * 80, TC_Q6_D = TC_Q6_SC + TC_ROWS * 16;
+__host__ __device__ constexpr uint32_t tc_raw_stage_bytes(int path) {
+    return path == TC_PATH_Q4K ? TC_ROWS * 144u : (path == TC_PATH_Q5K ? TC_ROWS * 176u : (path == TC_PATH_Q6K ? TC_Q6_D + TC_ROWS * 16u : 0u));
+}
+
+__device__ __forceinline__ uint4 tc_lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t tc_lds16(uint32_t a) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+
+// One row's block of the step -> shared memory (the thread's own arrival announces the bytes).  `kb` = block number in the row.
+template <int PATH>
+__device__ __forceinline__ void tc_issue_raw(const uint8_t *wrow, uint32_t kb, uint32_t raw, uint32_t row, uint32_t bar) {
+    auto copy = [&](uint32_t dst, const uint8_t *src, uint32_t bytes) {
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    };
+    if (PATH == TC_PATH_Q4K || PATH == TC_PATH_Q5K) {
+        constexpr uint32_t B = PATH == TC_PATH_Q4K ? 144u : 176u;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(B) : "memory");
+        copy(raw + row * B, wrow + (size_t)kb * B, B);
+    } else if (PATH == TC_PATH_Q6K) {
+        const uint8_t *grp = wrow + (size_t)(kb >> 3) * 1680;
+        const uint32_t bb = kb & 7;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(128u + 64u + 16u + 16u) : "memory");
+        copy(raw + TC_Q6_QL + row * 144, grp + 128 * bb, 128);
+        copy(raw + TC_Q6_QH + row * 80, grp + 1024 + 64 * bb, 64);
+        copy(raw + TC_Q6_SC + row * 16, grp + 1536 + 16 * bb, 16);
+        copy(raw + TC_Q6_D + row * 16, grp + 1664, 16);
+    }
+}
+
+// The thread's bytes of the 64-column quarter `c` of the block (half `kh` of it): shared memory -> registers.
+template <int PATH>
+__device__ __forceinline__ void tc_read_raw(uint32_t raw, uint32_t row, uint32_t kb, uint32_t c, uint32_t kh, TcRaw &r) {
+    if (PATH == TC_PATH_Q4K) {
+        const uint32_t blk = raw + row * 144;
+        r.v[0] = tc_lds128(blk);
+        r.v[1] = tc_lds128(blk + 16 + 32 * c);
+        r.v[2] = tc_lds128(blk + 32 + 32 * c);
+    } else if (PATH == TC_PATH_Q5K) {
+        const uint32_t blk = raw + row * 176;
+        r.v[0] = tc_lds128(blk);
+        r.v[1] = tc_lds128(blk + 48 + 32 * c);
+        r.v[2] = tc_lds128(blk + 64 + 32 * c);
+        r.v[3] = tc_lds128(blk + 16);
+        r.v[4] = tc_lds128(blk + 32);
+    } else if (PATH == TC_PATH_Q6K) {
+        const uint32_t i = c >> 1, g = (2 * c + kh) & 3;
+        const uint32_t ql = raw + TC_Q6_QL + row * 144 + 64 * i + 32 * (g & 1), qh = raw + TC_Q6_QH + row * 80 + 32 * i;
+        r.v[0] = tc_lds128(ql); r.v[1] = tc_lds128(ql + 16); r.v[2] = tc_lds128(qh); r.v[3] = tc_lds128(qh + 16);
+        r.s = tc_lds16(raw + TC_Q6_SC + row * 16 + 8 * i + 2 * g);   // scales of l < 16 and l >= 16
+        r.d = tc_lds16(raw + TC_Q6_D + row * 16 + 2 * (kb & 7));
+    }
+}
+
 // crates/inferi/src/quantization.rs:364-402 (Q4_K) and :287-329 (Q5_K): sub-block j of the block, low or high nibbles of a
 // 32-byte chunk, w = d * sc * q - dmin * m
-template <bool Q5>
-__device__ __forceinline__ void tc_load32_q45k(const uint8_t *row, uint32_t k0, TcRaw &r) {
-    const uint8_t *blk = row + (size_t)(k0 >> 8) * (Q5 ? 176 : 144);
-    const uint32_t c = (k0 & 255) >> 6;
-    r.v[0] = __ldg(reinterpret_cast<const uint4 *>(blk));
-    const uint4 *qs = reinterpret_cast<const uint4 *>(blk + (Q5 ? 48 : 16) + 32 * c);
-    r.v[1] = __ldg(qs);
-    r.v[2] = __ldg(qs + 1);
-    if (Q5) { r.v[3] = __ldg(reinterpret_cast<const uint4 *>(blk + 16)); r.v[4] = __ldg(reinterpret_cast<const uint4 *>(blk + 32)); }
-}
 template <bool Q5>
 __device__ __forceinline__ void tc_convert32_q45k(const TcRaw &r, uint32_t k0, float (&w)[32]) {
     const uint32_t j = (k0 & 255) >> 5, c = j >> 1, high = j & 1;
@@ -126,15 +192,6 @@ __device__ __forceinline__ void tc_convert32_q45k(const TcRaw &r, uint32_t k0, f
 }
 
 // crates/inferi/src/quantization.rs:227-256, rows stored as groups of 8 blocks [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d]
-__device__ __forceinline__ void tc_load32_q6k_soa(const uint8_t *row, uint32_t k0, TcRaw &r) {
-    const uint32_t b = k0 >> 8, bb = b & 7, e0 = k0 & 255, i = e0 >> 7, g = (e0 >> 5) & 3;
-    const uint8_t *grp = row + (size_t)(b >> 3) * 1680;
-    const uint4 *ql = reinterpret_cast<const uint4 *>(grp + 128 * bb + 64 * i + 32 * (g & 1));
-    const uint4 *qh = reinterpret_cast<const uint4 *>(grp + 1024 + 64 * bb + 32 * i);
-    r.v[0] = __ldg(ql); r.v[1] = __ldg(ql + 1); r.v[2] = __ldg(qh); r.v[3] = __ldg(qh + 1);
-    r.s = __ldg(reinterpret_cast<const unsigned short *>(grp + 1536 + 16 * bb + 8 * i + 2 * g));   // scales of l < 16 and l >= 16
-    r.d = __ldg(reinterpret_cast<const unsigned short *>(grp + 1664 + 2 * bb));
-}
 __device__ __forceinline__ void tc_convert32_q6k_soa(const TcRaw &r, uint32_t k0, float (&w)[32]) {
     const uint32_t g = ((k0 & 255) >> 5) & 3;
     const float d = tc_h2f(r.d);
@@ -151,52 +208,62 @@ __device__ __forceinline__ void tc_convert32_q6k_soa(const TcRaw &r, uint32_t k0
     }
 }
 
-// 0: Q4_K, 1: Q5_K, 2: Q6_K in the 8-block row layout, 3: everything else (converted element by element, no prefetch)
-__device__ __forceinline__ uint32_t tc_path(const QDesc &q) {
-    return q.qtype == IB_Q4_K ? 0u : (q.qtype == IB_Q5_K ? 1u : ((q.qtype == IB_Q6_K && q.layout == LAYOUT_SOA) ? 2u : 3u));
-}
-__device__ __forceinline__ void tc_load32(uint32_t path, const uint8_t *row, uint32_t k0, TcRaw &r) {
-    if (path == 0) tc_load32_q45k<false>(row, k0, r);
-    else if (path == 1) tc_load32_q45k<true>(row, k0, r);
-    else if (path == 2) tc_load32_q6k_soa(row, k0, r);
-}
-__device__ __forceinline__ void tc_convert32(uint32_t path, const QDesc &q, const uint8_t *row, const TcRaw &r, uint32_t k0, float (&w)[32]) {
-    if (path == 0) tc_convert32_q45k<false>(r, k0, w);
-    else if (path == 1) tc_convert32_q45k<true>(r, k0, w);
-    else if (path == 2) tc_convert32_q6k_soa(r, k0, w);
+template <int PATH>
+__device__ __forceinline__ void tc_convert32(const QDesc &q, const uint8_t *row, const TcRaw &r, uint32_t k0, float (&w)[32]) {
+    if (PATH == TC_PATH_Q4K) tc_convert32_q45k<false>(r, k0, w);
+    else if (PATH == TC_PATH_Q5K) tc_convert32_q45k<true>(r, k0, w);
+    else if (PATH == TC_PATH_Q6K) tc_convert32_q6k_soa(r, k0, w);
     else {
 #pragma unroll
         for (int e = 0; e < 32; e++) w[e] = dequant_at(q, row, k0 + e);   // unrolled: w stays in registers
     }
 }
 
+// The tokens' inputs in global memory are laid out the way the tensor core reads them from shared memory: per 64 columns
+// one tile of 128 token rows in the K-major core-matrix layout (16 KiB), so that a stage's tile is one bulk copy.
+__host__ __device__ inline size_t tc_x_index(uint32_t t, uint32_t c) {
+    return (size_t)(c >> 6) * (TC_ROWS * TC_KSTAGE) + ((t >> 3) * TC_SBO + ((c & 63) >> 3) * TC_LBO + (t & 7) * 16) / 2 + (c & 7);
+}
+
 struct GemmTcParams {
     QDesc w;                    // the quantized matrix, device layout
     uint32_t rows, cols;        // rows % 128 == 0, cols % 256 == 0
-    const __half *x_hi, *x_lo;  // [n_pad][cols] row-major: the tokens' inputs split into two f16
-    uint32_t n_tokens, n_pad;   // n_pad = n_tokens rounded up to 16, <= 128; rows n_tokens .. n_pad-1 of x_* are zero
+    const __half *x_hi, *x_lo;  // the tokens' inputs split into two f16, tiled (tc_x_index); rows n_tokens .. n_pad-1 are zero
+    uint32_t n_tokens, n_pad;   // n_pad = n_tokens rounded up to 16, <= 128
     float *out;                 // [ksplit][n_tokens][rows] partial planes
     uint32_t ksplit;            // gridDim.y; cols / ksplit is a multiple of 256
+    uint32_t raw_stages;        // depth of the ring of raw blocks
     uint32_t *err;
     unsigned long long wait_ns;
 };
 
+template <int PATH>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const GemmTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES);   // full[S], empty[S], acc
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 1);
+    constexpr uint32_t RAW_BYTES = tc_raw_stage_bytes(PATH);
+    const uint32_t R = p.raw_stages;
+    const uint32_t raw0 = tc_smem_u32(smem + TC_STAGES * TC_STAGE_BYTES);
+    // barriers: full[S], empty[S], accumulator, raw_full[R], raw_empty[R]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES + R * RAW_BYTES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 1 + 2 * TC_RAW_MAX);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bar0 = tc_smem_u32(bars);
+    const uint32_t bar_acc = bar0 + 8 * (2 * TC_STAGES), bar_rawfull = bar_acc + 8, bar_rawempty = bar_rawfull + 8 * TC_RAW_MAX;
     const uint32_t row0 = blockIdx.x * TC_ROWS;
-    const uint32_t kspan = p.cols / p.ksplit, kbeg = blockIdx.y * kspan, nstage = kspan / TC_KSTAGE;
+    const uint32_t kspan = p.cols / p.ksplit, kbeg = blockIdx.y * kspan, nstage = kspan / TC_KSTAGE, nblk = kspan / 256;
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(TC_PRODUCER_WARPS * 32));   // full: every producer thread
+            // full: every producer thread + the thread that announces the bytes of the inputs' tiles
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(TC_PRODUCER_WARPS * 32 + 1));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (TC_STAGES + s)), "r"(1));  // empty: one tcgen05.commit
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (2 * TC_STAGES)), "r"(1));       // accumulator complete
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_acc), "r"(1));       // accumulator complete
+        for (uint32_t s = 0; s < TC_RAW_MAX; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawfull + 8 * s), "r"(TC_ROWS));                    // one arrival per row copy
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawempty + 8 * s), "r"(TC_PRODUCER_WARPS * 32));    // every producer thread has read it
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_PRODUCER_WARPS) {
@@ -211,70 +278,73 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     bool ok = true;
 
     if (warp < TC_PRODUCER_WARPS) {
-        // ===== producers: thread = (weight row and token row `tid & 127`, half `tid >> 7` of the stage's 64 columns) =====
+        // ===== producers: thread = (weight row `tid & 127`, half `tid >> 7` of the stage's 64 columns) =====
         const uint32_t row = tid & (TC_ROWS - 1), kh = tid >> 7;
         const uint8_t *wrow = p.w.w + (size_t)(row0 + row) * p.w.row_bytes;
-        // The tokens' inputs are copied by all producer threads together, in an order that keeps the global loads dense: the
-        // 32 lanes of a warp take 8 token rows x 4 consecutive 16-byte chunks (64 contiguous bytes per row), not one row
-        // each (that was 32 cache lines per load instruction and made the L1 the limiter of the whole kernel).
-        uint32_t xrow[4], xk8[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const uint32_t id = i * (TC_PRODUCER_WARPS * 32) + tid;   // chunk number: 128 rows x 8 chunks per tile
-            xrow[i] = ((id >> 6) << 3) | (id & 7);
-            xk8[i] = (id >> 3) & 7;
-        }
-        // the bytes of a stage are requested one stage ahead of their use: the conversion of stage i overlaps the loads of
-        // stage i + 1 (weights and inputs do not depend on a stage of shared memory being free)
-        const uint32_t path = tc_path(p.w);
-        TcRaw raw;
-        uint4 xa[4], xb[4];
-        auto fetch = [&](uint32_t it) {
-            const uint32_t kst = kbeg + it * TC_KSTAGE;
-            tc_load32(path, wrow, kst + 32 * kh, raw);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const bool has = xrow[j] < p.n_pad;
-                const size_t at = (size_t)(has ? xrow[j] : 0) * p.cols + kst + 8 * xk8[j];
-                xa[j] = has ? __ldg(reinterpret_cast<const uint4 *>(p.x_hi + at)) : make_uint4(0, 0, 0, 0);
-                xb[j] = has ? __ldg(reinterpret_cast<const uint4 *>(p.x_lo + at)) : make_uint4(0, 0, 0, 0);
-            }
-        };
-        if (nstage) fetch(0);
+        const uint32_t kb0 = kbeg >> 8;
+        constexpr bool RAW = PATH != TC_PATH_OTHER;
+        // the ring of raw blocks is filled ahead: one block of every row per step, each row by its own bulk copy
+        if (RAW && tid < TC_ROWS)
+            for (uint32_t b = 0; b < R && b < nblk; b++) tc_issue_raw<PATH>(wrow, kb0 + b, raw0 + b * RAW_BYTES, row, bar_rawfull + 8 * b);
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
+            const uint32_t b = it >> 2, c = it & 3, slot = b % R;
+            if (RAW && c == 0) {
+                if (b >= 1 && tid < TC_ROWS && b - 1 + R < nblk) {
+                    // the slot of the previous step is refilled once every producer thread has read it
+                    const uint32_t ps = (b - 1) % R;
+                    ok = tc_wait(bar_rawempty + 8 * ps, ((b - 1) / R) & 1, p.wait_ns, p.err, 8);
+                    if (!ok) break;
+                    tc_issue_raw<PATH>(wrow, kb0 + b - 1 + R, raw0 + ps * RAW_BYTES, row, bar_rawfull + 8 * ps);
+                }
+                ok = tc_wait(bar_rawfull + 8 * slot, (b / R) & 1, p.wait_ns, p.err, 8);
+                if (!ok) break;
+            }
             const uint32_t k0 = kbeg + it * TC_KSTAGE + 32 * kh;
+            TcRaw raw;
+            if (RAW) tc_read_raw<PATH>(raw0 + slot * RAW_BYTES, row, kb0 + b, c, kh, raw);
             float w[32];
-            tc_convert32(path, p.w, wrow, raw, k0, w);
-            uint4 ca[4], cb[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) { ca[j] = xa[j]; cb[j] = xb[j]; }
-            if (it + 1 < nstage) fetch(it + 1);
+            tc_convert32<PATH>(p.w, wrow, raw, k0, w);
+            if (RAW && c == 3) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_rawempty + 8 * slot) : "memory");
             if (round > 0) ok = tc_wait(bar0 + 8 * (TC_STAGES + s), (round - 1) & 1, p.wait_ns, p.err, 8);
             if (!ok) break;
             uint8_t *st = smem + s * TC_STAGE_BYTES;
+            if (tid == 0) {
+                // the inputs' two tiles of this stage: one bulk copy each, straight into the layout the tensor core reads
+                const uint32_t full = bar0 + 8 * s, dst = tc_smem_u32(st + 2 * TC_TILE_BYTES);
+                const size_t at = (size_t)((kbeg >> 6) + it) * (TC_ROWS * TC_KSTAGE);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * TC_TILE_BYTES) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p.x_hi + at),
+                             "r"(TC_TILE_BYTES), "r"(full)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + TC_TILE_BYTES), "l"(p.x_lo + at),
+                             "r"(TC_TILE_BYTES), "r"(full)
+                             : "memory");
+            }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 uint4 hi, lo;
                 uint32_t *hp = &hi.x, *lp = &lo.x;
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const float a = w[8 * j + 2 * e], b = w[8 * j + 2 * e + 1];
-                    const __half2 h = __floats2half2_rn(a, b);
+                    const float a = w[8 * j + 2 * e], b2 = w[8 * j + 2 * e + 1];
+                    const __half2 h = __floats2half2_rn(a, b2);
                     const float2 back = __half22float2(h);
-                    const __half2 l = __floats2half2_rn(a - back.x, b - back.y);
+                    const __half2 l = __floats2half2_rn(a - back.x, b2 - back.y);
                     hp[e] = *reinterpret_cast<const uint32_t *>(&h);
                     lp[e] = *reinterpret_cast<const uint32_t *>(&l);
                 }
                 const uint32_t off = tc_chunk_off(row, 4 * kh + j);
                 *reinterpret_cast<uint4 *>(st + off) = hi;
                 *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = lo;
-                const uint32_t xoff = tc_chunk_off(xrow[j], xk8[j]);
-                *reinterpret_cast<uint4 *>(st + 2 * TC_TILE_BYTES + xoff) = ca[j];
-                *reinterpret_cast<uint4 *>(st + 3 * TC_TILE_BYTES + xoff) = cb[j];
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
+        }
+        if (!ok) {
+            // a wait gave up: bulk copies of this CTA may still be in flight; give them time to land before the CTA ends
+            const unsigned long long t0 = tc_ns();
+            while (tc_ns() - t0 < 100000ull) {}
         }
     } else if (lane == 0) {
         // ===== MMA issue: one thread =====
@@ -296,13 +366,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
             }
             tc_commit(bar0 + 8 * (TC_STAGES + s));   // the stage is free again once these MMAs have read it
         }
-        if (ok) tc_commit(bar0 + 8 * (2 * TC_STAGES));   // ... and the accumulator is complete when all of them are done
+        if (ok) tc_commit(bar_acc);   // ... and the accumulator is complete when all of them are done
     }
 
     if (warp < TC_PRODUCER_WARPS) {
         // ===== epilogue: TMEM lane = weight row, column = token; stored as [token][row].  A warp reaches the 32 lanes
         // 32 * (warp % 4); warps 0-3 take the first half of the token columns, warps 4-7 the second =====
-        if (ok) ok = tc_wait(bar0 + 8 * (2 * TC_STAGES), 0, p.wait_ns, p.err, 10);
+        if (ok) ok = tc_wait(bar_acc, 0, p.wait_ns, p.err, 10);
         ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-wide instructions
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
@@ -350,12 +420,12 @@ __global__ void prefill_embed_kernel(QDesc embd, const uint32_t *tokens, uint32_
 }
 
 // One CTA per token row: y = (x * rsqrt(mean(x^2) + eps)) * w (crates/inferi-shaders/src/rms_norm.rs:112-120; `w` null: y = x),
-// stored as the two f16 halves the GEMM reads.  Rows n .. n_pad-1 are zero-filled.
+// stored as the two f16 halves the GEMM reads, in its tiled layout (tc_x_index).  Rows n .. n_pad-1 are zero-filled.
 __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X, const float *w, float eps, uint32_t n, uint32_t cols, __half *hi, __half *lo) {
     __shared__ float red[8];
     const uint32_t t = blockIdx.x;
     if (t >= n) {
-        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { hi[(size_t)t * cols + c] = __float2half_rn(0.f); lo[(size_t)t * cols + c] = __float2half_rn(0.f); }
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { hi[tc_x_index(t, c)] = __float2half_rn(0.f); lo[tc_x_index(t, c)] = __float2half_rn(0.f); }
         return;
     }
     const float *x = X + (size_t)t * cols;
@@ -371,7 +441,7 @@ __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X,
         for (int i = 0; i < 8; i++) tot += red[i];
         rms = 1.0f / sqrtf(tot / (float)cols + eps);
     }
-    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) split_store(hi, lo, (size_t)t * cols + c, w ? (x[c] * rms) * w[c] : x[c]);
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) split_store(hi, lo, tc_x_index(t, c), w ? (x[c] * rms) * w[c] : x[c]);
 }
 
 __device__ __forceinline__ float plane_sum(const float *planes, uint32_t ksplit, size_t plane_elems, size_t i) {
@@ -382,16 +452,23 @@ __device__ __forceinline__ float plane_sum(const float *planes, uint32_t ksplit,
 
 // One thread per pair of neighbouring rows (the rotation acts on pairs).
 __global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
-    const size_t plane = (size_t)p.n * p.rows, pairs = plane / 2;
+    // PE_SWIGLU also zero-fills the padding rows n .. n_pad-1 of the split product (the GEMM that follows reads them)
+    const uint32_t n_rows = p.mode == PE_SWIGLU ? ((p.n + 15) & ~15u) : p.n;
+    const size_t plane = (size_t)p.n * p.rows, pairs = (size_t)n_rows * p.rows / 2;
     for (size_t pi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pi < pairs; pi += (size_t)gridDim.x * blockDim.x) {
         const size_t i = 2 * pi;
         const uint32_t t = (uint32_t)(i / p.rows), r = (uint32_t)(i % p.rows);
+        if (t >= p.n) {
+            split_store(p.hi, p.lo, tc_x_index(t, r), 0.f);
+            split_store(p.hi, p.lo, tc_x_index(t, r + 1), 0.f);
+            continue;
+        }
         float a = plane_sum(p.planes, p.ksplit, plane, i), b = plane_sum(p.planes, p.ksplit, plane, i + 1);
         if (p.mode == PE_SWIGLU) {
             // crates/inferi-shaders/src/silu.rs:16-19,46-52
             const float ua = plane_sum(p.planes2, p.ksplit, plane, i), ub = plane_sum(p.planes2, p.ksplit, plane, i + 1);
-            split_store(p.hi, p.lo, i, ua * (a / (1.0f + expf(-a))));
-            split_store(p.hi, p.lo, i + 1, ub * (b / (1.0f + expf(-b))));
+            split_store(p.hi, p.lo, tc_x_index(t, r), ua * (a / (1.0f + expf(-a))));
+            split_store(p.hi, p.lo, tc_x_index(t, r + 1), ub * (b / (1.0f + expf(-b))));
             continue;
         }
         if (p.mode == PE_RESIDUAL) { p.out[i] += a; p.out[i + 1] += b; continue; }
@@ -430,17 +507,28 @@ bool prefill_gemm_eligible(const ib_qtensor *m) {
 }
 
 int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, const __half *x_hi, const __half *x_lo, uint32_t n, float *planes, uint32_t ksplit) {
-    static bool attr_set[16] = {false};
-    if (!attr_set[ctx->device & 15]) {
-        IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_quant_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
-        attr_set[ctx->device & 15] = true;
+    const int path = tc_path((uint32_t)m->qtype, m->layout);
+    const uint32_t raw_bytes = tc_raw_stage_bytes(path);
+    uint32_t raw_stages = raw_bytes ? (TC_SMEM_LIMIT - TC_SMEM_FIXED) / raw_bytes : 1;
+    if (raw_stages > TC_RAW_MAX) raw_stages = TC_RAW_MAX;
+    const uint32_t smem_bytes = TC_SMEM_FIXED + raw_stages * raw_bytes;
+    void (*kernel)(GemmTcParams) = path == TC_PATH_Q4K ? gemm_quant_tc_kernel<TC_PATH_Q4K>
+                                   : (path == TC_PATH_Q5K ? gemm_quant_tc_kernel<TC_PATH_Q5K>
+                                                          : (path == TC_PATH_Q6K ? gemm_quant_tc_kernel<TC_PATH_Q6K> : gemm_quant_tc_kernel<TC_PATH_OTHER>));
+    static bool attr_set[16][4] = {};
+    if (!attr_set[ctx->device & 15][path]) {
+        IB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+        attr_set[ctx->device & 15][path] = true;
     }
+    IB_REQUIRE(((uintptr_t)m->dev % 16) == 0 && (m->row_bytes % 16) == 0 && ((uintptr_t)x_hi % 16) == 0 && ((uintptr_t)x_lo % 16) == 0,
+               "prefill GEMM: the matrix rows and the input tiles must be 16-byte aligned for the bulk copies");
     GemmTcParams p;
+    p.raw_stages = raw_stages;
     p.w = QDesc{m->dev, m->row_bytes, (uint32_t)m->qtype, m->layout, m->nb};
     p.rows = (uint32_t)m->rows; p.cols = (uint32_t)m->cols;
     p.x_hi = x_hi; p.x_lo = x_lo; p.n_tokens = n; p.n_pad = (n + 15) & ~15u;
     p.out = planes; p.ksplit = ksplit; p.err = ctx->err_dev; p.wait_ns = ctx->wait_limit_ns;
-    gemm_quant_tc_kernel<<<dim3(p.rows / TC_ROWS, ksplit), TC_THREADS, TC_SMEM_BYTES, s>>>(p);
+    kernel<<<dim3(p.rows / TC_ROWS, ksplit), TC_THREADS, smem_bytes, s>>>(p);
     ctx->launches++;
     IB_CHECK_CUDA(cudaGetLastError());
     return IB_OK;
@@ -463,17 +551,9 @@ int32_t launch_prefill_norm_split(ib_ctx *ctx, cudaStream_t s, const float *X, c
 }
 
 int32_t launch_prefill_epilogue(ib_ctx *ctx, cudaStream_t s, const PrefillEpiParams &p) {
-    const size_t pairs = (size_t)p.n * p.rows / 2;
+    const size_t pairs = (size_t)((p.n + 15) & ~15u) * p.rows / 2;
     unsigned grid = (unsigned)((pairs + 255) / 256);
     if (grid > 4096) grid = 4096;
-    if (p.mode == PE_SWIGLU) {
-        // the padding rows of the split product must be zero for the GEMM that follows
-        const uint32_t n_pad = (p.n + 15) & ~15u;
-        if (n_pad > p.n) {
-            IB_CHECK_CUDA(cudaMemsetAsync(p.hi + (size_t)p.n * p.rows, 0, (size_t)(n_pad - p.n) * p.rows * sizeof(__half), s));
-            IB_CHECK_CUDA(cudaMemsetAsync(p.lo + (size_t)p.n * p.rows, 0, (size_t)(n_pad - p.n) * p.rows * sizeof(__half), s));
-        }
-    }
     prefill_epilogue_kernel<<<grid, 256, 0, s>>>(p);
     ctx->launches++;
     IB_CHECK_CUDA(cudaGetLastError());

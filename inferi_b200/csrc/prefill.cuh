@@ -22,7 +22,8 @@ struct PrefillEpiParams {
 
 uint32_t prefill_ksplit(const ib_ctx *ctx, uint32_t rows, uint32_t cols);
 bool prefill_gemm_eligible(const ib_qtensor *m);
-// planes[ksplit][n][rows] = partial sums of W . x_t over the K ranges; x_hi / x_lo: [(n rounded up to 16)][cols], padding rows zero
+// planes[ksplit][n][rows] = partial sums of W . x_t over the K ranges; x_hi / x_lo: 128 x cols halves in the tiled layout that
+// launch_prefill_norm_split and the PE_SWIGLU epilogue write (one 16 KiB tile per 64 columns), rows n .. (n rounded up to 16) - 1 zero
 int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, const __half *x_hi, const __half *x_lo, uint32_t n, float *planes, uint32_t ksplit);
 int32_t launch_prefill_embed(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *embd, const uint32_t *tokens_dev, uint32_t n, uint32_t vocab, float *X);
 int32_t launch_prefill_norm_split(ib_ctx *ctx, cudaStream_t s, const float *X, const float *w, float eps, uint32_t n, uint32_t cols, __half *hi, __half *lo);

@@ -108,8 +108,8 @@ def test_turn_ends_when_the_context_is_full(backend, weights):
 def test_full_turn_from_a_gguf_file(backend, tmp_path):
     """Template -> tokenizer -> token loop on a file with a vocabulary: the three event kinds in the reference's order."""
     from inferi_b200 import gguf as G
-    cfg = Llama2Config(256, 512, 2, 4, 2, 300, 256, 10000.0, 1e-5)
-    w = synth_weights(cfg, seed=9)
+    cfg = CFG
+    w = synth_weights(cfg, seed=9, recipe=RECIPE)
     vocab = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "[", "]", "INST", "/", "hi", "▁hi", "he", "l", "o", "▁[", "a", "b", "c"]
     vocab += [f"w{i}" for i in range(cfg.vocab_size - len(vocab))]
     path = str(tmp_path / "chat.gguf")
