@@ -29,13 +29,14 @@ namespace ib {
 
 constexpr int TC_ROWS = 128;              // weight rows per CTA = M of the MMA
 constexpr int TC_KSTAGE = 64;             // columns per stage
-constexpr int TC_STAGES = 2;                // stages of split f16 tiles (W hi, W lo, X hi, X lo: 64 KiB each)
+constexpr int TC_STAGES = 2;                // stages of the weights' split f16 tiles (W hi, W lo: 32 KiB each)
+constexpr int TC_XSTAGES = 3;               // stages of the inputs' tiles (X hi, X lo: 32 KiB each), requested further ahead: they come from L2
 constexpr uint32_t TC_RAW_MAX = 4;         // most stages of raw blocks (as many as fit are used)
-constexpr int TC_PRODUCER_WARPS = 8;       // two threads per weight row, 32 columns each per stage
-constexpr int TC_THREADS = (TC_PRODUCER_WARPS + 1) * 32;   // + 1 MMA warp
+constexpr int TC_PRODUCER_WARPS = 16;      // four threads per weight row, 16 columns each per stage (4 warps per scheduler hide the conversion's latencies)
+constexpr int TC_THREADS = (TC_PRODUCER_WARPS + 2) * 32;   // + the MMA warp + the warp that requests the inputs' tiles
 constexpr uint32_t TC_TILE_BYTES = TC_ROWS * TC_KSTAGE * 2;                  // one f16 tile of 128 x 64
-constexpr uint32_t TC_STAGE_BYTES = 4 * TC_TILE_BYTES;                        // W hi, W lo, X hi, X lo
-constexpr uint32_t TC_SMEM_FIXED = TC_STAGES * TC_STAGE_BYTES + 1024 + 1024;  // + barriers and TMEM address, + slack to align the tiles to 1 KiB
+constexpr uint32_t TC_STAGE_BYTES = 2 * TC_TILE_BYTES;                        // hi and lo
+constexpr uint32_t TC_SMEM_FIXED = (TC_STAGES + TC_XSTAGES) * TC_STAGE_BYTES + 1024 + 1024;  // + barriers and TMEM address, + slack to align the tiles to 1 KiB
 constexpr uint32_t TC_SMEM_LIMIT = 227 * 1024;
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -46,10 +47,17 @@ __device__ __forceinline__ unsigned long long tc_ns() {
 }
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns, uint32_t *err, uint32_t code) {
     uint32_t ok = 0;
+    // the common case - the phase is already complete - costs one instruction; the clock (a long-latency read) is only
+    // looked at once a try has failed
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
     const unsigned long long t0 = tc_ns();
     for (;;) {
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
+#pragma unroll 1
+        for (int i = 0; i < 64; i++) {
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) return true;
+        }
         if (tc_ns() - t0 > limit_ns) break;
     }
     if (err) {
@@ -88,14 +96,8 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 constexpr uint32_t TC_LBO = 128, TC_SBO = (TC_KSTAGE / 8) * 128;
 __device__ __forceinline__ uint32_t tc_chunk_off(uint32_t row, uint32_t k8) { return (row >> 3) * TC_SBO + k8 * TC_LBO + (row & 7) * 16; }
 
-// ---- 32 consecutive weights of a row (k0 a multiple of 32) as f32 ----
+// ---- 16 consecutive weights of a row (k0 a multiple of 16) as f32 ----
 __device__ __forceinline__ float tc_h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
-
-// The bytes a thread needs for its 32 weights, read from the stage of raw blocks in shared memory.
-struct TcRaw {
-    uint4 v[5];       // Q4_K: header, 32 quant bytes; Q5_K: + the 32 high-bit bytes; Q6_K: 32 low and 32 high bytes
-    uint32_t s, d;    // Q6_K: the two scales, the block's f16 scale
-};
 
 // How a matrix reaches the producers.  0: Q4_K, 1: Q5_K, 2: Q6_K in the 8-block row layout - their blocks are copied into
 // shared memory by bulk copies, one 256-column block of every row of the tile per step; 3: everything else (read from
@@ -116,13 +118,19 @@ __device__ __forceinline__ uint4 tc_lds128(uint32_t a) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
+__device__ __forceinline__ uint32_t tc_lds8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ uint32_t tc_lds16(uint32_t a) {
     unsigned short v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
     return v;
 }
 
-// One row's block of the step -> shared memory (the thread's own arrival announces the bytes).  `kb` = block number in the row.
+// One row's block of the step -> shared memory; called by whole warps (lane 0's arrival announces the warp's bytes: an arrival
+// per thread would be hundreds of serialized updates of one barrier word per step).  `kb` = block number in the row.
 template <int PATH>
 __device__ __forceinline__ void tc_issue_raw(const uint8_t *wrow, uint32_t kb, uint32_t raw, uint32_t row, uint32_t bar) {
     auto copy = [&](uint32_t dst, const uint8_t *src, uint32_t bytes) {
@@ -130,12 +138,14 @@ __device__ __forceinline__ void tc_issue_raw(const uint8_t *wrow, uint32_t kb, u
     };
     if (PATH == TC_PATH_Q4K || PATH == TC_PATH_Q5K) {
         constexpr uint32_t B = PATH == TC_PATH_Q4K ? 144u : 176u;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(B) : "memory");
+        if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(32u * B) : "memory");
+        __syncwarp();
         copy(raw + row * B, wrow + (size_t)kb * B, B);
     } else if (PATH == TC_PATH_Q6K) {
         const uint8_t *grp = wrow + (size_t)(kb >> 3) * 1680;
         const uint32_t bb = kb & 7;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(128u + 64u + 16u + 16u) : "memory");
+        if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(32u * (128u + 64u + 16u + 16u)) : "memory");
+        __syncwarp();
         copy(raw + TC_Q6_QL + row * 144, grp + 128 * bb, 128);
         copy(raw + TC_Q6_QH + row * 80, grp + 1024 + 64 * bb, 64);
         copy(raw + TC_Q6_SC + row * 16, grp + 1536 + 16 * bb, 16);
@@ -143,26 +153,28 @@ __device__ __forceinline__ void tc_issue_raw(const uint8_t *wrow, uint32_t kb, u
     }
 }
 
-// The thread's bytes of the 64-column quarter `c` of the block (half `kh` of it): shared memory -> registers.
+// The thread's bytes of 16 weights - sixteenth `kq` (0..3) of the 64-column quarter `c` of the block: shared memory -> registers.
+struct TcRaw {
+    uint4 hdr, q, h;  // Q4_K / Q5_K: header, 16 quant bytes, (Q5_K) the 16 high-bit bytes; Q6_K: q = low bits, h = high bits
+    uint32_t s, d;    // Q6_K: the scale of the 16 weights, the block's f16 scale
+};
 template <int PATH>
-__device__ __forceinline__ void tc_read_raw(uint32_t raw, uint32_t row, uint32_t kb, uint32_t c, uint32_t kh, TcRaw &r) {
+__device__ __forceinline__ void tc_read_raw(uint32_t raw, uint32_t row, uint32_t kb, uint32_t c, uint32_t kq, TcRaw &r) {
+    const uint32_t hq = kq & 1;   // which 16 of the sub-block's 32 weights
     if (PATH == TC_PATH_Q4K) {
         const uint32_t blk = raw + row * 144;
-        r.v[0] = tc_lds128(blk);
-        r.v[1] = tc_lds128(blk + 16 + 32 * c);
-        r.v[2] = tc_lds128(blk + 32 + 32 * c);
+        r.hdr = tc_lds128(blk);
+        r.q = tc_lds128(blk + 16 + 32 * c + 16 * hq);
     } else if (PATH == TC_PATH_Q5K) {
         const uint32_t blk = raw + row * 176;
-        r.v[0] = tc_lds128(blk);
-        r.v[1] = tc_lds128(blk + 48 + 32 * c);
-        r.v[2] = tc_lds128(blk + 64 + 32 * c);
-        r.v[3] = tc_lds128(blk + 16);
-        r.v[4] = tc_lds128(blk + 32);
+        r.hdr = tc_lds128(blk);
+        r.q = tc_lds128(blk + 48 + 32 * c + 16 * hq);
+        r.h = tc_lds128(blk + 16 + 16 * hq);
     } else if (PATH == TC_PATH_Q6K) {
-        const uint32_t i = c >> 1, g = (2 * c + kh) & 3;
-        const uint32_t ql = raw + TC_Q6_QL + row * 144 + 64 * i + 32 * (g & 1), qh = raw + TC_Q6_QH + row * 80 + 32 * i;
-        r.v[0] = tc_lds128(ql); r.v[1] = tc_lds128(ql + 16); r.v[2] = tc_lds128(qh); r.v[3] = tc_lds128(qh + 16);
-        r.s = tc_lds16(raw + TC_Q6_SC + row * 16 + 8 * i + 2 * g);   // scales of l < 16 and l >= 16
+        const uint32_t i = c >> 1, g = (2 * c + (kq >> 1)) & 3;
+        r.q = tc_lds128(raw + TC_Q6_QL + row * 144 + 64 * i + 32 * (g & 1) + 16 * hq);
+        r.h = tc_lds128(raw + TC_Q6_QH + row * 80 + 32 * i + 16 * hq);
+        r.s = tc_lds8(raw + TC_Q6_SC + row * 16 + 8 * i + 2 * g + hq);
         r.d = tc_lds16(raw + TC_Q6_D + row * 16 + 2 * (kb & 7));
     }
 }
@@ -170,9 +182,9 @@ __device__ __forceinline__ void tc_read_raw(uint32_t raw, uint32_t row, uint32_t
 // crates/inferi/src/quantization.rs:364-402 (Q4_K) and :287-329 (Q5_K): sub-block j of the block, low or high nibbles of a
 // 32-byte chunk, w = d * sc * q - dmin * m
 template <bool Q5>
-__device__ __forceinline__ void tc_convert32_q45k(const TcRaw &r, uint32_t k0, float (&w)[32]) {
+__device__ __forceinline__ void tc_convert16_q45k(const TcRaw &r, uint32_t k0, float (&w)[16]) {
     const uint32_t j = (k0 & 255) >> 5, c = j >> 1, high = j & 1;
-    const uint4 hdr = r.v[0];
+    const uint4 hdr = r.hdr;
     // get_scale_min_k4 (quantization.rs:394-402) on the 12 scale bytes held in hdr.y, hdr.z, hdr.w
     const uint32_t sb[3] = {hdr.y, hdr.z, hdr.w};
     auto byte_at = [&](uint32_t i) { return (sb[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
@@ -180,10 +192,10 @@ __device__ __forceinline__ void tc_convert32_q45k(const TcRaw &r, uint32_t k0, f
     if (j < 4) { sc = byte_at(j) & 63; mn = byte_at(j + 4) & 63; }
     else { sc = (byte_at(j + 4) & 0xF) | ((byte_at(j - 4) >> 6) << 4); mn = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4); }
     const float dsc = tc_h2f(hdr.x & 0xFFFFu) * (float)sc, dm = tc_h2f(hdr.x >> 16) * (float)mn;
-    const uint32_t qw[8] = {r.v[1].x, r.v[1].y, r.v[1].z, r.v[1].w, r.v[2].x, r.v[2].y, r.v[2].z, r.v[2].w};
-    const uint32_t hw[8] = {r.v[3].x, r.v[3].y, r.v[3].z, r.v[3].w, r.v[4].x, r.v[4].y, r.v[4].z, r.v[4].w};
+    const uint32_t qw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+    const uint32_t hw[4] = {r.h.x, r.h.y, r.h.z, r.h.w};
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < 4; i++) {
         uint32_t nib = high ? (qw[i] >> 4) & 0x0F0F0F0Fu : qw[i] & 0x0F0F0F0Fu;
         if (Q5) nib |= ((hw[i] >> (2 * c + high)) & 0x01010101u) << 4;
 #pragma unroll
@@ -192,30 +204,28 @@ __device__ __forceinline__ void tc_convert32_q45k(const TcRaw &r, uint32_t k0, f
 }
 
 // crates/inferi/src/quantization.rs:227-256, rows stored as groups of 8 blocks [8 x 128 ql][8 x 64 qh][8 x 16 scales][8 x 2 d]
-__device__ __forceinline__ void tc_convert32_q6k_soa(const TcRaw &r, uint32_t k0, float (&w)[32]) {
+__device__ __forceinline__ void tc_convert16_q6k_soa(const TcRaw &r, uint32_t k0, float (&w)[16]) {
     const uint32_t g = ((k0 & 255) >> 5) & 3;
-    const float d = tc_h2f(r.d);
-    const float s0 = d * (float)(int)(int8_t)(r.s & 0xFF), s1 = d * (float)(int)(int8_t)(r.s >> 8);
-    const uint32_t lw[8] = {r.v[0].x, r.v[0].y, r.v[0].z, r.v[0].w, r.v[1].x, r.v[1].y, r.v[1].z, r.v[1].w};
-    const uint32_t hw[8] = {r.v[2].x, r.v[2].y, r.v[2].z, r.v[2].w, r.v[3].x, r.v[3].y, r.v[3].z, r.v[3].w};
+    const float sc = tc_h2f(r.d) * (float)(int)(int8_t)(r.s & 0xFF);
+    const uint32_t lw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+    const uint32_t hw[4] = {r.h.x, r.h.y, r.h.z, r.h.w};
 #pragma unroll
-    for (int wi = 0; wi < 8; wi++) {
+    for (int wi = 0; wi < 4; wi++) {
         const uint32_t nib = (g & 2) ? (lw[wi] >> 4) & 0x0F0F0F0Fu : lw[wi] & 0x0F0F0F0Fu;
         const uint32_t q = nib | (((hw[wi] >> (2 * g)) & 0x03030303u) << 4);
-        const float sc = wi < 4 ? s0 : s1;
 #pragma unroll
         for (int bt = 0; bt < 4; bt++) w[4 * wi + bt] = sc * (float)((int)((q >> (8 * bt)) & 0xFFu) - 32);
     }
 }
 
 template <int PATH>
-__device__ __forceinline__ void tc_convert32(const QDesc &q, const uint8_t *row, const TcRaw &r, uint32_t k0, float (&w)[32]) {
-    if (PATH == TC_PATH_Q4K) tc_convert32_q45k<false>(r, k0, w);
-    else if (PATH == TC_PATH_Q5K) tc_convert32_q45k<true>(r, k0, w);
-    else if (PATH == TC_PATH_Q6K) tc_convert32_q6k_soa(r, k0, w);
+__device__ __forceinline__ void tc_convert16(const QDesc &q, const uint8_t *row, const TcRaw &r, uint32_t k0, float (&w)[16]) {
+    if (PATH == TC_PATH_Q4K) tc_convert16_q45k<false>(r, k0, w);
+    else if (PATH == TC_PATH_Q5K) tc_convert16_q45k<true>(r, k0, w);
+    else if (PATH == TC_PATH_Q6K) tc_convert16_q6k_soa(r, k0, w);
     else {
 #pragma unroll
-        for (int e = 0; e < 32; e++) w[e] = dequant_at(q, row, k0 + e);   // unrolled: w stays in registers
+        for (int e = 0; e < 16; e++) w[e] = dequant_at(q, row, k0 + e);   // unrolled: w stays in registers
     }
 }
 
@@ -243,26 +253,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t RAW_BYTES = tc_raw_stage_bytes(PATH);
     const uint32_t R = p.raw_stages;
-    const uint32_t raw0 = tc_smem_u32(smem + TC_STAGES * TC_STAGE_BYTES);
-    // barriers: full[S], empty[S], accumulator, raw_full[R], raw_empty[R]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES + R * RAW_BYTES);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 1 + 2 * TC_RAW_MAX);
+    uint8_t *xst = smem + TC_STAGES * TC_STAGE_BYTES;                                   // the inputs' stages
+    const uint32_t raw0 = tc_smem_u32(smem + (TC_STAGES + TC_XSTAGES) * TC_STAGE_BYTES);
+    // barriers: full[S], empty[S], accumulator, raw_full[RAW_MAX], raw_empty[RAW_MAX], x_full[XS], x_empty[XS]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (TC_STAGES + TC_XSTAGES) * TC_STAGE_BYTES + R * RAW_BYTES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 1 + 2 * TC_RAW_MAX + 2 * TC_XSTAGES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bar0 = tc_smem_u32(bars);
     const uint32_t bar_acc = bar0 + 8 * (2 * TC_STAGES), bar_rawfull = bar_acc + 8, bar_rawempty = bar_rawfull + 8 * TC_RAW_MAX;
+    const uint32_t bar_xfull = bar_rawempty + 8 * TC_RAW_MAX, bar_xempty = bar_xfull + 8 * TC_XSTAGES;
     const uint32_t row0 = blockIdx.x * TC_ROWS;
     const uint32_t kspan = p.cols / p.ksplit, kbeg = blockIdx.y * kspan, nstage = kspan / TC_KSTAGE, nblk = kspan / 256;
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
-            // full: every producer thread + the thread that announces the bytes of the inputs' tiles
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(TC_PRODUCER_WARPS * 32 + 1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(TC_PRODUCER_WARPS));   // full: one arrival per producer warp
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (TC_STAGES + s)), "r"(1));  // empty: one tcgen05.commit
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_acc), "r"(1));       // accumulator complete
         for (uint32_t s = 0; s < TC_RAW_MAX; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawfull + 8 * s), "r"(TC_ROWS));                    // one arrival per row copy
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawempty + 8 * s), "r"(TC_PRODUCER_WARPS * 32));    // every producer thread has read it
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawfull + 8 * s), "r"(TC_ROWS / 32));               // one arrival per copying warp
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawempty + 8 * s), "r"(TC_PRODUCER_WARPS));         // every producer warp has read it
+        }
+        for (int s = 0; s < TC_XSTAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_xfull + 8 * s), "r"(1));    // the requesting thread's arrival + the bytes
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_xempty + 8 * s), "r"(1));   // one tcgen05.commit
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -278,8 +293,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     bool ok = true;
 
     if (warp < TC_PRODUCER_WARPS) {
-        // ===== producers: thread = (weight row `tid & 127`, half `tid >> 7` of the stage's 64 columns) =====
-        const uint32_t row = tid & (TC_ROWS - 1), kh = tid >> 7;
+        // ===== producers: thread = (weight row `tid & 127`, quarter `tid >> 7` of the stage's 64 columns) =====
+        const uint32_t row = tid & (TC_ROWS - 1), kq = tid >> 7;
         const uint8_t *wrow = p.w.w + (size_t)(row0 + row) * p.w.row_bytes;
         const uint32_t kb0 = kbeg >> 8;
         constexpr bool RAW = PATH != TC_PATH_OTHER;
@@ -293,36 +308,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
                 if (b >= 1 && tid < TC_ROWS && b - 1 + R < nblk) {
                     // the slot of the previous step is refilled once every producer thread has read it
                     const uint32_t ps = (b - 1) % R;
-                    ok = tc_wait(bar_rawempty + 8 * ps, ((b - 1) / R) & 1, p.wait_ns, p.err, 8);
+                    ok = __all_sync(0xffffffffu, tc_wait(bar_rawempty + 8 * ps, ((b - 1) / R) & 1, p.wait_ns, p.err, 8));   // warp-uniform: the lanes stay together
                     if (!ok) break;
                     tc_issue_raw<PATH>(wrow, kb0 + b - 1 + R, raw0 + ps * RAW_BYTES, row, bar_rawfull + 8 * ps);
                 }
-                ok = tc_wait(bar_rawfull + 8 * slot, (b / R) & 1, p.wait_ns, p.err, 8);
+                ok = __all_sync(0xffffffffu, tc_wait(bar_rawfull + 8 * slot, (b / R) & 1, p.wait_ns, p.err, 8));
                 if (!ok) break;
             }
-            const uint32_t k0 = kbeg + it * TC_KSTAGE + 32 * kh;
+            const uint32_t k0 = kbeg + it * TC_KSTAGE + 16 * kq;
             TcRaw raw;
-            if (RAW) tc_read_raw<PATH>(raw0 + slot * RAW_BYTES, row, kb0 + b, c, kh, raw);
-            float w[32];
-            tc_convert32<PATH>(p.w, wrow, raw, k0, w);
-            if (RAW && c == 3) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_rawempty + 8 * slot) : "memory");
-            if (round > 0) ok = tc_wait(bar0 + 8 * (TC_STAGES + s), (round - 1) & 1, p.wait_ns, p.err, 8);
+            if (RAW) tc_read_raw<PATH>(raw0 + slot * RAW_BYTES, row, kb0 + b, c, kq, raw);
+            float w[16];
+            tc_convert16<PATH>(p.w, wrow, raw, k0, w);
+            if (RAW && c == 3) {
+                __syncwarp();   // every lane has read its part of the raw stage
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_rawempty + 8 * slot) : "memory");
+            }
+            if (round > 0) ok = __all_sync(0xffffffffu, tc_wait(bar0 + 8 * (TC_STAGES + s), (round - 1) & 1, p.wait_ns, p.err, 8));
             if (!ok) break;
             uint8_t *st = smem + s * TC_STAGE_BYTES;
-            if (tid == 0) {
-                // the inputs' two tiles of this stage: one bulk copy each, straight into the layout the tensor core reads
-                const uint32_t full = bar0 + 8 * s, dst = tc_smem_u32(st + 2 * TC_TILE_BYTES);
-                const size_t at = (size_t)((kbeg >> 6) + it) * (TC_ROWS * TC_KSTAGE);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * TC_TILE_BYTES) : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p.x_hi + at),
-                             "r"(TC_TILE_BYTES), "r"(full)
-                             : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + TC_TILE_BYTES), "l"(p.x_lo + at),
-                             "r"(TC_TILE_BYTES), "r"(full)
-                             : "memory");
-            }
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 2; j++) {
                 uint4 hi, lo;
                 uint32_t *hp = &hi.x, *lp = &lo.x;
 #pragma unroll
@@ -334,53 +340,75 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
                     hp[e] = *reinterpret_cast<const uint32_t *>(&h);
                     lp[e] = *reinterpret_cast<const uint32_t *>(&l);
                 }
-                const uint32_t off = tc_chunk_off(row, 4 * kh + j);
+                const uint32_t off = tc_chunk_off(row, 2 * kq + j);
                 *reinterpret_cast<uint4 *>(st + off) = hi;
                 *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = lo;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
+            __syncwarp();   // one arrival per warp, behind every lane's stores and fence
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
         }
         if (!ok) {
             // a wait gave up: bulk copies of this CTA may still be in flight; give them time to land before the CTA ends
             const unsigned long long t0 = tc_ns();
             while (tc_ns() - t0 < 100000ull) {}
         }
-    } else if (lane == 0) {
+    } else if (warp == TC_PRODUCER_WARPS && lane == 0) {
         // ===== MMA issue: one thread =====
         const uint32_t idesc = tc_idesc_f16(TC_ROWS, p.n_pad);
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
-            ok = tc_wait(bar0 + 8 * s, round & 1, p.wait_ns, p.err, 9);
+            const uint32_t xs = it % TC_XSTAGES;
+            ok = tc_wait(bar_xfull + 8 * xs, (it / TC_XSTAGES) & 1, p.wait_ns, p.err, 9) && tc_wait(bar0 + 8 * s, round & 1, p.wait_ns, p.err, 9);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t st = tc_smem_u32(smem + s * TC_STAGE_BYTES);
+            const uint32_t st = tc_smem_u32(smem + s * TC_STAGE_BYTES), xt = tc_smem_u32(xst + xs * TC_STAGE_BYTES);
 #pragma unroll
             for (uint32_t kk = 0; kk < TC_KSTAGE / 16; kk++) {
                 const uint32_t koff = kk * 2 * TC_LBO;   // 16 columns = two core matrices along K
                 const uint64_t w_hi = tc_smem_desc(st + koff, TC_LBO, TC_SBO), w_lo = tc_smem_desc(st + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
-                const uint64_t x_hi = tc_smem_desc(st + 2 * TC_TILE_BYTES + koff, TC_LBO, TC_SBO), x_lo = tc_smem_desc(st + 3 * TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
+                const uint64_t x_hi = tc_smem_desc(xt + koff, TC_LBO, TC_SBO), x_lo = tc_smem_desc(xt + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
                 tc_mma_f16(tmem_base, w_hi, x_hi, idesc, (it | kk) != 0);
                 tc_mma_f16(tmem_base, w_hi, x_lo, idesc, 1);
                 tc_mma_f16(tmem_base, w_lo, x_hi, idesc, 1);
             }
             tc_commit(bar0 + 8 * (TC_STAGES + s));   // the stage is free again once these MMAs have read it
+            tc_commit(bar_xempty + 8 * xs);
         }
         if (ok) tc_commit(bar_acc);   // ... and the accumulator is complete when all of them are done
     }
 
+    if (warp == TC_PRODUCER_WARPS + 1 && lane == 0) {
+        // ===== the inputs' tiles: two bulk copies per stage (hi, lo), straight into the layout the tensor core reads, as far
+        // ahead as there are stages =====
+        bool okx = true;
+        for (uint32_t it = 0; it < nstage && okx; it++) {
+            const uint32_t xs = it % TC_XSTAGES;
+            if (it >= (uint32_t)TC_XSTAGES) okx = tc_wait(bar_xempty + 8 * xs, (it / TC_XSTAGES - 1) & 1, p.wait_ns, p.err, 8);
+            if (!okx) break;
+            const uint32_t full = bar_xfull + 8 * xs, dst = tc_smem_u32(xst + xs * TC_STAGE_BYTES);
+            const size_t at = (size_t)((kbeg >> 6) + it) * (TC_ROWS * TC_KSTAGE);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * TC_TILE_BYTES) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p.x_hi + at), "r"(TC_TILE_BYTES),
+                         "r"(full)
+                         : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + TC_TILE_BYTES), "l"(p.x_lo + at),
+                         "r"(TC_TILE_BYTES), "r"(full)
+                         : "memory");
+        }
+    }
+
     if (warp < TC_PRODUCER_WARPS) {
         // ===== epilogue: TMEM lane = weight row, column = token; stored as [token][row].  A warp reaches the 32 lanes
-        // 32 * (warp % 4); warps 0-3 take the first half of the token columns, warps 4-7 the second =====
+        // 32 * (warp % 4); the four warps that share a lane group take every fourth group of 16 token columns =====
         if (ok) ok = tc_wait(bar_acc, 0, p.wait_ns, p.err, 10);
         ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-wide instructions
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            const uint32_t row = tid & (TC_ROWS - 1), groups = p.n_pad / 16, gsplit = (groups + 1) / 2;
-            const uint32_t g_beg = (warp < 4) ? 0 : gsplit, g_end = (warp < 4) ? gsplit : groups;
+            const uint32_t row = tid & (TC_ROWS - 1), groups = p.n_pad / 16;
             float *out = p.out + (size_t)blockIdx.y * p.n_tokens * p.rows + row0 + row;
             const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            for (uint32_t c0 = 16 * g_beg; c0 < 16 * g_end; c0 += 16) {
+            for (uint32_t c0 = 16 * (warp >> 2); c0 < 16 * groups; c0 += 16 * (TC_PRODUCER_WARPS / 4)) {
                 uint32_t r[16];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
