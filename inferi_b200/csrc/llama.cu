@@ -723,11 +723,11 @@ static int32_t prefill_prepare(ib_llama *m) {
     const ib_llama_config &c = m->cfg;
     const uint32_t H = c.hidden_size, F = m->ffn_l, Q = m->q_dim_l, KV = m->kv_dim_l, N = PREFILL_MAX_TOKENS;
     const uint32_t widest = F > H ? (F > Q ? F : Q) : (H > Q ? H : Q);
-    size_t plane_elems = 0;   // largest ksplit * rows over the matrices (per token)
+    size_t plane_elems = 0;   // largest planes * rows over the matrices (per token)
     const ib_llama_layer_weights &w = m->layers[0];
     const ib_qtensor *mats[] = {w.attn_q, w.attn_k, w.attn_v, w.attn_output, w.ffn_gate, w.ffn_up, w.ffn_down};
     for (const ib_qtensor *t : mats) {
-        const size_t e = (size_t)prefill_ksplit(m->ctx, (uint32_t)t->rows, (uint32_t)t->cols) * t->rows;
+        const size_t e = (size_t)prefill_max_pieces(prefill_streamk(m->ctx, (uint32_t)t->rows, (uint32_t)t->cols), (uint32_t)t->rows) * t->rows;
         if (e > plane_elems) plane_elems = e;
     }
     ib_attn_params ap{c.max_position_embeddings, KV, c.num_attention_heads / c.num_key_value_heads, m->n_heads_l, m->head_size, 0};
@@ -773,8 +773,8 @@ int32_t ib_llama_prefill(ib_llama *m, void *stream, const uint32_t *tokens_host,
     cudaStream_t s = (cudaStream_t)stream;
     const uint32_t H = c.hidden_size, F = m->ffn_l, Q = m->q_dim_l, KV = m->kv_dim_l;
     auto &B = m->pf;
-    auto gemm = [&](const ib_qtensor *w, uint32_t nc, float *planes, uint32_t &ks) -> int32_t {
-        ks = prefill_ksplit(ctx, (uint32_t)w->rows, (uint32_t)w->cols);
+    auto gemm = [&](const ib_qtensor *w, uint32_t nc, float *planes, StreamK &ks) -> int32_t {
+        ks = prefill_streamk(ctx, (uint32_t)w->rows, (uint32_t)w->cols);
         return launch_prefill_gemm(ctx, s, w, B.hi, B.lo, nc, planes, ks);
     };
 #define PF(expr) do { if ((rc = (expr)) != IB_OK) return rc; } while (0)
@@ -784,19 +784,19 @@ int32_t ib_llama_prefill(ib_llama *m, void *stream, const uint32_t *tokens_host,
         PF(launch_prefill_embed(ctx, s, m->token_embd, B.tokens, nc, c.vocab_size, B.X));
         for (uint32_t l = 0; l < c.num_hidden_layers; l++) {
             const ib_llama_layer_weights &w = m->layers[l];
-            uint32_t ks = 1;
+            StreamK ks = {};
             PrefillEpiParams e = {};
             e.n = nc; e.theta = m->theta; e.head_size = m->head_size; e.pos0 = pos0; e.kv_dim = KV; e.kv_dtype = (uint32_t)m->kv_dtype;
             // q, k, v: RMSNorm, GEMM, bias, RoPE, cache append (transformer.rs:420-445)
             PF(launch_prefill_norm_split(ctx, s, B.X, w.attn_norm_dev, c.rms_norm_eps, nc, H, B.hi, B.lo));
             PF(gemm(w.attn_q, nc, B.planes, ks));
-            e.planes = B.planes; e.ksplit = ks; e.rows = Q; e.mode = PE_Q; e.bias = w.attn_q_bias_dev; e.out = B.q;
+            e.planes = B.planes; e.sk = ks; e.rows = Q; e.mode = PE_Q; e.bias = w.attn_q_bias_dev; e.out = B.q;
             PF(launch_prefill_epilogue(ctx, s, e));
             PF(gemm(w.attn_k, nc, B.planes, ks));
-            e.ksplit = ks; e.rows = KV; e.mode = PE_K; e.bias = w.attn_k_bias_dev; e.cache = m->k_cache[l];
+            e.sk = ks; e.rows = KV; e.mode = PE_K; e.bias = w.attn_k_bias_dev; e.cache = m->k_cache[l];
             PF(launch_prefill_epilogue(ctx, s, e));
             PF(gemm(w.attn_v, nc, B.planes, ks));
-            e.ksplit = ks; e.mode = PE_V; e.bias = w.attn_v_bias_dev; e.cache = m->v_cache[l];
+            e.sk = ks; e.mode = PE_V; e.bias = w.attn_v_bias_dev; e.cache = m->v_cache[l];
             PF(launch_prefill_epilogue(ctx, s, e));
             // causal attention: query t over positions 0 .. pos0 + t (transformer.rs:448), all queries in one launch
             AttnLaunch a = {};
@@ -809,17 +809,17 @@ int32_t ib_llama_prefill(ib_llama *m, void *stream, const uint32_t *tokens_host,
             // o_proj + residual (transformer.rs:450-453)
             PF(launch_prefill_norm_split(ctx, s, B.att, nullptr, 0.f, nc, Q, B.hi, B.lo));
             PF(gemm(w.attn_output, nc, B.planes, ks));
-            e.ksplit = ks; e.rows = H; e.mode = PE_RESIDUAL; e.bias = nullptr; e.out = B.X;
+            e.sk = ks; e.rows = H; e.mode = PE_RESIDUAL; e.bias = nullptr; e.out = B.X;
             PF(launch_prefill_epilogue(ctx, s, e));
             // gate, up, SwiGLU (transformer.rs:454-464)
             PF(launch_prefill_norm_split(ctx, s, B.X, w.ffn_norm_dev, c.rms_norm_eps, nc, H, B.hi, B.lo));
             PF(gemm(w.ffn_gate, nc, B.planes, ks));
             PF(gemm(w.ffn_up, nc, B.planes2, ks));
-            e.planes2 = B.planes2; e.ksplit = ks; e.rows = F; e.mode = PE_SWIGLU; e.hi = B.hi; e.lo = B.lo;
+            e.planes2 = B.planes2; e.sk = ks; e.rows = F; e.mode = PE_SWIGLU; e.hi = B.hi; e.lo = B.lo;
             PF(launch_prefill_epilogue(ctx, s, e));
             // down + residual (transformer.rs:465-468)
             PF(gemm(w.ffn_down, nc, B.planes, ks));
-            e.ksplit = ks; e.rows = H; e.mode = PE_RESIDUAL; e.out = B.X;
+            e.sk = ks; e.rows = H; e.mode = PE_RESIDUAL; e.out = B.X;
             PF(launch_prefill_epilogue(ctx, s, e));
         }
         if (t0 + nc == n) IB_CHECK_CUDA(cudaMemcpyAsync(m->x, B.X + (size_t)(nc - 1) * H, sizeof(float) * H, cudaMemcpyDeviceToDevice, s));

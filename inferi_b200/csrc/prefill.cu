@@ -240,12 +240,31 @@ struct GemmTcParams {
     uint32_t rows, cols;        // rows % 128 == 0, cols % 256 == 0
     const __half *x_hi, *x_lo;  // the tokens' inputs split into two f16, tiled (tc_x_index); rows n_tokens .. n_pad-1 are zero
     uint32_t n_tokens, n_pad;   // n_pad = n_tokens rounded up to 16, <= 128
-    float *out;                 // [ksplit][n_tokens][rows] partial planes
-    uint32_t ksplit;            // gridDim.y; cols / ksplit is a multiple of 256
+    float *out;                 // [piece][n_tokens][rows] partial planes
+    StreamK sk;                 // the hand-out of (tile, 256-column block) units; gridDim.x == sk.ctas
     uint32_t raw_stages;        // depth of the ring of raw blocks
     uint32_t *err;
     unsigned long long wait_ns;
 };
+
+// The accumulator of one (tile, K range) segment: TMEM lane = weight row, column = token; stored as [token][row].  A warp
+// reaches the 32 lanes 32 * (warp % 4); the four warps that share a lane group take every fourth group of 16 token columns.
+__device__ __forceinline__ void tc_drain(const GemmTcParams &p, uint32_t tmem_base, int warp, uint32_t row, float *out) {
+    const uint32_t groups = p.n_pad / 16;
+    const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    for (uint32_t c0 = 16 * (warp >> 2); c0 < 16 * groups; c0 += 16 * (TC_PRODUCER_WARPS / 4)) {
+        uint32_t r[16];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                       "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                     : "r"(taddr + c0)
+                     : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+            if (c0 + j < p.n_tokens) out[(size_t)(c0 + j) * p.rows + row] = __uint_as_float(r[j]);
+    }
+}
 
 template <int PATH>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const GemmTcParams p) {
@@ -262,15 +281,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     const uint32_t bar0 = tc_smem_u32(bars);
     const uint32_t bar_acc = bar0 + 8 * (2 * TC_STAGES), bar_rawfull = bar_acc + 8, bar_rawempty = bar_rawfull + 8 * TC_RAW_MAX;
     const uint32_t bar_xfull = bar_rawempty + 8 * TC_RAW_MAX, bar_xempty = bar_xfull + 8 * TC_XSTAGES;
-    const uint32_t row0 = blockIdx.x * TC_ROWS;
-    const uint32_t kspan = p.cols / p.ksplit, kbeg = blockIdx.y * kspan, nstage = kspan / TC_KSTAGE, nblk = kspan / 256;
+    // this CTA's units: u0 .. u1-1 of the tile-major list of (tile, 256-column block); four 64-column stages per unit
+    const StreamK sk = p.sk;
+    const uint32_t u0 = sk.first_unit(blockIdx.x), u1 = sk.first_unit(blockIdx.x + 1), nunits = u1 - u0, nstage = 4 * nunits;
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(TC_PRODUCER_WARPS));   // full: one arrival per producer warp
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * (TC_STAGES + s)), "r"(1));  // empty: one tcgen05.commit
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_acc), "r"(1));       // accumulator complete
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_acc), "r"(1));       // a segment's accumulator is complete
         for (uint32_t s = 0; s < TC_RAW_MAX; s++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawfull + 8 * s), "r"(TC_ROWS / 32));               // one arrival per copying warp
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawempty + 8 * s), "r"(TC_PRODUCER_WARPS));         // every producer warp has read it
@@ -293,31 +313,50 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     bool ok = true;
 
     if (warp < TC_PRODUCER_WARPS) {
-        // ===== producers: thread = (weight row `tid & 127`, quarter `tid >> 7` of the stage's 64 columns) =====
+        // ===== producers: thread = (weight row `tid & 127` of the unit's tile, quarter `tid >> 7` of the stage's 64 columns) =====
         const uint32_t row = tid & (TC_ROWS - 1), kq = tid >> 7;
-        const uint8_t *wrow = p.w.w + (size_t)(row0 + row) * p.w.row_bytes;
-        const uint32_t kb0 = kbeg >> 8;
         constexpr bool RAW = PATH != TC_PATH_OTHER;
-        // the ring of raw blocks is filled ahead: one block of every row per step, each row by its own bulk copy
-        if (RAW && tid < TC_ROWS)
-            for (uint32_t b = 0; b < R && b < nblk; b++) tc_issue_raw<PATH>(wrow, kb0 + b, raw0 + b * RAW_BYTES, row, bar_rawfull + 8 * b);
+        // Every index of the loop is carried forward by additions: a division by a run-time value (ring depth, blocks per
+        // row) per stage and thread costs more instructions than the 16 weights' conversion.
+        uint32_t tile = u0 / sk.nb, kb = u0 - tile * sk.nb;          // the current unit
+        uint32_t ptile = tile, pkb = kb;                              // the next unit to request into the ring
+        auto row_at = [&](uint32_t t) { return p.w.w + (size_t)(t * TC_ROWS + row) * p.w.row_bytes; };
+        // the ring of raw blocks is filled ahead: one block of every row of the unit's tile per step, each row by its own bulk copy
+        uint32_t issued = 0;
+        for (; issued < R && issued < nunits; issued++) {
+            if (RAW && tid < TC_ROWS) tc_issue_raw<PATH>(row_at(ptile), pkb, raw0 + issued * RAW_BYTES, row, bar_rawfull + 8 * issued);
+            if (++pkb == sk.nb) { pkb = 0; ptile++; }
+        }
+        uint32_t slot = 0, slot_par = 0;        // ring slot of the current unit and the parity of its use
+        uint32_t pslot = 0, pslot_par = 0;      // the same for the previous unit (the slot that is refilled next)
+        const uint8_t *wrow = row_at(tile);
+        uint32_t seg = 0;   // segments (tile, K range) finished so far: the parity of the accumulator barrier
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
-            const uint32_t b = it >> 2, c = it & 3, slot = b % R;
+            const uint32_t j = it >> 2, c = it & 3, u = u0 + j;
+            if (c == 0 && j >= 1) {
+                pslot = slot; pslot_par = slot_par;
+                if (++slot == R) { slot = 0; slot_par ^= 1u; }
+                if (++kb == sk.nb) { kb = 0; tile++; }
+                wrow = row_at(tile);
+            }
             if (RAW && c == 0) {
-                if (b >= 1 && tid < TC_ROWS && b - 1 + R < nblk) {
+                if (j >= 1 && issued < nunits) {
                     // the slot of the previous step is refilled once every producer thread has read it
-                    const uint32_t ps = (b - 1) % R;
-                    ok = __all_sync(0xffffffffu, tc_wait(bar_rawempty + 8 * ps, ((b - 1) / R) & 1, p.wait_ns, p.err, 8));   // warp-uniform: the lanes stay together
-                    if (!ok) break;
-                    tc_issue_raw<PATH>(wrow, kb0 + b - 1 + R, raw0 + ps * RAW_BYTES, row, bar_rawfull + 8 * ps);
+                    if (tid < TC_ROWS) {
+                        ok = __all_sync(0xffffffffu, tc_wait(bar_rawempty + 8 * pslot, pslot_par, p.wait_ns, p.err, 8));   // warp-uniform: the lanes stay together
+                        if (!ok) break;
+                        tc_issue_raw<PATH>(row_at(ptile), pkb, raw0 + pslot * RAW_BYTES, row, bar_rawfull + 8 * pslot);
+                    }
+                    issued++;
+                    if (++pkb == sk.nb) { pkb = 0; ptile++; }
                 }
-                ok = __all_sync(0xffffffffu, tc_wait(bar_rawfull + 8 * slot, (b / R) & 1, p.wait_ns, p.err, 8));
+                ok = __all_sync(0xffffffffu, tc_wait(bar_rawfull + 8 * slot, slot_par, p.wait_ns, p.err, 8));
                 if (!ok) break;
             }
-            const uint32_t k0 = kbeg + it * TC_KSTAGE + 16 * kq;
+            const uint32_t k0 = kb * 256 + c * TC_KSTAGE + 16 * kq;
             TcRaw raw;
-            if (RAW) tc_read_raw<PATH>(raw0 + slot * RAW_BYTES, row, kb0 + b, c, kq, raw);
+            if (RAW) tc_read_raw<PATH>(raw0 + slot * RAW_BYTES, row, kb, c, kq, raw);
             float w[16];
             tc_convert16<PATH>(p.w, wrow, raw, k0, w);
             if (RAW && c == 3) {
@@ -328,25 +367,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
             if (!ok) break;
             uint8_t *st = smem + s * TC_STAGE_BYTES;
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
+            for (int h = 0; h < 2; h++) {
                 uint4 hi, lo;
                 uint32_t *hp = &hi.x, *lp = &lo.x;
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const float a = w[8 * j + 2 * e], b2 = w[8 * j + 2 * e + 1];
-                    const __half2 h = __floats2half2_rn(a, b2);
-                    const float2 back = __half22float2(h);
+                    const float a = w[8 * h + 2 * e], b2 = w[8 * h + 2 * e + 1];
+                    const __half2 hh = __floats2half2_rn(a, b2);
+                    const float2 back = __half22float2(hh);
                     const __half2 l = __floats2half2_rn(a - back.x, b2 - back.y);
-                    hp[e] = *reinterpret_cast<const uint32_t *>(&h);
+                    hp[e] = *reinterpret_cast<const uint32_t *>(&hh);
                     lp[e] = *reinterpret_cast<const uint32_t *>(&l);
                 }
-                const uint32_t off = tc_chunk_off(row, 2 * kq + j);
+                const uint32_t off = tc_chunk_off(row, 2 * kq + h);
                 *reinterpret_cast<uint4 *>(st + off) = hi;
                 *reinterpret_cast<uint4 *>(st + TC_TILE_BYTES + off) = lo;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
             __syncwarp();   // one arrival per warp, behind every lane's stores and fence
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * s) : "memory");
+            if (c == 3 && (kb + 1 == sk.nb || u + 1 == u1)) {
+                // the tile's K range in this CTA ends here: when its MMAs are done, the accumulator goes to the plane that
+                // this CTA holds among the tile's CTAs.  The next segment's first stage only becomes full after every
+                // producer warp has arrived on it, i.e. after every warp is through with this read of tensor memory.
+                ok = __all_sync(0xffffffffu, tc_wait(bar_acc, seg & 1, p.wait_ns, p.err, 10));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t piece = blockIdx.x - sk.cta_of(tile * sk.nb);
+                tc_drain(p, tmem_base, warp, tile * TC_ROWS + row, p.out + (size_t)piece * p.n_tokens * p.rows);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                seg++;
+            }
         }
         if (!ok) {
             // a wait gave up: bulk copies of this CTA may still be in flight; give them time to land before the CTA ends
@@ -359,6 +410,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
             const uint32_t xs = it % TC_XSTAGES;
+            const uint32_t j = it >> 2, c = it & 3, u = u0 + j, kb = u % sk.nb;
+            const bool seg_first = c == 0 && (j == 0 || kb == 0), seg_last = c == 3 && (kb + 1 == sk.nb || u + 1 == u1);
             ok = tc_wait(bar_xfull + 8 * xs, (it / TC_XSTAGES) & 1, p.wait_ns, p.err, 9) && tc_wait(bar0 + 8 * s, round & 1, p.wait_ns, p.err, 9);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -368,14 +421,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
                 const uint32_t koff = kk * 2 * TC_LBO;   // 16 columns = two core matrices along K
                 const uint64_t w_hi = tc_smem_desc(st + koff, TC_LBO, TC_SBO), w_lo = tc_smem_desc(st + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
                 const uint64_t x_hi = tc_smem_desc(xt + koff, TC_LBO, TC_SBO), x_lo = tc_smem_desc(xt + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
-                tc_mma_f16(tmem_base, w_hi, x_hi, idesc, (it | kk) != 0);
+                tc_mma_f16(tmem_base, w_hi, x_hi, idesc, !(seg_first && kk == 0));   // a segment starts a new sum
                 tc_mma_f16(tmem_base, w_hi, x_lo, idesc, 1);
                 tc_mma_f16(tmem_base, w_lo, x_hi, idesc, 1);
             }
             tc_commit(bar0 + 8 * (TC_STAGES + s));   // the stage is free again once these MMAs have read it
             tc_commit(bar_xempty + 8 * xs);
+            if (seg_last) tc_commit(bar_acc);         // ... and the segment's accumulator is complete when all of them are done
         }
-        if (ok) tc_commit(bar_acc);   // ... and the accumulator is complete when all of them are done
     }
 
     if (warp == TC_PRODUCER_WARPS + 1 && lane == 0) {
@@ -387,41 +440,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
             if (it >= (uint32_t)TC_XSTAGES) okx = tc_wait(bar_xempty + 8 * xs, (it / TC_XSTAGES - 1) & 1, p.wait_ns, p.err, 8);
             if (!okx) break;
             const uint32_t full = bar_xfull + 8 * xs, dst = tc_smem_u32(xst + xs * TC_STAGE_BYTES);
-            const size_t at = (size_t)((kbeg >> 6) + it) * (TC_ROWS * TC_KSTAGE);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * TC_TILE_BYTES) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p.x_hi + at), "r"(TC_TILE_BYTES),
+            const uint32_t kb = (u0 + (it >> 2)) % sk.nb;
+            const size_t at = (size_t)(4 * kb + (it & 3)) * (TC_ROWS * TC_KSTAGE);
+            // the tile's first n_pad token rows are its first n_pad / 8 groups of 1 KiB: only those are read by the MMA
+            const uint32_t xbytes = p.n_pad * (TC_KSTAGE * 2);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * xbytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p.x_hi + at), "r"(xbytes),
                          "r"(full)
                          : "memory");
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + TC_TILE_BYTES), "l"(p.x_lo + at),
-                         "r"(TC_TILE_BYTES), "r"(full)
+                         "r"(xbytes), "r"(full)
                          : "memory");
         }
     }
 
-    if (warp < TC_PRODUCER_WARPS) {
-        // ===== epilogue: TMEM lane = weight row, column = token; stored as [token][row].  A warp reaches the 32 lanes
-        // 32 * (warp % 4); the four warps that share a lane group take every fourth group of 16 token columns =====
-        if (ok) ok = tc_wait(bar_acc, 0, p.wait_ns, p.err, 10);
-        ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-wide instructions
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const uint32_t row = tid & (TC_ROWS - 1), groups = p.n_pad / 16;
-            float *out = p.out + (size_t)blockIdx.y * p.n_tokens * p.rows + row0 + row;
-            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            for (uint32_t c0 = 16 * (warp >> 2); c0 < 16 * groups; c0 += 16 * (TC_PRODUCER_WARPS / 4)) {
-                uint32_t r[16];
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-                               "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                             : "r"(taddr + c0)
-                             : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 16; j++)
-                    if (c0 + j < p.n_tokens) out[(size_t)(c0 + j) * p.rows] = __uint_as_float(r[j]);
-            }
-        }
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == TC_PRODUCER_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
@@ -472,9 +504,9 @@ __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X,
     for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) split_store(hi, lo, tc_x_index(t, c), w ? (x[c] * rms) * w[c] : x[c]);
 }
 
-__device__ __forceinline__ float plane_sum(const float *planes, uint32_t ksplit, size_t plane_elems, size_t i) {
+__device__ __forceinline__ float plane_sum(const float *planes, uint32_t pieces, size_t plane_elems, size_t i) {
     float v = 0.f;
-    for (uint32_t s = 0; s < ksplit; s++) v += planes[s * plane_elems + i];   // fixed order: deterministic
+    for (uint32_t s = 0; s < pieces; s++) v += planes[s * plane_elems + i];   // fixed order: deterministic
     return v;
 }
 
@@ -491,10 +523,11 @@ __global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
             split_store(p.hi, p.lo, tc_x_index(t, r + 1), 0.f);
             continue;
         }
-        float a = plane_sum(p.planes, p.ksplit, plane, i), b = plane_sum(p.planes, p.ksplit, plane, i + 1);
+        const uint32_t np = p.sk.pieces(r / 128);   // the planes that the row's tile was spread over
+        float a = plane_sum(p.planes, np, plane, i), b = plane_sum(p.planes, np, plane, i + 1);
         if (p.mode == PE_SWIGLU) {
             // crates/inferi-shaders/src/silu.rs:16-19,46-52
-            const float ua = plane_sum(p.planes2, p.ksplit, plane, i), ub = plane_sum(p.planes2, p.ksplit, plane, i + 1);
+            const float ua = plane_sum(p.planes2, np, plane, i), ub = plane_sum(p.planes2, np, plane, i + 1);
             split_store(p.hi, p.lo, tc_x_index(t, r), ua * (a / (1.0f + expf(-a))));
             split_store(p.hi, p.lo, tc_x_index(t, r + 1), ub * (b / (1.0f + expf(-b))));
             continue;
@@ -520,21 +553,24 @@ __global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
 // ---------------------------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------------------------
-// K split of a matrix: enough CTAs to fill the GPU, a divisor of the number of 256-column blocks
-uint32_t prefill_ksplit(const ib_ctx *ctx, uint32_t rows, uint32_t cols) {
-    const uint32_t tiles = rows / TC_ROWS, blocks = cols / 256;
-    uint32_t want = ((uint32_t)ctx->sm_count + tiles - 1) / tiles, ks = 1;
-    if (want > 16) want = 16;
-    for (uint32_t d = 1; d <= blocks && d <= 16; d++)
-        if (blocks % d == 0) { ks = d; if (d >= want) break; }
-    return ks;
+StreamK prefill_streamk(const ib_ctx *ctx, uint32_t rows, uint32_t cols) {
+    StreamK sk;
+    sk.nb = cols / 256;
+    sk.total = (rows / TC_ROWS) * sk.nb;
+    sk.ctas = sk.total < (uint32_t)ctx->sm_count ? sk.total : (uint32_t)ctx->sm_count;
+    return sk;
+}
+uint32_t prefill_max_pieces(const StreamK &sk, uint32_t rows) {
+    uint32_t most = 1;
+    for (uint32_t t = 0; t < rows / TC_ROWS; t++) most = sk.pieces(t) > most ? sk.pieces(t) : most;
+    return most;
 }
 
 bool prefill_gemm_eligible(const ib_qtensor *m) {
     return m->rows % TC_ROWS == 0 && m->cols % 256 == 0 && (m->qtype == IB_Q4_K || m->qtype == IB_Q5_K || m->qtype == IB_Q6_K || m->qtype == IB_Q8_0);
 }
 
-int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, const __half *x_hi, const __half *x_lo, uint32_t n, float *planes, uint32_t ksplit) {
+int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, const __half *x_hi, const __half *x_lo, uint32_t n, float *planes, const StreamK &sk) {
     const int path = tc_path((uint32_t)m->qtype, m->layout);
     const uint32_t raw_bytes = tc_raw_stage_bytes(path);
     uint32_t raw_stages = raw_bytes ? (TC_SMEM_LIMIT - TC_SMEM_FIXED) / raw_bytes : 1;
@@ -555,8 +591,8 @@ int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, co
     p.w = QDesc{m->dev, m->row_bytes, (uint32_t)m->qtype, m->layout, m->nb};
     p.rows = (uint32_t)m->rows; p.cols = (uint32_t)m->cols;
     p.x_hi = x_hi; p.x_lo = x_lo; p.n_tokens = n; p.n_pad = (n + 15) & ~15u;
-    p.out = planes; p.ksplit = ksplit; p.err = ctx->err_dev; p.wait_ns = ctx->wait_limit_ns;
-    kernel<<<dim3(p.rows / TC_ROWS, ksplit), TC_THREADS, smem_bytes, s>>>(p);
+    p.out = planes; p.sk = sk; p.err = ctx->err_dev; p.wait_ns = ctx->wait_limit_ns;
+    kernel<<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p);
     ctx->launches++;
     IB_CHECK_CUDA(cudaGetLastError());
     return IB_OK;
@@ -603,7 +639,9 @@ extern "C" int32_t ib_gemm_quant(ib_ctx *ctx, void *stream, float *out_dev, cons
     cudaGetDevice(&prev);
     IB_REQUIRE(cudaSetDevice(ctx->device) == cudaSuccess, "cudaSetDevice failed");
     cudaStream_t s = (cudaStream_t)stream;
-    const uint32_t rows = (uint32_t)m->rows, cols = (uint32_t)m->cols, ks = prefill_ksplit(ctx, rows, cols);
+    const uint32_t rows = (uint32_t)m->rows, cols = (uint32_t)m->cols;
+    const StreamK sk = prefill_streamk(ctx, rows, cols);
+    const uint32_t ks = prefill_max_pieces(sk, rows);
     const size_t half_bytes = (size_t)TC_ROWS * cols * sizeof(__half), plane_bytes = (size_t)ks * TC_ROWS * rows * sizeof(float);
     const size_t need = 2 * half_bytes + plane_bytes;
     int32_t rc = IB_OK;
@@ -622,10 +660,10 @@ extern "C" int32_t ib_gemm_quant(ib_ctx *ctx, void *stream, float *out_dev, cons
     for (uint32_t t0 = 0; rc == IB_OK && t0 < n; t0 += TC_ROWS) {
         const uint32_t nc = n - t0 < (uint32_t)TC_ROWS ? n - t0 : (uint32_t)TC_ROWS;
         rc = launch_prefill_norm_split(ctx, s, x_dev + (size_t)t0 * cols, nullptr, 0.f, nc, cols, hi, lo);
-        if (rc == IB_OK) rc = launch_prefill_gemm(ctx, s, m, hi, lo, nc, planes, ks);
+        if (rc == IB_OK) rc = launch_prefill_gemm(ctx, s, m, hi, lo, nc, planes, sk);
         if (rc == IB_OK) {
             PrefillEpiParams e = {};
-            e.planes = planes; e.ksplit = ks; e.n = nc; e.rows = rows; e.mode = PE_STORE; e.out = out_dev + (size_t)t0 * rows;
+            e.planes = planes; e.sk = sk; e.n = nc; e.rows = rows; e.mode = PE_STORE; e.out = out_dev + (size_t)t0 * rows;
             rc = launch_prefill_epilogue(ctx, s, e);
         }
     }
