@@ -479,7 +479,7 @@ def main():
                    "frac_of_bf16_sustained_peak": round(flops / (p_ms * 1e-3) / 1e12 / 1385.0, 4),
                    "weight_stream_bound_ms": round(cfg.weight_bytes() / (peak_hbm() * 1e9) * 1e3, 3),
                    "decode_path_ms_for_the_same_prompt": round(128 * ms / K, 1), "next_token_matches_decode_path": bool(nxt_p == loop_first),
-                   "note": "f16 hi/lo operand pairs, 3 tcgen05.mma per 16 columns, f32 accumulation in tensor memory; flops counted once (2 x matrix parameters x tokens, classifier excluded)"}
+                   "note": "Q4_K / Q5_K: exact integer weights (scale x quant) in f16 x inputs split hi / lo, 2 tcgen05.mma per 16 columns, per-block f32 scaling from tensor memory; Q6_K: weights and inputs split hi / lo, 3 tcgen05.mma per 16 columns; flops counted once (2 x matrix parameters x tokens, classifier excluded)"}
 
     # ---- roofline --------------------------------------------------------------------------------------------
     peak1, peak_src = measured_peaks()

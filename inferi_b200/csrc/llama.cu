@@ -736,8 +736,8 @@ static int32_t prefill_prepare(ib_llama *m) {
     IB_CHECK_CUDA(cudaMalloc(&m->pf.X, sizeof(float) * N * H));
     IB_CHECK_CUDA(cudaMalloc(&m->pf.q, sizeof(float) * N * Q));
     IB_CHECK_CUDA(cudaMalloc(&m->pf.att, sizeof(float) * N * Q));
-    IB_CHECK_CUDA(cudaMalloc(&m->pf.hi, sizeof(__half) * N * widest));
-    IB_CHECK_CUDA(cudaMalloc(&m->pf.lo, sizeof(__half) * N * widest));
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.hi, sizeof(__half) * (N + 8) * widest));   // the inputs' tiles + the tiles of their sub-block sums
+    IB_CHECK_CUDA(cudaMalloc(&m->pf.lo, sizeof(__half) * (N + 8) * widest));
     IB_CHECK_CUDA(cudaMalloc(&m->pf.planes, sizeof(float) * N * plane_elems));
     IB_CHECK_CUDA(cudaMalloc(&m->pf.planes2, sizeof(float) * N * plane_elems));
     IB_CHECK_CUDA(cudaMalloc(&m->pf.tokens, sizeof(uint32_t) * N));

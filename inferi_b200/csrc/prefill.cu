@@ -25,6 +25,8 @@
 // tensor memory.
 #include "prefill.cuh"
 
+#include <cuda.h>   // CUtensorMap and the enumerations of cuTensorMapEncodeTiled (the entry point is looked up at run time)
+
 namespace ib {
 
 constexpr int TC_ROWS = 128;              // weight rows per CTA = M of the MMA
@@ -235,6 +237,14 @@ __host__ __device__ inline size_t tc_x_index(uint32_t t, uint32_t c) {
     return (size_t)(c >> 6) * (TC_ROWS * TC_KSTAGE) + ((t >> 3) * TC_SBO + ((c & 63) >> 3) * TC_LBO + (t & 7) * 16) / 2 + (c & 7);
 }
 
+// Behind the input tiles of a vector of `cols` columns sit the tiles of its sub-block sums: per 256 columns one tile of 128
+// token rows x 16 halves in the same core-matrix layout (K = 16: the sums of the unit's eight 32-column sub-blocks, then
+// eight zeros), hi and lo halves like the inputs.  The k-quant GEMM multiplies them with the sub-blocks' minimums.
+__host__ __device__ inline size_t tc_s_index(uint32_t t, uint32_t sb, uint32_t cols) {
+    return (size_t)TC_ROWS * cols + (size_t)(sb >> 3) * (TC_ROWS * 16) + ((t >> 3) * 256 + (t & 7) * 16) / 2 + (sb & 7);
+}
+__host__ __device__ inline size_t tc_x_halves(uint32_t cols) { return (size_t)(TC_ROWS + 8) * cols; }   // halves per split buffer (hi or lo)
+
 struct GemmTcParams {
     QDesc w;                    // the quantized matrix, device layout
     uint32_t rows, cols;        // rows % 128 == 0, cols % 256 == 0
@@ -407,23 +417,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
     } else if (warp == TC_PRODUCER_WARPS && lane == 0) {
         // ===== MMA issue: one thread =====
         const uint32_t idesc = tc_idesc_f16(TC_ROWS, p.n_pad);
+        // per MMA the issuing thread does as little as possible (it is one warp's serial instruction stream): the
+        // descriptors of stage 0 are built once, the block index is carried by additions
+        const uint64_t wdesc0 = tc_smem_desc(tc_smem_u32(smem), TC_LBO, TC_SBO), xdesc0 = tc_smem_desc(tc_smem_u32(xst), TC_LBO, TC_SBO);
+        uint32_t kb = u0 % sk.nb;
         for (uint32_t it = 0; it < nstage && ok; it++) {
             const uint32_t s = it % TC_STAGES, round = it / TC_STAGES;
             const uint32_t xs = it % TC_XSTAGES;
-            const uint32_t j = it >> 2, c = it & 3, u = u0 + j, kb = u % sk.nb;
+            const uint32_t j = it >> 2, c = it & 3, u = u0 + j;
+            if (c == 0 && j >= 1 && ++kb == sk.nb) kb = 0;
             const bool seg_first = c == 0 && (j == 0 || kb == 0), seg_last = c == 3 && (kb + 1 == sk.nb || u + 1 == u1);
             ok = tc_wait(bar_xfull + 8 * xs, (it / TC_XSTAGES) & 1, p.wait_ns, p.err, 9) && tc_wait(bar0 + 8 * s, round & 1, p.wait_ns, p.err, 9);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t st = tc_smem_u32(smem + s * TC_STAGE_BYTES), xt = tc_smem_u32(xst + xs * TC_STAGE_BYTES);
+            // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes): one addition each
+            const uint64_t wh = wdesc0 + s * (TC_STAGE_BYTES >> 4), wl = wh + (TC_TILE_BYTES >> 4);
+            const uint64_t xh = xdesc0 + xs * (TC_STAGE_BYTES >> 4), xl = xh + (TC_TILE_BYTES >> 4);
 #pragma unroll
             for (uint32_t kk = 0; kk < TC_KSTAGE / 16; kk++) {
-                const uint32_t koff = kk * 2 * TC_LBO;   // 16 columns = two core matrices along K
-                const uint64_t w_hi = tc_smem_desc(st + koff, TC_LBO, TC_SBO), w_lo = tc_smem_desc(st + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
-                const uint64_t x_hi = tc_smem_desc(xt + koff, TC_LBO, TC_SBO), x_lo = tc_smem_desc(xt + TC_TILE_BYTES + koff, TC_LBO, TC_SBO);
-                tc_mma_f16(tmem_base, w_hi, x_hi, idesc, !(seg_first && kk == 0));   // a segment starts a new sum
-                tc_mma_f16(tmem_base, w_hi, x_lo, idesc, 1);
-                tc_mma_f16(tmem_base, w_lo, x_hi, idesc, 1);
+                const uint32_t ko = kk * (2 * TC_LBO >> 4);   // 16 columns = two core matrices along K
+                tc_mma_f16(tmem_base, wh + ko, xh + ko, idesc, !(seg_first && kk == 0));   // a segment starts a new sum
+                tc_mma_f16(tmem_base, wh + ko, xl + ko, idesc, 1);
+                tc_mma_f16(tmem_base, wl + ko, xh + ko, idesc, 1);
             }
             tc_commit(bar0 + 8 * (TC_STAGES + s));   // the stage is free again once these MMAs have read it
             tc_commit(bar_xempty + 8 * xs);
@@ -461,6 +476,349 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
 
 
 // ---------------------------------------------------------------------------------------------------------------------
+// gemm_kquant_tc_kernel: the GEMM for Q4_K and Q5_K, with exact integer weights on the tensor cores.
+//
+// A k-quant weight is w = d * (sc * q) - dmin * m with d, dmin one f16 pair per 256 columns and row, sc / m 6-bit integers
+// per 32 columns, q a 4- or 5-bit integer (crates/inferi/src/quantization.rs:287-402).  sc * q <= 63 * 31 < 2048 is an
+// integer that f16 holds exactly, so per 256-column block
+//     sum_k w_k x_k = d * P - Z,   P = sum_k (sc * q)_k x_k,   Z = sum_sb (dmin * m_sb) * S_sb,   S_sb = sum_{k in sb} x_k
+// and P needs no hi / lo split of the weights: two MMAs per 16 columns (x hi, x lo) instead of three, one f16 tile to
+// write instead of two, and a conversion that is a byte permute and one packed f16 multiply-add per two weights
+// ((1024 + q) * sc - 1024 * sc, exact) instead of ~12 instructions per weight - the producers' instruction stream is what
+// bounds the general kernel.  The price: P must be scaled by d per (row, block), so every block's P is accumulated in
+// its own tensor-memory buffer (two, alternating) and folded into register accumulators by the producer warps
+// (tcgen05.ld, one f32 multiply-add per value) while the next block's MMAs run; Z (minimums x sub-block sums of the
+// inputs, both split hi / lo) accumulates over the whole K range in a third buffer: three small MMAs per block.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int KQ_WSTAGES = 3;                 // stages of the weights' tile (one f16 tile of 128 x 64: 16 KiB)
+constexpr int KQ_XSTAGES = 3;                 // stages of the inputs' tiles (hi, lo: 32 KiB)
+constexpr uint32_t KQ_ZTILE = TC_ROWS * 16 * 2;   // a 128 x 16 f16 tile of minimums or of sub-block sums: 4 KiB
+constexpr uint32_t KQ_ZSLOT = 4 * KQ_ZTILE;       // minimums hi, lo; sums hi, lo
+constexpr uint32_t KQ_SMEM_FIXED = KQ_WSTAGES * TC_TILE_BYTES + KQ_XSTAGES * 2 * TC_TILE_BYTES + 2 * KQ_ZSLOT + 1024 + 1024;
+constexpr uint32_t KQ_ZLBO = 128, KQ_ZSBO = 256;  // core matrices of the 16-column tiles
+
+template <bool Q5>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap wmap) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int PATH = Q5 ? TC_PATH_Q5K : TC_PATH_Q4K;
+    constexpr uint32_t RAW_BYTES = tc_raw_stage_bytes(PATH), RB = Q5 ? 176u : 144u;
+    const uint32_t R = p.raw_stages;
+    uint8_t *wst = smem;                                                   // weights' stages
+    uint8_t *xst = wst + KQ_WSTAGES * TC_TILE_BYTES;                       // inputs' stages
+    uint8_t *zst = xst + KQ_XSTAGES * 2 * TC_TILE_BYTES;                   // minimum / sum slots
+    const uint32_t raw0 = tc_smem_u32(zst + 2 * KQ_ZSLOT);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(zst + 2 * KQ_ZSLOT + R * RAW_BYTES);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // barriers, in this order
+    const uint32_t b_wfull = tc_smem_u32(bars), b_wempty = b_wfull + 8 * KQ_WSTAGES, b_xfull = b_wempty + 8 * KQ_WSTAGES, b_xempty = b_xfull + 8 * KQ_XSTAGES;
+    const uint32_t b_zfull = b_xempty + 8 * KQ_XSTAGES, b_zempty = b_zfull + 16, b_rawfull = b_zempty + 16, b_rawempty = b_rawfull + 8 * TC_RAW_MAX;
+    const uint32_t b_pdone = b_rawempty + 8 * TC_RAW_MAX, b_pfree = b_pdone + 16, b_zdone = b_pfree + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * KQ_WSTAGES + 2 * KQ_XSTAGES + 4 + 2 * TC_RAW_MAX + 5);
+    const StreamK sk = p.sk;
+    const uint32_t u0 = sk.first_unit(blockIdx.x), u1 = sk.first_unit(blockIdx.x + 1), nunits = u1 - u0, nstage = 4 * nunits;
+
+    if (tid == 0) {
+        auto init = [](uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); };
+        for (int s = 0; s < KQ_WSTAGES; s++) { init(b_wfull + 8 * s, TC_PRODUCER_WARPS); init(b_wempty + 8 * s, 1); }
+        for (int s = 0; s < KQ_XSTAGES; s++) { init(b_xfull + 8 * s, 1); init(b_xempty + 8 * s, 1); }
+        for (int s = 0; s < 2; s++) {
+            init(b_zfull + 8 * s, TC_PRODUCER_WARPS + 1);   // the producer warps' minimums + the loader's arrival with the sums' bytes
+            init(b_zempty + 8 * s, 1);
+            init(b_pdone + 8 * s, 1);                       // tcgen05.commit: the block's P is complete
+            init(b_pfree + 8 * s, TC_PRODUCER_WARPS);       // every producer warp has folded it into its registers
+        }
+        for (uint32_t s = 0; s < TC_RAW_MAX; s++) { init(b_rawfull + 8 * s, 1); init(b_rawempty + 8 * s, TC_PRODUCER_WARPS); }
+        init(b_zdone, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < TC_ROWS) {
+        // columns 8..15 of the minimums' tiles stay zero for the whole kernel
+        for (int s = 0; s < 2; s++)
+            for (int t = 0; t < 2; t++)
+                *reinterpret_cast<uint4 *>(zst + s * KQ_ZSLOT + t * KQ_ZTILE + (tid >> 3) * KQ_ZSBO + KQ_ZLBO + (tid & 7) * 16) = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == TC_PRODUCER_WARPS) {
+        // tensor memory: two P buffers and Z, 128 columns each (512 allocated: a power of two)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t groups = p.n_pad / 16;
+    bool ok = true;
+
+    if (warp < TC_PRODUCER_WARPS) {
+        // ===== producers: thread = (weight row `tid & 127` of the unit's tile, quarter `tid >> 7` of a stage's 64 columns);
+        // the same thread owns row `tid & 127` x 32 token columns of the output (tensor-memory lane = row) =====
+        const uint32_t row = tid & (TC_ROWS - 1), kq = tid >> 7;
+        uint32_t tile = u0 / sk.nb, kb = u0 - tile * sk.nb, ptile = tile, pkb = kb;
+        // One block of each of the tile's 128 rows = one box of the matrix seen as a 2-D byte array [rows][row_bytes]: a
+        // single tiled TMA copy per step.  (128 one-row bulk copies per step went through the copy engine at ~45 ns each,
+        // 5.8 us per step: more than everything else the step does.)
+        auto issue_raw = [&](uint32_t t, uint32_t b, uint32_t dst, uint32_t bar) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)TC_ROWS * RB) : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                         "l"(reinterpret_cast<uint64_t>(&wmap)), "r"(b * RB), "r"(t * (uint32_t)TC_ROWS), "r"(bar)
+                         : "memory");
+        };
+        uint32_t issued = 0;
+        for (; issued < R && issued < nunits; issued++) {
+            if (tid == 0) issue_raw(ptile, pkb, raw0 + issued * RAW_BYTES, b_rawfull + 8 * issued);
+            if (++pkb == sk.nb) { pkb = 0; ptile++; }
+        }
+        uint32_t slot = 0, slot_par = 0, pslot = 0, pslot_par = 0;
+        uint32_t ws = 0, wround = 0;                 // weights' stage and how often the ring has wrapped
+        float Y[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) Y[i] = 0.f;
+        float d_cur = 0.f, d_prev = 0.f;
+        uint32_t seg = 0;   // segments (tile, K range) finished so far: the parity of the Z barrier
+        uint32_t sc_y = 0, sc_z = 0, sc_w = 0;       // the block's twelve scale bytes
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        // fold P buffer `pb` (scaled by `dd`) into Y: the warp's 32 lanes x its token columns
+        auto fold = [&](uint32_t pb, float dd) {
+#pragma unroll
+            for (int g = 0; g < 2; g++) {
+                const uint32_t c0 = 16 * (warp >> 2) + 64 * g;
+                if (c0 < 16 * groups) {
+                    uint32_t r[16];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                                   "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                                 : "r"(taddr + pb * 128 + c0)
+                                 : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; i++) Y[16 * g + i] = fmaf(dd, __uint_as_float(r[i]), Y[16 * g + i]);
+                }
+            }
+        };
+        for (uint32_t it = 0; it < nstage && ok; it++) {
+            const uint32_t j = it >> 2, c = it & 3, u = u0 + j, zs = j & 1;
+            if (c == 0) {
+                if (j >= 1) {
+                    pslot = slot; pslot_par = slot_par;
+                    if (++slot == R) { slot = 0; slot_par ^= 1u; }
+                    if (++kb == sk.nb) { kb = 0; tile++; }
+                    if (issued < nunits) {
+                        // the slot of the previous step is refilled once every producer thread has read it
+                        if (warp == 0) {
+                            ok = __all_sync(0xffffffffu, tc_wait(b_rawempty + 8 * pslot, pslot_par, p.wait_ns, p.err, 8));
+                            if (!ok) break;
+                            if (lane == 0) issue_raw(ptile, pkb, raw0 + pslot * RAW_BYTES, b_rawfull + 8 * pslot);
+                        }
+                        issued++;
+                        if (++pkb == sk.nb) { pkb = 0; ptile++; }
+                    }
+                }
+                ok = __all_sync(0xffffffffu, tc_wait(b_rawfull + 8 * slot, slot_par, p.wait_ns, p.err, 8));
+                if (!ok) break;
+                // the block's header: d, dmin and the twelve scale bytes stay in registers for its four stages
+                const uint4 hdr = tc_lds128(raw0 + slot * RAW_BYTES + row * RB);
+                d_prev = d_cur;
+                d_cur = tc_h2f(hdr.x & 0xFFFFu);
+                sc_y = hdr.y; sc_z = hdr.z; sc_w = hdr.w;
+                // the minimums of sub-blocks 2 kq and 2 kq + 1, times dmin, split hi / lo: columns 2 kq, 2 kq + 1 of the
+                // block's 128 x 16 tile (get_scale_min_k4, quantization.rs:394-402)
+                if (j >= 2) {
+                    ok = __all_sync(0xffffffffu, tc_wait(b_zempty + 8 * zs, ((j >> 1) - 1) & 1, p.wait_ns, p.err, 8));
+                    if (!ok) break;
+                }
+                {
+                    const float dmin = tc_h2f(hdr.x >> 16);
+                    const uint32_t sb[3] = {sc_y, sc_z, sc_w};
+                    auto byte_at = [&](uint32_t i) { return (sb[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+                    float mm[2];
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const uint32_t jj = 2 * kq + e;
+                        const uint32_t mn = jj < 4 ? (byte_at(jj + 4) & 63u) : ((byte_at(jj + 4) >> 4) | ((byte_at(jj) >> 6) << 4));
+                        mm[e] = dmin * (float)mn;
+                    }
+                    const __half2 h = __floats2half2_rn(mm[0], mm[1]);
+                    const float2 back = __half22float2(h);
+                    const __half2 l = __floats2half2_rn(mm[0] - back.x, mm[1] - back.y);
+                    uint8_t *zt = zst + zs * KQ_ZSLOT + (row >> 3) * KQ_ZSBO + (row & 7) * 16 + 4 * kq;
+                    *reinterpret_cast<__half2 *>(zt) = h;
+                    *reinterpret_cast<__half2 *>(zt + KQ_ZTILE) = l;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_zfull + 8 * zs) : "memory");
+                }
+            }
+            // ---- the stage's 16 weights of this thread: sub-block jj = 2 c + (kq >> 1), bytes 16 (kq & 1) .. + 15 of its 32 ----
+            const uint32_t jj = 2 * c + (kq >> 1), high = jj & 1, hq = kq & 1;
+            const uint32_t blk = raw0 + slot * RAW_BYTES + row * RB;
+            const uint4 qv = tc_lds128(blk + (Q5 ? 48 : 16) + 32 * c + 16 * hq);
+            uint4 hv = make_uint4(0, 0, 0, 0);
+            if (Q5) hv = tc_lds128(blk + 16 + 16 * hq);
+            uint32_t sc;
+            {
+                const uint32_t sb[3] = {sc_y, sc_z, sc_w};
+                auto byte_at = [&](uint32_t i) { return (sb[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+                sc = jj < 4 ? (byte_at(jj) & 63u) : ((byte_at(jj + 4) & 0xFu) | ((byte_at(jj - 4) >> 6) << 4));
+            }
+            // (1024 + q) * sc - 1024 * sc = q * sc, exact in f16 (q * sc < 2048; 1024 * sc <= 64512 is representable)
+            const __half2 sc2 = __float2half2_rn((float)sc), off2 = __float2half2_rn(-1024.0f * (float)sc);
+            const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, hw[4] = {hv.x, hv.y, hv.z, hv.w};
+            uint32_t out[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t nib = high ? (qw[i] >> 4) & 0x0F0F0F0Fu : qw[i] & 0x0F0F0F0Fu;
+                if (Q5) nib |= ((hw[i] >> (2 * c + high)) & 0x01010101u) << 4;
+                const uint32_t p01 = __byte_perm(nib, 0x64646464u, 0x4140), p23 = __byte_perm(nib, 0x64646464u, 0x4342);   // f16 pairs (1024 + q)
+                const __half2 r01 = __hfma2(*reinterpret_cast<const __half2 *>(&p01), sc2, off2);
+                const __half2 r23 = __hfma2(*reinterpret_cast<const __half2 *>(&p23), sc2, off2);
+                out[2 * i] = *reinterpret_cast<const uint32_t *>(&r01);
+                out[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&r23);
+            }
+            if (c == 3) {
+                __syncwarp();   // every lane has read its part of the raw stage
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_rawempty + 8 * slot) : "memory");
+            }
+            if (wround > 0) ok = __all_sync(0xffffffffu, tc_wait(b_wempty + 8 * ws, (wround - 1) & 1, p.wait_ns, p.err, 8));
+            if (!ok) break;
+            uint8_t *st = wst + ws * TC_TILE_BYTES;
+            *reinterpret_cast<uint4 *>(st + tc_chunk_off(row, 2 * kq)) = make_uint4(out[0], out[1], out[2], out[3]);
+            *reinterpret_cast<uint4 *>(st + tc_chunk_off(row, 2 * kq + 1)) = make_uint4(out[4], out[5], out[6], out[7]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_wfull + 8 * ws) : "memory");
+            if (++ws == KQ_WSTAGES) { ws = 0; wround++; }
+            if (c == 3) {
+                const bool seg_end = kb + 1 == sk.nb || u + 1 == u1, seg_start = j == 0 || kb == 0;
+                // the previous block's P (complete long ago: its MMAs ran while this block was converted)
+                if (!seg_start) {
+                    ok = __all_sync(0xffffffffu, tc_wait(b_pdone + 8 * (zs ^ 1), ((j - 1) >> 1) & 1, p.wait_ns, p.err, 10));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    fold(zs ^ 1, d_prev);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_pfree + 8 * (zs ^ 1)) : "memory");
+                }
+                if (seg_end) {
+                    // the tile's K range in this CTA ends: this block's P too, then Z, then the plane
+                    ok = __all_sync(0xffffffffu, tc_wait(b_pdone + 8 * zs, (j >> 1) & 1, p.wait_ns, p.err, 10));
+                    if (ok) ok = __all_sync(0xffffffffu, tc_wait(b_zdone, seg & 1, p.wait_ns, p.err, 10));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    fold(zs, d_cur);
+                    fold(2, -1.0f);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_pfree + 8 * zs) : "memory");
+                    const uint32_t piece = blockIdx.x - sk.cta_of(tile * sk.nb);
+                    float *outp = p.out + (size_t)piece * p.n_tokens * p.rows + tile * TC_ROWS + row;
+#pragma unroll
+                    for (int g = 0; g < 2; g++)
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const uint32_t t = 16 * (warp >> 2) + 64 * g + i;
+                            if (t < p.n_tokens) outp[(size_t)t * p.rows] = Y[16 * g + i];
+                            Y[16 * g + i] = 0.f;
+                        }
+                    seg++;
+                }
+            }
+        }
+        if (!ok) {
+            const unsigned long long t0 = tc_ns();
+            while (tc_ns() - t0 < 100000ull) {}
+        }
+    } else if (warp == TC_PRODUCER_WARPS && lane == 0) {
+        // ===== MMA issue: one thread =====
+        const uint32_t idesc = tc_idesc_f16(TC_ROWS, p.n_pad);
+        uint32_t ws = 0, wpar = 0, xs = 0, xpar = 0;
+        // The issuing thread is one warp's instruction stream: whatever it computes per MMA is serial latency between two
+        // MMAs.  Building a 64-bit descriptor per operand and MMA kept the tensor pipe idle three quarters of the time.
+        const uint64_t wdesc0 = tc_smem_desc(tc_smem_u32(wst), TC_LBO, TC_SBO), xdesc0 = tc_smem_desc(tc_smem_u32(xst), TC_LBO, TC_SBO);
+        const uint64_t zdesc0 = tc_smem_desc(tc_smem_u32(zst), KQ_ZLBO, KQ_ZSBO);
+        uint32_t kb = u0 % sk.nb;
+        for (uint32_t it = 0; it < nstage && ok; it++) {
+            const uint32_t j = it >> 2, c = it & 3, u = u0 + j, pb = j & 1;
+            if (c == 0 && j >= 1 && ++kb == sk.nb) kb = 0;
+            const bool seg_start = j == 0 || kb == 0, seg_end = kb + 1 == sk.nb || u + 1 == u1;
+            if (c == 0) {
+                // the P buffer of this block must have been folded (two blocks ago); then Z: the block's minimums x sums
+                if (j >= 2) ok = tc_wait(b_pfree + 8 * pb, ((j >> 1) - 1) & 1, p.wait_ns, p.err, 9);
+                if (ok) ok = tc_wait(b_zfull + 8 * pb, (j >> 1) & 1, p.wait_ns, p.err, 9);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t m_hi = zdesc0 + pb * (KQ_ZSLOT >> 4), m_lo = m_hi + (KQ_ZTILE >> 4), s_hi = m_hi + 2 * (KQ_ZTILE >> 4), s_lo = m_hi + 3 * (KQ_ZTILE >> 4);
+                tc_mma_f16(tmem_base + 256, m_hi, s_hi, idesc, !seg_start);
+                tc_mma_f16(tmem_base + 256, m_hi, s_lo, idesc, 1);
+                tc_mma_f16(tmem_base + 256, m_lo, s_hi, idesc, 1);
+                tc_commit(b_zempty + 8 * pb);
+            }
+            ok = tc_wait(b_xfull + 8 * xs, xpar, p.wait_ns, p.err, 9) && tc_wait(b_wfull + 8 * ws, wpar, p.wait_ns, p.err, 9);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes): one addition each
+            const uint64_t wd = wdesc0 + ws * (TC_TILE_BYTES >> 4), xh = xdesc0 + xs * (2 * TC_TILE_BYTES >> 4), xl = xh + (TC_TILE_BYTES >> 4);
+#pragma unroll
+            for (uint32_t kk = 0; kk < TC_KSTAGE / 16; kk++) {
+                const uint32_t ko = kk * (2 * TC_LBO >> 4);   // 16 columns = two core matrices along K
+                tc_mma_f16(tmem_base + pb * 128, wd + ko, xh + ko, idesc, !(c == 0 && kk == 0));   // every block starts a new P
+                tc_mma_f16(tmem_base + pb * 128, wd + ko, xl + ko, idesc, 1);
+            }
+            tc_commit(b_wempty + 8 * ws);
+            tc_commit(b_xempty + 8 * xs);
+            if (c == 3) {
+                tc_commit(b_pdone + 8 * pb);
+                if (seg_end) tc_commit(b_zdone);
+            }
+            if (++ws == KQ_WSTAGES) { ws = 0; wpar ^= 1u; }
+            if (++xs == KQ_XSTAGES) { xs = 0; xpar ^= 1u; }
+        }
+    }
+
+    if (warp == TC_PRODUCER_WARPS + 1 && lane == 0) {
+        // ===== the inputs' tiles (two bulk copies per stage) and, per block, the tiles of their sub-block sums =====
+        bool okx = true;
+        const uint32_t xbytes = p.n_pad * (TC_KSTAGE * 2), sbytes = p.n_pad * 32;
+        const __half *s_hi = p.x_hi + (size_t)TC_ROWS * p.cols, *s_lo = p.x_lo + (size_t)TC_ROWS * p.cols;
+        uint32_t xs = 0, xround = 0;
+        for (uint32_t it = 0; it < nstage && okx; it++) {
+            const uint32_t j = it >> 2, c = it & 3, kb = (u0 + j) % sk.nb;
+            if (c == 0) {
+                const uint32_t zs = j & 1;
+                if (j >= 2) okx = tc_wait(b_zempty + 8 * zs, ((j >> 1) - 1) & 1, p.wait_ns, p.err, 8);
+                if (!okx) break;
+                const uint32_t full = b_zfull + 8 * zs, dst = tc_smem_u32(zst + zs * KQ_ZSLOT + 2 * KQ_ZTILE);
+                const size_t at = (size_t)kb * (TC_ROWS * 16);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * sbytes) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(s_hi + at), "r"(sbytes), "r"(full)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + KQ_ZTILE), "l"(s_lo + at), "r"(sbytes),
+                             "r"(full)
+                             : "memory");
+            }
+            if (xround > 0) okx = tc_wait(b_xempty + 8 * xs, (xround - 1) & 1, p.wait_ns, p.err, 8);
+            if (!okx) break;
+            const uint32_t full = b_xfull + 8 * xs, dst = tc_smem_u32(xst + xs * 2 * TC_TILE_BYTES);
+            const size_t at = (size_t)(4 * kb + c) * (TC_ROWS * TC_KSTAGE);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * xbytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p.x_hi + at), "r"(xbytes), "r"(full)
+                         : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + TC_TILE_BYTES), "l"(p.x_lo + at), "r"(xbytes),
+                         "r"(full)
+                         : "memory");
+            if (++xs == KQ_XSTAGES) { xs = 0; xround++; }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == TC_PRODUCER_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------------
 // element-wise kernels around the GEMMs (one thread per element or pair; rows = tokens)
 // ---------------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void split_store(__half *hi, __half *lo, size_t i, float v) {
@@ -486,6 +844,11 @@ __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X,
     const uint32_t t = blockIdx.x;
     if (t >= n) {
         for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { hi[tc_x_index(t, c)] = __float2half_rn(0.f); lo[tc_x_index(t, c)] = __float2half_rn(0.f); }
+        for (uint32_t k = threadIdx.x; k < cols / 16; k += blockDim.x) {   // 16 halves per 256 columns
+            const size_t at = tc_s_index(t, (k >> 4) * 8, cols) + ((k & 8) ? 64 : 0) + (k & 7);
+            hi[at] = __float2half_rn(0.f);
+            lo[at] = __float2half_rn(0.f);
+        }
         return;
     }
     const float *x = X + (size_t)t * cols;
@@ -501,7 +864,19 @@ __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X,
         for (int i = 0; i < 8; i++) tot += red[i];
         rms = 1.0f / sqrtf(tot / (float)cols + eps);
     }
-    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) split_store(hi, lo, tc_x_index(t, c), w ? (x[c] * rms) * w[c] : x[c]);
+    // cols is a multiple of 256 = blockDim.x: a warp's lanes hold one 32-column sub-block per pass
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float y = w ? (x[c] * rms) * w[c] : x[c];
+        split_store(hi, lo, tc_x_index(t, c), y);
+        float sum = y;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if ((threadIdx.x & 31) == 0) split_store(hi, lo, tc_s_index(t, c >> 5, cols), sum);
+        if ((threadIdx.x & 31) == 1 && ((c >> 5) & 7) == 0) {   // the eight zero halves of the unit's tile row
+            *reinterpret_cast<uint4 *>(hi + tc_s_index(t, c >> 5, cols) + 64) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(lo + tc_s_index(t, c >> 5, cols) + 64) = make_uint4(0, 0, 0, 0);
+        }
+    }
 }
 
 __device__ __forceinline__ float plane_sum(const float *planes, uint32_t pieces, size_t plane_elems, size_t i) {
@@ -521,6 +896,11 @@ __global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
         if (t >= p.n) {
             split_store(p.hi, p.lo, tc_x_index(t, r), 0.f);
             split_store(p.hi, p.lo, tc_x_index(t, r + 1), 0.f);
+            if ((r & 31) == 0) split_store(p.hi, p.lo, tc_s_index(t, r >> 5, p.rows), 0.f);
+            if ((r & 255) == 2) {
+                *reinterpret_cast<uint4 *>(p.hi + tc_s_index(t, (r >> 8) * 8, p.rows) + 64) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(p.lo + tc_s_index(t, (r >> 8) * 8, p.rows) + 64) = make_uint4(0, 0, 0, 0);
+            }
             continue;
         }
         const uint32_t np = p.sk.pieces(r / 128);   // the planes that the row's tile was spread over
@@ -528,8 +908,19 @@ __global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
         if (p.mode == PE_SWIGLU) {
             // crates/inferi-shaders/src/silu.rs:16-19,46-52
             const float ua = plane_sum(p.planes2, np, plane, i), ub = plane_sum(p.planes2, np, plane, i + 1);
-            split_store(p.hi, p.lo, tc_x_index(t, r), ua * (a / (1.0f + expf(-a))));
-            split_store(p.hi, p.lo, tc_x_index(t, r + 1), ub * (b / (1.0f + expf(-b))));
+            const float ya = ua * (a / (1.0f + expf(-a))), yb = ub * (b / (1.0f + expf(-b)));
+            split_store(p.hi, p.lo, tc_x_index(t, r), ya);
+            split_store(p.hi, p.lo, tc_x_index(t, r + 1), yb);
+            // the sums of the 32-column sub-blocks for the GEMM that follows: 16 neighbouring threads hold one sub-block
+            // (whole warps run this loop together: the number of pairs is a multiple of 64)
+            float sum = ya + yb;
+#pragma unroll
+            for (int o = 8; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((r & 31) == 0) split_store(p.hi, p.lo, tc_s_index(t, r >> 5, p.rows), sum);
+            if ((r & 255) == 2) {
+                *reinterpret_cast<uint4 *>(p.hi + tc_s_index(t, (r >> 8) * 8, p.rows) + 64) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(p.lo + tc_s_index(t, (r >> 8) * 8, p.rows) + 64) = make_uint4(0, 0, 0, 0);
+            }
             continue;
         }
         if (p.mode == PE_RESIDUAL) { p.out[i] += a; p.out[i + 1] += b; continue; }
@@ -566,22 +957,38 @@ uint32_t prefill_max_pieces(const StreamK &sk, uint32_t rows) {
     return most;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) ptr = nullptr;
+        return (EncodeTiledFn)ptr;
+    }();
+    return fn;
+}
+
 bool prefill_gemm_eligible(const ib_qtensor *m) {
     return m->rows % TC_ROWS == 0 && m->cols % 256 == 0 && (m->qtype == IB_Q4_K || m->qtype == IB_Q5_K || m->qtype == IB_Q6_K || m->qtype == IB_Q8_0);
 }
 
 int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, const __half *x_hi, const __half *x_lo, uint32_t n, float *planes, const StreamK &sk) {
     const int path = tc_path((uint32_t)m->qtype, m->layout);
-    const uint32_t raw_bytes = tc_raw_stage_bytes(path);
-    uint32_t raw_stages = raw_bytes ? (TC_SMEM_LIMIT - TC_SMEM_FIXED) / raw_bytes : 1;
+    const bool exact = path == TC_PATH_Q4K || path == TC_PATH_Q5K;   // integer weights on the tensor cores (gemm_kquant_tc_kernel)
+    const uint32_t raw_bytes = tc_raw_stage_bytes(path), fixed = exact ? KQ_SMEM_FIXED : TC_SMEM_FIXED;
+    uint32_t raw_stages = raw_bytes ? (TC_SMEM_LIMIT - fixed) / raw_bytes : 1;
     if (raw_stages > TC_RAW_MAX) raw_stages = TC_RAW_MAX;
-    const uint32_t smem_bytes = TC_SMEM_FIXED + raw_stages * raw_bytes;
-    void (*kernel)(GemmTcParams) = path == TC_PATH_Q4K ? gemm_quant_tc_kernel<TC_PATH_Q4K>
-                                   : (path == TC_PATH_Q5K ? gemm_quant_tc_kernel<TC_PATH_Q5K>
-                                                          : (path == TC_PATH_Q6K ? gemm_quant_tc_kernel<TC_PATH_Q6K> : gemm_quant_tc_kernel<TC_PATH_OTHER>));
+    const uint32_t smem_bytes = fixed + raw_stages * raw_bytes;
+    void (*kernel)(GemmTcParams) = path == TC_PATH_Q6K ? gemm_quant_tc_kernel<TC_PATH_Q6K> : gemm_quant_tc_kernel<TC_PATH_OTHER>;   // when not `exact`
     static bool attr_set[16][4] = {};
     if (!attr_set[ctx->device & 15][path]) {
-        IB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+        if (exact) {
+            IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_kquant_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+            IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_kquant_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+        } else {
+            IB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+        }
         attr_set[ctx->device & 15][path] = true;
     }
     IB_REQUIRE(((uintptr_t)m->dev % 16) == 0 && (m->row_bytes % 16) == 0 && ((uintptr_t)x_hi % 16) == 0 && ((uintptr_t)x_lo % 16) == 0,
@@ -592,7 +999,21 @@ int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, co
     p.rows = (uint32_t)m->rows; p.cols = (uint32_t)m->cols;
     p.x_hi = x_hi; p.x_lo = x_lo; p.n_tokens = n; p.n_pad = (n + 15) & ~15u;
     p.out = planes; p.sk = sk; p.err = ctx->err_dev; p.wait_ns = ctx->wait_limit_ns;
-    kernel<<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p);
+    if (exact) {
+        // the matrix as a 2-D byte array [rows][row_bytes]; a box = one block (144 / 176 bytes) of 128 consecutive rows
+        CUtensorMap wmap;
+        const cuuint64_t dims[2] = {(cuuint64_t)m->row_bytes, (cuuint64_t)m->rows}, strides[1] = {(cuuint64_t)m->row_bytes};
+        const cuuint32_t box[2] = {path == TC_PATH_Q5K ? 176u : 144u, (cuuint32_t)TC_ROWS}, estr[2] = {1, 1};
+        EncodeTiledFn encode = encode_tiled();
+        IB_REQUIRE(encode, "prefill GEMM: the driver does not export cuTensorMapEncodeTiled");
+        const CUresult cr = encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)m->dev, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        IB_REQUIRE(cr == CUDA_SUCCESS, "prefill GEMM: cuTensorMapEncodeTiled failed with %d", (int)cr);
+        if (path == TC_PATH_Q5K) gemm_kquant_tc_kernel<true><<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p, wmap);
+        else gemm_kquant_tc_kernel<false><<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p, wmap);
+    } else {
+        kernel<<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p);
+    }
     ctx->launches++;
     IB_CHECK_CUDA(cudaGetLastError());
     return IB_OK;
@@ -642,7 +1063,7 @@ extern "C" int32_t ib_gemm_quant(ib_ctx *ctx, void *stream, float *out_dev, cons
     const uint32_t rows = (uint32_t)m->rows, cols = (uint32_t)m->cols;
     const StreamK sk = prefill_streamk(ctx, rows, cols);
     const uint32_t ks = prefill_max_pieces(sk, rows);
-    const size_t half_bytes = (size_t)TC_ROWS * cols * sizeof(__half), plane_bytes = (size_t)ks * TC_ROWS * rows * sizeof(float);
+    const size_t half_bytes = tc_x_halves(cols) * sizeof(__half), plane_bytes = (size_t)ks * TC_ROWS * rows * sizeof(float);
     const size_t need = 2 * half_bytes + plane_bytes;
     int32_t rc = IB_OK;
     if (need > ctx->tc_scratch_bytes) {
