@@ -17,6 +17,7 @@ pytestmark = pytest.mark.gpu
     (quant.Q4_K, 128, 256, 16), (quant.Q4_K, 128, 256, 1), (quant.Q6_K, 128, 2048, 7), (quant.Q8_0, 256, 512, 33), (quant.Q5_K, 128, 1024, 128),
     (quant.Q4_K, 512, 2048, 32), (quant.Q6_K, 1024, 4096, 37), (quant.Q4_K, 4096, 4096, 128), (quant.Q4_K, 256, 14336, 5), (quant.Q6_K, 2048, 8192, 100),
     (quant.Q4_K, 384, 1024, 300),   # more rows than one pass takes: chunks of 128
+    (quant.Q4_K, 14336, 4096, 96), (quant.Q5_K, 4096, 14336, 50),   # 1792 units over one wave of CTAs: tiles split between two or three of them
 ])
 def test_gemm_matches_row_by_row_gemv(backend, qt, rows, cols, n):
     blocks = quant.random_blocks(qt, rows, cols, seed=rows + cols + n, scale=0.05)
@@ -29,7 +30,7 @@ def test_gemm_matches_row_by_row_gemv(backend, qt, rows, cols, n):
     for t in sorted({0, n // 2, n - 1}):
         ref = oracle.gemv_ref(qt, rows, cols, blocks, x[t])
         e = assert_close(got[t], ref, what=f"gemm {quant.NAMES[qt]} {rows}x{cols} row {t} of {n}")
-        assert e < 1e-4     # two f16 halves per operand carry ~21 bits
+        assert e < 1e-4     # two f16 halves per split operand carry ~21 bits (the k-quant weights are exact integers)
     m.close()
 
 
