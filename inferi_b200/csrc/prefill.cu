@@ -5,22 +5,25 @@
 // (crates/inferi-chat/src/chat_llama2.rs:137-155, crates/inferi-chat/src/sampler.rs:102-107), which reads every weight
 // once per prompt token.  Here the weights are read once per prompt.
 //
-// gemm_quant_tc_kernel: out^T tile = W tile (128 rows of the quantized matrix) x X^T (the tokens' input vectors).
-//  * the quantized blocks of the tile's 128 rows travel to shared memory by bulk copies (cp.async.bulk, one 256-column
-//    block per row and step, a ring of steps ahead of their use) - no thread-per-row global loads, which were 32 cache
-//    lines per load instruction and kept the L1 busy 91 % of the time;
-//  * eight producer warps, two threads per weight row: read the row's block from shared memory, dequantize 64 columns of
+// Two GEMM kernels, both out^T tile = W tile (128 rows of the quantized matrix) x X^T (the tokens' input vectors):
+// gemm_kquant_tc_kernel for Q4_K / Q5_K (exact integer weights on the tensor cores; its own comment below) and
+// gemm_quant_tc_kernel for Q6_K and everything else:
+//  * the quantized blocks of the tile's 128 rows travel to shared memory by tiled TMA copies (one 256-column block of every
+//    row per step, a ring of steps ahead of their use) - no thread-per-row global loads, which were 32 cache lines per load
+//    instruction and kept the L1 busy 91 % of the time;
+//  * sixteen producer warps, four threads per weight row: read the row's block from shared memory, dequantize 64 columns of
 //    the row per stage to f32, split the value into two f16 (w = hi + lo, exact to ~2^-22) and store both into shared
 //    memory in the K-major core-matrix layout the tensor core reads (8 rows x 16 bytes per core matrix, no swizzle);
 //  * the tokens' inputs (already split into f16 hi / lo by the kernel that produced them, and laid out in global memory
-//    as tiles of that same layout) arrive by one bulk copy per tile;
+//    as tiles of that same layout) arrive by one bulk copy per tile, requested by a loader thread into a ring of their own;
 //  * one thread issues, per 16 columns, three tcgen05.mma (hi x hi, hi x lo, lo x hi; lo x lo is below f32 resolution)
 //    that accumulate in f32 in tensor memory: the result matches the f32 arithmetic of the decode path to ~1e-6;
 //  * shared-memory stages cycle through mbarriers (filled by the producers, released by tcgen05.commit);
-//  * when the K range is done the producer warps read the accumulator (tcgen05.ld: TMEM lane = weight row, column =
+//  * when a tile's K range is done the producer warps read the accumulator (tcgen05.ld: TMEM lane = weight row, column =
 //    token) and store it transposed, [token][row], coalesced over the rows.
-// Matrices with few row tiles split K over several CTAs; each writes its own partial plane and the element-wise kernel
-// that follows (RoPE + cache append, residual add, SwiGLU) adds the planes in a fixed order.
+// The (tile, 256-column block) units of a matrix are dealt out as equal contiguous ranges over one wave of CTAs (StreamK in
+// prefill.cuh); a tile whose K range falls to several CTAs gets one partial plane per CTA, and the element-wise kernel that
+// follows (RoPE + cache append, residual add, SwiGLU) adds a tile's planes in CTA order.
 // Every wait is bounded; a wait that gives up raises the context's error word and the kernel returns after freeing its
 // tensor memory.
 #include "prefill.cuh"
@@ -129,30 +132,6 @@ __device__ __forceinline__ uint32_t tc_lds16(uint32_t a) {
     unsigned short v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
     return v;
-}
-
-// One row's block of the step -> shared memory; called by whole warps (lane 0's arrival announces the warp's bytes: an arrival
-// per thread would be hundreds of serialized updates of one barrier word per step).  `kb` = block number in the row.
-template <int PATH>
-__device__ __forceinline__ void tc_issue_raw(const uint8_t *wrow, uint32_t kb, uint32_t raw, uint32_t row, uint32_t bar) {
-    auto copy = [&](uint32_t dst, const uint8_t *src, uint32_t bytes) {
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-    };
-    if (PATH == TC_PATH_Q4K || PATH == TC_PATH_Q5K) {
-        constexpr uint32_t B = PATH == TC_PATH_Q4K ? 144u : 176u;
-        if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(32u * B) : "memory");
-        __syncwarp();
-        copy(raw + row * B, wrow + (size_t)kb * B, B);
-    } else if (PATH == TC_PATH_Q6K) {
-        const uint8_t *grp = wrow + (size_t)(kb >> 3) * 1680;
-        const uint32_t bb = kb & 7;
-        if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(32u * (128u + 64u + 16u + 16u)) : "memory");
-        __syncwarp();
-        copy(raw + TC_Q6_QL + row * 144, grp + 128 * bb, 128);
-        copy(raw + TC_Q6_QH + row * 80, grp + 1024 + 64 * bb, 64);
-        copy(raw + TC_Q6_SC + row * 16, grp + 1536 + 16 * bb, 16);
-        copy(raw + TC_Q6_D + row * 16, grp + 1664, 16);
-    }
 }
 
 // The thread's bytes of 16 weights - sixteenth `kq` (0..3) of the 64-column quarter `c` of the block: shared memory -> registers.
@@ -277,7 +256,8 @@ __device__ __forceinline__ void tc_drain(const GemmTcParams &p, uint32_t tmem_ba
 }
 
 template <int PATH>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const GemmTcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap map_ql,
+                                                                      const __grid_constant__ CUtensorMap map_qh, const __grid_constant__ CUtensorMap map_16) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t RAW_BYTES = tc_raw_stage_bytes(PATH);
@@ -302,7 +282,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_acc), "r"(1));       // a segment's accumulator is complete
         for (uint32_t s = 0; s < TC_RAW_MAX; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawfull + 8 * s), "r"(TC_ROWS / 32));               // one arrival per copying warp
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawfull + 8 * s), "r"(1));                          // the copying thread's arrival + the bytes
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_rawempty + 8 * s), "r"(TC_PRODUCER_WARPS));         // every producer warp has read it
         }
         for (int s = 0; s < TC_XSTAGES; s++) {
@@ -331,10 +311,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
         uint32_t tile = u0 / sk.nb, kb = u0 - tile * sk.nb;          // the current unit
         uint32_t ptile = tile, pkb = kb;                              // the next unit to request into the ring
         auto row_at = [&](uint32_t t) { return p.w.w + (size_t)(t * TC_ROWS + row) * p.w.row_bytes; };
-        // the ring of raw blocks is filled ahead: one block of every row of the unit's tile per step, each row by its own bulk copy
+        // The ring of raw blocks is filled ahead, one block of each of the unit's 128 rows per step.  The re-tiled Q6_K row keeps a
+        // block's low bits, high bits, scales and d in four places: four tiled TMA copies (boxes of 128 rows; the boxes of the low
+        // and high bits are 16 bytes wider than the field, which gives the shared-memory rows their conflict-free strides of
+        // 144 and 80 bytes - the extra bytes are the row's own next bytes and are never read).
+        auto issue_raw = [&](uint32_t t, uint32_t b, uint32_t dst, uint32_t bar) {
+            const uint32_t x0 = (b >> 3) * 1680, bb = b & 7, y = t * (uint32_t)TC_ROWS;
+            auto copy = [&](const CUtensorMap &map, uint32_t d, uint32_t x) {
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(d),
+                             "l"(reinterpret_cast<uint64_t>(&map)), "r"(x), "r"(y), "r"(bar)
+                             : "memory");
+            };
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)TC_ROWS * (144u + 80u + 16u + 16u)) : "memory");
+            copy(map_ql, dst + TC_Q6_QL, x0 + 128 * bb);
+            copy(map_qh, dst + TC_Q6_QH, x0 + 1024 + 64 * bb);
+            copy(map_16, dst + TC_Q6_SC, x0 + 1536 + 16 * bb);
+            copy(map_16, dst + TC_Q6_D, x0 + 1664);
+        };
         uint32_t issued = 0;
         for (; issued < R && issued < nunits; issued++) {
-            if (RAW && tid < TC_ROWS) tc_issue_raw<PATH>(row_at(ptile), pkb, raw0 + issued * RAW_BYTES, row, bar_rawfull + 8 * issued);
+            if (RAW && tid == 0) issue_raw(ptile, pkb, raw0 + issued * RAW_BYTES, bar_rawfull + 8 * issued);
             if (++pkb == sk.nb) { pkb = 0; ptile++; }
         }
         uint32_t slot = 0, slot_par = 0;        // ring slot of the current unit and the parity of its use
@@ -353,10 +349,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
             if (RAW && c == 0) {
                 if (j >= 1 && issued < nunits) {
                     // the slot of the previous step is refilled once every producer thread has read it
-                    if (tid < TC_ROWS) {
+                    if (warp == 0) {
                         ok = __all_sync(0xffffffffu, tc_wait(bar_rawempty + 8 * pslot, pslot_par, p.wait_ns, p.err, 8));   // warp-uniform: the lanes stay together
                         if (!ok) break;
-                        tc_issue_raw<PATH>(row_at(ptile), pkb, raw0 + pslot * RAW_BYTES, row, bar_rawfull + 8 * pslot);
+                        if (lane == 0) issue_raw(ptile, pkb, raw0 + pslot * RAW_BYTES, bar_rawfull + 8 * pslot);
                     }
                     issued++;
                     if (++pkb == sk.nb) { pkb = 0; ptile++; }
@@ -980,14 +976,14 @@ int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, co
     uint32_t raw_stages = raw_bytes ? (TC_SMEM_LIMIT - fixed) / raw_bytes : 1;
     if (raw_stages > TC_RAW_MAX) raw_stages = TC_RAW_MAX;
     const uint32_t smem_bytes = fixed + raw_stages * raw_bytes;
-    void (*kernel)(GemmTcParams) = path == TC_PATH_Q6K ? gemm_quant_tc_kernel<TC_PATH_Q6K> : gemm_quant_tc_kernel<TC_PATH_OTHER>;   // when not `exact`
     static bool attr_set[16][4] = {};
     if (!attr_set[ctx->device & 15][path]) {
         if (exact) {
             IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_kquant_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
             IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_kquant_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
         } else {
-            IB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+            IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_quant_tc_kernel<TC_PATH_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
+            IB_CHECK_CUDA(cudaFuncSetAttribute(gemm_quant_tc_kernel<TC_PATH_OTHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM_LIMIT)));
         }
         attr_set[ctx->device & 15][path] = true;
     }
@@ -1012,7 +1008,22 @@ int32_t launch_prefill_gemm(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *m, co
         if (path == TC_PATH_Q5K) gemm_kquant_tc_kernel<true><<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p, wmap);
         else gemm_kquant_tc_kernel<false><<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p, wmap);
     } else {
-        kernel<<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p);
+        // Q6_K in the 8-block row layout: boxes of 128 rows x 144 / 80 / 16 bytes (see the kernel); other formats: unused
+        CUtensorMap maps[3] = {};
+        if (path == TC_PATH_Q6K) {
+            const cuuint64_t dims[2] = {(cuuint64_t)m->row_bytes, (cuuint64_t)m->rows}, strides[1] = {(cuuint64_t)m->row_bytes};
+            const cuuint32_t widths[3] = {144, 80, 16}, estr[2] = {1, 1};
+            EncodeTiledFn encode = encode_tiled();
+            IB_REQUIRE(encode, "prefill GEMM: the driver does not export cuTensorMapEncodeTiled");
+            for (int i = 0; i < 3; i++) {
+                const cuuint32_t box[2] = {widths[i], (cuuint32_t)TC_ROWS};
+                const CUresult cr = encode(&maps[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)m->dev, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                IB_REQUIRE(cr == CUDA_SUCCESS, "prefill GEMM: cuTensorMapEncodeTiled failed with %d", (int)cr);
+            }
+        }
+        if (path == TC_PATH_Q6K) gemm_quant_tc_kernel<TC_PATH_Q6K><<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p, maps[0], maps[1], maps[2]);
+        else gemm_quant_tc_kernel<TC_PATH_OTHER><<<sk.ctas, TC_THREADS, smem_bytes, s>>>(p, maps[0], maps[1], maps[2]);
     }
     ctx->launches++;
     IB_CHECK_CUDA(cudaGetLastError());
