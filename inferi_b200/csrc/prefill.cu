@@ -836,11 +836,13 @@ __global__ void prefill_embed_kernel(QDesc embd, const uint32_t *tokens, uint32_
 // One CTA per token row: y = (x * rsqrt(mean(x^2) + eps)) * w (crates/inferi-shaders/src/rms_norm.rs:112-120; `w` null: y = x),
 // stored as the two f16 halves the GEMM reads, in its tiled layout (tc_x_index).  Rows n .. n_pad-1 are zero-filled.
 __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X, const float *w, float eps, uint32_t n, uint32_t cols, __half *hi, __half *lo) {
+    // grid: (token row, chunk of 1024 columns).  Every CTA of a row forms the row's sum of squares itself (16 KiB from L2)
+    // rather than wait for a second kernel: with one CTA per row the kernel was a 16-pass latency chain of 14-19 us.
     __shared__ float red[8];
-    const uint32_t t = blockIdx.x;
+    const uint32_t t = blockIdx.x, c_beg = blockIdx.y * 1024, c_end = c_beg + 1024 < cols ? c_beg + 1024 : cols;
     if (t >= n) {
-        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { hi[tc_x_index(t, c)] = __float2half_rn(0.f); lo[tc_x_index(t, c)] = __float2half_rn(0.f); }
-        for (uint32_t k = threadIdx.x; k < cols / 16; k += blockDim.x) {   // 16 halves per 256 columns
+        for (uint32_t c = c_beg + threadIdx.x; c < c_end; c += blockDim.x) { hi[tc_x_index(t, c)] = __float2half_rn(0.f); lo[tc_x_index(t, c)] = __float2half_rn(0.f); }
+        for (uint32_t k = c_beg / 16 + threadIdx.x; k < c_end / 16; k += blockDim.x) {   // 16 halves per 256 columns
             const size_t at = tc_s_index(t, (k >> 4) * 8, cols) + ((k & 8) ? 64 : 0) + (k & 7);
             hi[at] = __float2half_rn(0.f);
             lo[at] = __float2half_rn(0.f);
@@ -861,7 +863,7 @@ __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X,
         rms = 1.0f / sqrtf(tot / (float)cols + eps);
     }
     // cols is a multiple of 256 = blockDim.x: a warp's lanes hold one 32-column sub-block per pass
-    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    for (uint32_t c = c_beg + threadIdx.x; c < c_end; c += blockDim.x) {
         const float y = w ? (x[c] * rms) * w[c] : x[c];
         split_store(hi, lo, tc_x_index(t, c), y);
         float sum = y;
@@ -875,9 +877,18 @@ __global__ void __launch_bounds__(256) prefill_norm_split_kernel(const float *X,
     }
 }
 
-__device__ __forceinline__ float plane_sum(const float *planes, uint32_t pieces, size_t plane_elems, size_t i) {
-    float v = 0.f;
-    for (uint32_t s = 0; s < pieces; s++) v += planes[s * plane_elems + i];   // fixed order: deterministic
+// Elements i, i + 1 (i even) summed over a tile's planes, in plane order (deterministic); the loads of the planes are
+// independent 8-byte loads, all in flight together.
+__device__ __forceinline__ float2 plane_sum2(const float *planes, uint32_t pieces, size_t plane_elems, size_t i) {
+    float2 v = make_float2(0.f, 0.f);
+    for (uint32_t s0 = 0; s0 < pieces; s0 += 4) {
+        float2 t[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            t[k] = s0 + k < pieces ? __ldcs(reinterpret_cast<const float2 *>(planes + (s0 + k) * plane_elems + i)) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 4; k++) { v.x += t[k].x; v.y += t[k].y; }
+    }
     return v;
 }
 
@@ -900,10 +911,12 @@ __global__ void prefill_epilogue_kernel(const PrefillEpiParams p) {
             continue;
         }
         const uint32_t np = p.sk.pieces(r / 128);   // the planes that the row's tile was spread over
-        float a = plane_sum(p.planes, np, plane, i), b = plane_sum(p.planes, np, plane, i + 1);
+        const float2 ab = plane_sum2(p.planes, np, plane, i);
+        float a = ab.x, b = ab.y;
         if (p.mode == PE_SWIGLU) {
             // crates/inferi-shaders/src/silu.rs:16-19,46-52
-            const float ua = plane_sum(p.planes2, np, plane, i), ub = plane_sum(p.planes2, np, plane, i + 1);
+            const float2 uab = plane_sum2(p.planes2, np, plane, i);
+            const float ua = uab.x, ub = uab.y;
             const float ya = ua * (a / (1.0f + expf(-a))), yb = ub * (b / (1.0f + expf(-b)));
             split_store(p.hi, p.lo, tc_x_index(t, r), ya);
             split_store(p.hi, p.lo, tc_x_index(t, r + 1), yb);
@@ -1040,7 +1053,7 @@ int32_t launch_prefill_embed(ib_ctx *ctx, cudaStream_t s, const ib_qtensor *embd
 }
 
 int32_t launch_prefill_norm_split(ib_ctx *ctx, cudaStream_t s, const float *X, const float *w, float eps, uint32_t n, uint32_t cols, __half *hi, __half *lo) {
-    prefill_norm_split_kernel<<<(n + 15) & ~15u, 256, 0, s>>>(X, w, eps, n, cols, hi, lo);
+    prefill_norm_split_kernel<<<dim3((n + 15) & ~15u, (cols + 1023) / 1024), 256, 0, s>>>(X, w, eps, n, cols, hi, lo);
     ctx->launches++;
     IB_CHECK_CUDA(cudaGetLastError());
     return IB_OK;
