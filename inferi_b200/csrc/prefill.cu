@@ -104,9 +104,9 @@ __device__ __forceinline__ uint32_t tc_chunk_off(uint32_t row, uint32_t k8) { re
 // ---- 16 consecutive weights of a row (k0 a multiple of 16) as f32 ----
 __device__ __forceinline__ float tc_h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
 
-// How a matrix reaches the producers.  0: Q4_K, 1: Q5_K, 2: Q6_K in the 8-block row layout - their blocks are copied into
-// shared memory by bulk copies, one 256-column block of every row of the tile per step; 3: everything else (read from
-// global memory element by element).
+// How a matrix reaches the producers.  0: Q4_K, 1: Q5_K (gemm_kquant_tc_kernel), 2: Q6_K in the 8-block row layout - their
+// blocks are copied into shared memory by tiled TMA copies, one 256-column block of every row of the tile per step;
+// 3: everything else (read from global memory element by element).
 constexpr int TC_PATH_Q4K = 0, TC_PATH_Q5K = 1, TC_PATH_Q6K = 2, TC_PATH_OTHER = 3;
 __host__ __device__ inline int tc_path(uint32_t qtype, uint32_t layout) {
     return qtype == IB_Q4_K ? TC_PATH_Q4K : (qtype == IB_Q5_K ? TC_PATH_Q5K : ((qtype == IB_Q6_K && layout == LAYOUT_SOA) ? TC_PATH_Q6K : TC_PATH_OTHER));
@@ -136,51 +136,18 @@ __device__ __forceinline__ uint32_t tc_lds16(uint32_t a) {
 
 // The thread's bytes of 16 weights - sixteenth `kq` (0..3) of the 64-column quarter `c` of the block: shared memory -> registers.
 struct TcRaw {
-    uint4 hdr, q, h;  // Q4_K / Q5_K: header, 16 quant bytes, (Q5_K) the 16 high-bit bytes; Q6_K: q = low bits, h = high bits
-    uint32_t s, d;    // Q6_K: the scale of the 16 weights, the block's f16 scale
+    uint4 q, h;       // Q6_K: 16 bytes of low bits, 16 bytes of high bits
+    uint32_t s, d;    // the scale of the 16 weights, the block's f16 scale
 };
 template <int PATH>
 __device__ __forceinline__ void tc_read_raw(uint32_t raw, uint32_t row, uint32_t kb, uint32_t c, uint32_t kq, TcRaw &r) {
     const uint32_t hq = kq & 1;   // which 16 of the sub-block's 32 weights
-    if (PATH == TC_PATH_Q4K) {
-        const uint32_t blk = raw + row * 144;
-        r.hdr = tc_lds128(blk);
-        r.q = tc_lds128(blk + 16 + 32 * c + 16 * hq);
-    } else if (PATH == TC_PATH_Q5K) {
-        const uint32_t blk = raw + row * 176;
-        r.hdr = tc_lds128(blk);
-        r.q = tc_lds128(blk + 48 + 32 * c + 16 * hq);
-        r.h = tc_lds128(blk + 16 + 16 * hq);
-    } else if (PATH == TC_PATH_Q6K) {
+    if (PATH == TC_PATH_Q6K) {
         const uint32_t i = c >> 1, g = (2 * c + (kq >> 1)) & 3;
         r.q = tc_lds128(raw + TC_Q6_QL + row * 144 + 64 * i + 32 * (g & 1) + 16 * hq);
         r.h = tc_lds128(raw + TC_Q6_QH + row * 80 + 32 * i + 16 * hq);
         r.s = tc_lds8(raw + TC_Q6_SC + row * 16 + 8 * i + 2 * g + hq);
         r.d = tc_lds16(raw + TC_Q6_D + row * 16 + 2 * (kb & 7));
-    }
-}
-
-// crates/inferi/src/quantization.rs:364-402 (Q4_K) and :287-329 (Q5_K): sub-block j of the block, low or high nibbles of a
-// 32-byte chunk, w = d * sc * q - dmin * m
-template <bool Q5>
-__device__ __forceinline__ void tc_convert16_q45k(const TcRaw &r, uint32_t k0, float (&w)[16]) {
-    const uint32_t j = (k0 & 255) >> 5, c = j >> 1, high = j & 1;
-    const uint4 hdr = r.hdr;
-    // get_scale_min_k4 (quantization.rs:394-402) on the 12 scale bytes held in hdr.y, hdr.z, hdr.w
-    const uint32_t sb[3] = {hdr.y, hdr.z, hdr.w};
-    auto byte_at = [&](uint32_t i) { return (sb[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
-    uint32_t sc, mn;
-    if (j < 4) { sc = byte_at(j) & 63; mn = byte_at(j + 4) & 63; }
-    else { sc = (byte_at(j + 4) & 0xF) | ((byte_at(j - 4) >> 6) << 4); mn = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4); }
-    const float dsc = tc_h2f(hdr.x & 0xFFFFu) * (float)sc, dm = tc_h2f(hdr.x >> 16) * (float)mn;
-    const uint32_t qw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
-    const uint32_t hw[4] = {r.h.x, r.h.y, r.h.z, r.h.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t nib = high ? (qw[i] >> 4) & 0x0F0F0F0Fu : qw[i] & 0x0F0F0F0Fu;
-        if (Q5) nib |= ((hw[i] >> (2 * c + high)) & 0x01010101u) << 4;
-#pragma unroll
-        for (int b = 0; b < 4; b++) w[4 * i + b] = (float)((nib >> (8 * b)) & 0xFFu) * dsc - dm;
     }
 }
 
@@ -201,9 +168,7 @@ __device__ __forceinline__ void tc_convert16_q6k_soa(const TcRaw &r, uint32_t k0
 
 template <int PATH>
 __device__ __forceinline__ void tc_convert16(const QDesc &q, const uint8_t *row, const TcRaw &r, uint32_t k0, float (&w)[16]) {
-    if (PATH == TC_PATH_Q4K) tc_convert16_q45k<false>(r, k0, w);
-    else if (PATH == TC_PATH_Q5K) tc_convert16_q45k<true>(r, k0, w);
-    else if (PATH == TC_PATH_Q6K) tc_convert16_q6k_soa(r, k0, w);
+    if (PATH == TC_PATH_Q6K) tc_convert16_q6k_soa(r, k0, w);
     else {
 #pragma unroll
         for (int e = 0; e < 16; e++) w[e] = dequant_at(q, row, k0 + e);   // unrolled: w stays in registers
