@@ -453,9 +453,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_quant_tc_kernel(const Gemm
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int KQ_WSTAGES = 3;                 // stages of the weights' tile (one f16 tile of 128 x 64: 16 KiB)
 constexpr int KQ_XSTAGES = 3;                 // stages of the inputs' tiles (hi, lo: 32 KiB)
+constexpr uint32_t KQ_ZSLOTS = 1;             // slots for a block's minimums / sub-block sums
 constexpr uint32_t KQ_ZTILE = TC_ROWS * 16 * 2;   // a 128 x 16 f16 tile of minimums or of sub-block sums: 4 KiB
 constexpr uint32_t KQ_ZSLOT = 4 * KQ_ZTILE;       // minimums hi, lo; sums hi, lo
-constexpr uint32_t KQ_SMEM_FIXED = KQ_WSTAGES * TC_TILE_BYTES + KQ_XSTAGES * 2 * TC_TILE_BYTES + 2 * KQ_ZSLOT + 1024 + 1024;
+constexpr uint32_t KQ_SMEM_FIXED = KQ_WSTAGES * TC_TILE_BYTES + KQ_XSTAGES * 2 * TC_TILE_BYTES + KQ_ZSLOTS * KQ_ZSLOT + 1024 + 1024;
 constexpr uint32_t KQ_ZLBO = 128, KQ_ZSBO = 256;  // core matrices of the 16-column tiles
 
 template <bool Q5>
@@ -468,8 +469,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
     uint8_t *wst = smem;                                                   // weights' stages
     uint8_t *xst = wst + KQ_WSTAGES * TC_TILE_BYTES;                       // inputs' stages
     uint8_t *zst = xst + KQ_XSTAGES * 2 * TC_TILE_BYTES;                   // minimum / sum slots
-    const uint32_t raw0 = tc_smem_u32(zst + 2 * KQ_ZSLOT);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(zst + 2 * KQ_ZSLOT + R * RAW_BYTES);
+    const uint32_t raw0 = tc_smem_u32(zst + KQ_ZSLOTS * KQ_ZSLOT);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(zst + KQ_ZSLOTS * KQ_ZSLOT + R * RAW_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // barriers, in this order
     const uint32_t b_wfull = tc_smem_u32(bars), b_wempty = b_wfull + 8 * KQ_WSTAGES, b_xfull = b_wempty + 8 * KQ_WSTAGES, b_xempty = b_xfull + 8 * KQ_XSTAGES;
@@ -495,7 +496,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
     }
     if (tid < TC_ROWS) {
         // columns 8..15 of the minimums' tiles stay zero for the whole kernel
-        for (int s = 0; s < 2; s++)
+        for (uint32_t s = 0; s < KQ_ZSLOTS; s++)
             for (int t = 0; t < 2; t++)
                 *reinterpret_cast<uint4 *>(zst + s * KQ_ZSLOT + t * KQ_ZTILE + (tid >> 3) * KQ_ZSBO + KQ_ZLBO + (tid & 7) * 16) = make_uint4(0, 0, 0, 0);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -542,6 +543,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
         const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         // fold P buffer `pb` (scaled by `dd`) into Y: the warp's 32 lanes x its token columns
         auto fold = [&](uint32_t pb, float dd) {
+            // one 16-column read at a time: both in flight at once need 16 more registers than 18 warps leave (96 per thread)
 #pragma unroll
             for (int g = 0; g < 2; g++) {
                 const uint32_t c0 = 16 * (warp >> 2) + 64 * g;
@@ -559,7 +561,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
             }
         };
         for (uint32_t it = 0; it < nstage && ok; it++) {
-            const uint32_t j = it >> 2, c = it & 3, u = u0 + j, zs = j & 1;
+            const uint32_t j = it >> 2, c = it & 3, u = u0 + j, pb = j & 1, zs = j % KQ_ZSLOTS, zuse = j / KQ_ZSLOTS;
             if (c == 0) {
                 if (j >= 1) {
                     pslot = slot; pslot_par = slot_par;
@@ -585,8 +587,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
                 sc_y = hdr.y; sc_z = hdr.z; sc_w = hdr.w;
                 // the minimums of sub-blocks 2 kq and 2 kq + 1, times dmin, split hi / lo: columns 2 kq, 2 kq + 1 of the
                 // block's 128 x 16 tile (get_scale_min_k4, quantization.rs:394-402)
-                if (j >= 2) {
-                    ok = __all_sync(0xffffffffu, tc_wait(b_zempty + 8 * zs, ((j >> 1) - 1) & 1, p.wait_ns, p.err, 8));
+                if (j >= KQ_ZSLOTS) {
+                    ok = __all_sync(0xffffffffu, tc_wait(b_zempty + 8 * zs, (zuse - 1) & 1, p.wait_ns, p.err, 8));
                     if (!ok) break;
                 }
                 {
@@ -654,25 +656,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
                 const bool seg_end = kb + 1 == sk.nb || u + 1 == u1, seg_start = j == 0 || kb == 0;
                 // the previous block's P (complete long ago: its MMAs ran while this block was converted)
                 if (!seg_start) {
-                    ok = __all_sync(0xffffffffu, tc_wait(b_pdone + 8 * (zs ^ 1), ((j - 1) >> 1) & 1, p.wait_ns, p.err, 10));
+                    ok = __all_sync(0xffffffffu, tc_wait(b_pdone + 8 * (pb ^ 1), ((j - 1) >> 1) & 1, p.wait_ns, p.err, 10));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    fold(zs ^ 1, d_prev);
+                    fold(pb ^ 1, d_prev);
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_pfree + 8 * (zs ^ 1)) : "memory");
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_pfree + 8 * (pb ^ 1)) : "memory");
                 }
                 if (seg_end) {
                     // the tile's K range in this CTA ends: this block's P too, then Z, then the plane
-                    ok = __all_sync(0xffffffffu, tc_wait(b_pdone + 8 * zs, (j >> 1) & 1, p.wait_ns, p.err, 10));
+                    ok = __all_sync(0xffffffffu, tc_wait(b_pdone + 8 * pb, (j >> 1) & 1, p.wait_ns, p.err, 10));
                     if (ok) ok = __all_sync(0xffffffffu, tc_wait(b_zdone, seg & 1, p.wait_ns, p.err, 10));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    fold(zs, d_cur);
+                    fold(pb, d_cur);
                     fold(2, -1.0f);
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_pfree + 8 * zs) : "memory");
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_pfree + 8 * pb) : "memory");
                     const uint32_t piece = blockIdx.x - sk.cta_of(tile * sk.nb);
                     float *outp = p.out + (size_t)piece * p.n_tokens * p.rows + tile * TC_ROWS + row;
 #pragma unroll
@@ -707,14 +709,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
             if (c == 0) {
                 // the P buffer of this block must have been folded (two blocks ago); then Z: the block's minimums x sums
                 if (j >= 2) ok = tc_wait(b_pfree + 8 * pb, ((j >> 1) - 1) & 1, p.wait_ns, p.err, 9);
-                if (ok) ok = tc_wait(b_zfull + 8 * pb, (j >> 1) & 1, p.wait_ns, p.err, 9);
+                const uint32_t zs = j % KQ_ZSLOTS, zuse = j / KQ_ZSLOTS;
+                if (ok) ok = tc_wait(b_zfull + 8 * zs, zuse & 1, p.wait_ns, p.err, 9);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t m_hi = zdesc0 + pb * (KQ_ZSLOT >> 4), m_lo = m_hi + (KQ_ZTILE >> 4), s_hi = m_hi + 2 * (KQ_ZTILE >> 4), s_lo = m_hi + 3 * (KQ_ZTILE >> 4);
+                const uint64_t m_hi = zdesc0 + zs * (KQ_ZSLOT >> 4), m_lo = m_hi + (KQ_ZTILE >> 4), s_hi = m_hi + 2 * (KQ_ZTILE >> 4), s_lo = m_hi + 3 * (KQ_ZTILE >> 4);
                 tc_mma_f16(tmem_base + 256, m_hi, s_hi, idesc, !seg_start);
                 tc_mma_f16(tmem_base + 256, m_hi, s_lo, idesc, 1);
                 tc_mma_f16(tmem_base + 256, m_lo, s_hi, idesc, 1);
-                tc_commit(b_zempty + 8 * pb);
+                tc_commit(b_zempty + 8 * zs);
             }
             ok = tc_wait(b_xfull + 8 * xs, xpar, p.wait_ns, p.err, 9) && tc_wait(b_wfull + 8 * ws, wpar, p.wait_ns, p.err, 9);
             if (!ok) break;
@@ -747,8 +750,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
         for (uint32_t it = 0; it < nstage && okx; it++) {
             const uint32_t j = it >> 2, c = it & 3, kb = (u0 + j) % sk.nb;
             if (c == 0) {
-                const uint32_t zs = j & 1;
-                if (j >= 2) okx = tc_wait(b_zempty + 8 * zs, ((j >> 1) - 1) & 1, p.wait_ns, p.err, 8);
+                const uint32_t zs = j % KQ_ZSLOTS, zuse = j / KQ_ZSLOTS;
+                if (j >= KQ_ZSLOTS) okx = tc_wait(b_zempty + 8 * zs, (zuse - 1) & 1, p.wait_ns, p.err, 8);
                 if (!okx) break;
                 const uint32_t full = b_zfull + 8 * zs, dst = tc_smem_u32(zst + zs * KQ_ZSLOT + 2 * KQ_ZTILE);
                 const size_t at = (size_t)kb * (TC_ROWS * 16);
