@@ -519,8 +519,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
         const uint32_t row = tid & (TC_ROWS - 1), kq = tid >> 7;
         uint32_t tile = u0 / sk.nb, kb = u0 - tile * sk.nb, ptile = tile, pkb = kb;
         // One block of each of the tile's 128 rows = one box of the matrix seen as a 2-D byte array [rows][row_bytes]: a
-        // single tiled TMA copy per step.  (128 one-row bulk copies per step went through the copy engine at ~45 ns each,
-        // 5.8 us per step: more than everything else the step does.)
+        // single tiled TMA copy per step.  (With 128 one-row bulk copies per step the producers waited 1.6 us per step
+        // for the block: the copies completed ~6 us after they were issued.)
         auto issue_raw = [&](uint32_t t, uint32_t b, uint32_t dst, uint32_t bar) {
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)TC_ROWS * RB) : "memory");
             asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -698,7 +698,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_kquant_tc_kernel(const Gem
         const uint32_t idesc = tc_idesc_f16(TC_ROWS, p.n_pad);
         uint32_t ws = 0, wpar = 0, xs = 0, xpar = 0;
         // The issuing thread is one warp's instruction stream: whatever it computes per MMA is serial latency between two
-        // MMAs.  Building a 64-bit descriptor per operand and MMA kept the tensor pipe idle three quarters of the time.
+        // MMAs, so the descriptors of stage 0 are built once and the others are one addition away.
         const uint64_t wdesc0 = tc_smem_desc(tc_smem_u32(wst), TC_LBO, TC_SBO), xdesc0 = tc_smem_desc(tc_smem_u32(xst), TC_LBO, TC_SBO);
         const uint64_t zdesc0 = tc_smem_desc(tc_smem_u32(zst), KQ_ZLBO, KQ_ZSBO);
         uint32_t kb = u0 % sk.nb;
