@@ -508,7 +508,7 @@ def main():
 
     line = {
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a weights x 3-limb int8 activations, f32 accumulate",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a weights x 2-limb int8 activations (16-bit block fixed point), f32 accumulate",
         "data": "synthetic",
         "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}" if world > 1 else "single GPU", "prompt_tokens": W, "decode_tokens": K, "l2": "weights per token (4.9 GB) exceed L2 (126 MB)",
                    "prefill": "prompt fed through the decode path (as the reference does), untimed"},

@@ -45,7 +45,7 @@ __device__ __forceinline__ void dot_q4k(const uint8_t *const (&row)[NR], uint32_
         const uint32_t e16 = 16 * b + 4 * c;  // index of the unit's first 16-element group
         int D[NR][2][3];
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
+        for (int k = 0; k < ACT_LIMBS; k++) {
             const uint4 *L = A.limb(k) + e16;
             const uint4 aL0 = L[0], aL1 = L[1], aH0 = L[2], aH1 = L[3];
 #pragma unroll
@@ -77,8 +77,8 @@ __device__ __forceinline__ void dot_q4k(const uint8_t *const (&row)[NR], uint32_
             const float d = h2f(hdr[r].x & 0xFFFFu), dmin = h2f(hdr[r].x >> 16);
             const float d_lo = d * (float)(sc2 & 0xFFu), d_hi = d * (float)(sc2 >> 8);
             const float m_lo = dmin * (float)(m2 & 0xFFu), m_hi = dmin * (float)(m2 >> 8);
-            float v = d_lo * (s_lo * limb_combine(D[r][0][0], D[r][0][1], D[r][0][2])) - m_lo * x_lo;
-            v += d_hi * (s_hi * limb_combine(D[r][1][0], D[r][1][1], D[r][1][2])) - m_hi * x_hi;
+            float v = d_lo * (s_lo * limb_combine(D[r][0])) - m_lo * x_lo;
+            v += d_hi * (s_hi * limb_combine(D[r][1])) - m_hi * x_hi;
             acc[r] += v;
         }
     }
@@ -111,7 +111,7 @@ __device__ __forceinline__ void dot_q5k(const uint8_t *const (&row)[NR], uint32_
             }
             int D[2][3];
 #pragma unroll
-            for (int k = 0; k < 3; k++) {
+            for (int k = 0; k < ACT_LIMBS; k++) {
                 const uint4 *L = A.limb(k) + e16;
                 const uint4 aL0 = L[0], aL1 = L[1], aH0 = L[2], aH1 = L[3];
                 const uint32_t al[8] = {aL0.x, aL0.y, aL0.z, aL0.w, aL1.x, aL1.y, aL1.z, aL1.w};
@@ -129,8 +129,8 @@ __device__ __forceinline__ void dot_q5k(const uint8_t *const (&row)[NR], uint32_
             const float d = h2f(hdr.x & 0xFFFFu), dmin = h2f(hdr.x >> 16);
             const float d_lo = d * (float)(sc2 & 0xFFu), d_hi = d * (float)(sc2 >> 8);
             const float m_lo = dmin * (float)(m2 & 0xFFu), m_hi = dmin * (float)(m2 >> 8);
-            float v = d_lo * (s_lo * limb_combine(D[0][0], D[0][1], D[0][2])) - m_lo * x_lo;
-            v += d_hi * (s_hi * limb_combine(D[1][0], D[1][1], D[1][2])) - m_hi * x_hi;
+            float v = d_lo * (s_lo * limb_combine(D[0])) - m_lo * x_lo;
+            v += d_hi * (s_hi * limb_combine(D[1])) - m_hi * x_hi;
             acc[r] += v;
         }
     }
@@ -159,7 +159,7 @@ __device__ __forceinline__ void dot_q6k(const uint8_t *const (&row)[NR], uint32_
         const uint32_t j0 = 8 * b + 4 * i;        // 32-element sub-block of g = 0
         int D[NR][4][3];
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
+        for (int k = 0; k < ACT_LIMBS; k++) {
             const uint4 *L = A.limb(k) + e16;
             const uint4 a0 = L[0], a1 = L[2], a2 = L[4], a3 = L[6];
 #pragma unroll
@@ -195,7 +195,7 @@ __device__ __forceinline__ void dot_q6k(const uint8_t *const (&row)[NR], uint32_
             for (int g = 0; g < 4; g++) {
                 const uint32_t word = (g < 2) ? w01 : w23;
                 const int sc = (int)(int8_t)(word >> (8 * (2 * (g & 1) + h)));
-                const float dot = SC[j0 + g] * limb_combine(D[r][g][0], D[r][g][1], D[r][g][2]) - 32.0f * SX[e16 + 2 * g];
+                const float dot = SC[j0 + g] * limb_combine(D[r][g]) - 32.0f * SX[e16 + 2 * g];
                 v += (d * (float)sc) * dot;
             }
             acc[r] += v;
@@ -219,7 +219,7 @@ __device__ __forceinline__ void dot_q80(const uint8_t *const (&row)[NR], uint32_
         }
         int D[NR][3];
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
+        for (int k = 0; k < ACT_LIMBS; k++) {
             const uint4 *L = A.limb(k) + 2 * b;
             const uint4 a0 = L[0], a1 = L[1];
 #pragma unroll
@@ -232,7 +232,7 @@ __device__ __forceinline__ void dot_q80(const uint8_t *const (&row)[NR], uint32_
         }
         const float s = SC[b];
 #pragma unroll
-        for (int r = 0; r < NR; r++) acc[r] += h2f(dbits[r]) * (s * limb_combine(D[r][0], D[r][1], D[r][2]));
+        for (int r = 0; r < NR; r++) acc[r] += h2f(dbits[r]) * (s * limb_combine(D[r]));
     }
 }
 

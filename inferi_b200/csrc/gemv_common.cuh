@@ -10,10 +10,16 @@ constexpr int PACK_THREADS = 512;        // threads that take part in the activa
 constexpr uint32_t GEMV_MAX_COLS = 32768;
 
 // Activation form in shared memory, for `cols` columns (a multiple of 32):
-//   3 int8 limbs a0,a1,a2 [cols] each;  f32 scale s/127 per 32 columns;  f32 sum of x per 16 columns
-//   x ~= (s/127) * (a0 + a1/254 + a2/254^2)      (resolution 6e-8 * max|x| of the 32-group)
+//   ACT_LIMBS int8 limbs a0, a1 [cols] each;  f32 scale s/127 per 32 columns;  f32 sum of the quantized x per 16 columns
+//   x ~= (s/127) * (a0 + a1/254)      (resolution 1.6e-5 * max|x| of the 32-group: 16-bit block fixed point)
 //   (+ 192 bytes: in the group-major chunk order each limb array carries one 16-byte skew per group, see act_chunk_pos)
-__host__ __device__ inline size_t act_smem_bytes(uint32_t cols) { return (size_t)cols * 3 + cols / 32 * 4 + cols / 16 * 4 + 192; }
+// The 16-column sums (used for the k-quants' minimums and the Q6_K -32 terms) are sums of the QUANTIZED values, so that
+// sum_k w_k a_k is evaluated exactly for the a_k the dot products see; the only error of a GEMV is sum_k w_k (a_k - x_k),
+// 2e-5 .. 1e-4 relative.  (A third limb - 24-bit fixed point - costs a third more dp4a and 16 more registers per lane: 583
+// against 619 tok/s on the 8B architecture; the logits of the 1B architecture then differ from the f32 oracle's by 7e-4
+// instead of 2.7e-3 max-abs, at a tolerance of 2e-2.)
+constexpr int ACT_LIMBS = 2;
+__host__ __device__ inline size_t act_smem_bytes(uint32_t cols) { return (size_t)cols * ACT_LIMBS + cols / 32 * 4 + cols / 16 * 4 + 192; }
 
 struct Act {
     const uint8_t *base;
@@ -22,7 +28,7 @@ struct Act {
     __device__ __forceinline__ uint32_t pos(uint32_t e16) const { return nq ? (e16 & 3u) * (nq + 1) + (e16 >> 2) : e16; }
     __device__ __forceinline__ uint32_t lstride() const { return cols + (nq ? 64u : 0u); }
     __device__ __forceinline__ const uint4 *limb(int k) const { return reinterpret_cast<const uint4 *>(base + (size_t)k * lstride()); }
-    __device__ __forceinline__ const float *sc() const { return reinterpret_cast<const float *>(base + (size_t)3 * lstride()); }
+    __device__ __forceinline__ const float *sc() const { return reinterpret_cast<const float *>(base + (size_t)ACT_LIMBS * lstride()); }
     __device__ __forceinline__ const float *sx16() const { return sc() + cols / 32; }
 };
 
@@ -32,8 +38,11 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-__device__ __forceinline__ float limb_combine(int d0, int d1, int d2) {
-    return (float)d0 + (float)d1 * (1.0f / 254.0f) + (float)d2 * (1.0f / 64516.0f);
+// the integer dot products of the limbs -> the dot product in units of the group's scale; d[0 .. ACT_LIMBS-1]
+__device__ __forceinline__ float limb_combine(const int *d) {
+    float v = (float)d[0] + (float)d[1] * (1.0f / 254.0f);
+    if (ACT_LIMBS > 2) v += (float)d[ACT_LIMBS - 1] * (1.0f / 64516.0f);
+    return v;
 }
 __device__ __forceinline__ float h2f(uint32_t bits16) { return __half2float(__ushort_as_half((unsigned short)bits16)); }
 
@@ -79,12 +88,9 @@ __device__ __forceinline__ uint32_t act_chunk_pos(uint32_t run, uint32_t nq) { r
 
 __device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uint32_t cols, uint8_t *smem, bool store, uint32_t nq = 0) {
     const int lane = threadIdx.x & 31;
-    float amax = 0.f, sum = 0.f;
+    float amax = 0.f, sum = 0.f;   // sum: of the quantized values, in units of the group's scale
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
-        sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
-    }
+    for (int j = 0; j < 4; j++) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));   // the other half of the 32-column group
     const float inv = amax > 0.f ? __fdividef(127.0f, amax) : 0.f;   // 2 ulp: the limbs absorb it (|t| stays within 127 + 1e-5)
     // round-to-nearest-even by adding 1.5 * 2^23: the sum's low mantissa byte is the rounded value in two's complement
@@ -98,11 +104,13 @@ __device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uin
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             const float t = e[k] * inv;
-            const float r0 = t + MAGIC;
-            const float t1 = (t - (r0 - MAGIC)) * 254.0f;
-            const float r1 = t1 + MAGIC;
-            const float r2 = (t1 - (r1 - MAGIC)) * 254.0f + MAGIC;
+            const float r0 = t + MAGIC, q0 = r0 - MAGIC;            // the limbs as floats: q0, q1, q2
+            const float t1 = (t - q0) * 254.0f;
+            const float r1 = t1 + MAGIC, q1 = r1 - MAGIC;
+            const float t2 = (t1 - q1) * 254.0f;
+            const float r2 = t2 + MAGIC;
             b0[k] = __float_as_uint(r0); b1[k] = __float_as_uint(r1); b2[k] = __float_as_uint(r2);
+            sum += q0 + q1 * (1.0f / 254.0f) + (ACT_LIMBS > 2 ? (r2 - MAGIC) * (1.0f / 64516.0f) : 0.f);
         }
         // low bytes of four words -> one word
         w0[j] = __byte_perm(__byte_perm(b0[0], b0[1], 0x0040), __byte_perm(b0[2], b0[3], 0x0040), 0x5410);
@@ -112,13 +120,13 @@ __device__ __forceinline__ void pack_run(const float4 (&v)[4], uint32_t run, uin
     if (store) {
         const size_t ls = cols + (nq ? 64u : 0u);   // = Act::lstride()
         uint4 *l0 = reinterpret_cast<uint4 *>(smem), *l1 = reinterpret_cast<uint4 *>(smem + ls), *l2 = reinterpret_cast<uint4 *>(smem + 2 * ls);
-        float *sc = reinterpret_cast<float *>(smem + 3 * ls), *sx16 = sc + cols / 32;
+        float *sc = reinterpret_cast<float *>(smem + ACT_LIMBS * ls), *sx16 = sc + cols / 32;
         const uint32_t at = act_chunk_pos(run, nq);
         l0[at] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
         l1[at] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
-        l2[at] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+        if (ACT_LIMBS > 2) l2[at] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
         if ((lane & 1) == 0) sc[run >> 1] = amax * (1.0f / 127.0f);
-        sx16[run] = sum;
+        sx16[run] = sum * (amax * (1.0f / 127.0f));
     }
 }
 

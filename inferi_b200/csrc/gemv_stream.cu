@@ -9,7 +9,7 @@
 //    before the kernel waits for its predecessor (programmatic dependent launch): weights never depend on the
 //    previous kernel, so the ring fills while that kernel is still finishing.
 //  * Sixteen consumer warps split a row's columns: every lane owns one 64-weight unit of the row and keeps that
-//    unit's activations — three int8 limbs per column, see gemv_common.cuh — in registers for the whole kernel, so
+//    unit's activations — two int8 limbs per column, see gemv_common.cuh — in registers for the whole kernel, so
 //    the inner loop touches shared memory only for weights.  Per weight the work is a byte mask and dp4a.
 //  * Per row the lane partials are shuffled down, per-warp partials meet in shared memory, and the last warp of a
 //    row group to arrive adds them in a fixed order and runs the epilogue (store / residual add / SwiGLU /

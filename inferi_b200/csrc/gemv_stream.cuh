@@ -219,7 +219,7 @@ struct TileCursor {
 
 // ---- per-lane activation registers of one 64-weight unit ----
 struct UnitAct {
-    uint4 l[3][4];   // 3 limbs x 4 groups of 16 columns
+    uint4 l[ACT_LIMBS][4];   // limbs x 4 groups of 16 columns
     float s[4];      // per-group scale (already divided where the format needs it)
     float x[4];      // per-group sum of x
 };
@@ -241,12 +241,12 @@ __device__ __forceinline__ void load_unit_act(uint32_t qtype, uint32_t u, const 
     // 32-bit shared addresses, computed once; volatile loads: they must stay where they are (as ordinary loads they are
     // loop-invariant and would be hoisted to one place where every format's copies stay live at once)
     const uint32_t base = smem_u32(A.base), ls = A.lstride();
-    const uint32_t sc0 = base + 3 * ls, sx0 = sc0 + A.cols / 8;   // f32 scale per 32 columns, then f32 sum per 16 columns
+    const uint32_t sc0 = base + ACT_LIMBS * ls, sx0 = sc0 + A.cols / 8;   // f32 scale per 32 columns, then f32 sum per 16 columns
 #pragma unroll
     for (int g = 0; g < 4; g++) {
         const uint32_t at = base + 16 * A.pos(e16[g]);
 #pragma unroll
-        for (int k = 0; k < 3; k++) ua.l[k][g] = lds128(at + k * ls);
+        for (int k = 0; k < ACT_LIMBS; k++) ua.l[k][g] = lds128(at + k * ls);
         ua.s[g] = __uint_as_float(lds32(sc0 + 4 * (e16[g] >> 1)));
         ua.x[g] = __uint_as_float(lds32(sx0 + 4 * e16[g]));
     }
@@ -301,7 +301,7 @@ template <> struct Unit<IB_Q4_K> {
         for (int w = 0; w < 4; w++) {
             const uint32_t lo = qa[w] & 0x0F0F0F0Fu, hi = qa[w] & 0xF0F0F0F0u;
 #pragma unroll
-            for (int k = 0; k < 3; k++) {
+            for (int k = 0; k < ACT_LIMBS; k++) {
                 L[k] = dp4a_ss(lo, comp(ua.l[k][0], w), L[k]);
                 H[k] = dp4a_us(hi, comp(ua.l[k][2], w), H[k]);
             }
@@ -310,14 +310,14 @@ template <> struct Unit<IB_Q4_K> {
         for (int w = 0; w < 4; w++) {
             const uint32_t lo = qb[w] & 0x0F0F0F0Fu, hi = qb[w] & 0xF0F0F0F0u;
 #pragma unroll
-            for (int k = 0; k < 3; k++) {
+            for (int k = 0; k < ACT_LIMBS; k++) {
                 L[k] = dp4a_ss(lo, comp(ua.l[k][1], w), L[k]);
                 H[k] = dp4a_us(hi, comp(ua.l[k][3], w), H[k]);
             }
         }
         uint32_t sc2, m2;
         kquant_scales_lane(hdr, lc, sc2, m2);
-        return kquant_finish(hdr, sc2, m2, ua.s[0] * limb_combine(L[0], L[1], L[2]), ua.s[2] * limb_combine(H[0], H[1], H[2]), ua.x[0], ua.x[2]);
+        return kquant_finish(hdr, sc2, m2, ua.s[0] * limb_combine(L), ua.s[2] * limb_combine(H), ua.x[0], ua.x[2]);
     }
 };
 
@@ -340,14 +340,14 @@ template <> struct Unit<IB_Q5_K> {
             const uint32_t lo = (qw[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
             const uint32_t hi = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
 #pragma unroll
-            for (int k = 0; k < 3; k++) {
+            for (int k = 0; k < ACT_LIMBS; k++) {
                 L[k] = dp4a_ss(lo, comp(ua.l[k][i >> 2], i & 3), L[k]);
                 H[k] = dp4a_ss(hi, comp(ua.l[k][2 + (i >> 2)], i & 3), H[k]);
             }
         }
         uint32_t sc2, m2;
         kquant_scales_lane(hdr, lc, sc2, m2);
-        return kquant_finish(hdr, sc2, m2, ua.s[0] * limb_combine(L[0], L[1], L[2]), ua.s[2] * limb_combine(H[0], H[1], H[2]), ua.x[0], ua.x[2]);
+        return kquant_finish(hdr, sc2, m2, ua.s[0] * limb_combine(L), ua.s[2] * limb_combine(H), ua.x[0], ua.x[2]);
     }
 };
 
@@ -376,7 +376,7 @@ template <> struct Unit<IB_Q6_K> {
             const uint32_t g2 = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
             const uint32_t g3 = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
 #pragma unroll
-            for (int k = 0; k < 3; k++) {
+            for (int k = 0; k < ACT_LIMBS; k++) {
                 D[0][k] = dp4a_ss(g0, comp(ua.l[k][0], w), D[0][k]);
                 D[1][k] = dp4a_ss(g1, comp(ua.l[k][1], w), D[1][k]);
                 D[2][k] = dp4a_ss(g2, comp(ua.l[k][2], w), D[2][k]);
@@ -387,10 +387,10 @@ template <> struct Unit<IB_Q6_K> {
         const uint32_t sx = scw.x >> lc.k, sy = scw.y >> lc.k;
         const float s0 = (float)(int)(int8_t)(sx & 0xFF), s1 = (float)(int)(int8_t)((sx >> 16) & 0xFF);
         const float s2 = (float)(int)(int8_t)(sy & 0xFF), s3 = (float)(int)(int8_t)((sy >> 16) & 0xFF);
-        float v = s0 * (ua.s[0] * limb_combine(D[0][0], D[0][1], D[0][2]) - 32.0f * ua.x[0]);
-        v += s1 * (ua.s[1] * limb_combine(D[1][0], D[1][1], D[1][2]) - 32.0f * ua.x[1]);
-        v += s2 * (ua.s[2] * limb_combine(D[2][0], D[2][1], D[2][2]) - 32.0f * ua.x[2]);
-        v += s3 * (ua.s[3] * limb_combine(D[3][0], D[3][1], D[3][2]) - 32.0f * ua.x[3]);
+        float v = s0 * (ua.s[0] * limb_combine(D[0]) - 32.0f * ua.x[0]);
+        v += s1 * (ua.s[1] * limb_combine(D[1]) - 32.0f * ua.x[1]);
+        v += s2 * (ua.s[2] * limb_combine(D[2]) - 32.0f * ua.x[2]);
+        v += s3 * (ua.s[3] * limb_combine(D[3]) - 32.0f * ua.x[3]);
         return d * v;
     }
 };
@@ -413,11 +413,11 @@ template <> struct Unit<IB_Q8_0> {
 #pragma unroll
             for (int w = 0; w < 4; w++)
 #pragma unroll
-                for (int k = 0; k < 3; k++) {
+                for (int k = 0; k < ACT_LIMBS; k++) {
                     if (g < 2) A[k] = dp4a_ss(comp(q[g], w), comp(ua.l[k][g], w), A[k]);
                     else B[k] = dp4a_ss(comp(q[g], w), comp(ua.l[k][g], w), B[k]);
                 }
-        return dd.x * (ua.s[0] * limb_combine(A[0], A[1], A[2])) + dd.y * (ua.s[2] * limb_combine(B[0], B[1], B[2]));
+        return dd.x * (ua.s[0] * limb_combine(A)) + dd.y * (ua.s[2] * limb_combine(B));
     }
 };
 

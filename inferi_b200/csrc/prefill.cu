@@ -17,7 +17,7 @@
 //  * the tokens' inputs (already split into f16 hi / lo by the kernel that produced them, and laid out in global memory
 //    as tiles of that same layout) arrive by one bulk copy per tile, requested by a loader thread into a ring of their own;
 //  * one thread issues, per 16 columns, three tcgen05.mma (hi x hi, hi x lo, lo x hi; lo x lo is below f32 resolution)
-//    that accumulate in f32 in tensor memory: the result matches the f32 arithmetic of the decode path to ~1e-6;
+//    that accumulate in f32 in tensor memory: the result matches an f32 GEMV to ~1e-6 relative;
 //  * shared-memory stages cycle through mbarriers (filled by the producers, released by tcgen05.commit);
 //  * when a tile's K range is done the producer warps read the accumulator (tcgen05.ld: TMEM lane = weight row, column =
 //    token) and store it transposed, [token][row], coalesced over the rows.
