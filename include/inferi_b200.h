@@ -86,7 +86,9 @@ IB_API int32_t ib_qtensor_upload(ib_ctx *ctx, int32_t qtype, uint64_t rows, uint
 IB_API int32_t ib_qtensor_destroy(ib_qtensor *qt);
 IB_API int32_t ib_qtensor_info(const ib_qtensor *qt, int32_t *qtype, uint64_t *rows, uint64_t *cols, uint64_t *nbytes);
 
-/* Replaces `GemvQuant::launch` (crates/inferi/src/ops/gemv_quant.rs:183-341): out[rows] = W . v[cols]. */
+/* Replaces `GemvQuant::launch` (crates/inferi/src/ops/gemv_quant.rs:183-341): out[rows] = W . v[cols].  The streaming kernels
+ * take v as 16-bit block fixed point (per 32 columns a scale and two int8 limbs): the result differs from an f32 evaluation by
+ * 2e-5 to 1e-4 relative (the reference's shaders accumulate in f32; the tolerance of the parity tests is 1e-3). */
 IB_API int32_t ib_gemv_quant(ib_ctx *ctx, void *stream, float *out_dev, const ib_qtensor *m, const float *v_dev);
 /* The same call for host buffers: copies v in, runs the kernel, copies out back, synchronises. */
 IB_API int32_t ib_gemv_quant_host(ib_ctx *ctx, float *out_host, const ib_qtensor *m, const float *v_host);
