@@ -80,6 +80,10 @@ bool attn_gqa4_eligible(const AttnLaunch &a) {
            ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && ((uintptr_t)a.scratch % 16) == 0;
 }
 
+uint32_t attn_cluster_positions(const AttnLaunch &a) {
+    return attn_gqa4_eligible(a) ? gqa4_cluster_size(a.max_splits) * GQA4_CLUSTER_PER : 0u;
+}
+
 int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     const ib_attn_params &p = a.p;
     IB_REQUIRE(p.kv_mul >= 1 && p.n_heads % p.kv_mul == 0, "attention: n_heads=%u is not a multiple of kv_mul=%u", p.n_heads, p.kv_mul);
@@ -88,7 +92,7 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
     IB_REQUIRE(a.pos_ptr || p.pos < p.seq_len, "attention: pos=%u outside the cache of %u rows", p.pos, p.seq_len);
     IB_REQUIRE(a.max_splits >= 1 && a.max_splits <= 2 * p.head_size && a.max_splits <= 256, "attention: %u position slices exceed what the merge step holds (%u)",
                a.max_splits, 2 * p.head_size < 256 ? 2 * p.head_size : 256);
-    AttnArgs args{p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, a.pdl, a.q_step, a.out_step, a.counter_step, a.scratch_step};
+    AttnArgs args{p, a.pos_ptr, a.q, a.k_cache, a.v_cache, a.out, a.scratch, a.counters, a.max_splits, a.pdl, 0u, a.q_step, a.out_step, a.counter_step, a.scratch_step};
     const bool f16 = a.kv_dtype == IB_KV_F16;
     const bool gqa4 = attn_gqa4_eligible(a);
     const uint32_t nq = a.n_queries > 1 ? a.n_queries : 1;
@@ -101,17 +105,31 @@ int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a) {
         else attn_split_plan(p.pos + nq, a.max_splits, need, per);
         if (need < splits) splits = need;
     }
+    if (gqa4) {
+        // short contexts merge inside a thread-block cluster (the first one of the kv head)
+        if (a.pos_ptr) {
+            args.cluster = a.short_context ? gqa4_cluster_size(splits) : 0u;
+        } else if (p.pos + nq <= GQA4_CLUSTER_MAX * GQA4_CLUSTER_PER) {
+            const uint32_t want = (p.pos + nq + GQA4_MIN_PER_SPLIT - 1) / GQA4_MIN_PER_SPLIT;
+            const uint32_t cs = want < GQA4_CLUSTER_MAX ? want : GQA4_CLUSTER_MAX;
+            if (cs >= 2 && cs <= a.max_splits) { splits = cs; args.cluster = cs; }
+        }
+    }
     const dim3 grid(n_kv, splits, nq);
     if (gqa4) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(ATTN_THREADS);
         cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = args.cluster ? args.cluster : 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = args.pdl ? 1 : 0;
+        cfg.numAttrs = args.pdl ? 2 : 1;
         if (p.head_size == 128) IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, attn_gqa4_kernel<128>, args));
         else IB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, attn_gqa4_kernel<64>, args));
         ctx->launches++;

@@ -25,6 +25,7 @@ struct AttnArgs {
     unsigned int *counters;
     uint32_t max_splits;
     uint32_t pdl;
+    uint32_t cluster;   // CTAs per thread-block cluster along the slices of a kv head (attn_gqa4_kernel only); 0: no clusters
     // Several queries in one launch (prompt prefill; gridDim.z = number of queries, only in the kernel for the Llama-3
     // shape): query z sits at position p.pos + z, its vectors, scratch and counters `*_step` elements after query 0's.
     uint32_t q_step, out_step, counter_step;

@@ -17,6 +17,8 @@
 
 #include "attention.cuh"
 
+#include <cooperative_groups.h>
+
 namespace ib {
 
 constexpr uint32_t GQA4_ROWS_PER_WARP_STEP = 8;
@@ -25,6 +27,31 @@ constexpr uint32_t GQA4_ROWS_PER_WARP_STEP = 8;
 // launch at 128 / 512 / 2048 / 8192 positions): 32 per slice throughout 4.6 / 6.1 / 12.6 / 17.1; 128 per slice 5.4 / 7.6 /
 // 9.1 / 17.1; 256 per slice 5.4 / 10.6 / 11.3 / 16.1.
 constexpr uint32_t GQA4_MIN_PER_SPLIT = ATTN_WARPS * GQA4_ROWS_PER_WARP_STEP, GQA4_KNEE = 16, GQA4_KNEE_PER = 128;
+// Short contexts: the slices of a kv head (at most 8) are the CTAs of one thread-block cluster.  They leave their partials in
+// the shared memory of the cluster's first CTA (distributed shared memory) and meet at the cluster barrier; the first CTA
+// merges from its own shared memory.  Publishing the partials through global memory, counting arrivals with an atomic and
+// reading them back are three L2 round trips (~2.6 us of a ~6 us kernel at these lengths); the cluster barrier is one
+// hardware barrier.  Longer contexts use more slices than a cluster has CTAs and keep the global-memory merge.
+// The cluster size is a divisor of the launch's slice count (so that no CTA is launched for the clusters' sake: with 55
+// slices x 8 kv heads = 440 CTAs the grid is exactly one wave of 148 SMs x 3, and rounding 55 up to 56 made a second wave
+// that cost 40 % at long contexts); `cluster` = 0: no clusters.
+constexpr uint32_t GQA4_CLUSTER_MAX = 8, GQA4_CLUSTER_PER = 64;   // beyond two row-loop iterations per slice the sixteen slices of the global merge are faster
+__host__ __device__ __forceinline__ uint32_t gqa4_cluster_size(uint32_t splits) {
+    for (uint32_t c = GQA4_CLUSTER_MAX; c >= 2; c--)
+        if (splits % c == 0) return c;
+    return 0;
+}
+__host__ __device__ __forceinline__ void gqa4_plan(uint32_t total, uint32_t max_splits, uint32_t cluster, uint32_t &nsplit, uint32_t &per, bool &in_cluster) {
+    in_cluster = cluster != 0 && total <= cluster * GQA4_CLUSTER_PER;
+    if (in_cluster) {
+        nsplit = (total + GQA4_MIN_PER_SPLIT - 1) / GQA4_MIN_PER_SPLIT;
+        if (nsplit > cluster) nsplit = cluster;
+        per = (total + nsplit - 1) / nsplit;
+        nsplit = (total + per - 1) / per;
+    } else {
+        attn_split_plan(total, max_splits, nsplit, per, GQA4_MIN_PER_SPLIT, GQA4_KNEE, GQA4_KNEE_PER);
+    }
+}
 
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
     unsigned long long ra, rb, rc, rd;
@@ -71,14 +98,22 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnAr
     __shared__ __align__(16) float sm_p[ATTN_WARPS][32];
     __shared__ __align__(16) float sm_alpha[ATTN_WARPS][4];
     __shared__ uint32_t sm_last;
+    __shared__ __align__(16) float sm_cl[GQA4_CLUSTER_MAX * KVM * (HS + 2)];   // cluster mode: the slices' partials, in the first CTA
 
     if (a.pdl) asm volatile("griddepcontrol.launch_dependents;");
     // The position was written at the end of the previous token, not by the predecessor: it can be read before the wait.
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t total = (a.pos_ptr ? *a.pos_ptr : a.p.pos) + 1;
     uint32_t nsplit, per;
-    attn_split_plan(total, a.max_splits, nsplit, per, GQA4_MIN_PER_SPLIT, GQA4_KNEE, GQA4_KNEE_PER);
-    if (split >= nsplit) return;
+    bool in_cluster;
+    gqa4_plan(total, a.max_splits, a.cluster, nsplit, per, in_cluster);
+    // cluster mode: the first cluster of a kv head (slices 0 .. a.cluster - 1) does the work, all of its CTAs meet at the barrier below
+    // (the ones without a slice bring nothing); the other clusters leave as a whole
+    if (in_cluster ? split >= a.cluster : split >= nsplit) return;
+    if (in_cluster && split >= nsplit) {
+        if (nsplit > 1) cooperative_groups::this_cluster().sync();   // the barrier of the working CTAs below
+        return;
+    }
     const uint32_t t0 = split * per, t1 = min(total, t0 + per);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane / L, li = lane % L;
@@ -263,6 +298,34 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attn_gqa4_kernel(const AttnAr
 #pragma unroll
             for (int e = 0; e < PER; e += 2)
                 *reinterpret_cast<float2 *>(a.out + (size_t)(kvh * KVM + m_out) * HS + d_out + e) = make_float2(o[e] * inv, o[e + 1] * inv);
+            return;
+        }
+        if (in_cluster) {
+            // the partial goes into the first CTA's shared memory; after the cluster barrier that CTA merges the slices
+            namespace cg = cooperative_groups;
+            cg::cluster_group cluster = cg::this_cluster();
+            float *dst = cluster.map_shared_rank(sm_cl, 0) + ((size_t)split * KVM + m_out) * slot;
+#pragma unroll
+            for (int e = 0; e < PER; e += 2) *reinterpret_cast<float2 *>(dst + d_out + e) = make_float2(o[e], o[e + 1]);
+            if (d_out == 0) *reinterpret_cast<float2 *>(dst + HS) = make_float2(mx, ls);
+            cluster.sync();
+            if (split != 0) return;
+            float cm = -INFINITY;
+            for (uint32_t s = 0; s < nsplit; s++) cm = fmaxf(cm, sm_cl[(s * KVM + m_out) * slot + HS]);
+            float lsum = 0.f, acc[PER];
+#pragma unroll
+            for (int e = 0; e < PER; e++) acc[e] = 0.f;
+            for (uint32_t s = 0; s < nsplit; s++) {
+                const float *ps = sm_cl + (s * KVM + m_out) * slot;
+                const float wt = merge_weight(ps[HS], cm);
+                lsum += wt * ps[HS + 1];
+#pragma unroll
+                for (int e = 0; e < PER; e++) acc[e] += wt * ps[d_out + e];
+            }
+            const float inv = 1.0f / lsum;
+#pragma unroll
+            for (int e = 0; e < PER; e += 2)
+                *reinterpret_cast<float2 *>(a.out + (size_t)(kvh * KVM + m_out) * HS + d_out + e) = make_float2(acc[e] * inv, acc[e + 1] * inv);
             return;
         }
 #pragma unroll

@@ -208,6 +208,11 @@ struct AttnLaunch {
     unsigned int *counters;    // [n_kv_heads], zero before the first launch; the kernel re-zeroes them
     uint32_t max_splits;
     uint32_t pdl;
+    // With pos_ptr (a graph node that serves many positions): the caller promises that the position stays below
+    // attn_cluster_positions(); the launch then groups a kv head's slices into a thread-block cluster and merges them there.
+    // Such a launch is slower at long contexts (clusters constrain the placement of the grid's one wave of CTAs), so a graph
+    // for longer contexts is recorded without it.  With a host-known position the launch decides by itself.
+    uint32_t short_context;
     // batched launch (prompt prefill): n_queries > 1 queries at positions p.pos, p.pos + 1, ...; steps in elements between
     // consecutive queries' q / out / scratch / counters.  Only the kernel for the Llama-3 shape takes it.
     uint32_t n_queries, q_step, out_step, counter_step;
@@ -217,5 +222,6 @@ bool attn_gqa4_eligible(const AttnLaunch &a);
 size_t attn_scratch_bytes(const ib_attn_params &p, uint32_t max_splits);
 uint32_t attn_max_splits(const ib_ctx *ctx, const ib_attn_params &p);
 int32_t launch_attention(ib_ctx *ctx, cudaStream_t s, const AttnLaunch &a);
+uint32_t attn_cluster_positions(const AttnLaunch &a);   // positions (pos + 1) up to which `short_context` may be set; 0: never
 
 }  // namespace ib

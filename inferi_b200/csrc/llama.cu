@@ -124,6 +124,10 @@ struct ib_llama {
     uint32_t *h_pinned = nullptr;  // [4 + seq_cap] staging for control block and token ids
     cudaEvent_t staged = nullptr;  // the last copy out of h_pinned has been issued and finished
     cudaGraphExec_t graph_exec = nullptr;
+    // the same token for positions below `short_positions`: its attention nodes merge their slices inside thread-block clusters
+    cudaGraphExec_t graph_exec_short = nullptr, graph_exec_sample_short = nullptr;
+    uint32_t short_positions = 0;
+    bool recording_short = false;
     cudaStream_t own_stream = nullptr;
     uint64_t launches_per_token = 0;
     // sampling beyond greedy (ib_llama_set_sampler): parameters, scratch, and the graph that carries the sampler node
@@ -241,6 +245,8 @@ static int32_t record_token(ib_llama *m, cudaStream_t s, uint32_t pdl) {
         AttnLaunch a = {};
         a.p = ap; a.pos_ptr = &m->ctl->pos; a.q = m->q; a.k_cache = m->k_cache[l]; a.v_cache = m->v_cache[l]; a.kv_dtype = m->kv_dtype;
         a.out = m->xb; a.scratch = m->attn_scratch; a.counters = m->attn_counters; a.max_splits = m->attn_splits; a.pdl = pdl;
+        a.short_context = m->recording_short ? 1u : 0u;
+        if (l == 0) m->short_positions = attn_cluster_positions(a);
         if ((rc = emit_attn(a))) return rc;
         // o_proj + residual (transformer.rs:450-453)
         p = GemvParams{};
@@ -392,6 +398,8 @@ int32_t ib_llama_destroy(ib_llama *m) {
     cudaDeviceSynchronize();
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
     if (m->graph_exec_sample) cudaGraphExecDestroy(m->graph_exec_sample);
+    if (m->graph_exec_short) cudaGraphExecDestroy(m->graph_exec_short);
+    if (m->graph_exec_sample_short) cudaGraphExecDestroy(m->graph_exec_sample_short);
     if (m->sample_probs) cudaFree(m->sample_probs);
     if (m->sample_keys) cudaFree(m->sample_keys);
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
@@ -581,8 +589,16 @@ int32_t ib_llama_create(ib_ctx *ctx, const ib_llama_config *config, const ib_lla
 // Records the token graph (once every pointer it needs is known) and instantiates it.
 static int32_t finish_graph(ib_llama *m) {
     IB_CHECK_CUDA(cudaDeviceSynchronize());
-    return capture_graph(m, &m->graph_exec, &m->launches_per_token);
+    int32_t rc = capture_graph(m, &m->graph_exec, &m->launches_per_token);
+    if (rc != IB_OK || m->short_positions == 0) return rc;
+    // the variant for short contexts (record_token noted up to which position the attention kernel offers it)
+    if (m->graph_exec_short) { cudaGraphExecDestroy(m->graph_exec_short); m->graph_exec_short = nullptr; }
+    uint64_t same = 0;
+    m->recording_short = true;
+    rc = capture_graph(m, &m->graph_exec_short, &same);
+    return rc;
 }
+
 
 // Records the token's kernels (with the sampler node when a temperature is set) into a graph and instantiates it.
 static int32_t capture_graph(ib_llama *m, cudaGraphExec_t *exec, uint64_t *launches_per_token) {
@@ -592,6 +608,7 @@ static int32_t capture_graph(ib_llama *m, cudaGraphExec_t *exec, uint64_t *launc
     const int32_t rc = record_token(m, m->own_stream, 1);
     cudaGraph_t graph = nullptr;
     cudaError_t ce = cudaStreamEndCapture(m->own_stream, &graph);
+    m->recording_short = false;
     *launches_per_token = ctx->launches - before;
     ctx->launches = before;  // recording is not launching
     if (rc != IB_OK) {
@@ -617,13 +634,20 @@ int32_t ib_llama_set_sampler(ib_llama *m, float temperature, float topp, uint64_
     }
     IB_CHECK_CUDA(cudaDeviceSynchronize());
     if (m->graph_exec_sample) { cudaGraphExecDestroy(m->graph_exec_sample); m->graph_exec_sample = nullptr; }
+    if (m->graph_exec_sample_short) { cudaGraphExecDestroy(m->graph_exec_sample_short); m->graph_exec_sample_short = nullptr; }
     m->temperature = temperature; m->topp = topp; m->sample_seed = seed;
     if (temperature == 0.f) return IB_OK;   // greedy: the graph recorded at creation
     if (!m->sample_probs) {
         IB_CHECK_CUDA(cudaMalloc(&m->sample_probs, sizeof(float) * m->cfg.vocab_size));
         IB_CHECK_CUDA(cudaMalloc(&m->sample_keys, sizeof(unsigned long long) * sample_keys_capacity(m->cfg.vocab_size)));
     }
-    const int32_t rc = capture_graph(m, &m->graph_exec_sample, &m->launches_per_token_sample);
+    int32_t rc = capture_graph(m, &m->graph_exec_sample, &m->launches_per_token_sample);
+    if (rc == IB_OK && m->short_positions) {
+        if (m->graph_exec_sample_short) { cudaGraphExecDestroy(m->graph_exec_sample_short); m->graph_exec_sample_short = nullptr; }
+        uint64_t same = 0;
+        m->recording_short = true;
+        rc = capture_graph(m, &m->graph_exec_sample_short, &same);
+    }
     if (rc != IB_OK) { m->temperature = 0.f; return rc; }
     return IB_OK;
 }
@@ -694,7 +718,11 @@ static int32_t run_tokens(ib_llama *m, cudaStream_t s, const uint32_t *tokens, u
     IB_CHECK_CUDA(cudaEventRecord(m->staged, s));
     const bool sampled = m->temperature > 0.f && m->graph_exec_sample;
     for (uint32_t i = 0; i < n_steps; i++) {
-        IB_CHECK_CUDA(cudaGraphLaunch(sampled ? m->graph_exec_sample : m->graph_exec, s));
+        // positions below short_positions replay the graph whose attention nodes merge inside thread-block clusters
+        const bool shrt = (uint64_t)start_pos + i + 1 <= m->short_positions;
+        cudaGraphExec_t exec = sampled ? (shrt && m->graph_exec_sample_short ? m->graph_exec_sample_short : m->graph_exec_sample)
+                                       : (shrt && m->graph_exec_short ? m->graph_exec_short : m->graph_exec);
+        IB_CHECK_CUDA(cudaGraphLaunch(exec, s));
         m->ctx->launches += sampled ? m->launches_per_token_sample : m->launches_per_token;
     }
     return IB_OK;
