@@ -79,3 +79,32 @@ def test_prompt_display_and_jinja_input():
     assert p.to_jinja_input() == {"messages": [{"role": "system", "content": "s"}, {"role": "user", "content": "u"}]}
     p.clear()
     assert p.entries == []
+
+
+def test_writer_emits_what_the_llama_tokenizer_reads(tmp_path):
+    """`write_llama_gguf(..., tokens, scores, special)` carries everything `LlamaTokenizer::from_gguf` asks for
+    (crates/inferi/src/models/tokenizers/llama2_tokenizer.rs:23-40): the file loads and round-trips a string."""
+    from inferi_b200 import gguf as G
+    from inferi_b200.llama2 import Llama2Config, synth_weights
+    try:
+        G.load()
+    except Exception as e:
+        pytest.skip(f"shared library not built: {e}")
+    cfg = Llama2Config(256, 512, 1, 4, 2, 300, 64, 10000.0, 1e-5)
+    vocab = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "hi", "▁hi", "the", "re"]
+    vocab += [f"w{i}" for i in range(cfg.vocab_size - len(vocab))]
+    path = str(tmp_path / "t.gguf")
+    G.write_llama_gguf(path, cfg, synth_weights(cfg, seed=3), tokens=vocab, scores=[-float(i) for i in range(len(vocab))], special=(1, 2, 0),
+                       chat_template="{{ bos_token }}{{ messages[0]['content'] }}")
+    g = G.Gguf(path)
+    tok = G.LlamaTokenizer(g)
+    assert (tok.bos, tok.eos, tok.unk, tok.vocab_size) == (1, 2, 0, cfg.vocab_size)
+    ids = tok.encode("hi there", False, False)
+    text, prev = "", tok.bos
+    for t in ids:
+        text += tok.decode(prev, t)
+        prev = t
+    assert text == "hi there"
+    assert ChatTemplate.from_gguf(g).apply(prompt_of([["user", "x"]]), "<s>", "</s>") == "<s>x"
+    tok.close()
+    g.close()

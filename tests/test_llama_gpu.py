@@ -205,3 +205,32 @@ def test_bounded_wait_expires_when_a_rank_never_arrives(backend):
     assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * np.abs(ref).max()
     m.close()
     be.close()   # every tensor and model of this context is gone by now
+
+
+def test_logits_across_the_position_where_the_token_graph_changes(backend):
+    """Below position 320 the model replays a token graph whose attention nodes merge their slices inside thread-block
+    clusters, from there on the one that merges through global memory: the logits on both sides of the change must agree
+    with the oracle fed the same tokens (teacher forcing, so that a near-tie cannot send the two down different branches)."""
+    # 32 query / 8 kv heads of 64 (the 1B layer shapes): 8 kv heads make 55 slices, clusters of 5, and the change at 5 x 64 positions
+    cfg = Llama2Config(2048, 8192, 2, 32, 8, 1024, 512, 500000.0, 1e-5)
+    w = synth_weights(cfg, seed=4242)
+    dev_w = Llama2Weights(backend, cfg, w)
+    model = Llama2(backend, cfg, dev_w, kv_f16=True)
+    seq = [7, 300, 41, 9] + model.generate([7, 300, 41, 9], 330).tolist()      # the device loop crosses the change by itself
+    ref = oracle.Llama(oracle_cfg(cfg), weights_to_host(w), kv_f16=True)
+    first, last = 312, 328
+    probe = Llama2(backend, cfg, dev_w, kv_f16=True)
+    probe.generate(seq[:first], 0)                                               # cache rows 0 .. first - 1
+    worst = 0.0
+    for pos in range(last + 1):
+        want = ref.forward(seq[pos], pos)
+        if pos < first:
+            continue
+        nxt, logits = probe.forward(seq[pos], pos, want_logits=True)
+        worst = max(worst, float(np.abs(logits - want).max()))
+        assert nxt == seq[pos + 1], f"the per-token path and the device loop disagree at position {pos}"
+    assert worst <= LOGITS_MAX_ABS, f"logits differ by {worst} around the change of graphs"
+    print(f"logits around position 320 agree with the oracle to {worst:.3e}")
+    model.close()
+    probe.close()
+    dev_w.close()
